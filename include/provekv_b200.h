@@ -1,0 +1,225 @@
+/*
+ * provekv_b200.h -- C ABI of the B200 (sm_100a) KV-cache codec library.
+ *
+ * The library replaces one path of RecursiveIntell/proveKV: the batched
+ * fib-quant k4 cold-tier codec (FB2 wire), the batched turbo-quant hot-shell
+ * codec (TQB1 wire) and the decode step fused with the write into a
+ * framework's per-layer KV cache.  Every entry point is `extern "C"`, takes
+ * plain pointers and sizes, and returns a status code (0 = ok).  Nothing here
+ * falls back to the CPU: when no CUDA device is usable the calls fail with
+ * PKV_ERR_CUDA.
+ *
+ * Two levels are exported.
+ *  - "*_batch_compact": host buffers in, host buffers out, FB2 / TQB1 bytes
+ *    including the header.  These are what a binding of the reference's
+ *    FibQuantAdapter::{encode,decode}_batch_compact (proveKV/src/codec.rs:513-569)
+ *    and TurboQuantAdapter::{encode,decode}_batch_compact
+ *    (proveKV/src/codec.rs:248-326) calls.
+ *  - "*_dev": device pointers in and out, any number of (layer, K|V, agent)
+ *    batches per launch addressed through a pkv_layout, payload without
+ *    header.  This is the form the pool / shell code drives
+ *    (proveKV/src/pool.rs:246-309, proveKV/src/shell.rs:250-311) and the form
+ *    the fused decode-and-patch takes (quant-codec-core/src/codec.rs:27-34
+ *    `decode_slice` into a caller-owned output).
+ *
+ * Tables (rotation matrix, codebook, Rademacher signs, QJL matrix) are inputs:
+ * the reference derives them from a seed with rand_chacha / nalgebra / statrs,
+ * none of which is reproduced here; bit-exactness is defined given equal tables.
+ */
+#ifndef PROVEKV_B200_H
+#define PROVEKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  PKV_OK = 0,
+  PKV_ERR_INVALID_ARGUMENT = 1,
+  PKV_ERR_CUDA = 2,
+  PKV_ERR_UNSUPPORTED = 3,      /* shape outside what the kernels are built for */
+  PKV_ERR_EMPTY_BATCH = 4,      /* fib-quant/src/codec.rs:226, turbo-quant/src/wire.rs:303 */
+  PKV_ERR_CORRUPT_HEADER = 5,   /* magic / version / profile mismatch / length */
+  PKV_ERR_BUFFER_TOO_SMALL = 6,
+  /* Per-vector codes, reported together with the index of the first failing
+   * vector.  Within one vector the smaller code is the check the reference
+   * performs first. */
+  PKV_VEC_NONFINITE_INPUT = 16,   /* fib-quant/src/codec.rs:1059, turbo-quant/src/polar.rs:401 */
+  PKV_VEC_ZERO_NORM = 17,         /* fib-quant/src/codec.rs:603 */
+  PKV_VEC_BAD_RADIUS = 18,        /* turbo-quant/src/polar.rs:127, radius.rs:104,161 */
+  PKV_VEC_BAD_RADIUS_RANGE = 19,  /* turbo-quant/src/radius.rs:170 */
+  PKV_VEC_PADDING_BITS = 20,      /* fib-quant/src/bitpack.rs:66, turbo-quant/src/bitpack.rs:101 */
+  PKV_VEC_INDEX_RANGE = 21,       /* fib-quant/src/codec.rs:819 */
+  PKV_VEC_BAD_NORM = 22,          /* fib-quant/src/codec.rs:1029 */
+  PKV_VEC_NONFINITE_OUTPUT = 23,  /* fib-quant/src/codec.rs:840 */
+  PKV_VEC_NONFINITE_RESIDUAL = 24,/* turbo-quant/src/qjl.rs:210 */
+  PKV_VEC_NORM_RANGE = 25         /* fib-quant/src/codec.rs:1003 (second pass of encode_batch) */
+};
+
+const char* pkv_status_string(int status);
+int pkv_version(void);
+
+/* ---- configuration ----------------------------------------------------- */
+#define PKV_NORM_FP16 0 /* NormFormat::Fp16Paper, fib-quant/src/codec.rs:1001 */
+#define PKV_NORM_F32 1  /* NormFormat::F32Reference */
+
+#define PKV_ARGMIN_PAIRWISE 0   /* AVX2 order, gpu-backend/src/simd_nearest.rs:44-94 */
+#define PKV_ARGMIN_SEQUENTIAL 1 /* scalar order, gpu-backend/src/simd_nearest.rs:24-39 */
+
+#define PKV_FIB_NUMERICS_AUTO 0   /* batch numerics for n >= 4, single below: fib-quant/src/codec.rs:586-589 */
+#define PKV_FIB_NUMERICS_BATCH 1  /* normalised vector rounded to f32 before rotation, :607-609 */
+#define PKV_FIB_NUMERICS_SINGLE 2 /* normalised vector kept in f64, :481 */
+
+#define PKV_TURBO_POLAR_ONLY 0     /* TurboMode::PolarOnly,  polar_bits = bits */
+#define PKV_TURBO_POLAR_WITH_QJL 1 /* TurboMode::PolarWithQjl, polar_bits = bits - 1 */
+
+#define PKV_RADII_F32 0        /* RadiusCodecProfileV1::F32 */
+#define PKV_RADII_BLOCK_LOG_U8 1 /* RadiusCodecProfileV1::BlockLogU8 */
+
+typedef struct pkv_fib_config {
+  int32_t dim;           /* ambient_dim; kernels: 64 or 128 */
+  int32_t block_dim;     /* k; kernels: 4 */
+  int32_t codebook_size; /* N <= 32 */
+  int32_t norm_format;   /* PKV_NORM_* */
+  int32_t argmin_order;  /* PKV_ARGMIN_* */
+  int32_t numerics;      /* PKV_FIB_NUMERICS_* */
+} pkv_fib_config;
+
+typedef struct pkv_turbo_config {
+  int32_t dim;         /* power of two; kernels: 64 or 128 */
+  int32_t bits;        /* TurboQuantizer bits (turbo-quant/src/turbo.rs:124) */
+  int32_t mode;        /* PKV_TURBO_* */
+  int32_t projections; /* QJL rows m (multiple of 8, <= 64 in the kernels) */
+  int32_t radii_codec; /* PKV_RADII_* */
+  int32_t reserved;
+  uint64_t seed;       /* written to the TQB1 header only */
+} pkv_turbo_config;
+
+/* How the vectors of one launch are laid out in an f32 tensor.
+ * A launch covers n_batches[0]*n_batches[1]*n_batches[2] batches (for example
+ * agent x layer x {K,V}); batch (b0,b1,b2) holds n_tokens*n_heads vectors and
+ * vector v of a batch is (token = v / n_heads, head = v % n_heads), the order
+ * proveKV/src/pool.rs:246-257 gathers in.  Element offset of a vector:
+ *   base + b0*batch_stride[0] + b1*batch_stride[1] + b2*batch_stride[2]
+ *        + token*token_stride + head*head_stride  (+ r*replica_stride on decode)
+ * The dim values of a vector are contiguous.  All strides and base are in
+ * elements and must be multiples of 4 (16-byte accesses).  n_replicas > 1 makes
+ * the decode kernels write every vector to that many destinations (one decode,
+ * several caches); encode requires n_replicas == 1. */
+typedef struct pkv_layout {
+  int64_t base;
+  int64_t batch_stride[3];
+  int64_t token_stride;
+  int64_t head_stride;
+  int64_t replica_stride;
+  int32_t n_batches[3];
+  int32_t n_tokens;
+  int32_t n_heads;
+  int32_t n_replicas;
+} pkv_layout;
+
+typedef struct pkv_fib_profile pkv_fib_profile;
+typedef struct pkv_turbo_profile pkv_turbo_profile;
+
+/* ---- device / memory helpers ------------------------------------------ */
+int pkv_device_count(int* count);
+int pkv_set_device(int device);
+/* Pinned host memory for callers that want full PCIe rate on the compact calls. */
+int pkv_host_alloc(void** ptr, int64_t bytes);
+int pkv_host_free(void* ptr);
+int pkv_dev_alloc(void** ptr, int64_t bytes);
+int pkv_dev_free(void* ptr);
+int pkv_memcpy_h2d(void* dst_dev, const void* src_host, int64_t bytes, void* stream);
+int pkv_memcpy_d2h(void* dst_host, const void* src_dev, int64_t bytes, void* stream);
+int pkv_stream_synchronize(void* stream);
+
+/* The device error word: 0xFFFF...F = no error; otherwise the smallest
+ * (pass << 56 | vector_index << 8 | code) any thread reported.  Reset before a
+ * launch, read (synchronising the stream) after it. */
+int pkv_error_word_reset(uint64_t* err_dev, void* stream);
+int pkv_error_word_read(const uint64_t* err_dev, void* stream, int32_t* code, int64_t* vector_index);
+
+/* ---- fib-quant --------------------------------------------------------- */
+/* rotation: dim x dim f64 row-major (StoredRotation.matrix, fib-quant/src/rotation.rs:51-56);
+ * codebook: codebook_size x block_dim f32 row-major (fib-quant/src/codebook.rs:28-29). */
+int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, const float* codebook,
+                           pkv_fib_profile** out);
+int pkv_fib_profile_destroy(pkv_fib_profile* p);
+/* Bytes per vector in the FB2 payload: norm (2 or 4) + ceil(5*dim/4/8). */
+int32_t pkv_fib_record_bytes(const pkv_fib_profile* p);
+
+/* Replaces FibQuantizer::encode_batch + finish_batch_encode
+ * (fib-quant/src/codec.rs:578-729): one record per vector at
+ * payload_dev + batch*payload_batch_stride + v*record_bytes. */
+int pkv_fib_encode_dev(const pkv_fib_profile* p, const float* x_dev, const pkv_layout* layout,
+                       uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
+                       void* stream);
+/* Replaces FibQuantizer::decode_batch_fast (fib-quant/src/codec.rs:797-844) fused
+ * with the per-head relayout of proveKV/src/pool.rs:538-558 and the cache write of
+ * proveKV/scripts/ppl_validate_multi_agent.py:226-271. */
+int pkv_fib_decode_patch_dev(const pkv_fib_profile* p, const uint8_t* payload_dev,
+                             int64_t payload_batch_stride, const pkv_layout* layout,
+                             float* cache_dev, uint64_t* err_dev, void* stream);
+
+/* FibQuantAdapter::encode_batch_compact (proveKV/src/codec.rs:513-525): n vectors
+ * of dim f32, contiguous, host memory -> FB2 bytes (19-byte header + n records). */
+int pkv_fib_encode_batch_compact(const pkv_fib_profile* p, const float* vectors_host, int64_t n,
+                                 uint8_t* out_host, int64_t out_capacity, int64_t* out_len,
+                                 int32_t* vec_code, int64_t* vec_index);
+/* FibQuantAdapter::decode_batch_compact (proveKV/src/codec.rs:530-569), FB2 only. */
+int pkv_fib_decode_batch_compact(const pkv_fib_profile* p, const uint8_t* bytes_host, int64_t len,
+                                 float* out_host, int64_t out_capacity_floats, int64_t* n_vectors,
+                                 int32_t* vec_code, int64_t* vec_index);
+
+/* FB2 header, fib-quant/src/codec.rs:195-220 (19 bytes). */
+#define PKV_FB2_HEADER_BYTES 19
+int pkv_fb2_header_write(const pkv_fib_profile* p, uint32_t n_vectors, uint8_t* out19);
+int pkv_fb2_header_parse(const pkv_fib_profile* p, const uint8_t* bytes, int64_t len,
+                         uint32_t* n_vectors);
+
+/* ---- turbo-quant ------------------------------------------------------- */
+/* signs: dim values of +-1 (FastHadamardRotation.signs, turbo-quant/src/rotation.rs:152-155);
+ * qjl: projections x dim f32 row-major (turbo-quant/src/qjl.rs:341-352), NULL for polar-only;
+ * cos_lut/sin_lut: 2^polar_bits values of cosf/sinf at the dequantised angles
+ * (turbo-quant/src/polar.rs:91-95,312-313), NULL = computed with the host libm. */
+int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, const float* qjl,
+                             const float* cos_lut, const float* sin_lut, pkv_turbo_profile** out);
+int pkv_turbo_profile_destroy(pkv_turbo_profile* p);
+/* Bytes per vector in the TQB1 payload (turbo-quant/src/wire.rs:311-327). */
+int32_t pkv_turbo_record_bytes(const pkv_turbo_profile* p);
+
+/* Replaces TurboQuantizer::encode per vector (turbo-quant/src/turbo.rs:256-288) and
+ * the per-vector part of TurboCodeWireV1::encode_batch_with_radii (wire.rs:350-396). */
+int pkv_turbo_encode_dev(const pkv_turbo_profile* p, const float* x_dev, const pkv_layout* layout,
+                         uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
+                         void* stream);
+/* Replaces TurboCodeWireV1::decode_batch's per-vector part (wire.rs:497-565) and
+ * decode_approximate_batch (turbo.rs:414-420), fused with the cache write. */
+int pkv_turbo_decode_patch_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                               int64_t payload_batch_stride, const pkv_layout* layout,
+                               float* cache_dev, uint64_t* err_dev, void* stream);
+
+/* TurboQuantAdapter::{encode,decode}_batch_compact (proveKV/src/codec.rs:248-326). */
+int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* p, const float* vectors_host, int64_t n,
+                                   uint8_t* out_host, int64_t out_capacity, int64_t* out_len,
+                                   int32_t* vec_code, int64_t* vec_index);
+int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* p, const uint8_t* bytes_host,
+                                   int64_t len, float* out_host, int64_t out_capacity_floats,
+                                   int64_t* n_vectors, int32_t* vec_code, int64_t* vec_index);
+
+/* TQB1 header, turbo-quant/src/wire.rs:276-290 (38 bytes). */
+#define PKV_TQB1_HEADER_BYTES 38
+int pkv_tqb1_header_write(const pkv_turbo_profile* p, uint32_t n_vectors, uint8_t* out38);
+int pkv_tqb1_header_parse(const pkv_turbo_profile* p, const uint8_t* bytes, int64_t len,
+                          uint32_t* n_vectors);
+
+/* Number of kernel launches this process has issued through the library. */
+int64_t pkv_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PROVEKV_B200_H */

@@ -1,0 +1,206 @@
+"""Seeded generators for the tables the codec kernels take as inputs.
+
+The reference derives its tables from a seed with ``rand_chacha`` (ChaCha8),
+``rand_distr`` (ziggurat normal, gamma), ``nalgebra`` (Householder QR) and
+``statrs`` (inverse CDFs).  None of those streams is reproduced here: these
+generators follow the same *algorithms* with NumPy's PCG64 as the random
+source, so a table built here is a valid table of the same distribution but is
+not the table the Rust crate builds for the same seed.  Bit-exactness of the
+codec is defined given equal tables; tables are plain arrays that can also be
+loaded from a dump of the Rust side.
+
+Reference algorithms followed:
+  * Haar rotation        fib-quant/src/rotation.rs:24-58
+  * Lloyd-Max codebook   fib-quant/src/codebook.rs:158-203, lloyd.rs:105-317,
+                         directions.rs:38-114, spherical_beta.rs:6-139
+  * Rademacher signs     turbo-quant/src/rotation.rs:143-157
+  * QJL Gaussian matrix  turbo-quant/src/qjl.rs:341-352
+"""
+from __future__ import annotations
+
+import functools
+
+import numpy as np
+
+_MASK64 = (1 << 64) - 1
+
+
+def _rng(seed: int) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(seed & _MASK64))
+
+
+def haar_rotation(dim: int, seed: int) -> np.ndarray:
+    """dim x dim orthogonal f64 matrix, row-major.
+
+    Gaussian matrix filled column-major (``DMatrix::from_vec``), QR, then the
+    columns of Q whose R diagonal is negative are flipped
+    (fib-quant/src/rotation.rs:36-50).
+    """
+    if dim <= 0:
+        raise ValueError("dim must be positive")
+    data = _rng(seed).standard_normal(dim * dim)
+    m = data.reshape((dim, dim), order="F")
+    q, r = np.linalg.qr(m)
+    flip = np.diag(r) < 0.0
+    q = q.copy()
+    q[:, flip] *= -1.0
+    return np.ascontiguousarray(q, dtype=np.float64)
+
+
+def rademacher_signs(dim: int, seed: int) -> np.ndarray:
+    """dim values of +-1.0 (f32); seed offset as turbo-quant/src/rotation.rs:152."""
+    bits = _rng((seed + 0xA11CE55ED5A5EED5) & _MASK64).integers(0, 2, size=dim)
+    return np.where(bits == 1, 1.0, -1.0).astype(np.float32)
+
+
+def qjl_matrix(dim: int, projections: int, seed: int) -> np.ndarray:
+    """projections x dim N(0,1) f32, row-major.
+
+    ``seed`` is the TurboQuantizer seed; the two offsets are
+    turbo-quant/src/turbo.rs:167 and turbo-quant/src/qjl.rs:346.
+    """
+    s = (seed + 0xCAFEBABE00000001 + 0xDEADBEEF12345678) & _MASK64
+    g = _rng(s).standard_normal(projections * dim).astype(np.float32)
+    return np.ascontiguousarray(g.reshape(projections, dim))
+
+
+# --- fib-quant codebook ------------------------------------------------------
+
+def _roberts_phi(k: int) -> float:
+    lo, hi = 1.0, 2.0
+    for _ in range(128):
+        mid = (lo + hi) / 2.0
+        if mid ** (k + 1) - mid - 1.0 > 0.0:
+            hi = mid
+        else:
+            lo = mid
+    return (lo + hi) / 2.0
+
+
+def _roberts_kronecker(k: int, n: int) -> np.ndarray:
+    """fib-quant/src/directions.rs:38-74."""
+    from scipy.stats import norm
+
+    phi = _roberts_phi(k)
+    out = np.empty((n, k))
+    for idx in range(n):
+        for j in range(1, k + 1):
+            step = phi ** (-j)
+            frac = min(max(((idx + 0.5) * step) % 1.0, 1.0e-12), 1.0 - 1.0e-12)
+            out[idx, j - 1] = norm.ppf(frac)
+        out[idx] /= np.sqrt(np.sum(out[idx] ** 2))
+    return out
+
+
+def _beta_d_k(d: int, k: int) -> float:
+    """fib-quant/src/spherical_beta.rs:6-21."""
+    if k == d:
+        return 1.0
+    return (k / (k + 2.0)) * ((d - k - 2.0) / 2.0) + 1.0
+
+
+def _initial_codebook(d: int, k: int, n: int) -> np.ndarray:
+    """Radial-angular initialisation, fib-quant/src/codebook.rs:158-181 (k >= 4)."""
+    from scipy.stats import beta as beta_dist
+
+    if k < 4:
+        raise ValueError("only the k >= 4 (Roberts-Kronecker) path is implemented")
+    dirs = _roberts_kronecker(k, n)
+    out = np.empty((n, k))
+    for idx in range(n):
+        if k == d:
+            radius = 1.0
+        else:
+            q = (idx + 1 - 0.5) / n
+            radius = np.sqrt(min(max(beta_dist.ppf(q, k / 2.0, _beta_d_k(d, k)), 0.0), 1.0))
+        out[idx] = radius * dirs[idx]
+    return out
+
+
+def _nearest(samples: np.ndarray, codebook: np.ndarray):
+    d2 = ((samples[:, None, :] - codebook[None, :, :]) ** 2).sum(axis=2)
+    idx = np.argmin(d2, axis=1)  # first minimum == strict '<' scan
+    return idx, d2[np.arange(len(samples)), idx]
+
+
+def _lloyd_step(codebook: np.ndarray, samples: np.ndarray) -> None:
+    """One assign + update_centroids pass with the split-highest-distortion repair
+    (fib-quant/src/lloyd.rs:215-317)."""
+    n, k = codebook.shape
+    assign, dist = _nearest(samples, codebook)
+    counts = np.bincount(assign, minlength=n)
+    distortion = np.bincount(assign, weights=dist, minlength=n)
+    farthest = np.zeros((n, k))
+    far_d = np.full(n, -1.0)
+    for s, a, dd in zip(samples, assign, dist):
+        if dd > far_d[a]:
+            far_d[a] = dd
+            farthest[a] = s
+    sums = np.zeros((n, k))
+    np.add.at(sums, assign, samples)
+    nz = counts > 0
+    codebook[nz] = sums[nz] / counts[nz, None]
+    counts = counts.copy()
+    for empty in np.flatnonzero(counts == 0):
+        donors = np.flatnonzero(counts > 1)
+        if donors.size == 0:
+            raise RuntimeError("no donor cell")
+        # Rust's max_by keeps the last of equal maxima
+        best = donors[0]
+        for c in donors[1:]:
+            if distortion[c] >= distortion[best]:
+                best = c
+        residual = farthest[best] - codebook[best]
+        rn = np.sqrt(np.sum(residual ** 2))
+        if not np.isfinite(rn) or rn <= np.finfo(np.float64).eps:
+            raise RuntimeError("donor residual has zero direction")
+        direction = residual / rn
+        centroid = codebook[best].copy()
+        codebook[best] = centroid - 1.0e-6 * direction
+        codebook[empty] = centroid + 1.0e-6 * direction
+        counts[best] -= 1
+        counts[empty] = 1
+        distortion[best] = 0.0
+        distortion[empty] = 0.0
+
+
+@functools.lru_cache(maxsize=32)
+def _fib_codebook_cached(dim, k, n, seed, training_samples, restarts, iterations) -> bytes:
+    codebook_seed = (seed + 0x9E3779B97F4A7C15) & _MASK64  # fib-quant/src/profile.rs:161
+    initial = _initial_codebook(dim, k, n)
+    # training set: canonical spherical-Beta k-block source (lloyd.rs:184-195)
+    rng = _rng(codebook_seed ^ 0x465155414E54)
+    count = max(training_samples, n)
+    if k == dim:
+        g = rng.standard_normal((count, k))
+        samples = g / np.sqrt((g ** 2).sum(axis=1, keepdims=True))
+    else:
+        a = rng.gamma(k / 2.0, 1.0, size=count)
+        b = rng.gamma((dim - k) / 2.0, 1.0, size=count)
+        r = np.sqrt(a / (a + b))
+        g = rng.standard_normal((count, k))
+        samples = r[:, None] * g / np.sqrt((g ** 2).sum(axis=1, keepdims=True))
+    init_mse = float(_nearest(samples, initial)[1].mean())
+    best, best_mse = initial.copy(), init_mse
+    for restart in range(max(restarts, 1)):
+        if restart == 0:
+            cb = initial.copy()
+        else:  # rotated_initial, lloyd.rs:197-213
+            rot = haar_rotation(k, (codebook_seed + restart * 0x9E3779B9) & _MASK64)
+            cb = initial @ rot.T
+        for _ in range(iterations):
+            _lloyd_step(cb, samples)
+        mse = float(_nearest(samples, cb)[1].mean())
+        if mse < best_mse:
+            best, best_mse = cb.copy(), mse
+    return np.ascontiguousarray(best, dtype=np.float32).tobytes()
+
+
+def fib_codebook(dim: int, k: int = 4, n: int = 32, seed: int = 42, training_samples: int = 2048,
+                 restarts: int = 4, iterations: int = 8) -> np.ndarray:
+    """N x k f32 Lloyd-Max codebook for the k-block of a random unit vector in R^dim.
+
+    Defaults are proveKV's ``FibConfig::default_k4_n32`` (proveKV/src/policy.rs:137-145).
+    """
+    raw = _fib_codebook_cached(dim, k, n, seed, training_samples, restarts, iterations)
+    return np.frombuffer(raw, dtype=np.float32).reshape(n, k).copy()
