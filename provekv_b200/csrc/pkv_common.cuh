@@ -1,0 +1,135 @@
+// Shared declarations of the sm_100a codec kernels: launch geometry, vector
+// addressing, the device error word and the profile objects behind the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pkv_portable_math.h"
+#include "../../include/provekv_b200.h"
+
+#define PKV_MAX_DIM 128
+#define PKV_ERR_NONE 0xFFFFFFFFFFFFFFFFull
+
+// Everything a kernel needs to find the vectors and records of one launch.
+struct PkvGeom {
+  pkv_layout L;
+  int64_t payload_batch_stride;  // bytes between the payloads of two batches
+  int32_t vpb;                   // vectors per batch = n_tokens * n_heads
+  int32_t tiles_per_batch;       // ceil(vpb / tile vectors)
+  int32_t n_batches;             // n_batches[0] * [1] * [2]
+  int32_t rec_bytes;             // bytes per vector record
+};
+
+// Element offset of vector v of batch `batch` (see pkv_layout in the C header).
+__device__ __forceinline__ int64_t pkv_vec_offset(const pkv_layout& L, int batch, int v) {
+  int token = v / L.n_heads;
+  int head = v - token * L.n_heads;
+  int b2 = batch % L.n_batches[2];
+  int t = batch / L.n_batches[2];
+  int b1 = t % L.n_batches[1];
+  int b0 = t / L.n_batches[1];
+  return L.base + (int64_t)b0 * L.batch_stride[0] + (int64_t)b1 * L.batch_stride[1] +
+         (int64_t)b2 * L.batch_stride[2] + (int64_t)token * L.token_stride +
+         (int64_t)head * L.head_stride;
+}
+
+// Error word: the smallest (pass << 56 | global vector index << 8 | code) wins,
+// which is the error the reference's sequential loops would hit first.
+__device__ __forceinline__ void pkv_report(uint64_t* err, int pass, int64_t gvec, int code) {
+  unsigned long long w = ((unsigned long long)pass << 56) | ((unsigned long long)gvec << 8) |
+                         (unsigned long long)code;
+  atomicMin((unsigned long long*)err, w);
+}
+
+__device__ __forceinline__ bool pkv_finite(float x) {
+  return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u;
+}
+
+// IEEE binary16 <-> binary32 in integer arithmetic (round to nearest even), the
+// conversion half::f16::from_f32 / to_f32 perform (fib-quant/src/codec.rs:1002,1028).
+__device__ __forceinline__ uint32_t pkv_f32_to_f16_bits(float f) {
+  const uint32_t x = __float_as_uint(f);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  const uint32_t exp = (x >> 23) & 0xffu;
+  uint32_t man = x & 0x7fffffu;
+  if (exp == 0xffu) return sign | 0x7c00u | (man ? (0x200u | (man >> 13)) : 0u);
+  const int e = (int)exp - 127 + 15;
+  if (e >= 0x1f) return sign | 0x7c00u;
+  if (e <= 0) {
+    if (e < -10) return sign;
+    man |= 0x800000u;
+    const uint32_t shift = (uint32_t)(14 - e);
+    uint32_t hm = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1u);
+    const uint32_t halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (hm & 1u))) hm++;
+    return sign | hm;
+  }
+  uint32_t h = sign | ((uint32_t)e << 10) | (man >> 13);
+  const uint32_t rem = man & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h++;
+  return h;
+}
+
+__device__ __forceinline__ float pkv_f16_bits_to_f32(uint32_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16;
+  const uint32_t exp = (h >> 10) & 0x1fu;
+  uint32_t man = h & 0x3ffu;
+  if (exp == 0) {
+    if (man == 0) return __uint_as_float(sign);
+    int e = -1;
+    do {
+      man <<= 1;
+      e++;
+    } while (!(man & 0x400u));
+    return __uint_as_float(sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13));
+  }
+  if (exp == 0x1f) return __uint_as_float(sign | 0x7f800000u | (man << 13));
+  return __uint_as_float(sign | ((exp + 127 - 15) << 23) | (man << 13));
+}
+
+// ---- host-side objects ---------------------------------------------------
+
+struct PkvWorkspace {  // device staging of the *_batch_compact calls, grown on demand
+  void* in = nullptr;
+  void* out = nullptr;
+  uint64_t* err = nullptr;
+  int64_t in_cap = 0, out_cap = 0;
+};
+
+struct pkv_fib_profile {
+  pkv_fib_config cfg;
+  int device;
+  int idx_bits, norm_len, idx_len, rec_bytes, blocks;
+  double* rot_t_dev;    // [j][r]  = M[r][j], f64 (encode: lanes read consecutive rows)
+  float* rot32_dev;     // [row][col] = (f32) M[row][col] (decode, fib-quant/src/rotation.rs:139)
+  float* codebook_dev;  // 32 x 4 f32, rows >= N zero-filled
+  PkvWorkspace ws;
+};
+
+struct pkv_turbo_profile {
+  pkv_turbo_config cfg;
+  int device;
+  int polar_bits, pairs, rec_bytes, radii_words, angle_words, sign_words;
+  float scale;              // 1 / sqrtf(dim), turbo-quant/src/rotation.rs:394
+  uint32_t sign_mask[4];    // bit i set: signs[i] == -1
+  float* qjl_dev;           // projections x dim
+  float* lut_dev;           // [2][2^polar_bits]: cos then sin
+  PkvWorkspace ws;
+};
+
+int pkv_cuda_status(cudaError_t e);
+void pkv_count_launch();
+
+// launchers implemented in pkv_fib.cu / pkv_turbo.cu
+int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
+                          uint8_t* payload, uint64_t* err, int batch_numerics, cudaStream_t s);
+int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
+                          float* cache, uint64_t* err, cudaStream_t s);
+int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const PkvGeom& g,
+                            uint8_t* payload, uint64_t* err, cudaStream_t s);
+int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,
+                            float* cache, uint64_t* err, cudaStream_t s);
+int pkv_fib_tile_vectors(int dim, int encode);
+int pkv_turbo_tile_vectors(int dim);

@@ -1,0 +1,420 @@
+// fib-quant k=4 cold-tier kernels for sm_100a: batched encode (normalise, dense
+// f64 rotation, nearest-of-N codeword per 4-block, 5-bit pack, fp16 norm) and
+// decode fused with the write into the KV cache.
+//
+// Both kernels reproduce the reference's arithmetic order exactly:
+//  encode  fib-quant/src/codec.rs:578-729, rotation.rs:104-115,
+//          gpu-backend/src/simd_nearest.rs:24-94, fib-quant/src/bitpack.rs:4-44
+//  decode  fib-quant/src/codec.rs:797-844, rotation.rs:136-149
+// The dense rotation makes them ALU-bound, not HBM-bound: decode needs
+// 2*dim*dim separately rounded f32 operations per vector, encode the same count
+// in f64.
+#include "pkv_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 128;
+
+__device__ __forceinline__ uint32_t load_bits(const uint8_t* bytes, int pos, int width) {
+  // bits [pos, pos+width) of an LSB-first stream, width <= 8
+  uint32_t lo = bytes[pos >> 3];
+  uint32_t hi = bytes[(pos + width - 1) >> 3];
+  return (((hi << 8) | lo) >> (pos & 7)) & ((1u << width) - 1u);
+}
+
+// Copy `nbytes` from global (16-byte aligned) into shared memory.
+__device__ __forceinline__ void stage_in(uint8_t* dst, const uint8_t* src, int nbytes) {
+  int n16 = nbytes >> 4;
+  for (int i = threadIdx.x; i < n16; i += blockDim.x)
+    reinterpret_cast<uint4*>(dst)[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+  for (int i = (n16 << 4) + threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
+}
+__device__ __forceinline__ void stage_out(uint8_t* dst, const uint8_t* src, int nbytes) {
+  int n16 = nbytes >> 4;
+  for (int i = threadIdx.x; i < n16; i += blockDim.x)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  for (int i = (n16 << 4) + threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------
+// decode + patch
+// ---------------------------------------------------------------------------
+// One CTA decodes TV vectors.  Thread (cg, vg) owns columns {4cg..4cg+3} and
+// {D/2+4cg..+3} of vectors vg*8 .. vg*8+7 and walks the rows in ascending order,
+// so each of its 64 accumulators sees the reference's sum
+//   x_c = (((0 + m_0c r_0) + m_1c r_1) + ...)   with separately rounded * and +.
+template <int D>
+struct FibDec {
+  static constexpr int CG = D / 8;
+  static constexpr int VG = kThreads / CG;
+  static constexpr int TV = VG * 8;
+  static constexpr int B = D / 4;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
+                        const float* __restrict__ rot32, const float* __restrict__ codebook,
+                        int n_codewords, int idx_bits, int norm_len, float* __restrict__ cache,
+                        uint64_t* err) {
+  using K = FibDec<D>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* s_rot = reinterpret_cast<float*>(smem);                 // [D][D]
+  float4* s_cb = reinterpret_cast<float4*>(s_rot + D * D);       // [32]
+  int64_t* s_dst = reinterpret_cast<int64_t*>(s_cb + 32);        // [TV]
+  float* s_norm = reinterpret_cast<float*>(s_dst + K::TV);       // [TV]
+  uint8_t* s_idx = reinterpret_cast<uint8_t*>(s_norm + K::TV);   // [TV][B]
+  uint8_t* s_rec = s_idx + K::TV * K::B;                         // [TV][rec] (+16 pad)
+
+  const int tile = blockIdx.x % g.tiles_per_batch;
+  const int batch = blockIdx.x / g.tiles_per_batch;
+  const int v0 = tile * K::TV;
+  const int nv = min(K::TV, g.vpb - v0);
+  const int rec = g.rec_bytes;
+
+  for (int i = threadIdx.x; i < D * D / 4; i += kThreads)
+    reinterpret_cast<float4*>(s_rot)[i] = __ldg(reinterpret_cast<const float4*>(rot32) + i);
+  if (threadIdx.x < 32) s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
+  stage_in(s_rec, payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * rec, nv * rec);
+  __syncthreads();
+
+  // unpack + validate: one thread per vector (checks in the reference's order)
+  for (int v = threadIdx.x; v < K::TV; v += kThreads) {
+    float nf = 0.0f;
+    if (v < nv) {
+      const uint8_t* r = s_rec + v * rec;
+      const int64_t gvec = (int64_t)batch * g.vpb + v0 + v;
+      int code = 0;
+      const int used = K::B * idx_bits;
+      for (int pos = used; pos < (((used + 7) >> 3) << 3); pos++)
+        if ((r[norm_len + (pos >> 3)] >> (pos & 7)) & 1) code = PKV_VEC_PADDING_BITS;
+      for (int b = 0; b < K::B; b++) {
+        uint32_t idx = load_bits(r + norm_len, b * idx_bits, idx_bits);
+        if (idx >= (uint32_t)n_codewords) {
+          if (!code) code = PKV_VEC_INDEX_RANGE;
+          idx = 0;
+        }
+        s_idx[v * K::B + b] = (uint8_t)idx;
+      }
+      if (norm_len == 2) {
+        nf = pkv_f16_bits_to_f32((uint32_t)r[0] | ((uint32_t)r[1] << 8));
+      } else {
+        nf = __uint_as_float((uint32_t)r[0] | ((uint32_t)r[1] << 8) | ((uint32_t)r[2] << 16) |
+                             ((uint32_t)r[3] << 24));
+      }
+      if (!(pkv_finite(nf) && nf > 0.0f)) {
+        if (!code) code = PKV_VEC_BAD_NORM;
+      }
+      if (code) pkv_report(err, 0, gvec, code);
+      s_dst[v] = pkv_vec_offset(g.L, batch, v0 + v);
+    } else {
+      for (int b = 0; b < K::B; b++) s_idx[v * K::B + b] = 0;
+      s_dst[v] = 0;
+    }
+    s_norm[v] = nf;
+  }
+  __syncthreads();
+
+  const int cg = threadIdx.x % K::CG, vg = threadIdx.x / K::CG;
+  const int cA = 4 * cg, cB = D / 2 + 4 * cg;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int c = 0; c < 8; c++) acc[i][c] = 0.0f;
+
+#pragma unroll 1
+  for (int b = 0; b < K::B; b++) {
+    float4 cw[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) cw[i] = s_cb[s_idx[(vg * 8 + i) * K::B + b]];
+#pragma unroll
+    for (int rr = 0; rr < 4; rr++) {
+      const float* mrow = s_rot + (4 * b + rr) * D;
+      const float4 mA = *reinterpret_cast<const float4*>(mrow + cA);
+      const float4 mB = *reinterpret_cast<const float4*>(mrow + cB);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float r = rr == 0 ? cw[i].x : rr == 1 ? cw[i].y : rr == 2 ? cw[i].z : cw[i].w;
+        acc[i][0] = __fadd_rn(acc[i][0], __fmul_rn(mA.x, r));
+        acc[i][1] = __fadd_rn(acc[i][1], __fmul_rn(mA.y, r));
+        acc[i][2] = __fadd_rn(acc[i][2], __fmul_rn(mA.z, r));
+        acc[i][3] = __fadd_rn(acc[i][3], __fmul_rn(mA.w, r));
+        acc[i][4] = __fadd_rn(acc[i][4], __fmul_rn(mB.x, r));
+        acc[i][5] = __fadd_rn(acc[i][5], __fmul_rn(mB.y, r));
+        acc[i][6] = __fadd_rn(acc[i][6], __fmul_rn(mB.z, r));
+        acc[i][7] = __fadd_rn(acc[i][7], __fmul_rn(mB.w, r));
+      }
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int v = vg * 8 + i;
+    if (v >= nv) continue;
+    const float nf = s_norm[v];
+    float o[8];
+    bool ok = true;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      o[c] = __fmul_rn(acc[i][c], nf);
+      ok = ok && pkv_finite(o[c]);
+    }
+    if (!ok) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, PKV_VEC_NONFINITE_OUTPUT);
+    float* dst = cache + s_dst[v];
+    for (int r = 0; r < g.L.n_replicas; r++) {
+      *reinterpret_cast<float4*>(dst + cA) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4*>(dst + cB) = make_float4(o[4], o[5], o[6], o[7]);
+      dst += g.L.replica_stride;
+    }
+  }
+}
+
+template <int D>
+size_t fib_decode_smem(int rec) {
+  using K = FibDec<D>;
+  return sizeof(float) * D * D + sizeof(float4) * 32 + sizeof(int64_t) * K::TV +
+         sizeof(float) * K::TV + K::TV * K::B + (size_t)K::TV * rec + 16;
+}
+
+
+// ---------------------------------------------------------------------------
+// encode
+// ---------------------------------------------------------------------------
+// One CTA encodes TV vectors in three steps: (A) per-vector f64 norm and the
+// normalised vector, (B) rotation + argmin with thread (bg, vg) owning block bg
+// (rows 4bg..4bg+3) of vectors vg*8..vg*8+7, (C) per-vector bit packing.
+template <int D>
+struct FibEnc {
+  static constexpr int B = D / 4;
+  static constexpr int VG = kThreads / B;
+  static constexpr int TV = VG * 8;
+  static constexpr int XS = D + 1;  // padded row strides (elements)
+};
+
+__device__ __forceinline__ int nearest_codeword(const float4* s_cb, int n, int order, float s0,
+                                                float s1, float s2, float s3) {
+  int best = 0;
+  float best_dist = __int_as_float(0x7f800000);
+  const int paired = order == PKV_ARGMIN_PAIRWISE ? (n & ~1) : 0;
+  for (int c = 0; c < n; c++) {
+    const float4 w = s_cb[c];
+    float dist;
+    if (c < paired) {  // gpu-backend/src/simd_nearest.rs:62-70: (q0+q1)+(q2+q3), delta = cw - s
+      const float d0 = __fsub_rn(w.x, s0), d1 = __fsub_rn(w.y, s1);
+      const float d2 = __fsub_rn(w.z, s2), d3 = __fsub_rn(w.w, s3);
+      dist = __fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)),
+                       __fadd_rn(__fmul_rn(d2, d2), __fmul_rn(d3, d3)));
+    } else {  // :24-39 and the odd tail :82-92: ((q0+q1)+q2)+q3, delta = s - cw
+      const float d0 = __fsub_rn(s0, w.x), d1 = __fsub_rn(s1, w.y);
+      const float d2 = __fsub_rn(s2, w.z), d3 = __fsub_rn(s3, w.w);
+      dist = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)),
+                                 __fmul_rn(d2, d2)),
+                       __fmul_rn(d3, d3));
+    }
+    if (dist < best_dist) {
+      best_dist = dist;
+      best = c;
+    }
+  }
+  return best;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+fib_encode_kernel(PkvGeom g, const float* __restrict__ x, const double* __restrict__ rot_t,
+                  const float* __restrict__ codebook, int n_codewords, int idx_bits, int norm_len,
+                  int argmin_order, int batch_numerics, uint8_t* __restrict__ payload,
+                  uint64_t* err) {
+  using K = FibEnc<D>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  double* s_rot = reinterpret_cast<double*>(smem);                 // [j][r]
+  double* s_nrm = s_rot + D * D;                                   // [TV][XS]
+  double* s_norm = s_nrm + K::TV * K::XS;                          // [TV]
+  float4* s_cb = reinterpret_cast<float4*>(s_norm + K::TV);        // [32]
+  float* s_x = reinterpret_cast<float*>(s_cb + 32);                // [TV][XS]
+  uint8_t* s_idx = reinterpret_cast<uint8_t*>(s_x + K::TV * K::XS);  // [TV][B]
+  uint8_t* s_bad = s_idx + K::TV * K::B;                           // [TV]
+  uint8_t* s_rec = s_bad + K::TV;                                  // [TV][rec], 16-aligned below
+
+  const int tile = blockIdx.x % g.tiles_per_batch;
+  const int batch = blockIdx.x / g.tiles_per_batch;
+  const int v0 = tile * K::TV;
+  const int nv = min(K::TV, g.vpb - v0);
+  const int rec = g.rec_bytes;
+  s_rec += (16 - (reinterpret_cast<uintptr_t>(s_rec) & 15)) & 15;
+
+  for (int i = threadIdx.x; i < D * D / 2; i += kThreads)
+    reinterpret_cast<double2*>(s_rot)[i] = __ldg(reinterpret_cast<const double2*>(rot_t) + i);
+  if (threadIdx.x < 32) s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
+  // load the tile: D/4 lanes per vector, one float4 each
+  for (int i = threadIdx.x; i < K::TV * (D / 4); i += kThreads) {
+    const int v = i / (D / 4), q = i % (D / 4);
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (v < nv)
+      val = __ldg(reinterpret_cast<const float4*>(x + pkv_vec_offset(g.L, batch, v0 + v)) + q);
+    float* d = s_x + v * K::XS + 4 * q;
+    d[0] = val.x; d[1] = val.y; d[2] = val.z; d[3] = val.w;
+  }
+  __syncthreads();
+
+  // (A) check_finite, l2_norm (f64, sequential), fib-quant/src/codec.rs:601-606,1049-1064
+  for (int v = threadIdx.x; v < K::TV; v += kThreads) {
+    const float* xv = s_x + v * K::XS;
+    bool finite = true;
+    double acc = 0.0;
+    for (int j = 0; j < D; j++) {
+      const float f = xv[j];
+      finite = finite && pkv_finite(f);
+      const double t = (double)f;
+      acc = __dadd_rn(acc, __dmul_rn(t, t));
+    }
+    double norm = __dsqrt_rn(acc);
+    int bad = 0;
+    if (v < nv) {
+      if (!finite) bad = PKV_VEC_NONFINITE_INPUT;
+      else if (norm == 0.0) bad = PKV_VEC_ZERO_NORM;
+      if (bad) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, bad);
+    }
+    if (bad || v >= nv) norm = 1.0;
+    s_norm[v] = norm;
+    s_bad[v] = (uint8_t)(bad || v >= nv);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < K::TV * D; i += kThreads) {
+    const int v = i / D, j = i % D;
+    double q = __ddiv_rn((double)s_x[v * K::XS + j], s_norm[v]);
+    if (batch_numerics) q = (double)__double2float_rn(q);  // :607-609 then :662
+    if (s_bad[v]) q = 0.0;
+    s_nrm[v * K::XS + j] = q;
+  }
+  __syncthreads();
+
+  // (B) StoredRotation::apply (rotation.rs:104-115): y_r = sum_j M[r][j] n_j, j ascending, f64
+  const int bg = threadIdx.x % K::B, vg = threadIdx.x / K::B;
+  double acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int r = 0; r < 4; r++) acc[i][r] = 0.0;
+#pragma unroll 2
+  for (int j = 0; j < D; j++) {
+    const double2 m01 = *reinterpret_cast<const double2*>(s_rot + j * D + 4 * bg);
+    const double2 m23 = *reinterpret_cast<const double2*>(s_rot + j * D + 4 * bg + 2);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const double nj = s_nrm[(vg * 8 + i) * K::XS + j];
+      acc[i][0] = __dadd_rn(acc[i][0], __dmul_rn(m01.x, nj));
+      acc[i][1] = __dadd_rn(acc[i][1], __dmul_rn(m01.y, nj));
+      acc[i][2] = __dadd_rn(acc[i][2], __dmul_rn(m23.x, nj));
+      acc[i][3] = __dadd_rn(acc[i][3], __dmul_rn(m23.y, nj));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int idx = nearest_codeword(s_cb, n_codewords, argmin_order, __double2float_rn(acc[i][0]),
+                                     __double2float_rn(acc[i][1]), __double2float_rn(acc[i][2]),
+                                     __double2float_rn(acc[i][3]));
+    s_idx[(vg * 8 + i) * K::B + bg] = (uint8_t)idx;
+  }
+  __syncthreads();
+
+  // (C) encode_norm (:994-1020) + pack_indices (bitpack.rs:4-44)
+  for (int v = threadIdx.x; v < nv; v += kThreads) {
+    uint8_t* r = s_rec + v * rec;
+    for (int i = 0; i < rec; i++) r[i] = 0;
+    if (s_bad[v]) continue;
+    const float nf = __double2float_rn(s_norm[v]);
+    bool ok;
+    if (norm_len == 2) {
+      const uint32_t h = pkv_f32_to_f16_bits(nf);
+      ok = (h & 0x7fffu) < 0x7c00u && (h & 0x7fffu) != 0;
+      r[0] = (uint8_t)(h & 0xff);
+      r[1] = (uint8_t)(h >> 8);
+    } else {
+      const uint32_t u = __float_as_uint(nf);
+      ok = pkv_finite(nf) && nf > 0.0f;
+      r[0] = (uint8_t)u; r[1] = (uint8_t)(u >> 8); r[2] = (uint8_t)(u >> 16); r[3] = (uint8_t)(u >> 24);
+    }
+    if (!ok) {
+      pkv_report(err, 1, (int64_t)batch * g.vpb + v0 + v, PKV_VEC_NORM_RANGE);
+      for (int i = 0; i < norm_len; i++) r[i] = 0;
+      continue;
+    }
+    for (int b = 0; b < K::B; b++) {
+      const int pos = b * idx_bits;
+      const uint32_t val = (uint32_t)s_idx[v * K::B + b] << (pos & 7);
+      r[norm_len + (pos >> 3)] |= (uint8_t)val;
+      if (val >> 8) r[norm_len + (pos >> 3) + 1] |= (uint8_t)(val >> 8);
+    }
+  }
+  __syncthreads();
+  stage_out(payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * rec, s_rec, nv * rec);
+}
+
+template <int D>
+size_t fib_encode_smem(int rec) {
+  using K = FibEnc<D>;
+  return sizeof(double) * D * D + sizeof(double) * K::TV * K::XS + sizeof(double) * K::TV +
+         sizeof(float4) * 32 + sizeof(float) * K::TV * K::XS + K::TV * K::B + K::TV +
+         (size_t)K::TV * rec + 32;
+}
+
+template <typename F>
+int set_smem(F kernel, size_t bytes) {
+  if (bytes > 48 * 1024)
+    return pkv_cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return PKV_OK;
+}
+
+}  // namespace
+
+int pkv_fib_tile_vectors(int dim, int encode) {
+  if (dim == 64) return encode ? FibEnc<64>::TV : FibDec<64>::TV;
+  if (dim == 128) return encode ? FibEnc<128>::TV : FibDec<128>::TV;
+  return 0;
+}
+
+int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
+                          uint8_t* payload, uint64_t* err, int batch_numerics, cudaStream_t s) {
+  const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
+  if (grid == 0) return PKV_OK;
+  if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  int st;
+#define PKV_FIB_ENC(DIM)                                                                          \
+  {                                                                                               \
+    const size_t sm = fib_encode_smem<DIM>(g.rec_bytes);                                          \
+    if ((st = set_smem(fib_encode_kernel<DIM>, sm)) != PKV_OK) return st;                         \
+    fib_encode_kernel<DIM><<<(unsigned)grid, kThreads, sm, s>>>(                                  \
+        g, x, p->rot_t_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,      \
+        p->cfg.argmin_order, batch_numerics, payload, err);                                       \
+  }
+  if (p->cfg.dim == 64) PKV_FIB_ENC(64)
+  else if (p->cfg.dim == 128) PKV_FIB_ENC(128)
+  else return PKV_ERR_UNSUPPORTED;
+#undef PKV_FIB_ENC
+  pkv_count_launch();
+  return pkv_cuda_status(cudaGetLastError());
+}
+
+int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
+                          float* cache, uint64_t* err, cudaStream_t s) {
+  const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
+  if (grid == 0) return PKV_OK;
+  if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  int st;
+#define PKV_FIB_DEC(DIM)                                                                          \
+  {                                                                                               \
+    const size_t sm = fib_decode_smem<DIM>(g.rec_bytes);                                          \
+    if ((st = set_smem(fib_decode_patch_kernel<DIM>, sm)) != PKV_OK) return st;                   \
+    fib_decode_patch_kernel<DIM><<<(unsigned)grid, kThreads, sm, s>>>(                            \
+        g, payload, p->rot32_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits,             \
+        p->norm_len, cache, err);                                                                 \
+  }
+  if (p->cfg.dim == 64) PKV_FIB_DEC(64)
+  else if (p->cfg.dim == 128) PKV_FIB_DEC(128)
+  else return PKV_ERR_UNSUPPORTED;
+#undef PKV_FIB_DEC
+  pkv_count_launch();
+  return pkv_cuda_status(cudaGetLastError());
+}

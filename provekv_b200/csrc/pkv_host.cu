@@ -1,0 +1,588 @@
+// Host side of the C ABI (include/provekv_b200.h): profiles, launch geometry,
+// the host-buffer "*_batch_compact" calls and the FB2 / TQB1 headers.
+#include <math.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+#include <new>
+
+#include "pkv_common.cuh"
+
+namespace {
+
+std::atomic<int64_t> g_launches{0};
+
+int grow(void** ptr, int64_t* cap, int64_t need) {
+  if (need <= *cap) return PKV_OK;
+  if (*ptr) cudaFree(*ptr);
+  *ptr = nullptr;
+  *cap = 0;
+  int64_t want = need + need / 4 + 256;
+  cudaError_t e = cudaMalloc(ptr, (size_t)want);
+  if (e != cudaSuccess) return pkv_cuda_status(e);
+  *cap = want;
+  return PKV_OK;
+}
+
+int ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes) {
+  int st;
+  if ((st = grow(&ws->in, &ws->in_cap, in_bytes)) != PKV_OK) return st;
+  if ((st = grow(&ws->out, &ws->out_cap, out_bytes)) != PKV_OK) return st;
+  if (!ws->err) {
+    cudaError_t e = cudaMalloc((void**)&ws->err, sizeof(uint64_t));
+    if (e != cudaSuccess) return pkv_cuda_status(e);
+  }
+  return PKV_OK;
+}
+
+void ws_release(PkvWorkspace* ws) {
+  if (ws->in) cudaFree(ws->in);
+  if (ws->out) cudaFree(ws->out);
+  if (ws->err) cudaFree(ws->err);
+  *ws = PkvWorkspace();
+}
+
+std::mutex g_compact_mutex;  // the compact calls share each profile's staging buffers
+
+// Validate a layout and derive the launch geometry for tiles of `tile` vectors.
+int make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
+              bool encode, PkvGeom* g) {
+  if (!L) return PKV_ERR_INVALID_ARGUMENT;
+  if (L->n_tokens < 0 || L->n_heads <= 0 || L->n_replicas < 1) return PKV_ERR_INVALID_ARGUMENT;
+  if (encode && L->n_replicas != 1) return PKV_ERR_INVALID_ARGUMENT;
+  int64_t nb = 1;
+  for (int i = 0; i < 3; i++) {
+    if (L->n_batches[i] < 1) return PKV_ERR_INVALID_ARGUMENT;
+    nb *= L->n_batches[i];
+    if (L->batch_stride[i] % 4) return PKV_ERR_INVALID_ARGUMENT;
+  }
+  if (L->base % 4 || L->token_stride % 4 || L->head_stride % 4 || L->replica_stride % 4)
+    return PKV_ERR_INVALID_ARGUMENT;
+  const int64_t vpb = (int64_t)L->n_tokens * L->n_heads;
+  if (vpb * nb >= (int64_t)1 << 31 || nb >= (int64_t)1 << 31) return PKV_ERR_UNSUPPORTED;
+  if (payload_batch_stride % 16 || payload_batch_stride < vpb * rec_bytes)
+    return PKV_ERR_INVALID_ARGUMENT;
+  g->L = *L;
+  g->payload_batch_stride = payload_batch_stride;
+  g->vpb = (int32_t)vpb;
+  g->tiles_per_batch = (int32_t)((vpb + tile - 1) / tile);
+  g->n_batches = (int32_t)nb;
+  g->rec_bytes = rec_bytes;
+  return PKV_OK;
+}
+
+pkv_layout flat_layout(int64_t n, int dim) {
+  pkv_layout L;
+  memset(&L, 0, sizeof(L));
+  L.n_batches[0] = L.n_batches[1] = L.n_batches[2] = 1;
+  L.n_tokens = (int32_t)n;
+  L.n_heads = 1;
+  L.token_stride = dim;
+  L.head_stride = dim;
+  L.n_replicas = 1;
+  return L;
+}
+
+int decode_err_word(uint64_t w, int32_t* code, int64_t* index) {
+  if (w == PKV_ERR_NONE) {
+    if (code) *code = 0;
+    if (index) *index = -1;
+    return PKV_OK;
+  }
+  const int c = (int)(w & 0xff);
+  if (code) *code = c;
+  if (index) *index = (int64_t)((w >> 8) & 0xFFFFFFFFFFFFull);
+  return c;
+}
+
+int fib_index_bits(int n) {  // fib-quant/src/profile.rs:268-274
+  int b = 1;
+  while ((1 << b) < n) b++;
+  return b;
+}
+
+}  // namespace
+
+int pkv_cuda_status(cudaError_t e) { return e == cudaSuccess ? PKV_OK : PKV_ERR_CUDA; }
+void pkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+extern "C" {
+
+int64_t pkv_launch_count(void) { return g_launches.load(); }
+int pkv_version(void) { return 100; }
+
+const char* pkv_status_string(int s) {
+  switch (s) {
+    case PKV_OK: return "ok";
+    case PKV_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case PKV_ERR_CUDA: return "CUDA error (no usable device, out of memory or launch failure)";
+    case PKV_ERR_UNSUPPORTED: return "shape not supported by the kernels";
+    case PKV_ERR_EMPTY_BATCH: return "empty batch";
+    case PKV_ERR_CORRUPT_HEADER: return "corrupt or mismatching wire header";
+    case PKV_ERR_BUFFER_TOO_SMALL: return "output buffer too small";
+    case PKV_VEC_NONFINITE_INPUT: return "non-finite input value";
+    case PKV_VEC_ZERO_NORM: return "zero-norm vector";
+    case PKV_VEC_BAD_RADIUS: return "radius is not finite and non-negative";
+    case PKV_VEC_BAD_RADIUS_RANGE: return "radius codec range is malformed";
+    case PKV_VEC_PADDING_BITS: return "nonzero padding bits";
+    case PKV_VEC_INDEX_RANGE: return "codeword index out of range";
+    case PKV_VEC_BAD_NORM: return "invalid stored norm";
+    case PKV_VEC_NONFINITE_OUTPUT: return "non-finite decoded value";
+    case PKV_VEC_NONFINITE_RESIDUAL: return "non-finite residual";
+    case PKV_VEC_NORM_RANGE: return "norm not representable in the wire norm format";
+    default: return "unknown status";
+  }
+}
+
+int pkv_device_count(int* count) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (count) *count = e == cudaSuccess ? n : 0;
+  return pkv_cuda_status(e);
+}
+int pkv_set_device(int device) { return pkv_cuda_status(cudaSetDevice(device)); }
+int pkv_host_alloc(void** ptr, int64_t bytes) { return pkv_cuda_status(cudaMallocHost(ptr, (size_t)bytes)); }
+int pkv_host_free(void* ptr) { return pkv_cuda_status(cudaFreeHost(ptr)); }
+int pkv_dev_alloc(void** ptr, int64_t bytes) { return pkv_cuda_status(cudaMalloc(ptr, (size_t)bytes)); }
+int pkv_dev_free(void* ptr) { return pkv_cuda_status(cudaFree(ptr)); }
+int pkv_memcpy_h2d(void* d, const void* s, int64_t n, void* stream) {
+  return pkv_cuda_status(cudaMemcpyAsync(d, s, (size_t)n, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+}
+int pkv_memcpy_d2h(void* d, const void* s, int64_t n, void* stream) {
+  return pkv_cuda_status(cudaMemcpyAsync(d, s, (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+}
+int pkv_stream_synchronize(void* stream) { return pkv_cuda_status(cudaStreamSynchronize((cudaStream_t)stream)); }
+
+int pkv_error_word_reset(uint64_t* err_dev, void* stream) {
+  return pkv_cuda_status(cudaMemsetAsync(err_dev, 0xFF, sizeof(uint64_t), (cudaStream_t)stream));
+}
+int pkv_error_word_read(const uint64_t* err_dev, void* stream, int32_t* code, int64_t* index) {
+  uint64_t w = 0;
+  cudaError_t e = cudaMemcpyAsync(&w, err_dev, sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return PKV_ERR_CUDA;
+  return decode_err_word(w, code, index);
+}
+
+// ---------------------------------------------------------------------------
+// fib-quant
+// ---------------------------------------------------------------------------
+
+int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, const float* codebook,
+                           pkv_fib_profile** out) {
+  if (!cfg || !rotation || !codebook || !out) return PKV_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (cfg->dim <= 0 || cfg->block_dim <= 0 || cfg->dim % cfg->block_dim || cfg->codebook_size < 2)
+    return PKV_ERR_INVALID_ARGUMENT;
+  if ((cfg->dim != 64 && cfg->dim != 128) || cfg->block_dim != 4 || cfg->codebook_size > 32)
+    return PKV_ERR_UNSUPPORTED;
+  if (cfg->norm_format < 0 || cfg->norm_format > 1 || cfg->argmin_order < 0 ||
+      cfg->argmin_order > 1 || cfg->numerics < 0 || cfg->numerics > 2)
+    return PKV_ERR_INVALID_ARGUMENT;
+  pkv_fib_profile* p = new (std::nothrow) pkv_fib_profile();
+  if (!p) return PKV_ERR_CUDA;
+  p->cfg = *cfg;
+  p->blocks = cfg->dim / cfg->block_dim;
+  p->idx_bits = fib_index_bits(cfg->codebook_size);
+  p->norm_len = cfg->norm_format == PKV_NORM_FP16 ? 2 : 4;
+  p->idx_len = (p->blocks * p->idx_bits + 7) / 8;
+  p->rec_bytes = p->norm_len + p->idx_len;
+  p->rot_t_dev = nullptr;
+  p->rot32_dev = nullptr;
+  p->codebook_dev = nullptr;
+  const int d = cfg->dim;
+  cudaError_t e = cudaGetDevice(&p->device);
+  double* rt = new double[d * d];
+  float* r32 = new float[d * d];
+  float cb[128];
+  memset(cb, 0, sizeof(cb));
+  for (int r = 0; r < d; r++)
+    for (int j = 0; j < d; j++) {
+      rt[j * d + r] = rotation[r * d + j];
+      r32[r * d + j] = (float)rotation[r * d + j];  // fib-quant/src/rotation.rs:139
+    }
+  memcpy(cb, codebook, sizeof(float) * 4 * cfg->codebook_size);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot_t_dev, sizeof(double) * d * d);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot32_dev, sizeof(float) * d * d);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->codebook_dev, sizeof(cb));
+  if (e == cudaSuccess) e = cudaMemcpy(p->rot_t_dev, rt, sizeof(double) * d * d, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->rot32_dev, r32, sizeof(float) * d * d, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->codebook_dev, cb, sizeof(cb), cudaMemcpyHostToDevice);
+  delete[] rt;
+  delete[] r32;
+  if (e != cudaSuccess) {
+    pkv_fib_profile_destroy(p);
+    return PKV_ERR_CUDA;
+  }
+  *out = p;
+  return PKV_OK;
+}
+
+int pkv_fib_profile_destroy(pkv_fib_profile* p) {
+  if (!p) return PKV_OK;
+  if (p->rot_t_dev) cudaFree(p->rot_t_dev);
+  if (p->rot32_dev) cudaFree(p->rot32_dev);
+  if (p->codebook_dev) cudaFree(p->codebook_dev);
+  ws_release(&p->ws);
+  delete p;
+  return PKV_OK;
+}
+
+int32_t pkv_fib_record_bytes(const pkv_fib_profile* p) { return p ? p->rec_bytes : 0; }
+
+int pkv_fib_encode_dev(const pkv_fib_profile* p, const float* x_dev, const pkv_layout* layout,
+                       uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
+                       void* stream) {
+  if (!p || !x_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)x_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 1), true, &g);
+  if (st != PKV_OK) return st;
+  if (g.vpb == 0) return PKV_ERR_EMPTY_BATCH;
+  const int batch_numerics = p->cfg.numerics == PKV_FIB_NUMERICS_BATCH ||
+                             (p->cfg.numerics == PKV_FIB_NUMERICS_AUTO && g.vpb >= 4);
+  return pkv_launch_fib_encode(p, x_dev, g, payload_dev, err_dev, batch_numerics, (cudaStream_t)stream);
+}
+
+int pkv_fib_decode_patch_dev(const pkv_fib_profile* p, const uint8_t* payload_dev,
+                             int64_t payload_batch_stride, const pkv_layout* layout,
+                             float* cache_dev, uint64_t* err_dev, void* stream) {
+  if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
+  if (st != PKV_OK) return st;
+  return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_fb2_header_write(const pkv_fib_profile* p, uint32_t n_vectors, uint8_t* out) {
+  if (!p || !out) return PKV_ERR_INVALID_ARGUMENT;
+  const uint32_t blocks = (uint32_t)p->blocks;
+  const uint16_t nl = (uint16_t)p->norm_len, il = (uint16_t)p->idx_len;
+  out[0] = 'F'; out[1] = 'B'; out[2] = '2'; out[3] = 1;
+  out[4] = (uint8_t)p->idx_bits;
+  out[5] = 0;
+  memcpy(out + 6, &blocks, 4);
+  memcpy(out + 10, &n_vectors, 4);
+  out[14] = (uint8_t)p->cfg.norm_format;
+  memcpy(out + 15, &nl, 2);
+  memcpy(out + 17, &il, 2);
+  return PKV_OK;
+}
+
+int pkv_fb2_header_parse(const pkv_fib_profile* p, const uint8_t* b, int64_t len, uint32_t* n_vectors) {
+  if (!p || !b || !n_vectors) return PKV_ERR_INVALID_ARGUMENT;
+  if (len < PKV_FB2_HEADER_BYTES) return PKV_ERR_CORRUPT_HEADER;
+  if (b[0] != 'F' || b[1] != 'B' || b[2] != '2' || b[3] != 1) return PKV_ERR_CORRUPT_HEADER;
+  uint32_t blocks, n;
+  uint16_t nl, il;
+  memcpy(&blocks, b + 6, 4);
+  memcpy(&n, b + 10, 4);
+  memcpy(&nl, b + 15, 2);
+  memcpy(&il, b + 17, 2);
+  if (b[4] != p->idx_bits || blocks != (uint32_t)p->blocks) return PKV_ERR_CORRUPT_HEADER;
+  if (b[14] != p->cfg.norm_format) return PKV_ERR_CORRUPT_HEADER;
+  if (nl != p->norm_len || il != p->idx_len) return PKV_ERR_CORRUPT_HEADER;
+  if (len < PKV_FB2_HEADER_BYTES + (int64_t)n * (nl + il)) return PKV_ERR_CORRUPT_HEADER;
+  *n_vectors = n;
+  return PKV_OK;
+}
+
+int pkv_fib_encode_batch_compact(const pkv_fib_profile* cp, const float* vectors_host, int64_t n,
+                                 uint8_t* out_host, int64_t out_capacity, int64_t* out_len,
+                                 int32_t* vec_code, int64_t* vec_index) {
+  pkv_fib_profile* p = const_cast<pkv_fib_profile*>(cp);
+  if (!p || !out_host || !out_len || n < 0 || (n > 0 && !vectors_host)) return PKV_ERR_INVALID_ARGUMENT;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  *out_len = 0;
+  if (n == 0) return PKV_ERR_EMPTY_BATCH;  // FibCodeV1::encode_batch, fib-quant/src/codec.rs:226
+  if (n >= (int64_t)1 << 31) return PKV_ERR_UNSUPPORTED;
+  const int d = p->cfg.dim;
+  const int64_t total = PKV_FB2_HEADER_BYTES + n * p->rec_bytes;
+  if (out_capacity < total) return PKV_ERR_BUFFER_TOO_SMALL;
+  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  int st = ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
+  if (st != PKV_OK) return st;
+  cudaStream_t s = 0;
+  pkv_layout L = flat_layout(n, d);
+  const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
+  if (cudaMemcpyAsync(p->ws.in, vectors_host, (size_t)n * d * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  pkv_error_word_reset(p->ws.err, s);
+  st = pkv_fib_encode_dev(p, (const float*)p->ws.in, &L, (uint8_t*)p->ws.out, stride, p->ws.err, s);
+  if (st != PKV_OK) return st;
+  if (cudaMemcpyAsync(out_host + PKV_FB2_HEADER_BYTES, p->ws.out, (size_t)n * p->rec_bytes,
+                      cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
+  if (st != PKV_OK) return st;
+  pkv_fb2_header_write(p, (uint32_t)n, out_host);
+  *out_len = total;
+  return PKV_OK;
+}
+
+int pkv_fib_decode_batch_compact(const pkv_fib_profile* cp, const uint8_t* bytes_host, int64_t len,
+                                 float* out_host, int64_t out_capacity_floats, int64_t* n_vectors,
+                                 int32_t* vec_code, int64_t* vec_index) {
+  pkv_fib_profile* p = const_cast<pkv_fib_profile*>(cp);
+  if (!p || !bytes_host || !n_vectors) return PKV_ERR_INVALID_ARGUMENT;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  *n_vectors = 0;
+  uint32_t n32 = 0;
+  int st = pkv_fb2_header_parse(p, bytes_host, len, &n32);
+  if (st != PKV_OK) return st;
+  const int64_t n = n32;
+  const int d = p->cfg.dim;
+  if (n == 0) return PKV_OK;  // decode_batch_fast of no codes, fib-quant/src/codec.rs:798
+  if (!out_host || out_capacity_floats < n * d) return PKV_ERR_BUFFER_TOO_SMALL;
+  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  st = ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
+  if (st != PKV_OK) return st;
+  cudaStream_t s = 0;
+  pkv_layout L = flat_layout(n, d);
+  const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
+  if (cudaMemcpyAsync(p->ws.in, bytes_host + PKV_FB2_HEADER_BYTES, (size_t)n * p->rec_bytes,
+                      cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  pkv_error_word_reset(p->ws.err, s);
+  st = pkv_fib_decode_patch_dev(p, (const uint8_t*)p->ws.in, stride, &L, (float*)p->ws.out, p->ws.err, s);
+  if (st != PKV_OK) return st;
+  if (cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
+  if (st != PKV_OK) return st;
+  *n_vectors = n;
+  return PKV_OK;
+}
+
+
+// ---------------------------------------------------------------------------
+// turbo-quant
+// ---------------------------------------------------------------------------
+
+int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, const float* qjl,
+                             const float* cos_lut, const float* sin_lut, pkv_turbo_profile** out) {
+  if (!cfg || !signs || !out) return PKV_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  const int d = cfg->dim;
+  if (d <= 0 || (d & 1)) return PKV_ERR_INVALID_ARGUMENT;
+  if (cfg->mode != PKV_TURBO_POLAR_ONLY && cfg->mode != PKV_TURBO_POLAR_WITH_QJL)
+    return PKV_ERR_INVALID_ARGUMENT;
+  const bool with_qjl = cfg->mode == PKV_TURBO_POLAR_WITH_QJL;
+  // TurboQuantizer::new_with_mode_and_rotation, turbo-quant/src/turbo.rs:153-162
+  if (with_qjl ? (cfg->bits < 2 || cfg->bits > 16) : (cfg->bits < 1 || cfg->bits > 16))
+    return PKV_ERR_INVALID_ARGUMENT;
+  if (with_qjl && (cfg->projections <= 0 || !qjl)) return PKV_ERR_INVALID_ARGUMENT;
+  if (cfg->radii_codec != PKV_RADII_F32 && cfg->radii_codec != PKV_RADII_BLOCK_LOG_U8)
+    return PKV_ERR_INVALID_ARGUMENT;
+  const int pb = with_qjl ? cfg->bits - 1 : cfg->bits;
+  if ((d != 64 && d != 128) || pb > 8) return PKV_ERR_UNSUPPORTED;
+  if (with_qjl && (cfg->projections % 32 || cfg->projections > 64)) return PKV_ERR_UNSUPPORTED;
+  for (int i = 0; i < d; i++)
+    if (signs[i] != 1.0f && signs[i] != -1.0f) return PKV_ERR_INVALID_ARGUMENT;
+
+  pkv_turbo_profile* p = new (std::nothrow) pkv_turbo_profile();
+  if (!p) return PKV_ERR_CUDA;
+  p->cfg = *cfg;
+  p->polar_bits = pb;
+  p->pairs = d / 2;
+  const int radii_bytes = cfg->radii_codec == PKV_RADII_F32 ? p->pairs * 4 : p->pairs + 8;
+  const int angle_bytes = (p->pairs * pb + 7) / 8;
+  const int sign_bytes = with_qjl ? (cfg->projections + 7) / 8 : 0;
+  p->rec_bytes = radii_bytes + angle_bytes + sign_bytes;  // turbo-quant/src/wire.rs:311-327
+  p->radii_words = radii_bytes / 4;
+  p->angle_words = angle_bytes / 4;
+  p->sign_words = sign_bytes / 4;
+  p->scale = 1.0f / sqrtf((float)d);  // (n as f32).sqrt().recip(), rotation.rs:394
+  memset(p->sign_mask, 0, sizeof(p->sign_mask));
+  for (int i = 0; i < d; i++)
+    if (signs[i] < 0.0f) p->sign_mask[i >> 5] |= 1u << (i & 31);
+  p->qjl_dev = nullptr;
+  p->lut_dev = nullptr;
+  const int levels = 1 << pb;
+  float lut[512];
+  for (int i = 0; i < levels; i++) {
+    if (cos_lut && sin_lut) {
+      lut[i] = cos_lut[i];
+      lut[levels + i] = sin_lut[i];
+    } else {  // PolarCode::dequantize_angle + cosf/sinf of the host libm, polar.rs:91-95,312-313
+      const float pi = 3.14159274101257324f;
+      volatile float frac = (float)i / (float)levels;
+      volatile float scaled = frac * (2.0f * pi);
+      const float theta = scaled - pi;
+      lut[i] = cosf(theta);
+      lut[levels + i] = sinf(theta);
+    }
+  }
+  cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->lut_dev, sizeof(float) * 2 * levels);
+  if (e == cudaSuccess) e = cudaMemcpy(p->lut_dev, lut, sizeof(float) * 2 * levels, cudaMemcpyHostToDevice);
+  if (with_qjl) {
+    const size_t bytes = sizeof(float) * (size_t)cfg->projections * d;
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->qjl_dev, bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(p->qjl_dev, qjl, bytes, cudaMemcpyHostToDevice);
+  }
+  if (e != cudaSuccess) {
+    pkv_turbo_profile_destroy(p);
+    return PKV_ERR_CUDA;
+  }
+  *out = p;
+  return PKV_OK;
+}
+
+int pkv_turbo_profile_destroy(pkv_turbo_profile* p) {
+  if (!p) return PKV_OK;
+  if (p->qjl_dev) cudaFree(p->qjl_dev);
+  if (p->lut_dev) cudaFree(p->lut_dev);
+  ws_release(&p->ws);
+  delete p;
+  return PKV_OK;
+}
+
+int32_t pkv_turbo_record_bytes(const pkv_turbo_profile* p) { return p ? p->rec_bytes : 0; }
+
+int pkv_turbo_encode_dev(const pkv_turbo_profile* p, const float* x_dev, const pkv_layout* layout,
+                         uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
+                         void* stream) {
+  if (!p || !x_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)x_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), true, &g);
+  if (st != PKV_OK) return st;
+  if (g.vpb == 0) return PKV_ERR_EMPTY_BATCH;
+  return pkv_launch_turbo_encode(p, x_dev, g, payload_dev, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_turbo_decode_patch_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                               int64_t payload_batch_stride, const pkv_layout* layout,
+                               float* cache_dev, uint64_t* err_dev, void* stream) {
+  if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
+  if (st != PKV_OK) return st;
+  return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_tqb1_header_write(const pkv_turbo_profile* p, uint32_t n_vectors, uint8_t* out) {
+  if (!p || !out) return PKV_ERR_INVALID_ARGUMENT;
+  const uint16_t ver = 1, rot = 1;  // rotation flag 1 = FastHadamard, wire.rs:583-589
+  const uint32_t d = (uint32_t)p->cfg.dim, m = (uint32_t)p->cfg.projections;
+  const uint32_t rec = (uint32_t)p->rec_bytes;
+  memcpy(out, "TQB1", 4);
+  memcpy(out + 4, &ver, 2);
+  memcpy(out + 6, &rot, 2);
+  out[8] = 2;
+  out[9] = 0;
+  memcpy(out + 10, &d, 4);
+  out[14] = (uint8_t)p->polar_bits;
+  out[15] = (uint8_t)(p->cfg.radii_codec == PKV_RADII_F32 ? 0 : 1);
+  out[16] = 0;
+  out[17] = 0;
+  memcpy(out + 18, &m, 4);
+  memcpy(out + 22, &p->cfg.seed, 8);
+  memcpy(out + 30, &n_vectors, 4);
+  memcpy(out + 34, &rec, 4);
+  return PKV_OK;
+}
+
+// The reference decoder takes the radii codec from byte 15 (wire.rs:437-447); a
+// profile here is bound to one codec, so a payload written with the other one is
+// reported as a header mismatch and the caller picks the matching profile.
+int pkv_tqb1_header_parse(const pkv_turbo_profile* p, const uint8_t* b, int64_t len, uint32_t* n_vectors) {
+  if (!p || !b || !n_vectors) return PKV_ERR_INVALID_ARGUMENT;
+  if (len < PKV_TQB1_HEADER_BYTES) return PKV_ERR_CORRUPT_HEADER;
+  uint16_t ver, rot;
+  uint32_t d, m, n, rec;
+  uint64_t seed;
+  if (memcmp(b, "TQB1", 4)) return PKV_ERR_CORRUPT_HEADER;
+  memcpy(&ver, b + 4, 2);
+  memcpy(&rot, b + 6, 2);
+  memcpy(&d, b + 10, 4);
+  memcpy(&m, b + 18, 4);
+  memcpy(&seed, b + 22, 8);
+  memcpy(&n, b + 30, 4);
+  memcpy(&rec, b + 34, 4);
+  if (ver != 1 || rot != 1 || b[8] != 2) return PKV_ERR_CORRUPT_HEADER;
+  if (b[15] != (p->cfg.radii_codec == PKV_RADII_F32 ? 0 : 1)) return PKV_ERR_CORRUPT_HEADER;
+  if (d != (uint32_t)p->cfg.dim || m != (uint32_t)p->cfg.projections || seed != p->cfg.seed)
+    return PKV_ERR_CORRUPT_HEADER;
+  if (b[14] != p->polar_bits || rec != (uint32_t)p->rec_bytes) return PKV_ERR_CORRUPT_HEADER;
+  if (len != PKV_TQB1_HEADER_BYTES + (int64_t)n * rec) return PKV_ERR_CORRUPT_HEADER;  // WireCursor::finish
+  *n_vectors = n;
+  return PKV_OK;
+}
+
+int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* cp, const float* vectors_host, int64_t n,
+                                   uint8_t* out_host, int64_t out_capacity, int64_t* out_len,
+                                   int32_t* vec_code, int64_t* vec_index) {
+  pkv_turbo_profile* p = const_cast<pkv_turbo_profile*>(cp);
+  if (!p || !out_host || !out_len || n < 0 || (n > 0 && !vectors_host)) return PKV_ERR_INVALID_ARGUMENT;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  *out_len = 0;
+  if (n == 0) return PKV_ERR_EMPTY_BATCH;  // turbo-quant/src/wire.rs:302-306
+  if (n >= (int64_t)1 << 31) return PKV_ERR_UNSUPPORTED;
+  const int d = p->cfg.dim;
+  const int64_t total = PKV_TQB1_HEADER_BYTES + n * p->rec_bytes;
+  if (out_capacity < total) return PKV_ERR_BUFFER_TOO_SMALL;
+  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  int st = ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
+  if (st != PKV_OK) return st;
+  cudaStream_t s = 0;
+  pkv_layout L = flat_layout(n, d);
+  const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
+  if (cudaMemcpyAsync(p->ws.in, vectors_host, (size_t)n * d * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  pkv_error_word_reset(p->ws.err, s);
+  st = pkv_turbo_encode_dev(p, (const float*)p->ws.in, &L, (uint8_t*)p->ws.out, stride, p->ws.err, s);
+  if (st != PKV_OK) return st;
+  if (cudaMemcpyAsync(out_host + PKV_TQB1_HEADER_BYTES, p->ws.out, (size_t)n * p->rec_bytes,
+                      cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
+  if (st != PKV_OK) return st;
+  pkv_tqb1_header_write(p, (uint32_t)n, out_host);
+  *out_len = total;
+  return PKV_OK;
+}
+
+int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* cp, const uint8_t* bytes_host,
+                                   int64_t len, float* out_host, int64_t out_capacity_floats,
+                                   int64_t* n_vectors, int32_t* vec_code, int64_t* vec_index) {
+  pkv_turbo_profile* p = const_cast<pkv_turbo_profile*>(cp);
+  if (!p || !bytes_host || !n_vectors) return PKV_ERR_INVALID_ARGUMENT;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  *n_vectors = 0;
+  uint32_t n32 = 0;
+  int st = pkv_tqb1_header_parse(p, bytes_host, len, &n32);
+  if (st != PKV_OK) return st;
+  const int64_t n = n32;
+  const int d = p->cfg.dim;
+  if (n == 0) return PKV_OK;
+  if (!out_host || out_capacity_floats < n * d) return PKV_ERR_BUFFER_TOO_SMALL;
+  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  st = ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
+  if (st != PKV_OK) return st;
+  cudaStream_t s = 0;
+  pkv_layout L = flat_layout(n, d);
+  const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
+  if (cudaMemcpyAsync(p->ws.in, bytes_host + PKV_TQB1_HEADER_BYTES, (size_t)n * p->rec_bytes,
+                      cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  pkv_error_word_reset(p->ws.err, s);
+  st = pkv_turbo_decode_patch_dev(p, (const uint8_t*)p->ws.in, stride, &L, (float*)p->ws.out, p->ws.err, s);
+  if (st != PKV_OK) return st;
+  if (cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
+  if (st != PKV_OK) return st;
+  *n_vectors = n;
+  return PKV_OK;
+}
+
+}  // extern "C"

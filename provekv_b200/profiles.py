@@ -1,0 +1,178 @@
+"""Codec profiles: the tables of one quantizer uploaded to the GPU, plus thin
+methods over the C ABI (host-buffer "compact" calls and device-pointer calls).
+
+A profile corresponds to one ``FibQuantizer`` (fib-quant/src/codec.rs:428-452) or
+one ``TurboQuantizer`` (turbo-quant/src/turbo.rs:95-106) of the reference.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib as L
+from . import tables
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _raise_vec(status: int, code: int, index: int):
+    if status != L.OK:
+        raise L.PkvError(status, L.status_string(status), index if status >= 16 else -1)
+
+
+class _ProfileBase:
+    _destroy = None
+    handle = None
+
+    def close(self):
+        if self.handle is not None and L._lib is not None:
+            getattr(L.lib(), self._destroy)(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class FibProfile(_ProfileBase):
+    """fib-quant k=4 profile: dense rotation (dim x dim f64) + N x 4 f32 codebook."""
+    _destroy = "pkv_fib_profile_destroy"
+
+    def __init__(self, dim: int, rotation: np.ndarray, codebook: np.ndarray, *,
+                 norm_format: int = L.NORM_FP16, argmin_order: int = L.ARGMIN_PAIRWISE,
+                 numerics: int = L.FIB_NUMERICS_AUTO):
+        self.dim = dim
+        self.rotation = np.ascontiguousarray(rotation, dtype=np.float64).reshape(dim, dim)
+        self.codebook = np.ascontiguousarray(codebook, dtype=np.float32)
+        self.block_dim = self.codebook.shape[1]
+        self.codebook_size = self.codebook.shape[0]
+        cfg = L.FibConfigC(dim, self.block_dim, self.codebook_size, norm_format, argmin_order, numerics)
+        self.norm_format, self.argmin_order, self.numerics = norm_format, argmin_order, numerics
+        h = C.c_void_p()
+        L.check(L.lib().pkv_fib_profile_create(C.byref(cfg), _ptr(self.rotation), _ptr(self.codebook),
+                                               C.byref(h)))
+        self.handle = h
+        self.record_bytes = L.lib().pkv_fib_record_bytes(h)
+
+    @classmethod
+    def from_seed(cls, dim: int, seed: int, *, k: int = 4, n: int = 32, training_samples: int = 2048,
+                  restarts: int = 4, iterations: int = 8, **kw) -> "FibProfile":
+        """Tables from this package's own seeded generators (not the Rust streams)."""
+        return cls(dim, tables.haar_rotation(dim, seed),
+                   tables.fib_codebook(dim, k, n, seed, training_samples, restarts, iterations), **kw)
+
+    # -- host buffers, FB2 bytes (FibQuantAdapter::*_batch_compact) ------------
+    def encode_batch_compact(self, vectors: np.ndarray) -> bytes:
+        x = np.ascontiguousarray(vectors, dtype=np.float32).reshape(-1, self.dim)
+        n = x.shape[0]
+        out = np.empty(L.FB2_HEADER_BYTES + n * self.record_bytes, np.uint8)
+        out_len, code, idx = C.c_int64(0), C.c_int32(0), C.c_int64(-1)
+        st = L.lib().pkv_fib_encode_batch_compact(self.handle, _ptr(x), n, _ptr(out), out.size,
+                                                  C.byref(out_len), C.byref(code), C.byref(idx))
+        _raise_vec(st, code.value, idx.value)
+        return out[:out_len.value].tobytes()
+
+    def decode_batch_compact(self, payload: bytes) -> np.ndarray:
+        buf = np.frombuffer(payload, np.uint8)
+        n32 = C.c_uint32(0)
+        L.check(L.lib().pkv_fb2_header_parse(self.handle, _ptr(buf), buf.size, C.byref(n32)))
+        out = np.empty((n32.value, self.dim), np.float32)
+        n, code, idx = C.c_int64(0), C.c_int32(0), C.c_int64(-1)
+        st = L.lib().pkv_fib_decode_batch_compact(self.handle, _ptr(buf), buf.size, _ptr(out), out.size,
+                                                  C.byref(n), C.byref(code), C.byref(idx))
+        _raise_vec(st, code.value, idx.value)
+        return out
+
+    def header(self, n_vectors: int) -> bytes:
+        buf = (C.c_uint8 * L.FB2_HEADER_BYTES)()
+        L.check(L.lib().pkv_fb2_header_write(self.handle, n_vectors, buf))
+        return bytes(buf)
+
+    # -- device pointers -------------------------------------------------------
+    def encode_dev(self, x_ptr: int, layout: L.Layout, payload_ptr: int, payload_batch_stride: int,
+                   err_ptr: int, stream: int = 0) -> None:
+        L.check(L.lib().pkv_fib_encode_dev(self.handle, x_ptr, C.byref(layout), payload_ptr,
+                                           payload_batch_stride, err_ptr, stream))
+
+    def decode_patch_dev(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
+                         cache_ptr: int, err_ptr: int, stream: int = 0) -> None:
+        L.check(L.lib().pkv_fib_decode_patch_dev(self.handle, payload_ptr, payload_batch_stride,
+                                                 C.byref(layout), cache_ptr, err_ptr, stream))
+
+
+class TurboProfile(_ProfileBase):
+    """turbo-quant profile: Rademacher signs, optional QJL matrix, angle LUT."""
+    _destroy = "pkv_turbo_profile_destroy"
+
+    def __init__(self, dim: int, bits: int, signs: np.ndarray, qjl: np.ndarray | None = None, *,
+                 mode: int = L.TURBO_POLAR_WITH_QJL, radii_codec: int = L.RADII_F32, seed: int = 0,
+                 cos_lut: np.ndarray | None = None, sin_lut: np.ndarray | None = None):
+        self.dim, self.bits, self.mode, self.radii_codec, self.seed = dim, bits, mode, radii_codec, seed
+        self.signs = np.ascontiguousarray(signs, dtype=np.float32)
+        self.qjl = None if qjl is None else np.ascontiguousarray(qjl, dtype=np.float32)
+        self.projections = 0 if self.qjl is None else self.qjl.shape[0]
+        cfg = L.TurboConfigC(dim, bits, mode, self.projections, radii_codec, 0, seed)
+        cl = None if cos_lut is None else np.ascontiguousarray(cos_lut, np.float32)
+        sl = None if sin_lut is None else np.ascontiguousarray(sin_lut, np.float32)
+        h = C.c_void_p()
+        L.check(L.lib().pkv_turbo_profile_create(
+            C.byref(cfg), _ptr(self.signs), None if self.qjl is None else _ptr(self.qjl),
+            None if cl is None else _ptr(cl), None if sl is None else _ptr(sl), C.byref(h)))
+        self.handle = h
+        self.record_bytes = L.lib().pkv_turbo_record_bytes(h)
+
+    @classmethod
+    def from_seed(cls, dim: int, bits: int, projections: int, seed: int, *,
+                  mode: int = L.TURBO_POLAR_WITH_QJL, radii_codec: int = L.RADII_F32) -> "TurboProfile":
+        qjl = tables.qjl_matrix(dim, projections, seed) if mode == L.TURBO_POLAR_WITH_QJL else None
+        return cls(dim, bits, tables.rademacher_signs(dim, seed), qjl, mode=mode,
+                   radii_codec=radii_codec, seed=seed)
+
+    def encode_batch_compact(self, vectors: np.ndarray) -> bytes:
+        x = np.ascontiguousarray(vectors, dtype=np.float32).reshape(-1, self.dim)
+        n = x.shape[0]
+        out = np.empty(L.TQB1_HEADER_BYTES + n * self.record_bytes, np.uint8)
+        out_len, code, idx = C.c_int64(0), C.c_int32(0), C.c_int64(-1)
+        st = L.lib().pkv_turbo_encode_batch_compact(self.handle, _ptr(x), n, _ptr(out), out.size,
+                                                    C.byref(out_len), C.byref(code), C.byref(idx))
+        _raise_vec(st, code.value, idx.value)
+        return out[:out_len.value].tobytes()
+
+    def decode_batch_compact(self, payload: bytes) -> np.ndarray:
+        buf = np.frombuffer(payload, np.uint8)
+        n32 = C.c_uint32(0)
+        L.check(L.lib().pkv_tqb1_header_parse(self.handle, _ptr(buf), buf.size, C.byref(n32)))
+        out = np.empty((n32.value, self.dim), np.float32)
+        n, code, idx = C.c_int64(0), C.c_int32(0), C.c_int64(-1)
+        st = L.lib().pkv_turbo_decode_batch_compact(self.handle, _ptr(buf), buf.size, _ptr(out),
+                                                    out.size, C.byref(n), C.byref(code), C.byref(idx))
+        _raise_vec(st, code.value, idx.value)
+        return out
+
+    def header(self, n_vectors: int) -> bytes:
+        buf = (C.c_uint8 * L.TQB1_HEADER_BYTES)()
+        L.check(L.lib().pkv_tqb1_header_write(self.handle, n_vectors, buf))
+        return bytes(buf)
+
+    def encode_dev(self, x_ptr: int, layout: L.Layout, payload_ptr: int, payload_batch_stride: int,
+                   err_ptr: int, stream: int = 0) -> None:
+        L.check(L.lib().pkv_turbo_encode_dev(self.handle, x_ptr, C.byref(layout), payload_ptr,
+                                             payload_batch_stride, err_ptr, stream))
+
+    def decode_patch_dev(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
+                         cache_ptr: int, err_ptr: int, stream: int = 0) -> None:
+        L.check(L.lib().pkv_turbo_decode_patch_dev(self.handle, payload_ptr, payload_batch_stride,
+                                                   C.byref(layout), cache_ptr, err_ptr, stream))
+
+
+def read_error_word(err_ptr: int, stream: int = 0) -> None:
+    """Synchronise the stream and raise PkvError if a kernel reported a vector."""
+    code, idx = C.c_int32(0), C.c_int64(-1)
+    st = L.lib().pkv_error_word_read(err_ptr, stream, C.byref(code), C.byref(idx))
+    if st != L.OK:
+        raise L.PkvError(st, L.status_string(st), idx.value)
