@@ -174,6 +174,17 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* p, const uint8_t* bytes_
                                  float* out_host, int64_t out_capacity_floats, int64_t* n_vectors,
                                  int32_t* vec_code, int64_t* vec_index);
 
+/* Many equal-sized batches in one call: vectors_host is [n_batches][vectors_per_batch][dim],
+ * out_host receives n_batches FB2 blobs of 19 + vectors_per_batch*record_bytes bytes each, i.e.
+ * what proveKV/src/pool.rs:265-266 obtains from one encode_batch_compact call per (layer, K|V).
+ * Copies and kernels of successive chunks overlap; vec_index is the global vector index. */
+int pkv_fib_encode_batches_compact(const pkv_fib_profile* p, const float* vectors_host,
+                                   int64_t n_batches, int64_t vectors_per_batch, uint8_t* out_host,
+                                   int64_t out_capacity, int32_t* vec_code, int64_t* vec_index);
+int pkv_fib_decode_batches_compact(const pkv_fib_profile* p, const uint8_t* bytes_host,
+                                   int64_t n_batches, int64_t vectors_per_batch, float* out_host,
+                                   int64_t out_capacity_floats, int32_t* vec_code, int64_t* vec_index);
+
 /* FB2 header, fib-quant/src/codec.rs:195-220 (19 bytes). */
 #define PKV_FB2_HEADER_BYTES 19
 int pkv_fb2_header_write(const pkv_fib_profile* p, uint32_t n_vectors, uint8_t* out19);
@@ -209,6 +220,15 @@ int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* p, const float* vect
 int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* p, const uint8_t* bytes_host,
                                    int64_t len, float* out_host, int64_t out_capacity_floats,
                                    int64_t* n_vectors, int32_t* vec_code, int64_t* vec_index);
+
+/* Many equal-sized batches in one call (proveKV/src/shell.rs:266-267 issues one
+ * encode_batch_compact per (layer, K|V)): TQB1 blobs of 38 + vectors_per_batch*record_bytes. */
+int pkv_turbo_encode_batches_compact(const pkv_turbo_profile* p, const float* vectors_host,
+                                     int64_t n_batches, int64_t vectors_per_batch, uint8_t* out_host,
+                                     int64_t out_capacity, int32_t* vec_code, int64_t* vec_index);
+int pkv_turbo_decode_batches_compact(const pkv_turbo_profile* p, const uint8_t* bytes_host,
+                                     int64_t n_batches, int64_t vectors_per_batch, float* out_host,
+                                     int64_t out_capacity_floats, int32_t* vec_code, int64_t* vec_index);
 
 /* TQB1 header, turbo-quant/src/wire.rs:276-290 (38 bytes). */
 #define PKV_TQB1_HEADER_BYTES 38

@@ -11,6 +11,7 @@ from .codec import (CODEC_FIB_K4_N32, CODEC_FIB_K4_N32_BATCHED, CODEC_TURBO_8BIT
                     CODEC_TURBO_8BIT_BATCHED, CompressionFailed, DecompressionFailed, FibConfig,
                     FibQuantAdapter, InvalidPolicy, KVecCodec, ProveKvError, TurboConfig,
                     TurboQuantAdapter, create_codec, turbo_batched_codec_id)
-from .profiles import FibProfile, TurboProfile, read_error_word
+from .profiles import (FibProfile, TurboProfile, decode_batches_compact, encode_batches_compact,
+                       read_error_word)
 
 __all__ = [n for n in dir() if not n.startswith("_")]

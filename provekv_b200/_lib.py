@@ -142,6 +142,14 @@ _SIGS = {
     "pkv_tqb1_header_write": (C.c_int, [_V, C.c_uint32, _V]),
     "pkv_tqb1_header_parse": (C.c_int, [_V, _V, C.c_int64, C.POINTER(C.c_uint32)]),
     "pkv_launch_count": (C.c_int64, []),
+    "pkv_fib_encode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
+                                                 C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
+    "pkv_fib_decode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
+                                                 C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
+    "pkv_turbo_encode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
+                                                   C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
+    "pkv_turbo_decode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
+                                                   C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGS)

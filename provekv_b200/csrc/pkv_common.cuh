@@ -91,11 +91,14 @@ __device__ __forceinline__ float pkv_f16_bits_to_f32(uint32_t h) {
 
 // ---- host-side objects ---------------------------------------------------
 
-struct PkvWorkspace {  // device staging of the *_batch_compact calls, grown on demand
+#define PKV_WS_ERR_WORDS 16
+#define PKV_WS_STREAMS 3
+struct PkvWorkspace {  // device staging of the *_compact calls, grown on demand
   void* in = nullptr;
   void* out = nullptr;
-  uint64_t* err = nullptr;
+  uint64_t* err = nullptr;  // PKV_WS_ERR_WORDS error words
   int64_t in_cap = 0, out_cap = 0;
+  cudaStream_t streams[PKV_WS_STREAMS] = {nullptr, nullptr, nullptr};  // copy/compute pipeline
 };
 
 struct pkv_fib_profile {
@@ -120,6 +123,7 @@ struct pkv_turbo_profile {
 };
 
 int pkv_cuda_status(cudaError_t e);
+int pkv_ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes);
 void pkv_count_launch();
 
 // launchers implemented in pkv_fib.cu / pkv_turbo.cu

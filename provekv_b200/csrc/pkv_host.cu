@@ -25,25 +25,34 @@ int grow(void** ptr, int64_t* cap, int64_t need) {
   return PKV_OK;
 }
 
-int ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes) {
+}  // namespace
+
+int pkv_ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes) {
   int st;
   if ((st = grow(&ws->in, &ws->in_cap, in_bytes)) != PKV_OK) return st;
   if ((st = grow(&ws->out, &ws->out_cap, out_bytes)) != PKV_OK) return st;
   if (!ws->err) {
-    cudaError_t e = cudaMalloc((void**)&ws->err, sizeof(uint64_t));
+    cudaError_t e = cudaMalloc((void**)&ws->err, sizeof(uint64_t) * PKV_WS_ERR_WORDS);
     if (e != cudaSuccess) return pkv_cuda_status(e);
   }
   return PKV_OK;
 }
 
+namespace {
+
 void ws_release(PkvWorkspace* ws) {
   if (ws->in) cudaFree(ws->in);
   if (ws->out) cudaFree(ws->out);
   if (ws->err) cudaFree(ws->err);
+  for (int i = 0; i < PKV_WS_STREAMS; i++)
+    if (ws->streams[i]) cudaStreamDestroy(ws->streams[i]);
   *ws = PkvWorkspace();
 }
 
 std::mutex g_compact_mutex;  // the compact calls share each profile's staging buffers
+}  // namespace
+std::mutex& pkv_compact_mutex() { return g_compact_mutex; }
+namespace {
 
 // Validate a layout and derive the launch geometry for tiles of `tile` vectors.
 int make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
@@ -303,7 +312,7 @@ int pkv_fib_encode_batch_compact(const pkv_fib_profile* cp, const float* vectors
   const int64_t total = PKV_FB2_HEADER_BYTES + n * p->rec_bytes;
   if (out_capacity < total) return PKV_ERR_BUFFER_TOO_SMALL;
   std::lock_guard<std::mutex> lock(g_compact_mutex);
-  int st = ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
+  int st = pkv_ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
@@ -339,7 +348,7 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* cp, const uint8_t* bytes
   if (n == 0) return PKV_OK;  // decode_batch_fast of no codes, fib-quant/src/codec.rs:798
   if (!out_host || out_capacity_floats < n * d) return PKV_ERR_BUFFER_TOO_SMALL;
   std::lock_guard<std::mutex> lock(g_compact_mutex);
-  st = ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
+  st = pkv_ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
@@ -530,7 +539,7 @@ int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* cp, const float* vec
   const int64_t total = PKV_TQB1_HEADER_BYTES + n * p->rec_bytes;
   if (out_capacity < total) return PKV_ERR_BUFFER_TOO_SMALL;
   std::lock_guard<std::mutex> lock(g_compact_mutex);
-  int st = ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
+  int st = pkv_ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
@@ -566,7 +575,7 @@ int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* cp, const uint8_t* b
   if (n == 0) return PKV_OK;
   if (!out_host || out_capacity_floats < n * d) return PKV_ERR_BUFFER_TOO_SMALL;
   std::lock_guard<std::mutex> lock(g_compact_mutex);
-  st = ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
+  st = pkv_ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);

@@ -176,3 +176,28 @@ def read_error_word(err_ptr: int, stream: int = 0) -> None:
     st = L.lib().pkv_error_word_read(err_ptr, stream, C.byref(code), C.byref(idx))
     if st != L.OK:
         raise L.PkvError(st, L.status_string(st), idx.value)
+
+
+def _bulk(fn_name: str, profile, src_ptr: int, n_batches: int, vpb: int, dst_ptr: int, dst_capacity: int):
+    code, idx = C.c_int32(0), C.c_int64(-1)
+    st = getattr(L.lib(), fn_name)(profile.handle, src_ptr, n_batches, vpb, dst_ptr, dst_capacity,
+                                   C.byref(code), C.byref(idx))
+    _raise_vec(st, code.value, idx.value)
+
+
+def encode_batches_compact(profile, vectors_ptr: int, n_batches: int, vectors_per_batch: int,
+                           out_ptr: int, out_capacity: int) -> None:
+    """Host [n_batches][vpb][dim] f32 -> n_batches wire blobs (header + records) at out_ptr.
+
+    One call per pool / shell build instead of one per (layer, K|V); pointers are raw host
+    addresses (pinned memory gives full PCIe rate)."""
+    kind = "turbo" if isinstance(profile, TurboProfile) else "fib"
+    _bulk(f"pkv_{kind}_encode_batches_compact", profile, vectors_ptr, n_batches, vectors_per_batch,
+          out_ptr, out_capacity)
+
+
+def decode_batches_compact(profile, bytes_ptr: int, n_batches: int, vectors_per_batch: int,
+                           out_ptr: int, out_capacity_floats: int) -> None:
+    kind = "turbo" if isinstance(profile, TurboProfile) else "fib"
+    _bulk(f"pkv_{kind}_decode_batches_compact", profile, bytes_ptr, n_batches, vectors_per_batch,
+          out_ptr, out_capacity_floats)
