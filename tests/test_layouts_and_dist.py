@@ -1,0 +1,111 @@
+"""Host logic: pkv_layout addressing against NumPy strides, sharding, and the pool
+broadcast over a 2-rank gloo group (the CPU stand-in for NCCL)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from provekv_b200 import dist as pdist
+from provekv_b200 import pool
+
+
+def vec_offset(L, batch, v):
+    """Python restatement of pkv_vec_offset (provekv_b200/csrc/pkv_common.cuh)."""
+    token, head = divmod(v, L.n_heads)
+    b2 = batch % L.n_batches[2]
+    t = batch // L.n_batches[2]
+    b1 = t % L.n_batches[1]
+    b0 = t // L.n_batches[1]
+    return (L.base + b0 * L.batch_stride[0] + b1 * L.batch_stride[1] + b2 * L.batch_stride[2]
+            + token * L.token_stride + head * L.head_stride)
+
+
+def test_kv_tensor_layout_matches_numpy_indexing():
+    shape = pool.KvShape(3, 4, 8)
+    A, T, cap, first = 2, 5, 11, 4
+    kv = np.arange(A * 3 * 2 * 4 * cap * 8).reshape(A, 3, 2, 4, cap, 8)
+    L = pool.kv_tensor_layout(shape, A, T, token_capacity=cap, first_token=first)
+    assert L.batch_count == A * 3 * 2 and L.vectors_per_batch == T * 4
+    for batch in range(L.batch_count):
+        a, rem = divmod(batch, 6)
+        layer, side = divmod(rem, 2)
+        for v in range(L.vectors_per_batch):
+            t, h = divmod(v, 4)  # token-major, head-minor: proveKV/src/pool.rs:246-257
+            assert vec_offset(L, batch, v) == kv[a, layer, side, h, first + t, 0]
+    with pytest.raises(ValueError):
+        pool.kv_tensor_layout(shape, A, T, token_capacity=6, first_token=4)
+
+
+def test_patch_positions_and_strides():
+    # proveKV/scripts/ppl_validate_multi_agent.py:258: pos = n_shared + agent*n_unique + t
+    assert pool.agent_patch_position(800, 28, 0) == 800
+    assert pool.agent_patch_position(800, 28, 7) == 996
+    assert pool.agent_patch_position(800, 28, 7) + 28 == 1024
+    assert pool.payload_batch_stride(896, 144) == 896 * 144
+    assert pool.payload_batch_stride(3, 12) == 48 and pool.payload_batch_stride(5, 22) == 112
+    assert pool.SMOLLM2_1_7B.vectors(1024) == 1_572_864
+    assert pool.SMOLLM2_1_7B.vectors(28, 8) == 344_064
+    assert pool.LLAMA3_8B.vectors(131072) == 67_108_864
+
+
+def test_sharding_covers_everything_once():
+    for n, w in [(8, 1), (8, 2), (8, 8), (64, 8), (32, 8), (7, 4), (3, 8)]:
+        shards = pdist.all_shards(n, w)
+        flat = [i for lo, hi in shards for i in range(lo, hi)]
+        assert flat == list(range(n))
+        sizes = [hi - lo for lo, hi in shards]
+        assert max(sizes) - min(sizes) <= 1
+    assert list(pdist.shard_agents(64, 8, 3)) == list(range(24, 32))
+    assert list(pdist.shard_layers(32, 8, 7)) == [28, 29, 30, 31]
+    with pytest.raises(ValueError):
+        pdist.shard_range(8, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _gloo_worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 0 "encodes" the pool; everyone receives the same bytes
+        pool_bytes = torch.arange(4096, dtype=torch.int64).to(torch.uint8) if rank == 0 else \
+            torch.zeros(4096, dtype=torch.uint8)
+        pdist.broadcast_pool(pool_bytes, src=0)
+        ok_bcast = bool((pool_bytes == torch.arange(4096, dtype=torch.int64).to(torch.uint8)).all())
+        # layer-sharded encode then all-gather
+        lo, hi = pdist.shard_range(6, world, rank)
+        local = torch.full((hi - lo, 16), rank + 1, dtype=torch.uint8)
+        parts = pdist.gather_layer_shards(local, world)
+        ok_gather = [int(p[0, 0]) for p in parts] == list(range(1, world + 1))
+        agents = list(pdist.shard_agents(8, world, rank))
+        slow = pdist.max_over_ranks([1.0 + rank, 5.0 - rank])
+        q.put((rank, ok_bcast, ok_gather, agents, slow))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_broadcast_and_sharding():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res[0][1] and res[1][1] and res[0][2] and res[1][2]
+    assert res[0][3] == [0, 1, 2, 3] and res[1][3] == [4, 5, 6, 7]
+    assert res[0][4] == [2.0, 5.0] and res[1][4] == [2.0, 5.0]
