@@ -31,14 +31,44 @@ import numpy as np  # noqa: E402
 
 METRIC = "f32-KV GB/s encode & decode+patch"
 SEED = 42
+_C2 = dict(agents=8, layers=24, heads=32, tokens=28, dim=64, cache_tokens=1024, n_shared=800)
 WORKLOADS = {
-    # name: (agents, layers, heads, tokens, dim, cache tokens, first patched position)
-    "c2": dict(agents=8, layers=24, heads=32, tokens=28, dim=64, cache_tokens=1024, n_shared=800,
+    # the configuration the metric is quoted on
+    "c2": dict(_C2, codec="turbo", bits=4, mode=1, lossy=False,
                desc="C2 turbo b=4 (polar 3 bit + 32 QJL, f32 radii) hot shells: 8 agents x 28 tokens, "
                     "SmolLM2-1.7B shape 24x{K,V}x32x64"),
+    # the other radii codec / the literal 4-bit-angle reading of the same shape
+    "c2_lossy": dict(_C2, codec="turbo", bits=4, mode=1, lossy=True,
+                     desc="C2 turbo b=4 (polar 3 bit + 32 QJL, BlockLogU8 radii), 8 agents x 28 tokens"),
+    "c2_polar4": dict(_C2, codec="turbo", bits=4, mode=0, lossy=False,
+                      desc="C2 turbo polar-only 4-bit angles, f32 radii, 8 agents x 28 tokens"),
+    # cold tier: one whole SmolLM2-1.7B cache, fib k4_n32
+    "c1": dict(agents=1, layers=24, heads=32, tokens=1024, dim=64, cache_tokens=1024, n_shared=0,
+               codec="fib", desc="C1 fib k4_n32 cold tier: 24x{K,V}x32 heads x 1024 tokens x 64"),
 }
-TURBO_BITS, TURBO_PROJ = 4, 32
-ALGO_BYTES_PER_VECTOR = 400  # 4d + 2d + ceil(3P/8) + 4 at d=64: f32 in/out + TQB1 record
+TURBO_PROJ = 32
+
+
+def record_bytes(w):
+    d, p = w["dim"], w["dim"] // 2
+    if w["codec"] == "fib":
+        return 2 + (5 * d // 4 + 7) // 8
+    pb = w["bits"] - 1 if w["mode"] else w["bits"]
+    return (p + 8 if w["lossy"] else 4 * p) + (p * pb + 7) // 8 + (TURBO_PROJ // 8 if w["mode"] else 0)
+
+
+def algo_bytes_per_vector(w):
+    """f32 vector in or out plus its wire record (fib 268 B, turbo 400 / 312 B at d=64)."""
+    return 4 * w["dim"] + record_bytes(w)
+
+
+def make_profile(w):
+    import provekv_b200 as pk
+    from provekv_b200 import _lib as L
+    if w["codec"] == "fib":
+        return pk.FibProfile.from_seed(w["dim"], SEED)
+    return pk.TurboProfile.from_seed(w["dim"], w["bits"], TURBO_PROJ, SEED, mode=w["mode"],
+                                     radii_codec=L.RADII_BLOCK_LOG_U8 if w["lossy"] else L.RADII_F32)
 
 
 def measured_hbm_peak():
@@ -121,18 +151,32 @@ def cpu_codec_rate(w, seconds_budget, nthreads):
     import oracle
     from provekv_b200 import tables
     dim = w["dim"]
-    signs, qjl = tables.rademacher_signs(dim, SEED), tables.qjl_matrix(dim, TURBO_PROJ, SEED)
+    if w["codec"] == "fib":
+        rot, cb = tables.haar_rotation(dim, SEED), tables.fib_codebook(dim, seed=SEED)
 
-    def run(x):
-        t0 = time.perf_counter()
-        st, payload, _, _ = oracle.turbo_encode(x, signs, qjl, bits=TURBO_BITS, mode=1, radii_codec=0,
-                                                libm_mode=oracle.LIBM_PLATFORM, nthreads=nthreads)
-        assert st == 0
-        st, _, _, _ = oracle.turbo_decode(payload, dim, signs, bits=TURBO_BITS, mode=1,
-                                          projections=TURBO_PROJ, radii_codec=0,
-                                          libm_mode=oracle.LIBM_PLATFORM, nthreads=nthreads)
-        assert st == 0
-        return time.perf_counter() - t0
+        def run(x):
+            t0 = time.perf_counter()
+            st, payload, _, _ = oracle.fib_encode(x, rot, cb, nthreads=nthreads)
+            assert st == 0
+            st, _, _, _ = oracle.fib_decode(payload, dim, rot, cb, nthreads=nthreads)
+            assert st == 0
+            return time.perf_counter() - t0
+    else:
+        signs = tables.rademacher_signs(dim, SEED)
+        qjl = tables.qjl_matrix(dim, TURBO_PROJ, SEED) if w["mode"] else None
+        m, rc = (TURBO_PROJ if w["mode"] else 0), int(w["lossy"])
+
+        def run(x):
+            t0 = time.perf_counter()
+            st, payload, _, _ = oracle.turbo_encode(x, signs, qjl, bits=w["bits"], mode=w["mode"],
+                                                    radii_codec=rc, libm_mode=oracle.LIBM_PLATFORM,
+                                                    nthreads=nthreads)
+            assert st == 0
+            st, _, _, _ = oracle.turbo_decode(payload, dim, signs, bits=w["bits"], mode=w["mode"],
+                                              projections=m, radii_codec=rc,
+                                              libm_mode=oracle.LIBM_PLATFORM, nthreads=nthreads)
+            assert st == 0
+            return time.perf_counter() - t0
 
     probe = synthetic_vectors(4096 * max(1, nthreads // 4), dim, 1)
     run(probe[:256])
@@ -143,7 +187,7 @@ def cpu_codec_rate(w, seconds_budget, nthreads):
     x = synthetic_vectors(n, dim, 2)
     t = run(x)
     gbs = 2 * n * dim * 4 / t / 1e9
-    return gbs, t, f"{n} of {total} vectors (turbo b=4 encode + decode, platform libm), {nthreads} threads"
+    return gbs, t, f"{n} of {total} vectors ({w['codec']} encode + decode, host libm), {nthreads} threads"
 
 
 def run_reference(args, w):
@@ -199,8 +243,12 @@ def run_ours(args, w):
     scale = torch.exp(0.5 * torch.randn((1, w["layers"], 1, H, 1, d), generator=gen, device=dev))
     kv = torch.randn((A, w["layers"], 2, H, T, d), generator=gen, device=dev) * scale
     kv = kv.contiguous()
-    prof = pk.TurboProfile.from_seed(d, TURBO_BITS, TURBO_PROJ, SEED)
+    prof = make_profile(w)
     rec = prof.record_bytes
+    assert rec == record_bytes(w)
+    algo_bytes = algo_bytes_per_vector(w)
+    kind = w["codec"]
+    big = f32_bytes > (200 << 20)  # larger than L2: no flush needed
     vpb = T * H
     n_batches = A * w["layers"] * 2
     pstride = pool.payload_batch_stride(vpb, rec)
@@ -230,7 +278,8 @@ def run_ours(args, w):
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        flush.zero_()
+        if not big:
+            flush.zero_()
         step()
     torch.cuda.synchronize()
     assert int(err[0]) == -1 and int(err[1]) == -1, "a kernel reported a vector error"
@@ -241,7 +290,8 @@ def run_ours(args, w):
     with ClockSampler(local) as clocks:
         t_wall = time.perf_counter()
         for i in range(args.steps):
-            flush.zero_()  # evict the workload from L2; outside the per-step event bracket
+            if not big:
+                flush.zero_()  # evict the workload from L2; outside the per-step event bracket
             step(events[i])
         barrier()
         t_wall = time.perf_counter() - t_wall
@@ -251,7 +301,7 @@ def run_ours(args, w):
     step_ms = float(np.mean([e[0].elapsed_time(e[2]) for e in events]))
 
     # end to end through the host-buffer C ABI: pinned host f32 -> TQB1 blobs -> pinned host f32
-    blob = L.TQB1_HEADER_BYTES + vpb * rec
+    blob = (L.FB2_HEADER_BYTES if kind == "fib" else L.TQB1_HEADER_BYTES) + vpb * rec
     x_host = torch.empty((n_batches, vpb, d), dtype=torch.float32).pin_memory()
     # gather order of the reference: token-major, head-minor per (agent, layer, side)
     x_host.copy_(kv.permute(0, 1, 2, 4, 3, 5).reshape(n_batches, vpb, d))
@@ -283,28 +333,30 @@ def run_ours(args, w):
         peak, peak_kind = measured_hbm_peak()
         total_f32 = 2 * f32_bytes * world
         value = total_f32 / (step_ms * 1e-3) / 1e9
-        dom, dom_ms = ("turbo_encode_kernel<64>", enc_ms) if enc_ms >= dec_ms else (
-            "turbo_decode_patch_kernel<64>", dec_ms)
-        achieved = ALGO_BYTES_PER_VECTOR * n_vec / (dom_ms * 1e-3) / 1e9
+        dom, dom_ms = (f"{kind}_encode_kernel<{d}>", enc_ms) if enc_ms >= dec_ms else (
+            f"{kind}_decode_patch_kernel<{d}>", dec_ms)
+        achieved = algo_bytes * n_vec / (dom_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": w["desc"], "vectors_per_gpu": n_vec, "f32_bytes_per_gpu": f32_bytes,
                        "parallelism": f"{world} x independent agent shards, no collective on the codec path",
-                       "l2": "flushed between timed steps (512 MiB write)"},
+                       "l2": "inputs larger than L2" if big else "flushed between timed steps (512 MiB write)"},
             "encode_gbs": f32_bytes * world / (enc_ms * 1e-3) / 1e9,
             "decode_patch_gbs": f32_bytes * world / (dec_ms * 1e-3) / 1e9,
             "encode_ms": enc_ms, "decode_patch_ms": dec_ms,
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8000": achieved / 8000.0,
-                         "algorithmic_bytes_per_launch": ALGO_BYTES_PER_VECTOR * n_vec,
+                         "algorithmic_bytes_per_launch": algo_bytes * n_vec,
+                         "encode_achieved": algo_bytes * n_vec / (enc_ms * 1e-3) / 1e9,
+                         "decode_patch_achieved": algo_bytes * n_vec / (dec_ms * 1e-3) / 1e9,
                          "traffic": ncu_traffic(dom)},
             "e2e": {"value": total_f32 / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": f32_bytes + n_batches * vpb * rec,
                     "d2h_bytes_per_step": f32_bytes + n_batches * vpb * rec,
-                    "api": "pkv_turbo_{encode,decode}_batches_compact, pinned host buffers"},
+                    "api": f"pkv_{kind}_{{encode,decode}}_batches_compact, pinned host buffers"},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "wall_ms_timed_region": t_wall * 1e3,

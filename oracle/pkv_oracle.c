@@ -869,3 +869,106 @@ PKVO_API int pkvo_tqb1_header_parse(int dim, int bits, int mode, int projections
   *radii_codec = codec;
   return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* CPU check of the kernels' certified shortcuts (provekv_b200/csrc/pkv_fast_paths.h) */
+/* ------------------------------------------------------------------------ */
+#include "../provekv_b200/csrc/pkv_fast_paths.h"
+
+static uint64_t xs64(uint64_t* s) {
+  uint64_t x = *s;
+  x ^= x << 13;
+  x ^= x >> 7;
+  x ^= x << 17;
+  return *s = x;
+}
+static double unif(uint64_t* s) { return (double)(xs64(s) >> 11) * (1.0 / 9007199254740992.0); }
+
+/* Runs the bucket shortcut on n pairs: a mix of Gaussian-like pairs, pairs placed within
+ * +-spread radians of a sector boundary at many magnitudes, and degenerate pairs.  Every decided
+ * pair must equal the exact bucket (portable atan2f + polar.rs:415-420).  counts[0] = decided and
+ * wrong, counts[1] = undecided, counts[2] = decided. */
+PKVO_API void pkvo_fast_bucket_check(int polar_bits, int64_t n, uint64_t seed, double spread,
+                                     int64_t* counts) {
+  const int levels = 1 << polar_bits, rays = levels / 4 + 1;
+  float rc[80], rs[80];
+  for (int t = 0; t < rays; t++) {
+    double beta = 2.0 * 3.14159265358979323846 * t / levels;
+    rc[t] = (float)cos(beta);
+    rs[t] = (float)sin(beta);
+  }
+  uint64_t s = seed * 2654435761u + 88172645463325252ull;
+  counts[0] = counts[1] = counts[2] = 0;
+  for (int64_t i = 0; i < n; i++) {
+    float a, b;
+    int kind = (int)(xs64(&s) % 8);
+    if (kind < 3) {
+      a = (float)((unif(&s) + unif(&s) + unif(&s) - 1.5) * 4.0);
+      b = (float)((unif(&s) + unif(&s) + unif(&s) - 1.5) * 4.0);
+    } else if (kind < 7) {
+      int k = (int)(xs64(&s) % (uint64_t)levels);
+      double ang = -3.14159265358979323846 + 2.0 * 3.14159265358979323846 * k / levels +
+                   (unif(&s) - 0.5) * 2.0 * spread;
+      double r = exp((unif(&s) - 0.5) * (kind == 6 ? 160.0 : 12.0));
+      a = (float)(r * cos(ang));
+      b = (float)(r * sin(ang));
+    } else {
+      static const float sp[] = {0.0f, -0.0f, 1.0f, -1.0f, 1e-45f, -1e-45f, 3e38f, -3e38f, 1e-38f};
+      a = sp[xs64(&s) % 9];
+      b = sp[xs64(&s) % 9];
+    }
+    int certain = 0;
+    uint32_t fast = pkv_fast_bucket(a, b, polar_bits, rc, rs, &certain);
+    if (!certain) {
+      counts[1]++;
+      continue;
+    }
+    counts[2]++;
+    if (fast != angle_bucket(pkv_atan2f_portable(b, a), (uint32_t)levels)) counts[0]++;
+  }
+}
+
+/* Sign shortcut of the QJL rows: fused four-chain dot vs the reference's sequential dot.
+ * counts[0] = decided with the wrong sign, counts[1] = undecided, counts[2] = decided. */
+PKVO_API void pkvo_fast_qjl_check(int dim, int64_t n, uint64_t seed, double res_scale, int64_t* counts) {
+  uint64_t s = seed * 11400714819323198485ull + 1;
+  counts[0] = counts[1] = counts[2] = 0;
+  float g[128], x[128];
+  for (int64_t i = 0; i < n; i++) {
+    double g2 = 0.0, x2 = 0.0;
+    for (int j = 0; j < dim; j++) {
+      g[j] = (float)((unif(&s) + unif(&s) + unif(&s) + unif(&s) - 2.0) * 1.7);
+      x[j] = (float)((unif(&s) + unif(&s) + unif(&s) + unif(&s) - 2.0) * res_scale);
+      g2 += (double)g[j] * g[j];
+    }
+    /* every other case: make the exact dot tiny by projecting x off g */
+    if (i & 1) {
+      double dot = 0.0;
+      for (int j = 0; j < dim; j++) dot += (double)g[j] * x[j];
+      double f = dot / g2 * (1.0 - unif(&s) * 1e-6);
+      for (int j = 0; j < dim; j++) x[j] = (float)((double)x[j] - f * g[j]);
+    }
+    for (int j = 0; j < dim; j++) x2 += (double)x[j] * x[j];
+    float thr = (float)(sqrt(g2) * 1.0001) * PKV_QJL_REL_BOUND;
+    float s2 = 0.0f;
+    for (int j = 0; j < dim; j++) s2 = fmaf(x[j], x[j], s2);
+    float rnorm = sqrtf(s2) * 1.0001f;
+    float d0 = 0, d1 = 0, d2 = 0, d3 = 0;
+    for (int j = 0; j < dim; j += 4) {
+      d0 = fmaf(g[j], x[j], d0);
+      d1 = fmaf(g[j + 1], x[j + 1], d1);
+      d2 = fmaf(g[j + 2], x[j + 2], d2);
+      d3 = fmaf(g[j + 3], x[j + 3], d3);
+    }
+    float fast = (d0 + d1) + (d2 + d3);
+    float tau = fmaf(thr, rnorm, PKV_QJL_ABS_BOUND);
+    if (!(fabsf(fast) > tau)) {
+      counts[1]++;
+      continue;
+    }
+    counts[2]++;
+    float ref = 0.0f;
+    for (int j = 0; j < dim; j++) ref += g[j] * x[j];
+    if ((ref >= 0.0f) != (fast >= 0.0f)) counts[0]++;
+  }
+}

@@ -46,6 +46,20 @@ __device__ __forceinline__ bool pkv_finite(float x) {
   return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u;
 }
 
+// Asynchronous global -> shared copies (LDGSTS): a thread queues all of its copies and waits
+// once, so a tile's loads are all in flight together instead of one round trip per loop step.
+__device__ __forceinline__ void pkv_cp_async16(void* smem_dst, const void* gsrc) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void pkv_cp_async4(void* smem_dst, const void* gsrc) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void pkv_cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 // IEEE binary16 <-> binary32 in integer arithmetic (round to nearest even), the
 // conversion half::f16::from_f32 / to_f32 perform (fib-quant/src/codec.rs:1002,1028).
 __device__ __forceinline__ uint32_t pkv_f32_to_f16_bits(float f) {
@@ -117,8 +131,10 @@ struct pkv_turbo_profile {
   int polar_bits, pairs, rec_bytes, radii_words, angle_words, sign_words;
   float scale;              // 1 / sqrtf(dim), turbo-quant/src/rotation.rs:394
   uint32_t sign_mask[4];    // bit i set: signs[i] == -1
-  float* qjl_dev;           // projections x dim
-  float* lut_dev;           // [2][2^polar_bits]: cos then sin
+  int fast_bucket;          // 1: ray table validated, kernels may use the bucket shortcut
+  int ray_count;            // 2^polar_bits / 4 + 1, or 0
+  float* qjl_dev;           // projections x dim, then one sign-shortcut threshold per row
+  float* lut_dev;           // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
   PkvWorkspace ws;
 };
 

@@ -26,7 +26,7 @@ __device__ __forceinline__ uint32_t load_bits(const uint8_t* bytes, int pos, int
 __device__ __forceinline__ void stage_in(uint8_t* dst, const uint8_t* src, int nbytes) {
   int n16 = nbytes >> 4;
   for (int i = threadIdx.x; i < n16; i += blockDim.x)
-    reinterpret_cast<uint4*>(dst)[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    pkv_cp_async16(reinterpret_cast<uint4*>(dst) + i, reinterpret_cast<const uint4*>(src) + i);
   for (int i = (n16 << 4) + threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
 }
 __device__ __forceinline__ void stage_out(uint8_t* dst, const uint8_t* src, int nbytes) {
@@ -73,9 +73,10 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
   const int rec = g.rec_bytes;
 
   for (int i = threadIdx.x; i < D * D / 4; i += kThreads)
-    reinterpret_cast<float4*>(s_rot)[i] = __ldg(reinterpret_cast<const float4*>(rot32) + i);
+    pkv_cp_async16(reinterpret_cast<float4*>(s_rot) + i, reinterpret_cast<const float4*>(rot32) + i);
   if (threadIdx.x < 32) s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
   stage_in(s_rec, payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * rec, nv * rec);
+  pkv_cp_async_wait_all();
   __syncthreads();
 
   // unpack + validate: one thread per vector (checks in the reference's order)
@@ -245,7 +246,7 @@ fib_encode_kernel(PkvGeom g, const float* __restrict__ x, const double* __restri
   s_rec += (16 - (reinterpret_cast<uintptr_t>(s_rec) & 15)) & 15;
 
   for (int i = threadIdx.x; i < D * D / 2; i += kThreads)
-    reinterpret_cast<double2*>(s_rot)[i] = __ldg(reinterpret_cast<const double2*>(rot_t) + i);
+    pkv_cp_async16(reinterpret_cast<double2*>(s_rot) + i, reinterpret_cast<const double2*>(rot_t) + i);
   if (threadIdx.x < 32) s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
   // load the tile: D/4 lanes per vector, one float4 each
   for (int i = threadIdx.x; i < K::TV * (D / 4); i += kThreads) {
@@ -256,6 +257,7 @@ fib_encode_kernel(PkvGeom g, const float* __restrict__ x, const double* __restri
     float* d = s_x + v * K::XS + 4 * q;
     d[0] = val.x; d[1] = val.y; d[2] = val.z; d[3] = val.w;
   }
+  pkv_cp_async_wait_all();
   __syncthreads();
 
   // (A) check_finite, l2_norm (f64, sequential), fib-quant/src/codec.rs:601-606,1049-1064

@@ -8,6 +8,7 @@
 #include <new>
 
 #include "pkv_common.cuh"
+#include "pkv_fast_paths.h"
 
 namespace {
 
@@ -103,6 +104,46 @@ int decode_err_word(uint64_t w, int32_t* code, int64_t* index) {
   if (code) *code = c;
   if (index) *index = (int64_t)((w >> 8) & 0xFFFFFFFFFFFFull);
   return c;
+}
+
+// encode_pair's bucket before the modulo (turbo-quant/src/polar.rs:415-420), on the host.
+uint32_t raw_bucket_host(float theta, uint32_t levels) {
+  const float pi = 3.14159274101257324f;
+  volatile float sum = theta + pi;
+  volatile float normalized = sum / (2.0f * pi);
+  volatile float scaled = normalized * (float)levels;
+  const float fl = floorf(scaled);
+  return fl <= 0.0f ? 0u : (uint32_t)fl;
+}
+
+// For k = 1..levels find T_k, the smallest binary32 theta whose raw bucket is >= k (the bucket
+// is monotone in theta), and check that the point where a correctly rounded angle crosses it --
+// the midpoint of T_k and its predecessor -- is within 2e-6 rad of the ideal ray -pi + 2 pi k / L.
+bool turbo_bucket_boundaries_ok(int levels) {
+  auto key = [](float f) {  // order-preserving map of binary32 to int64
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    return (u & 0x80000000u) ? -(int64_t)(u & 0x7fffffffu) : (int64_t)u;
+  };
+  auto unkey = [](int64_t k) {
+    uint32_t u = k < 0 ? (0x80000000u | (uint32_t)(-k)) : (uint32_t)k;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+  };
+  for (int k = 1; k <= levels; k++) {
+    int64_t lo = key(-3.2f), hi = key(3.2f);  // bucket(lo) < k <= bucket(hi)
+    if (raw_bucket_host(unkey(hi), (uint32_t)levels) < (uint32_t)k) return false;
+    while (hi - lo > 1) {
+      const int64_t mid = lo + (hi - lo) / 2;
+      if (raw_bucket_host(unkey(mid), (uint32_t)levels) >= (uint32_t)k) hi = mid;
+      else lo = mid;
+    }
+    const double boundary = 0.5 * ((double)unkey(lo) + (double)unkey(hi));
+    const double ideal = -M_PI + 2.0 * M_PI * (double)k / (double)levels;
+    if (fabs(boundary - ideal) > 2.0e-6) return false;
+  }
+  return true;
 }
 
 int fib_index_bits(int n) {  // fib-quant/src/profile.rs:268-274
@@ -412,7 +453,7 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
   p->qjl_dev = nullptr;
   p->lut_dev = nullptr;
   const int levels = 1 << pb;
-  float lut[512];
+  float lut[1024];
   for (int i = 0; i < levels; i++) {
     if (cos_lut && sin_lut) {
       lut[i] = cos_lut[i];
@@ -426,13 +467,32 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
       lut[levels + i] = sinf(theta);
     }
   }
+  // Bucket shortcut (pkv_fast_paths.h): rays at 2 pi t / L, t = 0..L/4, usable only if every
+  // exact decision boundary lies within 2e-6 rad of its ray.
+  p->ray_count = pb >= 2 ? levels / 4 + 1 : 0;
+  p->fast_bucket = pb >= 2 && turbo_bucket_boundaries_ok(levels);
+  for (int t = 0; t < p->ray_count; t++) {
+    const double beta = 2.0 * M_PI * (double)t / (double)levels;
+    lut[2 * levels + t] = (float)cos(beta);
+    lut[2 * levels + p->ray_count + t] = (float)sin(beta);
+  }
+  const int lut_len = 2 * levels + 2 * p->ray_count;
   cudaError_t e = cudaGetDevice(&p->device);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&p->lut_dev, sizeof(float) * 2 * levels);
-  if (e == cudaSuccess) e = cudaMemcpy(p->lut_dev, lut, sizeof(float) * 2 * levels, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->lut_dev, sizeof(float) * lut_len);
+  if (e == cudaSuccess) e = cudaMemcpy(p->lut_dev, lut, sizeof(float) * lut_len, cudaMemcpyHostToDevice);
   if (with_qjl) {
-    const size_t bytes = sizeof(float) * (size_t)cfg->projections * d;
+    const int m = cfg->projections;
+    float* host = new float[(size_t)m * (d + 1)];
+    memcpy(host, qjl, sizeof(float) * (size_t)m * d);
+    for (int r = 0; r < m; r++) {  // |g_r| rounded up, times the relative bound of the sign shortcut
+      double s2 = 0.0;
+      for (int j = 0; j < d; j++) s2 += (double)qjl[r * d + j] * (double)qjl[r * d + j];
+      host[(size_t)m * d + r] = (float)(sqrt(s2) * 1.0001) * PKV_QJL_REL_BOUND;
+    }
+    const size_t bytes = sizeof(float) * (size_t)m * (d + 1);
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->qjl_dev, bytes);
-    if (e == cudaSuccess) e = cudaMemcpy(p->qjl_dev, qjl, bytes, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(p->qjl_dev, host, bytes, cudaMemcpyHostToDevice);
+    delete[] host;
   }
   if (e != cudaSuccess) {
     pkv_turbo_profile_destroy(p);

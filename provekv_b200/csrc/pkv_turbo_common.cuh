@@ -1,0 +1,114 @@
+// Pieces shared by the turbo-quant encode and decode kernels (pkv_turbo.cu).
+#pragma once
+
+#include "pkv_common.cuh"
+#include "pkv_fast_paths.h"
+
+namespace pkv_turbo {
+
+#define PKV_PI_F 3.14159274101257324f
+#define PKV_TWO_PI_F 6.28318548202514648f
+#define PKV_FLT_MIN 1.17549435e-38f
+#define PKV_FLT_EPS 1.1920929e-07f
+
+template <int D>
+struct Turbo {
+  static constexpr int TV = D == 64 ? 128 : 64;
+  static constexpr int XS = D + 4;   // f32 tile row stride (keeps float4 alignment)
+  static constexpr int WS = TV + 1;  // word-transposed record tile row stride
+  static constexpr int P = D / 2;
+  static constexpr int LPV = D / 4;  // lanes per vector in the coalesced copies
+};
+
+struct TurboParams {
+  int polar_bits, mode, projections, lossy;
+  int radii_words, angle_words, sign_words, rec_words;
+  float scale;
+  uint32_t sign_mask[4];
+  int fast_bucket;     // ray table present and validated against the exact thresholds
+  int ray_count;       // 2^polar_bits / 4 + 1 rays, 0 without the shortcut
+  const float* qjl;    // [m][dim] then m sign-shortcut thresholds
+  const float* lut;    // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
+};
+
+// fwht_normalized, turbo-quant/src/rotation.rs:379-398: butterflies for
+// step = 1, 2, 4, ... on pairs (i, i + step): (a, b) -> (a + b, a - b); then * scale.
+template <int D>
+__device__ __forceinline__ void fwht_regs(float (&v)[D], float scale) {
+#pragma unroll
+  for (int step = 1; step < D; step <<= 1) {
+#pragma unroll
+    for (int start = 0; start < D; start += 2 * step) {
+#pragma unroll
+      for (int o = 0; o < step; o++) {
+        const float a = v[start + o], b = v[start + o + step];
+        v[start + o] = __fadd_rn(a, b);
+        v[start + o + step] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], scale);
+}
+
+// value * sign with sign = +-1.0 is a sign-bit flip (also for zeros and NaNs).
+template <int D>
+__device__ __forceinline__ void apply_signs(float (&v)[D], const uint32_t (&mask)[4]) {
+#pragma unroll
+  for (int i = 0; i < D; i++)
+    v[i] = __uint_as_float(__float_as_uint(v[i]) ^ ((mask[i >> 5] << (31 - (i & 31))) & 0x80000000u));
+}
+
+// encode_pair's bucket, turbo-quant/src/polar.rs:415-420
+__device__ __forceinline__ uint32_t angle_bucket(float theta, uint32_t levels) {
+  const float normalized = __fdiv_rn(__fadd_rn(theta, PKV_PI_F), PKV_TWO_PI_F);
+  const float scaled = floorf(__fmul_rn(normalized, (float)levels));
+  return ((uint32_t)scaled) & (levels - 1u);  // f32 -> u32 saturates like Rust's `as`
+}
+
+// The exact (slow) forms, kept out of line: taken only by undecided pairs / projections.
+__device__ __noinline__ uint32_t exact_bucket(float b, float a, uint32_t levels) {
+  return angle_bucket(pkv_atan2f_portable(b, a), levels);
+}
+
+// QjlQuantizer::sketch's dot (qjl.rs:214-217): sequential, separately rounded * and +.
+// `res` is the thread's residual vector in shared memory (its row of the f32 tile).
+__device__ __noinline__ float exact_dot(const float* g, const float* res, int dim) {
+  float dot = 0.0f;
+  for (int j = 0; j < dim; j++) dot = __fadd_rn(dot, __fmul_rn(g[j], res[j]));
+  return dot;
+}
+
+// Packed two-lane f32 fused multiply-add (one issue slot for two FMAs on sm_100).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long ra, rb, rc, rd;
+  ra = *reinterpret_cast<unsigned long long*>(&a);
+  rb = *reinterpret_cast<unsigned long long*>(&b);
+  rc = *reinterpret_cast<unsigned long long*>(&c);
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  return *reinterpret_cast<float2*>(&rd);
+}
+
+// Records between global memory (vector-major words) and the shared tile ([word][vector]).
+// Word i of the tile belongs to vector i / rec_words; the pair (v, k) is advanced
+// incrementally so the loop has no division.
+template <int D, bool IN>
+__device__ __forceinline__ void stage_records(uint32_t* s_w, uint32_t* g, int nv, int rec_words) {
+  using K = Turbo<D>;
+  const int total = nv * rec_words;
+  int i = threadIdx.x;
+  int v = i / rec_words, k = i - v * rec_words;
+  const int dv = K::TV / rec_words, dk = K::TV - dv * rec_words;
+  for (; i < total; i += K::TV) {
+    if (IN) pkv_cp_async4(s_w + k * K::WS + v, g + i);  // caller waits (pkv_cp_async_wait_all)
+    else g[i] = s_w[k * K::WS + v];
+    v += dv;
+    k += dk;
+    if (k >= rec_words) {
+      k -= rec_words;
+      v++;
+    }
+  }
+}
+
+}  // namespace pkv_turbo

@@ -1,0 +1,146 @@
+// turbo-quant decode fused with the write into the KV cache.
+//  turbo-quant/src/wire.rs:497-565 (per-vector record), radius.rs:81-147,
+//  polar.rs:286-316 (dequantise angle, r cos / r sin), rotation.rs:170-194 (inverse FWHT, signs)
+#pragma once
+
+#include "pkv_turbo_common.cuh"
+
+namespace pkv_turbo {
+
+template <int D, int PB>
+__global__ void __launch_bounds__(Turbo<D>::TV)
+turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
+                          float* __restrict__ cache, uint64_t* err) {
+  using K = Turbo<D>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* s_x = reinterpret_cast<float*>(smem);                       // [TV][XS]
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);  // [TV]
+  float* s_q255 = reinterpret_cast<float*>(s_off + K::TV);           // [256]
+  float* s_lut = s_q255 + 256;                                       // cos[L], sin[L]
+  const int pb = PB ? PB : tp.polar_bits;
+  const int levels = 1 << pb;
+  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_lut + 2 * levels);   // [rec_words][WS]
+
+  const int tile = blockIdx.x % g.tiles_per_batch;
+  const int batch = blockIdx.x / g.tiles_per_batch;
+  const int v0 = tile * K::TV;
+  const int nv = min(K::TV, g.vpb - v0);
+  const int v = threadIdx.x;
+
+  stage_records<D, true>(
+      s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(
+               payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes)),
+      nv, tp.rec_words);
+  for (int i = threadIdx.x; i < 2 * levels; i += K::TV) pkv_cp_async4(s_lut + i, tp.lut + i);
+  if (tp.lossy)  // `*value as f32 / u8::MAX as f32`, radius.rs:143
+    for (int i = threadIdx.x; i < 256; i += K::TV) s_q255[i] = __fdiv_rn((float)i, 255.0f);
+  pkv_cp_async_wait_all();
+  __syncthreads();
+
+  if (v < nv) {
+    s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
+    const uint32_t* w = s_w + v;
+    int code = 0;
+    float y[D];
+    // radii -> y[2i] (temporarily)
+    if (!tp.lossy) {
+      uint32_t bad = 0;
+#pragma unroll
+      for (int i = 0; i < K::P; i++) {
+        const uint32_t u = w[i * K::WS];
+        // finite and non-negative (radius.rs:98-103): sign clear and exponent not all ones
+        bad |= (u >> 31) | (uint32_t)((u & 0x7f800000u) == 0x7f800000u);
+        y[2 * i] = __uint_as_float(u);
+      }
+      // -0.0 has the sign bit set but passes `value < 0.0`; re-check exactly when flagged
+      if (bad) {
+#pragma unroll 4
+        for (int i = 0; i < K::P; i++) {
+          const float r = __uint_as_float(w[i * K::WS]);
+          if (!code && (!pkv_finite(r) || r < 0.0f)) code = PKV_VEC_BAD_RADIUS;
+        }
+      }
+    } else {
+      const float mn = __uint_as_float(w[(K::P / 4) * K::WS]);
+      const float mx = __uint_as_float(w[(K::P / 4 + 1) * K::WS]);
+      if (!pkv_finite(mn) || !pkv_finite(mx) || mn > mx) code = PKV_VEC_BAD_RADIUS_RANGE;
+      const float span = __fsub_rn(mx, mn);
+#pragma unroll
+      for (int k = 0; k < K::P / 4; k++) {
+        const uint32_t q4 = w[k * K::WS];
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+          const float t = __fadd_rn(mn, __fmul_rn(span, s_q255[(q4 >> (8 * b)) & 0xffu]));
+          const float r = code ? 0.0f : pkv_expf_portable(t);
+          if (!code && !pkv_finite(r)) code = PKV_VEC_BAD_RADIUS;  // polar.rs:127-133
+          y[2 * (4 * k + b)] = r;
+        }
+      }
+    }
+    // angle indices (LSB-first stream, bitpack.rs:135-153) and the polar -> cartesian step
+    const uint32_t* aw = w + tp.radii_words * K::WS;
+    const uint32_t mask = (uint32_t)levels - 1u;
+    if constexpr (PB != 0) {
+      constexpr int NW = K::P * PB / 32;
+      uint32_t words[NW];
+#pragma unroll
+      for (int k = 0; k < NW; k++) words[k] = aw[k * K::WS];
+#pragma unroll
+      for (int i = 0; i < K::P; i++) {
+        const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
+        uint32_t idx = words[wi] >> sh;
+        if (sh + PB > 32) idx |= words[wi + 1] << (32 - sh);
+        idx &= mask;
+        const float r = y[2 * i];
+        y[2 * i] = __fmul_rn(r, s_lut[idx]);               // r * theta.cos(), polar.rs:312
+        y[2 * i + 1] = __fmul_rn(r, s_lut[levels + idx]);  // r * theta.sin(), polar.rs:313
+      }
+    } else {
+      uint64_t bitbuf = 0;
+      int nbits = 0, wk = 0;
+#pragma unroll
+      for (int i = 0; i < K::P; i++) {
+        if (nbits < pb) {
+          bitbuf |= (uint64_t)aw[wk * K::WS] << nbits;
+          wk++;
+          nbits += 32;
+        }
+        const uint32_t idx = (uint32_t)bitbuf & mask;
+        bitbuf >>= pb;
+        nbits -= pb;
+        const float r = y[2 * i];
+        y[2 * i] = __fmul_rn(r, s_lut[idx]);
+        y[2 * i + 1] = __fmul_rn(r, s_lut[levels + idx]);
+      }
+    }
+    if (code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
+    // FastHadamardRotation::apply_inverse, rotation.rs:212-221
+    fwht_regs<D>(y, tp.scale);
+    apply_signs<D>(y, tp.sign_mask);
+    float* row = s_x + v * K::XS;
+#pragma unroll
+    for (int i = 0; i < D; i += 4)
+      *reinterpret_cast<float4*>(row + i) = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
+  }
+  __syncthreads();
+
+  // coalesced write-out: D/4 lanes per vector, one float4 each, every replica
+  for (int i = threadIdx.x; i < nv * K::LPV; i += K::TV) {
+    const int vv = i / K::LPV, q = i % K::LPV;
+    const float4 val = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 4 * q);
+    float* dst = cache + s_off[vv] + 4 * q;
+    for (int r = 0; r < g.L.n_replicas; r++) {
+      *reinterpret_cast<float4*>(dst) = val;
+      dst += g.L.replica_stride;
+    }
+  }
+}
+
+template <int D>
+size_t turbo_decode_smem(const TurboParams& tp) {
+  using K = Turbo<D>;
+  return sizeof(float) * K::TV * K::XS + sizeof(int64_t) * K::TV + sizeof(float) * 256 +
+         sizeof(float) * 2 * (1 << tp.polar_bits) + sizeof(uint32_t) * tp.rec_words * K::WS;
+}
+
+}  // namespace pkv_turbo

@@ -1,0 +1,35 @@
+"""The kernels' certified shortcuts (provekv_b200/csrc/pkv_fast_paths.h) run on the CPU:
+whenever a shortcut declares a decision certain it must equal the exact operation sequence,
+including for pairs placed within nano-radians of a sector boundary."""
+import ctypes as C
+
+import pytest
+
+
+def _counts(fn, *args):
+    out = (C.c_int64 * 3)()
+    fn(*args, out)
+    return list(out)
+
+
+@pytest.mark.parametrize("polar_bits", [2, 3, 4, 7, 8])
+@pytest.mark.parametrize("spread", [1e-3, 3e-5, 1e-6, 1e-8])
+def test_bucket_shortcut_never_decides_wrong(oracle_mod, polar_bits, spread):
+    fn = oracle_mod.lib().pkvo_fast_bucket_check
+    fn.argtypes = [C.c_int, C.c_int64, C.c_uint64, C.c_double, C.POINTER(C.c_int64)]
+    wrong, undecided, decided = _counts(fn, polar_bits, 400_000, polar_bits * 17 + 1, spread)
+    assert wrong == 0
+    assert decided > 100_000          # the shortcut carries the bulk of ordinary pairs
+    if spread <= 1e-6:
+        assert undecided > 150_000    # boundary-hugging pairs are all sent to the exact path
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("scale", [1.0, 1e-3, 1e15, 1e-15])
+def test_qjl_sign_shortcut_never_decides_wrong(oracle_mod, dim, scale):
+    fn = oracle_mod.lib().pkvo_fast_qjl_check
+    fn.argtypes = [C.c_int, C.c_int64, C.c_uint64, C.c_double, C.POINTER(C.c_int64)]
+    wrong, undecided, decided = _counts(fn, dim, 200_000, dim + 3, scale)
+    assert wrong == 0
+    assert decided >= 99_000          # ordinary residuals are decided by the fused dot
+    assert undecided >= 50_000        # near-orthogonal ones are not
