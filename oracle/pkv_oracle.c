@@ -918,7 +918,7 @@ PKVO_API void pkvo_fast_bucket_check(int polar_bits, int64_t n, uint64_t seed, d
       b = sp[xs64(&s) % 9];
     }
     int certain = 0;
-    uint32_t fast = pkv_fast_bucket(a, b, polar_bits, rc, rs, &certain);
+    uint32_t fast = pkv_fast_bucket_any(a, b, polar_bits, rc, rs, &certain);
     if (!certain) {
       counts[1]++;
       continue;

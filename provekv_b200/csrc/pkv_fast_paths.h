@@ -55,6 +55,48 @@ PKV_HD uint32_t pkv_fast_bucket(float a, float b, int polar_bits, const float* r
   return (uint32_t)k;
 }
 
+/* The same shortcut for 8 levels (3 bits) with the rays folded into constants: inside the first
+ * quadrant the only interior ray is the diagonal, so the sector is `|b| >= |a|`, the distance to
+ * the axis rays is min(|a|, |b|) and the distance to the diagonal is ||b| - |a|| / sqrt 2. */
+PKV_HD uint32_t pkv_fast_bucket3(float a, float b, int* certain) {
+  const uint32_t ab = pkv_f32_bits(a), bb = pkv_f32_bits(b);
+  const float ax = pkv_f32_from_bits(ab & 0x7fffffffu), ay = pkv_f32_from_bits(bb & 0x7fffffffu);
+  const int j = ay >= ax;
+  const float axis = j ? ax : ay;
+  const float diff = PKV_FSUB(ay, ax);
+  const float diag = PKV_FMUL(pkv_f32_from_bits(pkv_f32_bits(diff) & 0x7fffffffu), 0.70710678118654752f);
+  const float m = axis < diag ? axis : diag;
+  *certain = m > PKV_FMUL(PKV_BUCKET_EPS, PKV_FADD(ax, ay));
+  const int neg_a = (int)(ab >> 31), neg_b = (int)(bb >> 31);
+  return (uint32_t)(neg_b ? (neg_a ? j : 3 - j) : (neg_a ? 7 - j : 4 + j));
+}
+
+/* 16 levels (4 bits): fold to the first octant (lo = min, hi = max of |a|, |b|); the interior ray
+ * is at 22.5 degrees, the octant's upper ray is the diagonal. */
+PKV_HD uint32_t pkv_fast_bucket4(float a, float b, int* certain) {
+  const uint32_t ab = pkv_f32_bits(a), bb = pkv_f32_bits(b);
+  const float ax = pkv_f32_from_bits(ab & 0x7fffffffu), ay = pkv_f32_from_bits(bb & 0x7fffffffu);
+  const int swap = ay > ax;
+  const float lo = swap ? ax : ay, hi = swap ? ay : ax;
+  const float t = PKV_FSUB(PKV_FMUL(lo, 0.92387953251128674f), PKV_FMUL(hi, 0.38268343236508977f));
+  const int jp = t >= 0.0f;
+  const float d_a = jp ? t : lo;
+  const float d_b = jp ? PKV_FMUL(PKV_FSUB(hi, lo), 0.70710678118654752f) : -t;
+  const float m = d_a < d_b ? d_a : d_b;
+  *certain = m > PKV_FMUL(PKV_BUCKET_EPS, PKV_FADD(ax, ay));
+  const int j = swap ? 3 - jp : jp;
+  const int neg_a = (int)(ab >> 31), neg_b = (int)(bb >> 31);
+  return (uint32_t)(neg_b ? (neg_a ? j : 7 - j) : (neg_a ? 15 - j : 8 + j));
+}
+
+/* Dispatch on the width: constant-folded when polar_bits is a compile-time constant. */
+PKV_HD uint32_t pkv_fast_bucket_any(float a, float b, int polar_bits, const float* ray_cos,
+                                    const float* ray_sin, int* certain) {
+  if (polar_bits == 3) return pkv_fast_bucket3(a, b, certain);
+  if (polar_bits == 4) return pkv_fast_bucket4(a, b, certain);
+  return pkv_fast_bucket(a, b, polar_bits, ray_cos, ray_sin, certain);
+}
+
 /* Relative threshold of the QJL sign shortcut: a dot product of n = dim <= 128 terms
  * evaluated in binary32 in any order, fused or not, differs from the exact sum by at most
  * gamma_n * sum|g_j x_j| <= gamma_n |g| |x| (gamma_n = n u / (1 - n u), u = 2^-24).  If the

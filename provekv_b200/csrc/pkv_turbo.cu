@@ -3,9 +3,9 @@
 // angle buckets, f32 or BlockLogU8 radii, optional QJL residual sign sketch,
 // and the inverse fused with the write into the KV cache.
 //
-// One thread owns one vector; a CTA stages TV vectors (f32 tile, padded rows)
-// and TV records (word-transposed, so record word k of vector v sits at
-// [k][v]) through shared memory so that every global access is coalesced.
+// One thread owns one vector and one warp owns a tile of 32 vectors, staged through its own
+// slice of shared memory (f32 tile with padded rows; records word-transposed, so record word k
+// of vector v sits at [k][v]) so that every global access is coalesced.
 // The kernels (pkv_turbo_encode.cuh, pkv_turbo_decode.cuh) are templated on the
 // dimension and on the angle width: 3, 4 and 7 bits are compiled with static bit
 // positions, any other width runs the generic variant (PB = 0).
@@ -49,7 +49,8 @@ int launch_encode(const TurboParams& tp, const float* x, const PkvGeom& g, uint8
   const size_t sm = turbo_encode_smem<D>(tp);
   int st = set_smem(turbo_encode_kernel<D, PB>, sm);
   if (st != PKV_OK) return st;
-  turbo_encode_kernel<D, PB><<<grid, Turbo<D>::TV, sm, s>>>(g, tp, x, payload, err);
+  const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;  // one warp per 32-vector tile
+  turbo_encode_kernel<D, PB><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
   return PKV_OK;
 }
 
@@ -59,13 +60,14 @@ int launch_decode(const TurboParams& tp, const uint8_t* payload, const PkvGeom& 
   const size_t sm = turbo_decode_smem<D>(tp);
   int st = set_smem(turbo_decode_patch_kernel<D, PB>, sm);
   if (st != PKV_OK) return st;
-  turbo_decode_patch_kernel<D, PB><<<grid, Turbo<D>::TV, sm, s>>>(g, tp, payload, cache, err);
+  const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
+  turbo_decode_patch_kernel<D, PB><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, cache, err);
   return PKV_OK;
 }
 
 }  // namespace
 
-int pkv_turbo_tile_vectors(int dim) { return dim == 64 ? Turbo<64>::TV : dim == 128 ? Turbo<128>::TV : 0; }
+int pkv_turbo_tile_vectors(int dim) { return (dim == 64 || dim == 128) ? 32 : 0; }
 
 #define PKV_DISPATCH_PB(FN, DIM, ...)                         \
   switch (tp.polar_bits) {                                    \

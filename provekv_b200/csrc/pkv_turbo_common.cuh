@@ -1,4 +1,8 @@
 // Pieces shared by the turbo-quant encode and decode kernels (pkv_turbo.cu).
+//
+// Work unit: one warp owns a tile of 32 vectors (one thread per vector) with its own slice of
+// shared memory, so warps never wait for each other; a CTA's warps only share the read-only
+// tables (QJL matrix, cos/sin and ray tables) loaded once at the start.
 #pragma once
 
 #include "pkv_common.cuh"
@@ -13,9 +17,11 @@ namespace pkv_turbo {
 
 template <int D>
 struct Turbo {
-  static constexpr int TV = D == 64 ? 128 : 64;
+  static constexpr int NWARPS = D == 64 ? 4 : 2;  // warps (tiles in flight) per CTA
+  static constexpr int THREADS = NWARPS * 32;
+  static constexpr int TV = 32;      // vectors per warp tile
   static constexpr int XS = D + 4;   // f32 tile row stride (keeps float4 alignment)
-  static constexpr int WS = TV + 1;  // word-transposed record tile row stride
+  static constexpr int WS = TV + 1;  // word-transposed record tile row stride (odd: no bank conflicts)
   static constexpr int P = D / 2;
   static constexpr int LPV = D / 4;  // lanes per vector in the coalesced copies
 };
@@ -89,18 +95,19 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   return *reinterpret_cast<float2*>(&rd);
 }
 
-// Records between global memory (vector-major words) and the shared tile ([word][vector]).
-// Word i of the tile belongs to vector i / rec_words; the pair (v, k) is advanced
-// incrementally so the loop has no division.
+// A warp's records between global memory (vector-major words) and its shared tile
+// ([word][vector]).  Word i of the tile belongs to vector i / rec_words; (v, k) is advanced
+// incrementally so the loop has no division.  Loads are asynchronous (caller waits).
 template <int D, bool IN>
-__device__ __forceinline__ void stage_records(uint32_t* s_w, uint32_t* g, int nv, int rec_words) {
+__device__ __forceinline__ void stage_records(uint32_t* s_w, uint32_t* g, int nv, int rec_words,
+                                              int lane) {
   using K = Turbo<D>;
   const int total = nv * rec_words;
-  int i = threadIdx.x;
+  int i = lane;
   int v = i / rec_words, k = i - v * rec_words;
-  const int dv = K::TV / rec_words, dk = K::TV - dv * rec_words;
-  for (; i < total; i += K::TV) {
-    if (IN) pkv_cp_async4(s_w + k * K::WS + v, g + i);  // caller waits (pkv_cp_async_wait_all)
+  const int dv = 32 / rec_words, dk = 32 - dv * rec_words;
+  for (; i < total; i += 32) {
+    if (IN) pkv_cp_async4(s_w + k * K::WS + v, g + i);
     else g[i] = s_w[k * K::WS + v];
     v += dv;
     k += dk;

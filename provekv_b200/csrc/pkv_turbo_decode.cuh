@@ -7,38 +7,53 @@
 
 namespace pkv_turbo {
 
+template <int D>
+struct TurboDecSmem {  // per-warp slices follow the CTA-wide tables
+  using K = Turbo<D>;
+  static __host__ __device__ size_t warp_bytes(int rec_words) {
+    const size_t n = sizeof(float) * K::TV * K::XS + sizeof(int64_t) * K::TV +
+                     sizeof(uint32_t) * rec_words * K::WS;
+    return (n + 15) & ~(size_t)15;  // the next warp's f32 tile stays 16-byte aligned
+  }
+  static __host__ __device__ size_t table_bytes(int levels) { return sizeof(float) * (256 + 2 * levels); }
+};
+
 template <int D, int PB>
-__global__ void __launch_bounds__(Turbo<D>::TV)
+__global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                           float* __restrict__ cache, uint64_t* err) {
   using K = Turbo<D>;
   extern __shared__ __align__(16) uint8_t smem[];
-  float* s_x = reinterpret_cast<float*>(smem);                       // [TV][XS]
-  int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);  // [TV]
-  float* s_q255 = reinterpret_cast<float*>(s_off + K::TV);           // [256]
-  float* s_lut = s_q255 + 256;                                       // cos[L], sin[L]
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
-  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_lut + 2 * levels);   // [rec_words][WS]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* s_q255 = reinterpret_cast<float*>(smem);  // [256]
+  float* s_lut = s_q255 + 256;                     // cos[L], sin[L]
+  uint8_t* wbase = smem + TurboDecSmem<D>::table_bytes(levels) + warp * TurboDecSmem<D>::warp_bytes(tp.rec_words);
+  float* s_x = reinterpret_cast<float*>(wbase);                       // [TV][XS]
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);   // [TV]
+  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);         // [rec_words][WS]
 
-  const int tile = blockIdx.x % g.tiles_per_batch;
-  const int batch = blockIdx.x / g.tiles_per_batch;
+  const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
+  const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
+  const int tile = active ? (int)(tile_id % g.tiles_per_batch) : 0;
+  const int batch = active ? (int)(tile_id / g.tiles_per_batch) : 0;
   const int v0 = tile * K::TV;
-  const int nv = min(K::TV, g.vpb - v0);
-  const int v = threadIdx.x;
+  const int nv = active ? min(K::TV, g.vpb - v0) : 0;
+  const int v = lane;
 
   stage_records<D, true>(
       s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(
                payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes)),
-      nv, tp.rec_words);
-  for (int i = threadIdx.x; i < 2 * levels; i += K::TV) pkv_cp_async4(s_lut + i, tp.lut + i);
+      nv, tp.rec_words, lane);
+  for (int i = threadIdx.x; i < 2 * levels; i += K::THREADS) pkv_cp_async4(s_lut + i, tp.lut + i);
   if (tp.lossy)  // `*value as f32 / u8::MAX as f32`, radius.rs:143
-    for (int i = threadIdx.x; i < 256; i += K::TV) s_q255[i] = __fdiv_rn((float)i, 255.0f);
+    for (int i = threadIdx.x; i < 256; i += K::THREADS) s_q255[i] = __fdiv_rn((float)i, 255.0f);
+  if (v < nv) s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
   pkv_cp_async_wait_all();
-  __syncthreads();
+  __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
 
   if (v < nv) {
-    s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
     const uint32_t* w = s_w + v;
     int code = 0;
     float y[D];
@@ -122,10 +137,11 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
     for (int i = 0; i < D; i += 4)
       *reinterpret_cast<float4*>(row + i) = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
   }
-  __syncthreads();
+  __syncwarp();
 
   // coalesced write-out: D/4 lanes per vector, one float4 each, every replica
-  for (int i = threadIdx.x; i < nv * K::LPV; i += K::TV) {
+#pragma unroll 4
+  for (int i = lane; i < nv * K::LPV; i += 32) {
     const int vv = i / K::LPV, q = i % K::LPV;
     const float4 val = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 4 * q);
     float* dst = cache + s_off[vv] + 4 * q;
@@ -138,9 +154,8 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
 
 template <int D>
 size_t turbo_decode_smem(const TurboParams& tp) {
-  using K = Turbo<D>;
-  return sizeof(float) * K::TV * K::XS + sizeof(int64_t) * K::TV + sizeof(float) * 256 +
-         sizeof(float) * 2 * (1 << tp.polar_bits) + sizeof(uint32_t) * tp.rec_words * K::WS;
+  return TurboDecSmem<D>::table_bytes(1 << tp.polar_bits) +
+         Turbo<D>::NWARPS * TurboDecSmem<D>::warp_bytes(tp.rec_words);
 }
 
 }  // namespace pkv_turbo

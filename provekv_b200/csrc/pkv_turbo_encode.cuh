@@ -1,11 +1,11 @@
-// turbo-quant encode: one thread per vector.
+// turbo-quant encode: one thread per vector, one warp per tile of 32 vectors.
 //  turbo-quant/src/turbo.rs:256-288, polar.rs:246-266,413-421, rotation.rs:202-221,379-398,
 //  qjl.rs:203-220, radius.rs:58-77, bitpack.rs:21-62, wire.rs:350-396
 //
 // The per-pair and per-projection work is written as straight-line unrolled passes without
 // calls or data-dependent branches, so the compiler can interleave independent pairs; the
 // decisions a shortcut could not certify are collected in bit masks and settled afterwards
-// by two out-of-line routines that run the exact operation sequence.
+// by out-of-line routines that run the exact operation sequence.
 #pragma once
 
 #include "pkv_turbo_common.cuh"
@@ -23,28 +23,63 @@ __device__ __forceinline__ void patch_angle(uint32_t* aw, int ws, int i, int pb,
   }
 }
 
-// Exact angle buckets for the pairs in `unc`: the rotated vector is rebuilt in local memory
-// with the reference's operation order (signs, butterflies step = 1, 2, 4, ..., scale), then
-// each pending pair takes atan2f + the bucket expression of polar.rs:415-420.
-__device__ __noinline__ void fix_pairs(const float* xrow, int dim, const uint32_t* sign_mask,
-                                       float scale, unsigned long long unc, uint32_t* aw, int ws,
-                                       int pb) {
-  float t[PKV_MAX_DIM];
-  for (int i = 0; i < dim; i++)
-    t[i] = __uint_as_float(__float_as_uint(xrow[i]) ^ (((sign_mask[i >> 5] >> (i & 31)) & 1u) << 31));
-  for (int step = 1; step < dim; step <<= 1)
-    for (int start = 0; start < dim; start += 2 * step)
+// Exact angle buckets for the undecided pairs `unc` of ONE vector, computed by the whole warp
+// (all 32 lanes call this together).  The rotated vector is rebuilt from the input row with
+// D/32 elements per lane: the butterflies pair the same elements in the same order as
+// fwht_normalized (in-lane for step < D/32, by lane-xor shuffles above), so every value is
+// bit-identical to the owner thread's.  Lane l then holds pairs l*D/64 .. and each pending pair
+// takes atan2f + the bucket expression of polar.rs:415-420; lane 0 patches the angle words.
+template <int D>
+__device__ __noinline__ void fix_pairs_warp(const float* xrow, const uint32_t* sign_mask, float scale,
+                                            unsigned long long unc, uint32_t* aw, int ws, int pb,
+                                            int lane) {
+  constexpr int E = D / 32;  // elements per lane (2 or 4)
+  float e[E];
+#pragma unroll
+  for (int k = 0; k < E; k++) {
+    const int i = lane * E + k;
+    e[k] = __uint_as_float(__float_as_uint(xrow[i]) ^ (((sign_mask[i >> 5] >> (i & 31)) & 1u) << 31));
+  }
+#pragma unroll
+  for (int step = 1; step < E; step <<= 1)
+#pragma unroll
+    for (int start = 0; start < E; start += 2 * step)
+#pragma unroll
       for (int o = 0; o < step; o++) {
-        const float a = t[start + o], b = t[start + o + step];
-        t[start + o] = __fadd_rn(a, b);
-        t[start + o + step] = __fsub_rn(a, b);
+        const float a = e[start + o], b = e[start + o + step];
+        e[start + o] = __fadd_rn(a, b);
+        e[start + o + step] = __fsub_rn(a, b);
       }
+#pragma unroll
+  for (int step = E; step < D; step <<= 1) {
+    const int lm = step / E;
+    const bool upper = (lane & lm) != 0;
+#pragma unroll
+    for (int k = 0; k < E; k++) {
+      const float p = __shfl_xor_sync(0xffffffffu, e[k], lm);
+      e[k] = upper ? __fsub_rn(p, e[k]) : __fadd_rn(e[k], p);  // (a, b) -> (a + b, a - b)
+    }
+  }
+  uint32_t mine[E / 2];
+#pragma unroll
+  for (int j = 0; j < E / 2; j++) {
+    const int i = lane * (E / 2) + j;
+    mine[j] = 0;
+    if ((unc >> i) & 1ull)
+      mine[j] = exact_bucket(__fmul_rn(e[2 * j + 1], scale), __fmul_rn(e[2 * j], scale), 1u << pb);
+  }
   while (unc) {
     const int i = __ffsll((long long)unc) - 1;
     unc &= unc - 1;
-    const float a = __fmul_rn(t[2 * i], scale), b = __fmul_rn(t[2 * i + 1], scale);
-    patch_angle(aw, ws, i, pb, exact_bucket(b, a, 1u << pb));
+    uint32_t val = 0;
+#pragma unroll
+    for (int j = 0; j < E / 2; j++) {
+      const uint32_t t = __shfl_sync(0xffffffffu, mine[j], i / (E / 2));
+      if (j == i % (E / 2)) val = t;
+    }
+    if (lane == 0) patch_angle(aw, ws, i, pb, val);
   }
+  __syncwarp();
 }
 
 // Exact QJL signs for the projections in `unc` (qjl.rs:214-217); `res` is the residual row.
@@ -61,45 +96,77 @@ __device__ __noinline__ void fix_signs(const float* g, const float* res, int dim
   }
 }
 
+// Which of the two encode errors applies when some radius came out non-finite: a non-finite
+// input value (turbo.rs:263, checked first by the reference) or an overflow in the butterflies
+// (PolarCode::from_parts, polar.rs:127-133).
+__device__ __noinline__ int classify_bad_vector(const float* xrow, int dim) {
+  for (int i = 0; i < dim; i++)
+    if (!pkv_finite(xrow[i])) return PKV_VEC_NONFINITE_INPUT;
+  return PKV_VEC_BAD_RADIUS;
+}
+
+template <int D>
+struct TurboEncSmem {
+  using K = Turbo<D>;
+  static __host__ __device__ size_t warp_bytes(int rec_words, int lossy) {
+    const size_t n = sizeof(float) * K::TV * K::XS + sizeof(int64_t) * K::TV +
+                     sizeof(uint32_t) * rec_words * K::WS + (lossy ? sizeof(float) * K::P * K::WS : 0);
+    return (n + 15) & ~(size_t)15;
+  }
+  static __host__ __device__ size_t table_bytes(int projections, int levels, int ray_count) {
+    const size_t n = sizeof(float) * (projections * (D + 1) + 2 * levels + 2 * ray_count);
+    return (n + 15) & ~(size_t)15;
+  }
+};
+
 template <int D, int PB>
-__global__ void __launch_bounds__(Turbo<D>::TV)
+__global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                     uint8_t* __restrict__ payload, uint64_t* err) {
   using K = Turbo<D>;
   extern __shared__ __align__(16) uint8_t smem[];
-  float* s_x = reinterpret_cast<float*>(smem);                 // [TV][XS]
-  float* s_g = s_x + K::TV * K::XS;                            // [m][D]
-  float* s_thr = s_g + tp.projections * D;                     // [m] sign-shortcut thresholds
-  float* s_lut = s_thr + tp.projections;                       // cos, sin, ray_cos, ray_sin
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* s_g = reinterpret_cast<float*>(smem);                 // [m][D]
+  float* s_thr = s_g + tp.projections * D;                     // [m] sign-shortcut thresholds
+  float* s_lut = s_thr + tp.projections;                       // cos, sin, ray_cos, ray_sin
   const int lut_len = 2 * levels + 2 * tp.ray_count;
   const float* s_ray_cos = s_lut + 2 * levels;
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
-  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_lut + lut_len);          // [rec_words][WS]
-  float* s_rad = reinterpret_cast<float*>(s_w + tp.rec_words * K::WS);   // [P][WS], lossy only
-  int64_t* s_off = reinterpret_cast<int64_t*>(
-      s_rad + (tp.lossy ? K::P * K::WS : 0) + ((tp.rec_words * K::WS) & 1));  // 8-byte aligned
+  uint8_t* wbase = smem + TurboEncSmem<D>::table_bytes(tp.projections, levels, tp.ray_count) +
+                   warp * TurboEncSmem<D>::warp_bytes(tp.rec_words, tp.lossy);
+  float* s_x = reinterpret_cast<float*>(wbase);                        // [TV][XS]
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);    // [TV]
+  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);          // [rec_words][WS]
+  float* s_rad = reinterpret_cast<float*>(s_w + tp.rec_words * K::WS); // [P][WS], lossy only
 
-  const int tile = blockIdx.x % g.tiles_per_batch;
-  const int batch = blockIdx.x / g.tiles_per_batch;
+  const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
+  const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
+  const int tile = active ? (int)(tile_id % g.tiles_per_batch) : 0;
+  const int batch = active ? (int)(tile_id / g.tiles_per_batch) : 0;
   const int v0 = tile * K::TV;
-  const int nv = min(K::TV, g.vpb - v0);
-  const int v = threadIdx.x;
+  const int nv = active ? min(K::TV, g.vpb - v0) : 0;
+  const int v = lane;
 
+  // the warp's 32 vectors: 16 lanes x 16 bytes per vector, all copies in flight at once
   if (v < nv) s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
-  for (int i = threadIdx.x; i < tp.projections * (D + 1) / 4; i += K::TV)
-    pkv_cp_async16(reinterpret_cast<float4*>(s_g) + i, reinterpret_cast<const float4*>(tp.qjl) + i);
-  for (int i = threadIdx.x; i < lut_len; i += K::TV) pkv_cp_async4(s_lut + i, tp.lut + i);
-  __syncthreads();
-  for (int i = threadIdx.x; i < nv * K::LPV; i += K::TV) {
+  __syncwarp();
+#pragma unroll 4
+  for (int i = lane; i < nv * K::LPV; i += 32) {
     const int vv = i / K::LPV, q = i % K::LPV;
     pkv_cp_async16(s_x + vv * K::XS + 4 * q, reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
+  for (int i = threadIdx.x; i < tp.projections * (D + 1) / 4; i += K::THREADS)
+    pkv_cp_async16(reinterpret_cast<float4*>(s_g) + i, reinterpret_cast<const float4*>(tp.qjl) + i);
+  for (int i = threadIdx.x; i < lut_len; i += K::THREADS) pkv_cp_async4(s_lut + i, tp.lut + i);
   pkv_cp_async_wait_all();
-  __syncthreads();
+  __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
 
-  if (v < nv) {
+  // Every lane runs the per-vector code (lanes beyond nv work on their unused tile rows and
+  // never report or get copied out), so the warp stays converged for the cooperative fix-up.
+  const bool valid = v < nv;
+  {
     float* row = s_x + v * K::XS;
     uint32_t* w = s_w + v;
     uint32_t* aw = w + tp.radii_words * K::WS;
@@ -110,11 +177,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       const float4 t = *reinterpret_cast<const float4*>(row + i);
       y[i] = t.x; y[i + 1] = t.y; y[i + 2] = t.z; y[i + 3] = t.w;
     }
-    bool finite = true;
-#pragma unroll
-    for (int i = 0; i < D; i++) finite = finite && pkv_finite(y[i]);
-    if (!finite) code = PKV_VEC_NONFINITE_INPUT;  // turbo.rs:263
-    // FastHadamardRotation::apply, rotation.rs:202-210
+    // FastHadamardRotation::apply, rotation.rs:202-210.  A non-finite input makes every output of
+    // the transform non-finite, so input finiteness is only looked at when a radius is bad.
     apply_signs<D>(y, tp.sign_mask);
     fwht_regs<D>(y, tp.scale);
 
@@ -129,16 +193,16 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       for (int k = 0; k < NW; k++) words[k] = 0;
       uint64_t bitbuf = 0;
       int nbits = 0, wk = 0;
-      bool rad_ok = true;
+      uint32_t rmax = 0;  // radii are >= 0 or NaN: the largest bit pattern tells if any is not finite
 #pragma unroll
       for (int i = 0; i < K::P; i++) {
         const float a = y[2 * i], b = y[2 * i + 1];
         const float r = __fsqrt_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
         int certain = 0;
         uint32_t idx = 0;
-        if (tp.fast_bucket) idx = pkv_fast_bucket(a, b, pb, s_ray_cos, s_ray_sin, &certain);
+        if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
         unc |= (unsigned long long)(certain ? 0u : 1u) << i;
-        rad_ok = rad_ok && pkv_finite(r);
+        rmax = max(rmax, __float_as_uint(r) & 0x7fffffffu);
         radp[i * K::WS] = r;
         if constexpr (PB != 0) {
           const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
@@ -161,9 +225,17 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       } else if (nbits > 0) {
         aw[wk * K::WS] = (uint32_t)bitbuf;
       }
-      if (!code && !rad_ok) code = PKV_VEC_BAD_RADIUS;  // PolarCode::from_parts, polar.rs:127-133
+      if (rmax >= 0x7f800000u) code = classify_bad_vector(row, D);
     }
-    if (unc) fix_pairs(row, D, tp.sign_mask, tp.scale, unc, aw, K::WS, pb);
+    if (!valid) unc = 0;
+    for (unsigned pending = __ballot_sync(0xffffffffu, unc != 0); pending; pending &= pending - 1) {
+      const int src = __ffs(pending) - 1;  // settle lane src's undecided pairs, all lanes helping
+      const unsigned long long m =
+          ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
+          __shfl_sync(0xffffffffu, (uint32_t)unc, src);
+      fix_pairs_warp<D>(s_x + src * K::XS, tp.sign_mask, tp.scale, m,
+                        s_w + src + tp.radii_words * K::WS, K::WS, pb, lane);
+    }
 
     if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
       // polar.decode (polar.rs:272-278,306-316): de-quantised pairs from the final indices
@@ -202,7 +274,6 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       // inverse rotation (rotation.rs:212-221), residual = vector - reconstruction (turbo.rs:268-273)
       fwht_regs<D>(y, tp.scale);
       apply_signs<D>(y, tp.sign_mask);
-      bool res_ok = true;
       float2 n2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < D; i += 4) {
@@ -216,14 +287,18 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         // the residual replaces x in the tile: the exact dot of an undecided row reads it there
         *reinterpret_cast<float4*>(row + i) = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
       }
-#pragma unroll
-      for (int i = 0; i < D; i++) res_ok = res_ok && pkv_finite(y[i]);
-      if (!code && !res_ok) code = PKV_VEC_NONFINITE_RESIDUAL;  // qjl.rs:210
+      // a non-finite residual element makes the squared norm non-finite (qjl.rs:210)
+      const float nsq = n2.x + n2.y;
+      if (!code && !pkv_finite(nsq)) {
+        bool res_ok = true;
+        for (int i = 0; i < D; i++) res_ok = res_ok && pkv_finite(row[i]);
+        if (!res_ok) code = PKV_VEC_NONFINITE_RESIDUAL;
+      }
       // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per row.  The dot is
       // first taken with packed fused multiply-adds in four chains; its sign is the reference's
       // whenever |dot| clears the rounding bound (pkv_fast_paths.h), else fix_signs decides.
       uint32_t* sw = w + (tp.radii_words + tp.angle_words) * K::WS;
-      const float rnorm = __fmul_rn(__fsqrt_rn(n2.x + n2.y), 1.0001f);
+      const float rnorm = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
       unsigned long long uncq = 0;
       uint32_t bits = 0;
 #pragma unroll 4
@@ -245,7 +320,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           bits = 0;
         }
       }
-      if (uncq) fix_signs(s_g, row, D, uncq, sw, K::WS);
+      if (valid && uncq) fix_signs(s_g, row, D, uncq, sw, K::WS);
     }
     if (tp.lossy) {
       // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371)
@@ -275,22 +350,19 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       w[(K::P / 4) * K::WS] = __float_as_uint(mn);
       w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
     }
-    if (code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
+    if (valid && code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
   }
-  __syncthreads();
+  __syncwarp();
   stage_records<D, false>(
       s_w, reinterpret_cast<uint32_t*>(payload + (int64_t)batch * g.payload_batch_stride +
                                        (int64_t)v0 * g.rec_bytes),
-      nv, tp.rec_words);
+      nv, tp.rec_words, lane);
 }
 
 template <int D>
 size_t turbo_encode_smem(const TurboParams& tp) {
-  using K = Turbo<D>;
-  return sizeof(float) * K::TV * K::XS + sizeof(float) * tp.projections * (D + 1) +
-         sizeof(float) * (2 * (1 << tp.polar_bits) + 2 * tp.ray_count) +
-         sizeof(uint32_t) * tp.rec_words * K::WS + (tp.lossy ? sizeof(float) * K::P * K::WS : 0) +
-         sizeof(int64_t) * (K::TV + 1);
+  return TurboEncSmem<D>::table_bytes(tp.projections, 1 << tp.polar_bits, tp.ray_count) +
+         Turbo<D>::NWARPS * TurboEncSmem<D>::warp_bytes(tp.rec_words, tp.lossy);
 }
 
 }  // namespace pkv_turbo
