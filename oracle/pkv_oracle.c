@@ -972,3 +972,66 @@ PKVO_API void pkvo_fast_qjl_check(int dim, int64_t n, uint64_t seed, double res_
     if ((ref >= 0.0f) != (fast >= 0.0f)) counts[0]++;
   }
 }
+
+/* The fib encoder's shortcuts on n vectors (batch numerics): certified normalisation, binary32
+ * fused rotation, certified block argmin -- against the exact sequence of fib_encode_one.
+ * counts[0] = decided blocks with the wrong index, [1] = flagged blocks, [2] = decided blocks,
+ * [3] = elements whose normalised value was declared certain but differs, [4] = uncertain elements,
+ * [5] = largest |y~ - y| seen, in units of 1e-9. */
+PKVO_API void pkvo_fib_fast_check(const float* x, int64_t n, int dim, const double* rot,
+                                  const float* codebook, int n_codewords, int order, int64_t* counts) {
+  const int blocks = dim / 4;
+  float* m32 = (float*)malloc(sizeof(float) * (size_t)dim * dim);
+  float hn[32];
+  for (int i = 0; i < dim * dim; i++) m32[i] = (float)rot[i];
+  for (int c = 0; c < n_codewords; c++) {
+    double s = 0.0;
+    for (int j = 0; j < 4; j++) s += (double)codebook[4 * c + j] * codebook[4 * c + j];
+    hn[c] = (float)(0.5 * s);
+  }
+  for (int k = 0; k < 6; k++) counts[k] = 0;
+  double worst = 0.0;
+  for (int64_t v = 0; v < n; v++) {
+    const float* xv = x + v * dim;
+    double acc = 0.0;
+    for (int i = 0; i < dim; i++) acc += (double)xv[i] * (double)xv[i];
+    const double norm = sqrt(acc);
+    if (!(norm > 0.0)) continue;
+    const double inv = 1.0 / norm;
+    float nf[512], ne[512];
+    for (int i = 0; i < dim; i++) {
+      int certain = 0;
+      nf[i] = pkv_fib_norm_quotient(xv[i], inv, &certain);
+      ne[i] = (float)((double)xv[i] / norm);
+      if (!certain) counts[4]++;
+      else if (pkv_f32_bits(nf[i]) != pkv_f32_bits(ne[i])) counts[3]++;
+    }
+    for (int b = 0; b < blocks; b++) {
+      float yf[4], ye[4];
+      for (int rr = 0; rr < 4; rr++) {
+        const int r = 4 * b + rr;
+        float a = 0.0f;
+        double s = 0.0;
+        for (int j = 0; j < dim; j++) {
+          a = __builtin_fmaf(m32[(size_t)r * dim + j], ne[j], a);
+          s += rot[(size_t)r * dim + j] * (double)ne[j];
+        }
+        yf[rr] = a;
+        ye[rr] = (float)s;
+        const double e = fabs((double)a - (double)ye[rr]);
+        if (e > worst) worst = e;
+      }
+      int certain = 0;
+      const uint32_t fast = pkv_fib_block_argmin_fast(yf[0], yf[1], yf[2], yf[3], codebook, hn,
+                                                      n_codewords, &certain);
+      if (!certain) {
+        counts[1]++;
+        continue;
+      }
+      counts[2]++;
+      if ((int)fast != pkvo_nearest_codeword(ye, codebook, n_codewords, 4, order)) counts[0]++;
+    }
+  }
+  counts[5] = (int64_t)(worst * 1e9);
+  free(m32);
+}

@@ -122,6 +122,9 @@ struct pkv_fib_profile {
   double* rot_t_dev;    // [j][r]  = M[r][j], f64 (encode: lanes read consecutive rows)
   float* rot32_dev;     // [row][col] = (f32) M[row][col] (decode, fib-quant/src/rotation.rs:139)
   float* codebook_dev;  // 32 x 4 f32, rows >= N zero-filled
+  double* rot_dev;      // [r][j] f64 (exact fix-up of undecided blocks)
+  float* rot32_t_dev;   // [j][r] = (f32) M[r][j] (shortcut encoder)
+  float* half_norm_dev; // |c|^2 / 2 per codeword
   PkvWorkspace ws;
 };
 
@@ -145,6 +148,9 @@ void pkv_count_launch();
 // launchers implemented in pkv_fib.cu / pkv_turbo.cu
 int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
                           uint8_t* payload, uint64_t* err, int batch_numerics, cudaStream_t s);
+int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
+                                            uint8_t* payload, uint64_t* err, uint32_t* scratch,
+                                            cudaStream_t s);
 int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
                           float* cache, uint64_t* err, cudaStream_t s);
 int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const PkvGeom& g,

@@ -17,7 +17,9 @@
 #define PKV_FMUL(a, b) __fmul_rn((a), (b))
 #define PKV_FSUB(a, b) __fsub_rn((a), (b))
 #define PKV_FADD(a, b) __fadd_rn((a), (b))
+#define PKV_FSQRT(a) __fsqrt_rn(a)
 #else
+#define PKV_FSQRT(a) __builtin_sqrtf(a)
 #define PKV_FMUL(a, b) ((a) * (b))
 #define PKV_FSUB(a, b) ((a) - (b))
 #define PKV_FADD(a, b) ((a) + (b))
@@ -106,5 +108,96 @@ PKV_HD uint32_t pkv_fast_bucket_any(float a, float b, int polar_bits, const floa
 #define PKV_QJL_REL_BOUND (2.0f * 129.0f * 5.9604645e-8f * 1.02f / (1.0f - 129.0f * 5.9604645e-8f))
 /* Absolute floor covering products that underflow to subnormals. */
 #define PKV_QJL_ABS_BOUND 1.0e-35f
+
+/* ------------------------------------------------------------------------------------------
+ * fib-quant encoder shortcuts (fib-quant/src/codec.rs:578-729).
+ *
+ * (1) Normalised element.  The reference takes n = (f32)((f64)x / norm).  With inv = RN(1/norm)
+ * the product q = RN(x * inv) differs from the exact quotient by a relative 3.4e-16 at most, so
+ * (f32)q equals the reference unless q lies within a few units in the last place of a binary32
+ * rounding boundary.  Those boundaries are where the low 29 bits of q's significand read
+ * 0x10000000; the test leaves 32 units of slack on either side (2^-47 relative).  Results in the
+ * binary32 subnormal range round at a different bit and are left to the exact path.
+ */
+PKV_HD float pkv_fib_norm_quotient(float x, double inv, int* certain) {
+  const double q = PKV_DMUL((double)x, inv);
+  uint64_t u;
+#if defined(__CUDA_ARCH__)
+  u = (uint64_t)__double_as_longlong(q);
+#else
+  memcpy(&u, &q, 8);
+#endif
+  const uint32_t lo29 = (uint32_t)(u & 0x1fffffffull);
+  const uint32_t dist = lo29 > 0x10000000u ? lo29 - 0x10000000u : 0x10000000u - lo29;
+  const uint32_t expo = (uint32_t)((u >> 52) & 0x7ffu);
+  /* exact zero is certain; otherwise demand a normal binary32 result (exponent >= -126) */
+  *certain = (x == 0.0f) || (dist > 32u && expo >= 1023u - 126u);
+  return PKV_D2F(q);
+}
+
+/* (2) Rotated value.  y~ = sum_j M32[r][j] n_j accumulated in binary32 with fused multiply-adds
+ * (j ascending) differs from the reference's y = (f32) sum_j M[r][j] n_j (binary64) by at most
+ *   |M32 - M| |n| + gamma_64 |M32| |n| + u |y|  <=  (1 + 65 + 1) u * |M_r|_2 |n|_2,  u = 2^-24,
+ * and the rows of an orthogonal M and the normalised n have 2-norm 1 (to 1e-7):   4.0e-6. */
+#define PKV_FIB_ROT_ERR 4.0e-6f
+
+/* (3) Nearest codeword of a 4-block.  Scores F_c = |c|^2/2 - s.c (so |s - c|^2 = 2 F_c + |s|^2) are
+ * evaluated with fused multiply-adds; the codeword index rides in the 5 low significand bits of
+ * the score, so best and second-best come from three min/max operations per codeword.  With
+ * |s~ - s|_2 <= 2 PKV_FIB_ROT_ERR the reference's rounded distances satisfy
+ *   | d_c - (2 F_c + |s~|^2) | <= 4 eta sqrt(D_c) + 4 eta^2 + 4 u D_c + e_F,   eta = PKV_FIB_ROT_ERR,
+ * with D_c = |s~ - c|^2 and e_F <= 2^-16 |F_c| (index bits and FMA rounding).  If the gap between
+ * best and second best exceeds the two bounds, the reference's strict-less-than scan
+ * (gpu-backend/src/simd_nearest.rs:72-79) selects the same codeword in either summation order. */
+#if defined(__CUDA_ARCH__)
+#define PKV_FMAF(a, b, c) fmaf((a), (b), (c))
+#else
+#define PKV_FMAF(a, b, c) __builtin_fmaf((a), (b), (c))
+#endif
+
+/* Score of codeword c (c0..c3, half squared norm hn) for the block s, index in the low bits. */
+PKV_HD float pkv_fib_key(float s0, float s1, float s2, float s3, float c0, float c1, float c2,
+                         float c3, float hn, uint32_t c) {
+  float f = PKV_FMAF(-s0, c0, hn);
+  f = PKV_FMAF(-s1, c1, f);
+  f = PKV_FMAF(-s2, c2, f);
+  f = PKV_FMAF(-s3, c3, f);
+  return pkv_f32_from_bits((pkv_f32_bits(f) & ~31u) | c);
+}
+
+/* Keep the two smallest keys seen so far. */
+PKV_HD void pkv_fib_top2(float* best, float* second, float key) {
+  const float lo = key < *best ? key : *best, hi = key < *best ? *best : key;
+  *second = hi < *second ? hi : *second;
+  *best = lo;
+}
+
+/* Is the best key's codeword provably the reference's choice?  (bound in the comment above) */
+PKV_HD int pkv_fib_certify(float best, float second, float s0, float s1, float s2, float s3) {
+  const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
+                            PKV_FADD(PKV_FMUL(s2, s2), PKV_FMUL(s3, s3)));
+  const float d1 = PKV_FADD(PKV_FMUL(2.0f, best), ss), d2 = PKV_FADD(PKV_FMUL(2.0f, second), ss);
+  /* B_c = 4 eta sqrt(D_c) + 4 eta^2 + 4 u D_c + 1e-5 |F_c|; certain when d2 - d1 > B_1 + B_2 */
+  const float eta = PKV_FIB_ROT_ERR;
+  const float d2p = d2 > 0.0f ? d2 : 0.0f, d1p = d1 > 0.0f ? d1 : 0.0f;
+  const float fb = pkv_f32_from_bits(pkv_f32_bits(best) & 0x7fffffffu);
+  const float fs = pkv_f32_from_bits(pkv_f32_bits(second) & 0x7fffffffu);
+  const float roots = PKV_FADD(PKV_FSQRT(d1p), PKV_FSQRT(d2p));
+  const float bound = PKV_FADD(
+      PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
+      PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(1.0e-5f, PKV_FADD(fb, fs))));
+  return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
+}
+
+PKV_HD uint32_t pkv_fib_block_argmin_fast(float s0, float s1, float s2, float s3, const float* cb,
+                                          const float* half_norm, int n_codewords, int* certain) {
+  float best = pkv_f32_from_bits(0x7f800000u), second = best;
+  for (int c = 0; c < n_codewords; c++)
+    pkv_fib_top2(&best, &second,
+                 pkv_fib_key(s0, s1, s2, s3, cb[4 * c], cb[4 * c + 1], cb[4 * c + 2], cb[4 * c + 3],
+                             half_norm[c], (uint32_t)c));
+  *certain = pkv_fib_certify(best, second, s0, s1, s2, s3);
+  return pkv_f32_bits(best) & 31u;
+}
 
 #endif /* PKV_FAST_PATHS_H */

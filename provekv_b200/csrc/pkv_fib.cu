@@ -10,6 +10,7 @@
 // 2*dim*dim separately rounded f32 operations per vector, encode the same count
 // in f64.
 #include "pkv_common.cuh"
+#include "pkv_fast_paths.h"
 
 namespace {
 
@@ -362,6 +363,8 @@ size_t fib_encode_smem(int rec) {
          (size_t)K::TV * rec + 32;
 }
 
+#include "pkv_fib_encode_fast.cuh"
+
 template <typename F>
 int set_smem(F kernel, size_t bytes) {
   if (bytes > 48 * 1024)
@@ -377,11 +380,37 @@ int pkv_fib_tile_vectors(int dim, int encode) {
   return 0;
 }
 
+// Shortcut path: fast kernel over all vectors, then the exact fix-up of the listed entries.  The
+// list (one counter + at most one entry per vector) is scratch memory taken from the stream's
+// memory pool for the duration of the two launches.
+template <int D>
+int launch_fib_encode_fast(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
+                           uint8_t* payload, uint64_t* err, cudaStream_t s) {
+  const int64_t n = (int64_t)g.n_batches * g.vpb;
+  const int tv = FibFast<D>::TV;
+  PkvGeom gf = g;
+  gf.tiles_per_batch = (g.vpb + tv - 1) / tv;
+  const int64_t grid = (int64_t)g.n_batches * gf.tiles_per_batch;
+  uint32_t* scratch = nullptr;
+  if (cudaMallocAsync((void**)&scratch, sizeof(uint32_t) * (size_t)(n + 1), s) != cudaSuccess)
+    return PKV_ERR_CUDA;
+  int st = pkv_launch_fib_encode_fast_with_scratch(p, x, g, payload, err, scratch, s);
+  (void)grid;
+  if (cudaFreeAsync(scratch, s) != cudaSuccess && st == PKV_OK) st = PKV_ERR_CUDA;
+  return st;
+}
+
 int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
                           uint8_t* payload, uint64_t* err, int batch_numerics, cudaStream_t s) {
   const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
   if (grid == 0) return PKV_OK;
   if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  // The shortcuts are proven for the batch numerics; list entries hold 27-bit vector indices.
+  if (batch_numerics && (int64_t)g.n_batches * g.vpb <= ((int64_t)1 << 27)) {
+    if (p->cfg.dim == 64) return launch_fib_encode_fast<64>(p, x, g, payload, err, s);
+    if (p->cfg.dim == 128) return launch_fib_encode_fast<128>(p, x, g, payload, err, s);
+    return PKV_ERR_UNSUPPORTED;
+  }
   int st;
 #define PKV_FIB_ENC(DIM)                                                                          \
   {                                                                                               \
@@ -396,6 +425,36 @@ int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeo
   else return PKV_ERR_UNSUPPORTED;
 #undef PKV_FIB_ENC
   pkv_count_launch();
+  return pkv_cuda_status(cudaGetLastError());
+}
+
+// scratch: uint32 counter followed by room for one uint32 entry per vector of the launch.
+int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
+                                            uint8_t* payload, uint64_t* err, uint32_t* scratch,
+                                            cudaStream_t s) {
+  if (cudaMemsetAsync(scratch, 0, sizeof(uint32_t), s) != cudaSuccess) return PKV_ERR_CUDA;
+  int st;
+#define PKV_FIB_FAST(DIM)                                                                           \
+  {                                                                                                 \
+    PkvGeom gf = g;                                                                                 \
+    gf.tiles_per_batch = (g.vpb + FibFast<DIM>::TV - 1) / FibFast<DIM>::TV;                         \
+    const int64_t grid = (int64_t)g.n_batches * gf.tiles_per_batch;                                 \
+    if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;                                              \
+    const size_t sm = fib_encode_fast_smem<DIM>(g.rec_bytes);                                       \
+    if ((st = set_smem(fib_encode_fast_kernel<DIM>, sm)) != PKV_OK) return st;                      \
+    fib_encode_fast_kernel<DIM><<<(unsigned)grid, kThreads, sm, s>>>(                               \
+        gf, x, p->rot32_t_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->idx_bits, \
+        p->norm_len, payload, err, scratch, scratch + 1);                                           \
+    pkv_count_launch();                                                                             \
+    fib_encode_fix_kernel<DIM><<<296, kThreads, 0, s>>>(                                            \
+        gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,         \
+        p->cfg.argmin_order, payload, scratch, scratch + 1);                                        \
+    pkv_count_launch();                                                                             \
+  }
+  if (p->cfg.dim == 64) PKV_FIB_FAST(64)
+  else if (p->cfg.dim == 128) PKV_FIB_FAST(128)
+  else return PKV_ERR_UNSUPPORTED;
+#undef PKV_FIB_FAST
   return pkv_cuda_status(cudaGetLastError());
 }
 

@@ -1,0 +1,318 @@
+// fib-quant encode, two kernels (included by pkv_fib.cu inside its unnamed namespace).
+//
+// fib_encode_fast_kernel: every vector through certified shortcuts (pkv_fast_paths.h): exact f64
+// norm, certified normalisation, binary32 fused rotation as a register-tiled product with the
+// f32 copy of the matrix, certified nearest-codeword per 4-block, 5-bit packing.  Blocks (or whole
+// vectors) whose decision could not be certified are appended to a list in global scratch memory.
+// fib_encode_fix_kernel: one warp per list entry redoes the entry with the reference's exact
+// operation sequence (fib-quant/src/codec.rs:594-729, rotation.rs:104-115,
+// gpu-backend/src/simd_nearest.rs:24-94) and patches the record.
+// Together they emit the same bytes as fib_encode_kernel; the exact f64 work shrinks from
+// 2*dim*dim operations per vector to a few per mille of the blocks.
+#pragma once
+
+// list entry: (global vector index << 5) | block, block 31 = every block of the vector
+#define PKV_FIB_ENTRY_ALL 31u
+
+template <int D>
+struct FibFast {
+  static constexpr int B = D / 4;
+  static constexpr int RG = D / 8;            // threads along the rows (8 rows = 2 blocks each)
+  static constexpr int VG = kThreads / RG;    // threads along the vectors (8 vectors each)
+  static constexpr int TV = VG * 8;           // 128 vectors (D = 64), 64 (D = 128)
+  static constexpr int XS = D + 4;            // row stride of the staged input tile
+  static constexpr size_t tile_floats = (size_t)TV * XS > (size_t)D * TV ? (size_t)TV * XS : (size_t)D * TV;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot32_t,
+                       const float* __restrict__ codebook, const float* __restrict__ half_norm,
+                       int n_codewords, int idx_bits, int norm_len, uint8_t* __restrict__ payload,
+                       uint64_t* err, uint32_t* flag_count, uint32_t* flag_list) {
+  using K = FibFast<D>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* s_m = reinterpret_cast<float*>(smem);                     // [j][r] = (f32) M[r][j]
+  float* s_t = s_m + D * D;                                        // input tile [TV][XS], then n~ [j][TV]
+  float4* s_cb = reinterpret_cast<float4*>(s_t + K::tile_floats);  // [32]
+  float* s_hn = reinterpret_cast<float*>(s_cb + 32);               // [32]
+  double* s_norm = reinterpret_cast<double*>(s_hn + 32);           // [TV]
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_norm + K::TV);     // [TV]
+  uint32_t* s_flag = reinterpret_cast<uint32_t*>(s_off + K::TV);   // [TV] undecided-block masks
+  uint8_t* s_bad = reinterpret_cast<uint8_t*>(s_flag + K::TV);     // [TV]
+  uint8_t* s_idx = s_bad + K::TV;                                  // [TV][B]
+  uint8_t* s_rec = s_idx + K::TV * K::B;                           // [TV][rec], 16-aligned below
+  s_rec += (16 - (reinterpret_cast<uintptr_t>(s_rec) & 15)) & 15;
+
+  const int tile = blockIdx.x % g.tiles_per_batch;
+  const int batch = blockIdx.x / g.tiles_per_batch;
+  const int v0 = tile * K::TV;
+  const int nv = min(K::TV, g.vpb - v0);
+  const int rec = g.rec_bytes;
+  const int tid = threadIdx.x;
+
+  for (int v = tid; v < K::TV; v += kThreads) {
+    s_off[v] = v < nv ? pkv_vec_offset(g.L, batch, v0 + v) : 0;
+    s_flag[v] = 0;
+  }
+  for (int i = tid; i < D * D / 4; i += kThreads)
+    pkv_cp_async16(reinterpret_cast<float4*>(s_m) + i, reinterpret_cast<const float4*>(rot32_t) + i);
+  if (tid < 32) {
+    s_cb[tid] = __ldg(reinterpret_cast<const float4*>(codebook) + tid);
+    s_hn[tid] = __ldg(half_norm + tid);
+  }
+  __syncthreads();
+  for (int i = tid; i < nv * (D / 4); i += kThreads) {
+    const int v = i / (D / 4), q = i % (D / 4);
+    pkv_cp_async16(s_t + v * K::XS + 4 * q, reinterpret_cast<const float4*>(x + s_off[v]) + q);
+  }
+  pkv_cp_async_wait_all();
+  __syncthreads();
+
+  // (A) one thread per vector: exact norm (codec.rs:1049-1057; the square of a binary32 value is
+  // exact in binary64, so the fused form rounds exactly like the reference's multiply-then-add),
+  // then the certified normalised vector written transposed, n~[j][v], over the input tile.
+  for (int vb = 0; vb < K::TV; vb += kThreads) {
+    const int v = vb + tid;
+    float xr[D];
+    if (v < K::TV) {
+      const float* row = s_t + v * K::XS;
+#pragma unroll
+      for (int i = 0; i < D; i += 4) {
+        const float4 t = v < nv ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        xr[i] = t.x; xr[i + 1] = t.y; xr[i + 2] = t.z; xr[i + 3] = t.w;
+      }
+    }
+    __syncthreads();  // every row is in registers: the tile may now be overwritten
+    if (v < K::TV) {
+      bool finite = true;
+      double acc = 0.0;
+#pragma unroll
+      for (int i = 0; i < D; i++) {
+        finite = finite && pkv_finite(xr[i]);
+        const double t = (double)xr[i];
+        acc = fma(t, t, acc);
+      }
+      double norm = __dsqrt_rn(acc);
+      int bad = 0;
+      if (v < nv) {
+        if (!finite) bad = PKV_VEC_NONFINITE_INPUT;
+        else if (norm == 0.0) bad = PKV_VEC_ZERO_NORM;
+        if (bad) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, bad);
+      }
+      const bool skip = bad || v >= nv;
+      if (skip) norm = 1.0;
+      s_norm[v] = norm;
+      s_bad[v] = (uint8_t)skip;
+      const double inv = __ddiv_rn(1.0, norm);
+      int all_certain = 1;
+#pragma unroll
+      for (int i = 0; i < D; i++) {
+        int certain;
+        const float q = pkv_fib_norm_quotient(xr[i], inv, &certain);
+        all_certain &= certain;
+        s_t[i * K::TV + v] = skip ? 0.0f : q;
+      }
+      if (!all_certain && !skip) s_flag[v] = 1u << 31;  // redo the whole vector exactly
+    }
+  }
+  __syncthreads();
+
+  // (B) y~ = M32 n~ as a register-tiled product: thread (rg, vg) owns rows 8rg..8rg+7 (two
+  // 4-blocks) of vectors 8vg..8vg+7 and accumulates over j with fused multiply-adds.
+  const int rg = tid % K::RG, vg = tid / K::RG;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int r = 0; r < 8; r++) acc[i][r] = 0.0f;
+#pragma unroll 2
+  for (int j = 0; j < D; j++) {
+    const float4 m0 = *reinterpret_cast<const float4*>(s_m + j * D + 8 * rg);
+    const float4 m1 = *reinterpret_cast<const float4*>(s_m + j * D + 8 * rg + 4);
+    const float4 n0 = *reinterpret_cast<const float4*>(s_t + j * K::TV + 8 * vg);
+    const float4 n1 = *reinterpret_cast<const float4*>(s_t + j * K::TV + 8 * vg + 4);
+    const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    const float nn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+      for (int r = 0; r < 8; r++) acc[i][r] = fmaf(mm[r], nn[i], acc[i][r]);
+  }
+
+  // (C) certified nearest codeword of the 16 (vector, block) pairs this thread holds
+  {
+    float best[16], second[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) best[k] = second[k] = __int_as_float(0x7f800000);
+#pragma unroll 2
+    for (int c = 0; c < n_codewords; c++) {
+      const float4 w = s_cb[c];
+      const float hn = s_hn[c];
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+          pkv_fib_top2(&best[2 * i + h], &second[2 * i + h],
+                       pkv_fib_key(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3],
+                                   w.x, w.y, w.z, w.w, hn, (uint32_t)c));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const int v = 8 * vg + i, b = 2 * rg + h;
+        s_idx[v * K::B + b] = (uint8_t)(__float_as_uint(best[2 * i + h]) & 31u);
+        if (!pkv_fib_certify(best[2 * i + h], second[2 * i + h], acc[i][4 * h], acc[i][4 * h + 1],
+                             acc[i][4 * h + 2], acc[i][4 * h + 3]))
+          atomicOr(&s_flag[v], 1u << b);
+      }
+  }
+  __syncthreads();
+
+  // (D) encode_norm (:994-1020) + pack_indices (bitpack.rs:4-44); undecided work goes to the list
+  for (int v = tid; v < nv; v += kThreads) {
+    uint8_t* r = s_rec + v * rec;
+    for (int i = 0; i < rec; i++) r[i] = 0;
+    if (s_bad[v]) continue;
+    const float nf = __double2float_rn(s_norm[v]);
+    bool ok;
+    if (norm_len == 2) {
+      const uint32_t h = pkv_f32_to_f16_bits(nf);
+      ok = (h & 0x7fffu) < 0x7c00u && (h & 0x7fffu) != 0;
+      r[0] = (uint8_t)(h & 0xff);
+      r[1] = (uint8_t)(h >> 8);
+    } else {
+      const uint32_t u = __float_as_uint(nf);
+      ok = pkv_finite(nf) && nf > 0.0f;
+      r[0] = (uint8_t)u; r[1] = (uint8_t)(u >> 8); r[2] = (uint8_t)(u >> 16); r[3] = (uint8_t)(u >> 24);
+    }
+    if (!ok) {
+      pkv_report(err, 1, (int64_t)batch * g.vpb + v0 + v, PKV_VEC_NORM_RANGE);
+      for (int i = 0; i < norm_len; i++) r[i] = 0;
+      continue;
+    }
+    for (int b = 0; b < K::B; b++) {
+      const int pos = b * idx_bits;
+      const uint32_t val = (uint32_t)s_idx[v * K::B + b] << (pos & 7);
+      r[norm_len + (pos >> 3)] |= (uint8_t)val;
+      if (val >> 8) r[norm_len + (pos >> 3) + 1] |= (uint8_t)(val >> 8);
+    }
+    const uint32_t fl = s_flag[v];
+    if (fl) {
+      const uint32_t blocks = fl & 0x7fffffffu;
+      const uint32_t which = ((fl >> 31) || (blocks & (blocks - 1))) ? PKV_FIB_ENTRY_ALL
+                                                                      : (uint32_t)(__ffs(blocks) - 1);
+      const uint32_t gvec = (uint32_t)((int64_t)batch * g.vpb + v0 + v);
+      flag_list[atomicAdd(flag_count, 1u)] = (gvec << 5) | which;
+    }
+  }
+  __syncthreads();
+  stage_out(payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * rec, s_rec, nv * rec);
+}
+
+template <int D>
+size_t fib_encode_fast_smem(int rec) {
+  using K = FibFast<D>;
+  return sizeof(float) * D * D + sizeof(float) * K::tile_floats + sizeof(float4) * 32 + sizeof(float) * 32 +
+         sizeof(double) * K::TV + sizeof(int64_t) * K::TV + sizeof(uint32_t) * K::TV + K::TV +
+         K::TV * K::B + (size_t)K::TV * rec + 32;
+}
+
+// One warp per list entry: the reference's exact sequence for one block (4 rows) or for the whole
+// vector, batch numerics (normalised vector rounded to binary32, codec.rs:607-609).
+// rot is the f64 matrix row-major, M[r][j].
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __restrict__ rot,
+                      const float* __restrict__ codebook, int n_codewords, int idx_bits, int norm_len,
+                      int argmin_order, uint8_t* __restrict__ payload, const uint32_t* flag_count,
+                      const uint32_t* flag_list) {
+  constexpr int E = D / 32;   // elements of the vector per lane
+  constexpr int RPL = D / 32; // rows per lane when the whole vector is redone
+  constexpr int B = D / 4;
+  const int lane = threadIdx.x & 31;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
+  const float4* cb4 = reinterpret_cast<const float4*>(codebook);
+  const uint32_t count = *flag_count;
+  for (uint32_t e = gw; e < count; e += nw) {
+    const uint32_t ent = flag_list[e], blk = ent & 31u, gvec = ent >> 5;
+    const int batch = (int)(gvec / (uint32_t)g.vpb), v = (int)(gvec % (uint32_t)g.vpb);
+    const float* xv = x + pkv_vec_offset(g.L, batch, v);
+    float xe[E];
+#pragma unroll
+    for (int k = 0; k < E; k++) xe[k] = xv[lane * E + k];
+    // l2_norm: sequential over j (codec.rs:1049-1057)
+    double acc = 0.0;
+    for (int j = 0; j < D; j++) {
+      float xj = 0.0f;
+#pragma unroll
+      for (int k = 0; k < E; k++) {
+        const float t = __shfl_sync(0xffffffffu, xe[k], j / E);
+        if (k == j % E) xj = t;
+      }
+      const double t = (double)xj;
+      acc = __dadd_rn(acc, __dmul_rn(t, t));
+    }
+    const double norm = __dsqrt_rn(acc);
+    double nd[E];
+#pragma unroll
+    for (int k = 0; k < E; k++) nd[k] = (double)__double2float_rn(__ddiv_rn((double)xe[k], norm));
+    // StoredRotation::apply (rotation.rs:104-115): each active lane one row at a time, j ascending
+    const bool whole = blk == PKV_FIB_ENTRY_ALL;
+    float yv[RPL];
+#pragma unroll
+    for (int rr = 0; rr < RPL; rr++) {
+      const int r = whole ? lane + 32 * rr : (int)(4 * blk) + (lane & 3);
+      const double* mrow = rot + (size_t)r * D;
+      double s = 0.0;
+      if (whole || rr == 0) {
+        for (int j = 0; j < D; j++) {
+          double nj = 0.0;
+#pragma unroll
+          for (int k = 0; k < E; k++) {
+            const double t = __shfl_sync(0xffffffffu, nd[k], j / E);
+            if (k == j % E) nj = t;
+          }
+          s = __dadd_rn(s, __dmul_rn(__ldg(mrow + j), nj));
+        }
+      }
+      yv[rr] = __double2float_rn(s);
+    }
+    // nearest codeword per block, reference order; lanes with lane % 4 == 0 own a block
+    uint32_t idx[RPL];
+#pragma unroll
+    for (int rr = 0; rr < RPL; rr++) {
+      const float s1 = __shfl_down_sync(0xffffffffu, yv[rr], 1);
+      const float s2 = __shfl_down_sync(0xffffffffu, yv[rr], 2);
+      const float s3 = __shfl_down_sync(0xffffffffu, yv[rr], 3);
+      idx[rr] = (uint32_t)nearest_codeword(cb4, n_codewords, argmin_order, yv[rr], s1, s2, s3);
+    }
+    uint8_t* rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v * g.rec_bytes + norm_len;
+    if (whole) {
+      // block b sits in lane 4 * (b % 8), slot b / 8; lane 0 rebuilds the whole index stream
+      uint8_t bytes[(B * 5 + 7) / 8 + 1];
+      for (int i = 0; i < (B * idx_bits + 7) / 8; i++) bytes[i] = 0;
+      for (int b = 0; b < B; b++) {
+        uint32_t val = 0;
+#pragma unroll
+        for (int rr = 0; rr < RPL; rr++) {
+          const uint32_t t = __shfl_sync(0xffffffffu, idx[rr], 4 * (b % 8));
+          if (rr == b / 8) val = t;
+        }
+        const int pos = b * idx_bits;
+        val <<= (pos & 7);
+        bytes[pos >> 3] |= (uint8_t)val;
+        if (val >> 8) bytes[(pos >> 3) + 1] |= (uint8_t)(val >> 8);
+      }
+      if (lane == 0)
+        for (int i = 0; i < (B * idx_bits + 7) / 8; i++) rec[i] = bytes[i];
+    } else if (lane == 0) {
+      const int pos = (int)blk * idx_bits;
+      const uint32_t m = ((1u << idx_bits) - 1u) << (pos & 7), val = idx[0] << (pos & 7);
+      rec[pos >> 3] = (uint8_t)((rec[pos >> 3] & ~m) | val);
+      if (m >> 8) rec[(pos >> 3) + 1] = (uint8_t)((rec[(pos >> 3) + 1] & ~(m >> 8)) | (val >> 8));
+    }
+    __syncwarp();
+  }
+}

@@ -241,6 +241,9 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
   p->rot_t_dev = nullptr;
   p->rot32_dev = nullptr;
   p->codebook_dev = nullptr;
+  p->rot_dev = nullptr;
+  p->rot32_t_dev = nullptr;
+  p->half_norm_dev = nullptr;
   const int d = cfg->dim;
   cudaError_t e = cudaGetDevice(&p->device);
   double* rt = new double[d * d];
@@ -259,6 +262,21 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
   if (e == cudaSuccess) e = cudaMemcpy(p->rot_t_dev, rt, sizeof(double) * d * d, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->rot32_dev, r32, sizeof(float) * d * d, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->codebook_dev, cb, sizeof(cb), cudaMemcpyHostToDevice);
+  // tables of the shortcut encoder: f64 matrix row-major, f32 matrix transposed, |c|^2 / 2
+  float hn[32];
+  for (int c = 0; c < 32; c++) {
+    double s = 0.0;
+    for (int j = 0; j < 4; j++) s += (double)cb[4 * c + j] * (double)cb[4 * c + j];
+    hn[c] = (float)(0.5 * s);
+  }
+  for (int r = 0; r < d; r++)
+    for (int j = 0; j < d; j++) r32[j * d + r] = (float)rotation[r * d + j];
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot_dev, sizeof(double) * d * d);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot32_t_dev, sizeof(float) * d * d);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->half_norm_dev, sizeof(hn));
+  if (e == cudaSuccess) e = cudaMemcpy(p->rot_dev, rotation, sizeof(double) * d * d, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->rot32_t_dev, r32, sizeof(float) * d * d, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->half_norm_dev, hn, sizeof(hn), cudaMemcpyHostToDevice);
   delete[] rt;
   delete[] r32;
   if (e != cudaSuccess) {
@@ -274,6 +292,9 @@ int pkv_fib_profile_destroy(pkv_fib_profile* p) {
   if (p->rot_t_dev) cudaFree(p->rot_t_dev);
   if (p->rot32_dev) cudaFree(p->rot32_dev);
   if (p->codebook_dev) cudaFree(p->codebook_dev);
+  if (p->rot_dev) cudaFree(p->rot_dev);
+  if (p->rot32_t_dev) cudaFree(p->rot32_t_dev);
+  if (p->half_norm_dev) cudaFree(p->half_norm_dev);
   ws_release(&p->ws);
   delete p;
   return PKV_OK;
