@@ -167,9 +167,15 @@ PKV_HD float pkv_fib_key(float s0, float s1, float s2, float s3, float c0, float
 
 /* Keep the two smallest keys seen so far. */
 PKV_HD void pkv_fib_top2(float* best, float* second, float key) {
+#if defined(__CUDA_ARCH__)
+  const float hi = fmaxf(*best, key);  // three min/max instructions, no predicates
+  *best = fminf(*best, key);
+  *second = fminf(*second, hi);
+#else
   const float lo = key < *best ? key : *best, hi = key < *best ? *best : key;
   *second = hi < *second ? hi : *second;
   *best = lo;
+#endif
 }
 
 /* Is the best key's codeword provably the reference's choice?  (bound in the comment above) */

@@ -446,7 +446,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
         gf, x, p->rot32_t_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->idx_bits, \
         p->norm_len, payload, err, scratch, scratch + 1);                                           \
     pkv_count_launch();                                                                             \
-    fib_encode_fix_kernel<DIM><<<296, kThreads, 0, s>>>(                                            \
+    fib_encode_fix_kernel<DIM><<<148 * 8, kThreads, 0, s>>>(                                            \
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,         \
         p->cfg.argmin_order, payload, scratch, scratch + 1);                                        \
     pkv_count_launch();                                                                             \

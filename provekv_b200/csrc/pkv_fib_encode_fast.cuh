@@ -228,10 +228,12 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
                       const float* __restrict__ codebook, int n_codewords, int idx_bits, int norm_len,
                       int argmin_order, uint8_t* __restrict__ payload, const uint32_t* flag_count,
                       const uint32_t* flag_list) {
-  constexpr int E = D / 32;   // elements of the vector per lane
+  constexpr int E = D / 32;   // elements of the vector each lane loads
   constexpr int RPL = D / 32; // rows per lane when the whole vector is redone
   constexpr int B = D / 4;
-  const int lane = threadIdx.x & 31;
+  __shared__ float s_x[kThreads / 32][D];
+  __shared__ double s_n[kThreads / 32][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
   const float4* cb4 = reinterpret_cast<const float4*>(codebook);
   const uint32_t count = *flag_count;
@@ -239,25 +241,25 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
     const uint32_t ent = flag_list[e], blk = ent & 31u, gvec = ent >> 5;
     const int batch = (int)(gvec / (uint32_t)g.vpb), v = (int)(gvec % (uint32_t)g.vpb);
     const float* xv = x + pkv_vec_offset(g.L, batch, v);
-    float xe[E];
+    // the vector, then its normalised form, are shared through a per-warp slice of shared memory
+    float* sx = s_x[warp];
+    double* sn = s_n[warp];
+    __syncwarp();
 #pragma unroll
-    for (int k = 0; k < E; k++) xe[k] = xv[lane * E + k];
-    // l2_norm: sequential over j (codec.rs:1049-1057)
+    for (int k = 0; k < E; k++) sx[lane * E + k] = xv[lane * E + k];
+    __syncwarp();
+    // l2_norm: sequential over j (codec.rs:1049-1057); every lane runs the same chain
     double acc = 0.0;
+#pragma unroll 8
     for (int j = 0; j < D; j++) {
-      float xj = 0.0f;
-#pragma unroll
-      for (int k = 0; k < E; k++) {
-        const float t = __shfl_sync(0xffffffffu, xe[k], j / E);
-        if (k == j % E) xj = t;
-      }
-      const double t = (double)xj;
+      const double t = (double)sx[j];
       acc = __dadd_rn(acc, __dmul_rn(t, t));
     }
     const double norm = __dsqrt_rn(acc);
-    double nd[E];
 #pragma unroll
-    for (int k = 0; k < E; k++) nd[k] = (double)__double2float_rn(__ddiv_rn((double)xe[k], norm));
+    for (int k = 0; k < E; k++)
+      sn[lane * E + k] = (double)__double2float_rn(__ddiv_rn((double)sx[lane * E + k], norm));
+    __syncwarp();
     // StoredRotation::apply (rotation.rs:104-115): each active lane one row at a time, j ascending
     const bool whole = blk == PKV_FIB_ENTRY_ALL;
     float yv[RPL];
@@ -267,15 +269,8 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
       const double* mrow = rot + (size_t)r * D;
       double s = 0.0;
       if (whole || rr == 0) {
-        for (int j = 0; j < D; j++) {
-          double nj = 0.0;
-#pragma unroll
-          for (int k = 0; k < E; k++) {
-            const double t = __shfl_sync(0xffffffffu, nd[k], j / E);
-            if (k == j % E) nj = t;
-          }
-          s = __dadd_rn(s, __dmul_rn(__ldg(mrow + j), nj));
-        }
+#pragma unroll 8
+        for (int j = 0; j < D; j++) s = __dadd_rn(s, __dmul_rn(__ldg(mrow + j), sn[j]));
       }
       yv[rr] = __double2float_rn(s);
     }
