@@ -44,6 +44,7 @@ enum {
   PKV_ERR_EMPTY_BATCH = 4,      /* fib-quant/src/codec.rs:226, turbo-quant/src/wire.rs:303 */
   PKV_ERR_CORRUPT_HEADER = 5,   /* magic / version / profile mismatch / length */
   PKV_ERR_BUFFER_TOO_SMALL = 6,
+  PKV_ERR_STATIC_SCRATCH_TOO_SMALL = 7, /* more vectors than pkv_fib_encode_dev_static can take */
   /* Per-vector codes, reported together with the index of the first failing
    * vector.  Within one vector the smaller code is the check the reference
    * performs first. */
@@ -157,6 +158,20 @@ int32_t pkv_fib_record_bytes(const pkv_fib_profile* p);
 int pkv_fib_encode_dev(const pkv_fib_profile* p, const float* x_dev, const pkv_layout* layout,
                        uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
                        void* stream);
+/* No counterpart in the reference.  Same work and same bytes as pkv_fib_encode_dev for callers
+ * that must not allocate device memory while encoding (memory fully budgeted at start-up, or an
+ * allocator that may not be re-entered): pkv_fib_encode_dev borrows a list of undecided blocks
+ * from the stream's memory pool, this call keeps it in a fixed array inside the library image
+ * and calls no allocating routine.  Limits: at most PKV_FIB_STATIC_MAX_VECTORS vectors per call
+ * (PKV_ERR_STATIC_SCRATCH_TOO_SMALL beyond), batches of at least 4 vectors (PKV_ERR_UNSUPPORTED
+ * below, unless the profile forces batch numerics).  The array (4 MiB on every GPU that loads the
+ * library) is shared by all calls on a device: calls that can overlap on the GPU race.  The first
+ * call on each device looks the array's address up; make that call before any stream capture. */
+#define PKV_FIB_STATIC_MAX_VECTORS (1 << 20)
+int pkv_fib_encode_dev_static(const pkv_fib_profile* p, const float* x_dev, const pkv_layout* layout,
+                              uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
+                              void* stream);
+
 /* Replaces FibQuantizer::decode_batch_fast (fib-quant/src/codec.rs:797-844) fused
  * with the per-head relayout of proveKV/src/pool.rs:538-558 and the cache write of
  * proveKV/scripts/ppl_validate_multi_agent.py:226-271. */

@@ -21,6 +21,7 @@ ERR_UNSUPPORTED = 3
 ERR_EMPTY_BATCH = 4
 ERR_CORRUPT_HEADER = 5
 ERR_BUFFER_TOO_SMALL = 6
+ERR_STATIC_SCRATCH_TOO_SMALL = 7
 VEC_NONFINITE_INPUT = 16
 VEC_ZERO_NORM = 17
 VEC_BAD_RADIUS = 18
@@ -124,6 +125,7 @@ _SIGS = {
     "pkv_fib_record_bytes": (C.c_int32, [_V]),
     "pkv_fib_encode_dev": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_decode_patch_dev": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, _V]),
+    "pkv_fib_encode_dev_static": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_encode_batch_compact": (C.c_int, [_V, _V, C.c_int64, _V, C.c_int64, C.POINTER(C.c_int64),
                                                C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_fib_decode_batch_compact": (C.c_int, [_V, _V, C.c_int64, _V, C.c_int64, C.POINTER(C.c_int64),

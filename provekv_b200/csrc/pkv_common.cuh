@@ -142,6 +142,8 @@ struct pkv_turbo_profile {
 };
 
 int pkv_cuda_status(cudaError_t e);
+int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
+                  bool encode, PkvGeom* g);
 int pkv_ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes);
 void pkv_count_launch();
 

@@ -9,6 +9,8 @@
 // The dense rotation makes them ALU-bound, not HBM-bound: decode needs
 // 2*dim*dim separately rounded f32 operations per vector, encode the same count
 // in f64.
+#include <mutex>
+
 #include "pkv_common.cuh"
 #include "pkv_fast_paths.h"
 
@@ -478,4 +480,60 @@ int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, cons
 #undef PKV_FIB_DEC
   pkv_count_launch();
   return pkv_cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// fib encode without any allocation
+// ---------------------------------------------------------------------------
+// Some embedders may not allocate device memory on the call path at all: a serving process
+// whose memory is fully budgeted up front (every byte of HBM handed to the KV cache and the
+// weights at start-up), a caller running under an allocator it must not re-enter, or code that
+// has already frozen its memory layout.  pkv_fib_encode_dev takes the undecided-block list of the
+// shortcut encoder from the stream's memory pool; the entry point below uses a fixed array that
+// is part of the loaded library image instead, so it calls no allocating routine whatsoever.
+//
+// The array holds one counter and one entry per vector, which bounds a call to
+// PKV_FIB_STATIC_MAX_VECTORS vectors.  Every GPU that loads the library carries these 4 MiB until
+// the process exits.  All calls on a device share the array and it keeps the previous call's
+// contents: the counter is zeroed at the start of each call, and two calls whose kernels overlap
+// on the GPU (different streams, no ordering) would corrupt each other's list.
+static __device__ __align__(256) uint32_t g_fib_static_scratch[PKV_FIB_STATIC_MAX_VECTORS + 64];
+
+namespace {
+std::mutex g_static_mutex;
+uint32_t* g_static_scratch_ptr[64] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int pkv_fib_encode_dev_static(const pkv_fib_profile* p, const float* x_dev,
+                                         const pkv_layout* layout, uint8_t* payload_dev,
+                                         int64_t payload_batch_stride, uint64_t* err_dev,
+                                         void* stream) {
+  if (!p || !x_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)x_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = pkv_make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 1),
+                         true, &g);
+  if (st != PKV_OK) return st;
+  if (g.vpb == 0) return PKV_ERR_EMPTY_BATCH;
+  // the shortcut encoder implements the batch numerics only (fib-quant/src/codec.rs:586-589)
+  const bool batch_numerics = p->cfg.numerics == PKV_FIB_NUMERICS_BATCH ||
+                              (p->cfg.numerics == PKV_FIB_NUMERICS_AUTO && g.vpb >= 4);
+  if (!batch_numerics) return PKV_ERR_UNSUPPORTED;
+  if ((int64_t)g.n_batches * g.vpb > PKV_FIB_STATIC_MAX_VECTORS) return PKV_ERR_STATIC_SCRATCH_TOO_SMALL;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PKV_ERR_CUDA;
+  uint32_t* scratch;
+  {
+    // Set-up, once per device: in host code the array's name is only a handle, the address a
+    // kernel can use comes from cudaGetSymbolAddress with that device current.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+      void* addr = nullptr;
+      if (cudaGetSymbolAddress(&addr, g_fib_static_scratch) != cudaSuccess || !addr) return PKV_ERR_CUDA;
+      g_static_scratch_ptr[dev] = static_cast<uint32_t*>(addr);
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  return pkv_launch_fib_encode_fast_with_scratch(p, x_dev, g, payload_dev, err_dev, scratch,
+                                                 (cudaStream_t)stream);
 }

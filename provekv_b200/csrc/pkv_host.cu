@@ -155,6 +155,10 @@ int fib_index_bits(int n) {  // fib-quant/src/profile.rs:268-274
 }  // namespace
 
 int pkv_cuda_status(cudaError_t e) { return e == cudaSuccess ? PKV_OK : PKV_ERR_CUDA; }
+int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
+                  bool encode, PkvGeom* g) {
+  return make_geom(L, rec_bytes, payload_batch_stride, tile, encode, g);
+}
 void pkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 extern "C" {
@@ -171,6 +175,8 @@ const char* pkv_status_string(int s) {
     case PKV_ERR_EMPTY_BATCH: return "empty batch";
     case PKV_ERR_CORRUPT_HEADER: return "corrupt or mismatching wire header";
     case PKV_ERR_BUFFER_TOO_SMALL: return "output buffer too small";
+    case PKV_ERR_STATIC_SCRATCH_TOO_SMALL:
+      return "too many vectors for the fixed scratch array of pkv_fib_encode_dev_static";
     case PKV_VEC_NONFINITE_INPUT: return "non-finite input value";
     case PKV_VEC_ZERO_NORM: return "zero-norm vector";
     case PKV_VEC_BAD_RADIUS: return "radius is not finite and non-negative";

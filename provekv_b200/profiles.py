@@ -99,6 +99,16 @@ class FibProfile(_ProfileBase):
         L.check(L.lib().pkv_fib_encode_dev(self.handle, x_ptr, C.byref(layout), payload_ptr,
                                            payload_batch_stride, err_ptr, stream))
 
+    def encode_dev_static(self, x_ptr: int, layout: L.Layout, payload_ptr: int,
+                          payload_batch_stride: int, err_ptr: int, stream: int = 0) -> None:
+        """encode_dev for callers that must not allocate device memory while encoding (HBM fully
+        budgeted at start-up, allocator that may not be re-entered): the undecided-block list
+        lives in a fixed 4 MiB array inside the library instead of the stream's memory pool.
+        At most 2**20 vectors per call, batches of >= 4 vectors; calls on one device share the
+        array, so do not let two of them overlap on the GPU."""
+        L.check(L.lib().pkv_fib_encode_dev_static(self.handle, x_ptr, C.byref(layout), payload_ptr,
+                                                  payload_batch_stride, err_ptr, stream))
+
     def decode_patch_dev(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
                          cache_ptr: int, err_ptr: int, stream: int = 0) -> None:
         L.check(L.lib().pkv_fib_decode_patch_dev(self.handle, payload_ptr, payload_batch_stride,

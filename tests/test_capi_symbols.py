@@ -38,7 +38,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 def test_status_strings_and_argument_checks_need_no_gpu():
     lib = L.lib()
     assert L.status_string(L.OK) == "ok"
-    for code in list(range(0, 7)) + list(range(16, 26)):
+    for code in list(range(0, 8)) + list(range(16, 26)):
         assert L.status_string(code) != "unknown status"
     assert L.status_string(99) == "unknown status"
     n = C.c_uint32(0)
