@@ -11,8 +11,9 @@ template <int D>
 struct TurboDecSmem {  // per-warp slices follow the CTA-wide tables
   using K = Turbo<D>;
   static __host__ __device__ size_t warp_bytes(int rec_words) {
-    const size_t n = sizeof(float) * K::TV * K::XS + sizeof(int64_t) * K::TV +
-                     sizeof(uint32_t) * rec_words * K::WS;
+    // the f32 output tile reuses the record tile's space (records are in registers by then)
+    const size_t tile = sizeof(float) * K::TV * K::XS, recs = sizeof(uint32_t) * rec_words * K::WS;
+    const size_t n = (tile > recs ? tile : recs) + sizeof(int64_t) * K::TV;
     return (n + 15) & ~(size_t)15;  // the next warp's f32 tile stays 16-byte aligned
   }
   static __host__ __device__ size_t table_bytes(int levels) { return sizeof(float) * (256 + 2 * levels); }
@@ -30,9 +31,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   float* s_q255 = reinterpret_cast<float*>(smem);  // [256]
   float* s_lut = s_q255 + 256;                     // cos[L], sin[L]
   uint8_t* wbase = smem + TurboDecSmem<D>::table_bytes(levels) + warp * TurboDecSmem<D>::warp_bytes(tp.rec_words);
-  float* s_x = reinterpret_cast<float*>(wbase);                       // [TV][XS]
-  int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);   // [TV]
+  int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                 // [TV]
   uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);         // [rec_words][WS]
+  float* s_x = reinterpret_cast<float*>(s_w);                         // [TV][XS], after the records are consumed
 
   const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
   const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
@@ -53,10 +54,10 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   pkv_cp_async_wait_all();
   __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
 
+  float y[D];
   if (v < nv) {
     const uint32_t* w = s_w + v;
     int code = 0;
-    float y[D];
     // radii -> y[2i] (temporarily)
     if (!tp.lossy) {
       uint32_t bad = 0;
@@ -132,6 +133,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
     // FastHadamardRotation::apply_inverse, rotation.rs:212-221
     fwht_regs<D>(y, tp.scale);
     apply_signs<D>(y, tp.sign_mask);
+  }
+  __syncwarp();  // every lane has consumed its record: the tile may now hold the f32 rows
+  if (v < nv) {
     float* row = s_x + v * K::XS;
 #pragma unroll
     for (int i = 0; i < D; i += 4)
