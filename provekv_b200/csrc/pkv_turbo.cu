@@ -47,10 +47,15 @@ template <int D, int PB>
 int launch_encode(const TurboParams& tp, const float* x, const PkvGeom& g, uint8_t* payload,
                   uint64_t* err, unsigned grid, cudaStream_t s) {
   const size_t sm = turbo_encode_smem<D>(tp);
-  int st = set_smem(turbo_encode_kernel<D, PB>, sm);
-  if (st != PKV_OK) return st;
   const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;  // one warp per 32-vector tile
-  turbo_encode_kernel<D, PB><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+  int st;
+  if (turbo_encode_direct(tp)) {
+    if ((st = set_smem(turbo_encode_kernel<D, PB, true>, sm)) != PKV_OK) return st;
+    turbo_encode_kernel<D, PB, true><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+  } else {
+    if ((st = set_smem(turbo_encode_kernel<D, PB, false>, sm)) != PKV_OK) return st;
+    turbo_encode_kernel<D, PB, false><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+  }
   return PKV_OK;
 }
 

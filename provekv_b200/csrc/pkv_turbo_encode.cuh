@@ -119,8 +119,13 @@ struct TurboEncSmem {
   }
 };
 
-template <int D, int PB>
-__global__ void __launch_bounds__(Turbo<D>::THREADS)
+// DIRECT (f32 radii, record a multiple of 16 bytes, angle + sign words a multiple of 4): the
+// record never passes through shared memory.  Radii stay in the registers of their pairs and are
+// stored by their thread as 16-byte pieces of its own record; only the few angle / sign words
+// sit in a small shared tile so that the cooperative fix-up can patch them.  The staged variant
+// handles every other record shape through a word-transposed tile.
+template <int D, int PB, bool DIRECT>
+__global__ void __launch_bounds__(Turbo<D>::THREADS, (D == 64 && DIRECT) ? 4 : 1)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                     uint8_t* __restrict__ payload, uint64_t* err) {
   using K = Turbo<D>;
@@ -134,12 +139,14 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   const int lut_len = 2 * levels + 2 * tp.ray_count;
   const float* s_ray_cos = s_lut + 2 * levels;
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
+  const int rw = DIRECT ? 0 : tp.radii_words;  // radii words present in the shared tile
+  const int tile_words = DIRECT ? tp.angle_words + tp.sign_words : tp.rec_words;
   uint8_t* wbase = smem + TurboEncSmem<D>::table_bytes(tp.projections, levels, tp.ray_count) +
-                   warp * TurboEncSmem<D>::warp_bytes(tp.rec_words, tp.lossy);
+                   warp * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
   float* s_x = reinterpret_cast<float*>(wbase);                        // [TV][XS]
   int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);    // [TV]
-  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);          // [rec_words][WS]
-  float* s_rad = reinterpret_cast<float*>(s_w + tp.rec_words * K::WS); // [P][WS], lossy only
+  uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);          // [tile_words][WS]
+  float* s_rad = reinterpret_cast<float*>(s_w + tile_words * K::WS);   // [P][WS], lossy only
 
   const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
   const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
@@ -169,7 +176,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   {
     float* row = s_x + v * K::XS;
     uint32_t* w = s_w + v;
-    uint32_t* aw = w + tp.radii_words * K::WS;
+    uint32_t* aw = w + rw * K::WS;
+    uint8_t* my_rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)(v0 + v) * g.rec_bytes;
     int code = 0;
     float y[D];
 #pragma unroll
@@ -203,7 +211,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
         unc |= (unsigned long long)(certain ? 0u : 1u) << i;
         rmax = max(rmax, __float_as_uint(r) & 0x7fffffffu);
-        radp[i * K::WS] = r;
+        if constexpr (DIRECT) y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
+        else radp[i * K::WS] = r;
         if constexpr (PB != 0) {
           const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
           words[wi] |= idx << sh;
@@ -234,7 +243,14 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
           __shfl_sync(0xffffffffu, (uint32_t)unc, src);
       fix_pairs_warp<D>(s_x + src * K::XS, tp.sign_mask, tp.scale, m,
-                        s_w + src + tp.radii_words * K::WS, K::WS, pb, lane);
+                        s_w + src + rw * K::WS, K::WS, pb, lane);
+    }
+    if constexpr (DIRECT) {
+      if (valid) {
+#pragma unroll
+        for (int k = 0; k < K::P / 4; k++)
+          reinterpret_cast<float4*>(my_rec)[k] = make_float4(y[8 * k], y[8 * k + 2], y[8 * k + 4], y[8 * k + 6]);
+      }
     }
 
     if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
@@ -266,7 +282,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
             bitbuf >>= pb;
             nbits -= pb;
           }
-          const float r = radp[i * K::WS];
+          const float r = DIRECT ? y[2 * i] : radp[i * K::WS];
           y[2 * i] = __fmul_rn(r, s_lut[idx]);
           y[2 * i + 1] = __fmul_rn(r, s_lut[levels + idx]);
         }
@@ -297,7 +313,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per row.  The dot is
       // first taken with packed fused multiply-adds in four chains; its sign is the reference's
       // whenever |dot| clears the rounding bound (pkv_fast_paths.h), else fix_signs decides.
-      uint32_t* sw = w + (tp.radii_words + tp.angle_words) * K::WS;
+      uint32_t* sw = w + (rw + tp.angle_words) * K::WS;
       const float rnorm = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
       unsigned long long uncq = 0;
       uint32_t bits = 0;
@@ -351,18 +367,32 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
     }
     if (valid && code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
+    if constexpr (DIRECT) {
+      if (valid) {  // angle and sign words (patched in place by the fix-ups) follow the radii
+        for (int k = 0; k < tile_words; k += 4)
+          *reinterpret_cast<uint4*>(my_rec + 4 * (K::P + k)) =
+              make_uint4(w[k * K::WS], w[(k + 1) * K::WS], w[(k + 2) * K::WS], w[(k + 3) * K::WS]);
+      }
+    }
   }
-  __syncwarp();
-  stage_records<D, false>(
-      s_w, reinterpret_cast<uint32_t*>(payload + (int64_t)batch * g.payload_batch_stride +
-                                       (int64_t)v0 * g.rec_bytes),
-      nv, tp.rec_words, lane);
+  if constexpr (!DIRECT) {
+    __syncwarp();
+    stage_records<D, false>(
+        s_w, reinterpret_cast<uint32_t*>(payload + (int64_t)batch * g.payload_batch_stride +
+                                         (int64_t)v0 * g.rec_bytes),
+        nv, tp.rec_words, lane);
+  }
+}
+
+inline bool turbo_encode_direct(const TurboParams& tp) {
+  return !tp.lossy && (tp.rec_words % 4) == 0 && ((tp.angle_words + tp.sign_words) % 4) == 0;
 }
 
 template <int D>
 size_t turbo_encode_smem(const TurboParams& tp) {
+  const int tile_words = turbo_encode_direct(tp) ? tp.angle_words + tp.sign_words : tp.rec_words;
   return TurboEncSmem<D>::table_bytes(tp.projections, 1 << tp.polar_bits, tp.ray_count) +
-         Turbo<D>::NWARPS * TurboEncSmem<D>::warp_bytes(tp.rec_words, tp.lossy);
+         Turbo<D>::NWARPS * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
 }
 
 }  // namespace pkv_turbo
