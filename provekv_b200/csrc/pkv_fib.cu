@@ -39,6 +39,19 @@ __device__ __forceinline__ void stage_out(uint8_t* dst, const uint8_t* src, int 
   for (int i = (n16 << 4) + threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
 }
 
+// acc += m * r on two adjacent accumulators: one packed multiply (mul.rn.f32x2 rounds each lane
+// separately) and two scalar adds.  The adds stay scalar on purpose: a packed multiply followed by
+// a packed add gets contracted into a fused multiply-add by the assembler, which changes the bits.
+__device__ __forceinline__ void mul_add2(float& a0, float& a1, float2 m, float2 r) {
+  unsigned long long pm, pr, pt;
+  pm = *reinterpret_cast<unsigned long long*>(&m);
+  pr = *reinterpret_cast<unsigned long long*>(&r);
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(pt) : "l"(pm), "l"(pr));
+  const float2 t = *reinterpret_cast<float2*>(&pt);
+  a0 = __fadd_rn(a0, t.x);
+  a1 = __fadd_rn(a1, t.y);
+}
+
 // ---------------------------------------------------------------------------
 // decode + patch
 // ---------------------------------------------------------------------------
@@ -140,14 +153,13 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         const float r = rr == 0 ? cw[i].x : rr == 1 ? cw[i].y : rr == 2 ? cw[i].z : cw[i].w;
-        acc[i][0] = __fadd_rn(acc[i][0], __fmul_rn(mA.x, r));
-        acc[i][1] = __fadd_rn(acc[i][1], __fmul_rn(mA.y, r));
-        acc[i][2] = __fadd_rn(acc[i][2], __fmul_rn(mA.z, r));
-        acc[i][3] = __fadd_rn(acc[i][3], __fmul_rn(mA.w, r));
-        acc[i][4] = __fadd_rn(acc[i][4], __fmul_rn(mB.x, r));
-        acc[i][5] = __fadd_rn(acc[i][5], __fmul_rn(mB.y, r));
-        acc[i][6] = __fadd_rn(acc[i][6], __fmul_rn(mB.z, r));
-        acc[i][7] = __fadd_rn(acc[i][7], __fmul_rn(mB.w, r));
+        // two columns per instruction: packed multiply, then packed add, each lane rounded on
+        // its own (no fusion), i.e. the same two IEEE operations per element as the scalar form
+        const float2 rr2 = make_float2(r, r);
+        mul_add2(acc[i][0], acc[i][1], make_float2(mA.x, mA.y), rr2);
+        mul_add2(acc[i][2], acc[i][3], make_float2(mA.z, mA.w), rr2);
+        mul_add2(acc[i][4], acc[i][5], make_float2(mB.x, mB.y), rr2);
+        mul_add2(acc[i][6], acc[i][7], make_float2(mB.z, mB.w), rr2);
       }
     }
   }
