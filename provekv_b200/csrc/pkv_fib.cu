@@ -394,22 +394,43 @@ int pkv_fib_tile_vectors(int dim, int encode) {
   return 0;
 }
 
+// The library's own stream-ordered memory pool, one per device, created on first use.  Its
+// release threshold is unlimited, so the scratch of one call is recycled by the next instead
+// of being returned to the driver at every synchronisation.
+cudaMemPool_t scratch_pool() {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) return nullptr;
+    uint64_t keep = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    pools[dev] = pool;
+  }
+  return pools[dev];
+}
+
 // Shortcut path: fast kernel over all vectors, then the exact fix-up of the listed entries.  The
-// list (one counter + at most one entry per vector) is scratch memory taken from the stream's
-// memory pool for the duration of the two launches.
+// list (one counter + at most one entry per vector) is scratch memory taken from the pool above,
+// ordered on the caller's stream, for the duration of the two launches.
 template <int D>
 int launch_fib_encode_fast(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
                            uint8_t* payload, uint64_t* err, cudaStream_t s) {
   const int64_t n = (int64_t)g.n_batches * g.vpb;
-  const int tv = FibFast<D>::TV;
-  PkvGeom gf = g;
-  gf.tiles_per_batch = (g.vpb + tv - 1) / tv;
-  const int64_t grid = (int64_t)g.n_batches * gf.tiles_per_batch;
+  cudaMemPool_t pool = scratch_pool();
+  if (!pool) return PKV_ERR_CUDA;
   uint32_t* scratch = nullptr;
-  if (cudaMallocAsync((void**)&scratch, sizeof(uint32_t) * (size_t)(n + 1), s) != cudaSuccess)
+  if (cudaMallocFromPoolAsync((void**)&scratch, sizeof(uint32_t) * (size_t)(n + 1), pool, s) != cudaSuccess)
     return PKV_ERR_CUDA;
   int st = pkv_launch_fib_encode_fast_with_scratch(p, x, g, payload, err, scratch, s);
-  (void)grid;
   if (cudaFreeAsync(scratch, s) != cudaSuccess && st == PKV_OK) st = PKV_ERR_CUDA;
   return st;
 }
