@@ -352,7 +352,7 @@ def run_ours(args, w):
                          "algorithmic_bytes_per_launch": algo_bytes * n_vec,
                          "encode_achieved": algo_bytes * n_vec / (enc_ms * 1e-3) / 1e9,
                          "decode_patch_achieved": algo_bytes * n_vec / (dec_ms * 1e-3) / 1e9,
-                         "traffic": ncu_traffic(dom)},
+                         "traffic": ncu_traffic(f"{args.workload}:{dom}")},
             "e2e": {"value": total_f32 / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": f32_bytes + n_batches * vpb * rec,
                     "d2h_bytes_per_step": f32_bytes + n_batches * vpb * rec,

@@ -39,17 +39,19 @@ __device__ __forceinline__ void stage_out(uint8_t* dst, const uint8_t* src, int 
   for (int i = (n16 << 4) + threadIdx.x; i < nbytes; i += blockDim.x) dst[i] = src[i];
 }
 
-// acc += m * r on two adjacent accumulators: one packed multiply (mul.rn.f32x2 rounds each lane
-// separately) and two scalar adds.  The adds stay scalar on purpose: a packed multiply followed by
-// a packed add gets contracted into a fused multiply-add by the assembler, which changes the bits.
-__device__ __forceinline__ void mul_add2(float& a0, float& a1, float2 m, float2 r) {
+// acc += m * r on two adjacent accumulators, each lane with a separately rounded product and sum:
+// a packed multiply (mul.rn.f32x2), then the packed sum t + acc written as fma.rn.f32x2(t, 1, acc),
+// which rounds exactly like an add (t * 1 is exact, signed zeros included).  A literal packed add
+// after the packed multiply -- or a multiplier the assembler can see is 1 -- gets contracted into a
+// fused multiply-add, which changes the bits; so the pair (1.0f, 1.0f) arrives as a kernel argument.
+constexpr unsigned long long kPackedOnes = 0x3f8000003f800000ull;
+__device__ __forceinline__ void mul_add2(unsigned long long& acc, float2 m, float2 r,
+                                         unsigned long long ones) {
   unsigned long long pm, pr, pt;
   pm = *reinterpret_cast<unsigned long long*>(&m);
   pr = *reinterpret_cast<unsigned long long*>(&r);
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(pt) : "l"(pm), "l"(pr));
-  const float2 t = *reinterpret_cast<float2*>(&pt);
-  a0 = __fadd_rn(a0, t.x);
-  a1 = __fadd_rn(a1, t.y);
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(pt), "l"(ones));
 }
 
 // ---------------------------------------------------------------------------
@@ -72,7 +74,7 @@ __global__ void __launch_bounds__(kThreads)
 fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
                         const float* __restrict__ rot32, const float* __restrict__ codebook,
                         int n_codewords, int idx_bits, int norm_len, float* __restrict__ cache,
-                        uint64_t* err) {
+                        uint64_t* err, unsigned long long ones) {
   using K = FibDec<D>;
   extern __shared__ __align__(16) uint8_t smem[];
   float* s_rot = reinterpret_cast<float*>(smem);                 // [D][D]
@@ -134,11 +136,11 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
 
   const int cg = threadIdx.x % K::CG, vg = threadIdx.x / K::CG;
   const int cA = 4 * cg, cB = D / 2 + 4 * cg;
-  float acc[8][8];
+  unsigned long long acc[8][4];  // packed pairs of adjacent columns
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
-    for (int c = 0; c < 8; c++) acc[i][c] = 0.0f;
+    for (int c = 0; c < 4; c++) acc[i][c] = 0ull;
 
 #pragma unroll 1
   for (int b = 0; b < K::B; b++) {
@@ -153,13 +155,13 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         const float r = rr == 0 ? cw[i].x : rr == 1 ? cw[i].y : rr == 2 ? cw[i].z : cw[i].w;
-        // two columns per instruction: packed multiply, then packed add, each lane rounded on
-        // its own (no fusion), i.e. the same two IEEE operations per element as the scalar form
+        // two columns per instruction, each lane rounded on its own: the same two IEEE
+        // operations per element as the scalar form
         const float2 rr2 = make_float2(r, r);
-        mul_add2(acc[i][0], acc[i][1], make_float2(mA.x, mA.y), rr2);
-        mul_add2(acc[i][2], acc[i][3], make_float2(mA.z, mA.w), rr2);
-        mul_add2(acc[i][4], acc[i][5], make_float2(mB.x, mB.y), rr2);
-        mul_add2(acc[i][6], acc[i][7], make_float2(mB.z, mB.w), rr2);
+        mul_add2(acc[i][0], make_float2(mA.x, mA.y), rr2, ones);
+        mul_add2(acc[i][1], make_float2(mA.z, mA.w), rr2, ones);
+        mul_add2(acc[i][2], make_float2(mB.x, mB.y), rr2, ones);
+        mul_add2(acc[i][3], make_float2(mB.z, mB.w), rr2, ones);
       }
     }
   }
@@ -173,7 +175,8 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
     bool ok = true;
 #pragma unroll
     for (int c = 0; c < 8; c++) {
-      o[c] = __fmul_rn(acc[i][c], nf);
+      const uint32_t bits = (uint32_t)(acc[i][c >> 1] >> (32 * (c & 1)));
+      o[c] = __fmul_rn(__uint_as_float(bits), nf);
       ok = ok && pkv_finite(o[c]);
     }
     if (!ok) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, PKV_VEC_NONFINITE_OUTPUT);
@@ -505,7 +508,7 @@ int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, cons
     if ((st = set_smem(fib_decode_patch_kernel<DIM>, sm)) != PKV_OK) return st;                   \
     fib_decode_patch_kernel<DIM><<<(unsigned)grid, kThreads, sm, s>>>(                            \
         g, payload, p->rot32_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits,             \
-        p->norm_len, cache, err);                                                                 \
+        p->norm_len, cache, err, kPackedOnes);                                                    \
   }
   if (p->cfg.dim == 64) PKV_FIB_DEC(64)
   else if (p->cfg.dim == 128) PKV_FIB_DEC(128)
