@@ -28,6 +28,11 @@ TurboParams make_params(const pkv_turbo_profile* p) {
   tp.rec_words = p->rec_bytes / 4;
   tp.scale = p->scale;
   for (int i = 0; i < 4; i++) tp.sign_mask[i] = p->sign_mask[i];
+  for (int i = 0; i < 128; i++) {
+    const bool neg = (p->sign_mask[i >> 5] >> (i & 31)) & 1u;
+    tp.sgn[i] = neg ? -1.0f : 1.0f;
+    tp.sgn_scale[i] = neg ? -p->scale : p->scale;
+  }
   tp.fast_bucket = p->fast_bucket;
   tp.ray_count = p->ray_count;
   tp.qjl = p->qjl_dev;

@@ -31,6 +31,8 @@ struct TurboParams {
   int radii_words, angle_words, sign_words, rec_words;
   float scale;
   uint32_t sign_mask[4];
+  float sgn[128];        // the Rademacher signs as +-1.0f and as +-scale: constant-bank operands, so a
+  float sgn_scale[128];  // sign flip costs one multiply (or none, merged with the 1/sqrt(d) scaling)
   int fast_bucket;     // ray table present and validated against the exact thresholds
   int ray_count;       // 2^polar_bits / 4 + 1 rays, 0 without the shortcut
   const float* qjl;    // [m][dim] then m sign-shortcut thresholds
@@ -55,6 +57,54 @@ __device__ __forceinline__ void fwht_regs(float (&v)[D], float scale) {
   }
 #pragma unroll
   for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], scale);
+}
+
+// Forward rotation, FastHadamardRotation::apply (rotation.rs:202-210): signs, butterflies, scale.
+// The sign multiplications are folded into the first butterfly stage: with a' = a * sa (exact),
+// fma(b, sb, a') = RN(a' + sb b) and fma(b, -sb, a') = RN(a' - sb b) are the reference's rounded
+// sum and difference of the two signed values.
+template <int D>
+__device__ __forceinline__ void fwht_forward_signed(float (&v)[D], const float (&sgn)[128], float scale) {
+#pragma unroll
+  for (int i = 0; i < D; i += 2) {
+    const float a = __fmul_rn(v[i], sgn[i]), b = v[i + 1];
+    v[i] = __fmaf_rn(b, sgn[i + 1], a);
+    v[i + 1] = __fmaf_rn(b, -sgn[i + 1], a);
+  }
+#pragma unroll
+  for (int step = 2; step < D; step <<= 1) {
+#pragma unroll
+    for (int start = 0; start < D; start += 2 * step) {
+#pragma unroll
+      for (int o = 0; o < step; o++) {
+        const float a = v[start + o], b = v[start + o + step];
+        v[start + o] = __fadd_rn(a, b);
+        v[start + o + step] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], scale);
+}
+
+// Inverse rotation, FastHadamardRotation::apply_inverse (rotation.rs:212-221): butterflies, scale,
+// signs.  RN(v * scale) * (+-1) = RN(v * (+-scale)): one multiply by the signed scale.
+template <int D>
+__device__ __forceinline__ void fwht_inverse_signed(float (&v)[D], const float (&sgn_scale)[128]) {
+#pragma unroll
+  for (int step = 1; step < D; step <<= 1) {
+#pragma unroll
+    for (int start = 0; start < D; start += 2 * step) {
+#pragma unroll
+      for (int o = 0; o < step; o++) {
+        const float a = v[start + o], b = v[start + o + step];
+        v[start + o] = __fadd_rn(a, b);
+        v[start + o + step] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], sgn_scale[i]);
 }
 
 // value * sign with sign = +-1.0 is a sign-bit flip (also for zeros and NaNs).

@@ -29,7 +29,7 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* s_q255 = reinterpret_cast<float*>(smem);  // [256]
-  float* s_lut = s_q255 + 256;                     // cos[L], sin[L]
+  float* s_lut = s_q255 + 256;                     // (cos, sin)[L]
   uint8_t* wbase = smem + TurboDecSmem<D>::table_bytes(levels) + warp * TurboDecSmem<D>::warp_bytes(tp.rec_words);
   int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                 // [TV]
   uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);         // [rec_words][WS]
@@ -47,7 +47,8 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
       s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(
                payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes)),
       nv, tp.rec_words, lane);
-  for (int i = threadIdx.x; i < 2 * levels; i += K::THREADS) pkv_cp_async4(s_lut + i, tp.lut + i);
+  for (int i = threadIdx.x; i < 2 * levels; i += K::THREADS)  // interleaved: one 8-byte read per pair
+    pkv_cp_async4(s_lut + (i < levels ? 2 * i : 2 * (i - levels) + 1), tp.lut + i);
   if (tp.lossy)  // `*value as f32 / u8::MAX as f32`, radius.rs:143
     for (int i = threadIdx.x; i < 256; i += K::THREADS) s_q255[i] = __fdiv_rn((float)i, 255.0f);
   if (v < nv) s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
@@ -108,8 +109,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
         if (sh + PB > 32) idx |= words[wi + 1] << (32 - sh);
         idx &= mask;
         const float r = y[2 * i];
-        y[2 * i] = __fmul_rn(r, s_lut[idx]);               // r * theta.cos(), polar.rs:312
-        y[2 * i + 1] = __fmul_rn(r, s_lut[levels + idx]);  // r * theta.sin(), polar.rs:313
+        const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
+        y[2 * i] = __fmul_rn(r, cs.x);      // r * theta.cos(), polar.rs:312
+        y[2 * i + 1] = __fmul_rn(r, cs.y);  // r * theta.sin(), polar.rs:313
       }
     } else {
       uint64_t bitbuf = 0;
@@ -125,14 +127,14 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
         bitbuf >>= pb;
         nbits -= pb;
         const float r = y[2 * i];
-        y[2 * i] = __fmul_rn(r, s_lut[idx]);
-        y[2 * i + 1] = __fmul_rn(r, s_lut[levels + idx]);
+        const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
+        y[2 * i] = __fmul_rn(r, cs.x);
+        y[2 * i + 1] = __fmul_rn(r, cs.y);
       }
     }
     if (code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
     // FastHadamardRotation::apply_inverse, rotation.rs:212-221
-    fwht_regs<D>(y, tp.scale);
-    apply_signs<D>(y, tp.sign_mask);
+    fwht_inverse_signed<D>(y, tp.sgn_scale);
   }
   __syncwarp();  // every lane has consumed its record: the tile may now hold the f32 rows
   if (v < nv) {

@@ -30,7 +30,7 @@ __device__ __forceinline__ void patch_angle(uint32_t* aw, int ws, int i, int pb,
 // bit-identical to the owner thread's.  Lane l then holds pairs l*D/64 .. and each pending pair
 // takes atan2f + the bucket expression of polar.rs:415-420; lane 0 patches the angle words.
 template <int D>
-__device__ __noinline__ void fix_pairs_warp(const float* xrow, const uint32_t* sign_mask, float scale,
+__device__ __noinline__ void fix_pairs_warp(const float* xrow, uint4 sign_mask, float scale,
                                             unsigned long long unc, uint32_t* aw, int ws, int pb,
                                             int lane) {
   constexpr int E = D / 32;  // elements per lane (2 or 4)
@@ -38,7 +38,10 @@ __device__ __noinline__ void fix_pairs_warp(const float* xrow, const uint32_t* s
 #pragma unroll
   for (int k = 0; k < E; k++) {
     const int i = lane * E + k;
-    e[k] = __uint_as_float(__float_as_uint(xrow[i]) ^ (((sign_mask[i >> 5] >> (i & 31)) & 1u) << 31));
+    const int wi = i >> 5;  // the mask travels by value: a pointer into the kernel parameters would
+                            // force a per-thread copy of the whole parameter block
+    const uint32_t mw = wi == 0 ? sign_mask.x : wi == 1 ? sign_mask.y : wi == 2 ? sign_mask.z : sign_mask.w;
+    e[k] = __uint_as_float(__float_as_uint(xrow[i]) ^ (((mw >> (i & 31)) & 1u) << 31));
   }
 #pragma unroll
   for (int step = 1; step < E; step <<= 1)
@@ -134,9 +137,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* s_g = reinterpret_cast<float*>(smem);                 // [m][D]
-  float* s_thr = s_g + tp.projections * D;                     // [m] sign-shortcut thresholds
-  float* s_lut = s_thr + tp.projections;                       // cos, sin, ray_cos, ray_sin
+  float* s_lut = s_g + tp.projections * D;                     // (cos, sin)[L], ray_cos, ray_sin
   const int lut_len = 2 * levels + 2 * tp.ray_count;
+  float* s_thr = s_lut + lut_len;                              // [m] sign-shortcut thresholds
   const float* s_ray_cos = s_lut + 2 * levels;
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
   const int rw = DIRECT ? 0 : tp.radii_words;  // radii words present in the shared tile
@@ -164,9 +167,12 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     const int vv = i / K::LPV, q = i % K::LPV;
     pkv_cp_async16(s_x + vv * K::XS + 4 * q, reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
-  for (int i = threadIdx.x; i < tp.projections * (D + 1) / 4; i += K::THREADS)
+  for (int i = threadIdx.x; i < tp.projections * D / 4; i += K::THREADS)
     pkv_cp_async16(reinterpret_cast<float4*>(s_g) + i, reinterpret_cast<const float4*>(tp.qjl) + i);
-  for (int i = threadIdx.x; i < lut_len; i += K::THREADS) pkv_cp_async4(s_lut + i, tp.lut + i);
+  for (int i = threadIdx.x; i < tp.projections; i += K::THREADS)
+    pkv_cp_async4(s_thr + i, tp.qjl + tp.projections * D + i);
+  for (int i = threadIdx.x; i < lut_len; i += K::THREADS)  // cos / sin interleaved: one 8-byte read per pair
+    pkv_cp_async4(s_lut + (i < levels ? 2 * i : i < 2 * levels ? 2 * (i - levels) + 1 : i), tp.lut + i);
   pkv_cp_async_wait_all();
   __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
 
@@ -187,8 +193,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     }
     // FastHadamardRotation::apply, rotation.rs:202-210.  A non-finite input makes every output of
     // the transform non-finite, so input finiteness is only looked at when a radius is bad.
-    apply_signs<D>(y, tp.sign_mask);
-    fwht_regs<D>(y, tp.scale);
+    fwht_forward_signed<D>(y, tp.sgn, tp.scale);
 
     // Pass 1, encode_pair (polar.rs:413-421): radius exactly, bucket by the shortcut.  Radii go
     // to the record (f32 codec) or to s_rad (BlockLogU8); undecided pairs are noted in `unc`.
@@ -242,7 +247,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       const unsigned long long m =
           ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
           __shfl_sync(0xffffffffu, (uint32_t)unc, src);
-      fix_pairs_warp<D>(s_x + src * K::XS, tp.sign_mask, tp.scale, m,
+      fix_pairs_warp<D>(s_x + src * K::XS,
+                        make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]), tp.scale, m,
                         s_w + src + rw * K::WS, K::WS, pb, lane);
     }
     if constexpr (DIRECT) {
@@ -283,13 +289,13 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
             nbits -= pb;
           }
           const float r = DIRECT ? y[2 * i] : radp[i * K::WS];
-          y[2 * i] = __fmul_rn(r, s_lut[idx]);
-          y[2 * i + 1] = __fmul_rn(r, s_lut[levels + idx]);
+          const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
+          y[2 * i] = __fmul_rn(r, cs.x);
+          y[2 * i + 1] = __fmul_rn(r, cs.y);
         }
       }
       // inverse rotation (rotation.rs:212-221), residual = vector - reconstruction (turbo.rs:268-273)
-      fwht_regs<D>(y, tp.scale);
-      apply_signs<D>(y, tp.sign_mask);
+      fwht_inverse_signed<D>(y, tp.sgn_scale);
       float2 n2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < D; i += 4) {
