@@ -85,20 +85,6 @@ __device__ __noinline__ void fix_pairs_warp(const float* xrow, uint4 sign_mask, 
   __syncwarp();
 }
 
-// Exact QJL signs for the projections in `unc` (qjl.rs:214-217); `res` is the residual row.
-__device__ __noinline__ void fix_signs(const float* g, const float* res, int dim,
-                                       unsigned long long unc, uint32_t* sw, int ws) {
-  while (unc) {
-    const int p = __ffsll((long long)unc) - 1;
-    unc &= unc - 1;
-    const float dot = exact_dot(g + p * dim, res, dim);
-    const uint32_t bit = 1u << (p & 31);
-    uint32_t w = sw[(p >> 5) * ws];
-    w = dot >= 0.0f ? (w | bit) : (w & ~bit);
-    sw[(p >> 5) * ws] = w;
-  }
-}
-
 // Which of the two encode errors applies when some radius came out non-finite: a non-finite
 // input value (turbo.rs:263, checked first by the reference) or an overflow in the butterflies
 // (PolarCode::from_parts, polar.rs:127-133).
@@ -117,7 +103,7 @@ struct TurboEncSmem {
     return (n + 15) & ~(size_t)15;
   }
   static __host__ __device__ size_t table_bytes(int projections, int levels, int ray_count) {
-    const size_t n = sizeof(float) * (projections * (D + 1) + 2 * levels + 2 * ray_count);
+    const size_t n = sizeof(float) * (projections * (K::XS + 1) + 2 * levels + 2 * ray_count);
     return (n + 15) & ~(size_t)15;
   }
 };
@@ -136,8 +122,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* s_g = reinterpret_cast<float*>(smem);                 // [m][D]
-  float* s_lut = s_g + tp.projections * D;                     // (cos, sin)[L], ray_cos, ray_sin
+  float* s_g = reinterpret_cast<float*>(smem);                 // [m][XS] (padded rows)
+  float* s_lut = s_g + tp.projections * K::XS;                 // (cos, sin)[L], ray_cos, ray_sin
   const int lut_len = 2 * levels + 2 * tp.ray_count;
   float* s_thr = s_lut + lut_len;                              // [m] sign-shortcut thresholds
   const float* s_ray_cos = s_lut + 2 * levels;
@@ -167,8 +153,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     const int vv = i / K::LPV, q = i % K::LPV;
     pkv_cp_async16(s_x + vv * K::XS + 4 * q, reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
-  for (int i = threadIdx.x; i < tp.projections * D / 4; i += K::THREADS)
-    pkv_cp_async16(reinterpret_cast<float4*>(s_g) + i, reinterpret_cast<const float4*>(tp.qjl) + i);
+  for (int i = threadIdx.x; i < tp.projections * K::LPV; i += K::THREADS)
+    pkv_cp_async16(s_g + (i / K::LPV) * K::XS + 4 * (i % K::LPV), reinterpret_cast<const float4*>(tp.qjl) + i);
   for (int i = threadIdx.x; i < tp.projections; i += K::THREADS)
     pkv_cp_async4(s_thr + i, tp.qjl + tp.projections * D + i);
   for (int i = threadIdx.x; i < lut_len; i += K::THREADS)  // cos / sin interleaved: one 8-byte read per pair
@@ -316,33 +302,71 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         for (int i = 0; i < D; i++) res_ok = res_ok && pkv_finite(row[i]);
         if (!res_ok) code = PKV_VEC_NONFINITE_RESIDUAL;
       }
-      // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per row.  The dot is
-      // first taken with packed fused multiply-adds in four chains; its sign is the reference's
-      // whenever |dot| clears the rounding bound (pkv_fast_paths.h), else fix_signs decides.
-      uint32_t* sw = w + (rw + tp.angle_words) * K::WS;
-      const float rnorm = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
-      unsigned long long uncq = 0;
-      uint32_t bits = 0;
-#pragma unroll 4
-      for (int p = 0; p < tp.projections; p++) {
-        const float* grow = s_g + p * D;
-        float2 d0 = make_float2(0.0f, 0.0f), d1 = d0;
+      // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per projection row.
+      // The residual rows now sit in the warp's tile, and the 32 x m dots are taken as a small
+      // register-tiled product from shared memory: lane (vg, pg) owns vectors 4vg..4vg+3 and, per
+      // chunk of 32 projections, rows pg, pg+4, .., pg+28 (rows 4 apart sit in different banks),
+      // with packed fused multiply-adds over even / odd columns.  The sign of such a dot is the
+      // reference's whenever |dot| clears the rounding bound (pkv_fast_paths.h); otherwise the
+      // lane takes the exact sequential dot for that (vector, row).
+      float* s_rn = reinterpret_cast<float*>(s_off);  // the vector offsets are spent
+      s_rn[v] = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
+      __syncwarp();
+      {
+        const int vg = lane >> 2, pg = lane & 3;
+        const float* xr = s_x + (4 * vg) * K::XS;
+        const float4 rn4 = *reinterpret_cast<const float4*>(s_rn + 4 * vg);
+        const float rn[4] = {rn4.x, rn4.y, rn4.z, rn4.w};
+        uint32_t* sw = s_w + (rw + tp.angle_words) * K::WS;
+        for (int c = 0; c < tp.projections; c += 32) {
+          const float* gr = s_g + (c + pg) * K::XS;
+          float2 acc[4][8];
 #pragma unroll
-        for (int j = 0; j < D; j += 4) {
-          const float4 gg = *reinterpret_cast<const float4*>(grow + j);
-          d0 = ffma2(make_float2(gg.x, gg.y), make_float2(y[j], y[j + 1]), d0);
-          d1 = ffma2(make_float2(gg.z, gg.w), make_float2(y[j + 2], y[j + 3]), d1);
-        }
-        const float dot = (d0.x + d0.y) + (d1.x + d1.y);
-        const float tau = fmaf(s_thr[p], rnorm, PKV_QJL_ABS_BOUND);
-        uncq |= (unsigned long long)(fabsf(dot) > tau ? 0u : 1u) << p;
-        bits |= (dot >= 0.0f ? 1u : 0u) << (p & 31);
-        if ((p & 31) == 31) {
-          sw[(p >> 5) * K::WS] = bits;
-          bits = 0;
+          for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int k = 0; k < 8; k++) acc[i][k] = make_float2(0.0f, 0.0f);
+#pragma unroll 2
+          for (int j = 0; j < D; j += 4) {
+            float4 r[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) r[i] = *reinterpret_cast<const float4*>(xr + i * K::XS + j);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+              const float4 gk = *reinterpret_cast<const float4*>(gr + 4 * k * K::XS + j);
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                acc[i][k] = ffma2(make_float2(gk.x, gk.y), make_float2(r[i].x, r[i].y), acc[i][k]);
+                acc[i][k] = ffma2(make_float2(gk.z, gk.w), make_float2(r[i].z, r[i].w), acc[i][k]);
+              }
+            }
+          }
+          uint32_t word[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            word[i] = 0;
+            uint32_t unc8 = 0;  // rows k whose sign the bound does not settle
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+              const float dot = acc[i][k].x + acc[i][k].y;
+              const float tau = fmaf(s_thr[c + pg + 4 * k], rn[i], PKV_QJL_ABS_BOUND);
+              unc8 |= (fabsf(dot) > tau ? 0u : 1u) << k;
+              word[i] |= (dot >= 0.0f ? 1u : 0u) << (pg + 4 * k);
+            }
+            if (4 * vg + i >= nv) unc8 = 0;
+            while (unc8) {
+              const int k = __ffs(unc8) - 1;
+              unc8 &= unc8 - 1;
+              const float dot = exact_dot(s_g + (c + pg + 4 * k) * K::XS, xr + i * K::XS, D);
+              const uint32_t bit = 1u << (pg + 4 * k);
+              word[i] = dot >= 0.0f ? (word[i] | bit) : (word[i] & ~bit);
+            }
+            word[i] |= __shfl_xor_sync(0xffffffffu, word[i], 1);
+            word[i] |= __shfl_xor_sync(0xffffffffu, word[i], 2);
+          }
+          sw[(c >> 5) * K::WS + 4 * vg + pg] = pg == 0 ? word[0] : pg == 1 ? word[1] : pg == 2 ? word[2] : word[3];
         }
       }
-      if (valid && uncq) fix_signs(s_g, row, D, uncq, sw, K::WS);
+      __syncwarp();
     }
     if (tp.lossy) {
       // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371)
