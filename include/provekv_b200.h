@@ -57,7 +57,8 @@ enum {
   PKV_VEC_BAD_NORM = 22,          /* fib-quant/src/codec.rs:1029 */
   PKV_VEC_NONFINITE_OUTPUT = 23,  /* fib-quant/src/codec.rs:840 */
   PKV_VEC_NONFINITE_RESIDUAL = 24,/* turbo-quant/src/qjl.rs:210 */
-  PKV_VEC_NORM_RANGE = 25         /* fib-quant/src/codec.rs:1003 (second pass of encode_batch) */
+  PKV_VEC_NORM_RANGE = 25,        /* fib-quant/src/codec.rs:1003 (second pass of encode_batch) */
+  PKV_VEC_DEVICE_WAIT = 26        /* no counterpart: a bounded wait inside a kernel ran out (the payload is not valid) */
 };
 
 const char* pkv_status_string(int status);

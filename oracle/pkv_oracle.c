@@ -973,6 +973,58 @@ PKVO_API void pkvo_fast_qjl_check(int dim, int64_t n, uint64_t seed, double res_
   }
 }
 
+/* Tensor-core (TF32) tier of the QJL sign shortcut: operands cut to 10 mantissa bits by truncation
+ * (variant 0) or round-to-nearest (variant 1), products summed in binary32 in blocks of 8 terms.
+ * counts as in pkvo_fast_qjl_check. */
+static float tf32_cut(float v, int variant) {
+  uint32_t u;
+  memcpy(&u, &v, 4);
+  if (variant) u += 0x00001000u;
+  u &= 0xffffe000u;
+  memcpy(&v, &u, 4);
+  return v;
+}
+
+PKVO_API void pkvo_fast_qjl_tf32_check(int dim, int64_t n, uint64_t seed, double res_scale, int variant,
+                                       int64_t* counts) {
+  uint64_t s = seed * 11400714819323198485ull + 1;
+  counts[0] = counts[1] = counts[2] = 0;
+  float g[128], x[128];
+  for (int64_t i = 0; i < n; i++) {
+    double g2 = 0.0;
+    for (int j = 0; j < dim; j++) {
+      g[j] = (float)((unif(&s) + unif(&s) + unif(&s) + unif(&s) - 2.0) * 1.7);
+      x[j] = (float)((unif(&s) + unif(&s) + unif(&s) + unif(&s) - 2.0) * res_scale);
+      g2 += (double)g[j] * g[j];
+    }
+    if (i & 1) { /* every other case: a dot near the threshold of this tier */
+      double dot = 0.0;
+      for (int j = 0; j < dim; j++) dot += (double)g[j] * x[j];
+      double f = dot / g2 * (1.0 - (unif(&s) - 0.5) * 0.1);
+      for (int j = 0; j < dim; j++) x[j] = (float)((double)x[j] - f * g[j]);
+    }
+    float thr = (float)(sqrt(g2) * 1.0001) * PKV_QJL_TF32_BOUND;
+    float s2 = 0.0f;
+    for (int j = 0; j < dim; j++) s2 = fmaf(x[j], x[j], s2);
+    float rnorm = sqrtf(s2) * 1.0001f;
+    float fast = 0.0f;
+    for (int j0 = 0; j0 < dim; j0 += 8) {
+      float blk = 0.0f;
+      for (int j = j0; j < j0 + 8; j++) blk += tf32_cut(g[j], variant) * tf32_cut(x[j], variant);
+      fast += blk;
+    }
+    float tau = fmaf(thr, rnorm, PKV_QJL_ABS_BOUND);
+    if (!(fabsf(fast) > tau)) {
+      counts[1]++;
+      continue;
+    }
+    counts[2]++;
+    float ref = 0.0f;
+    for (int j = 0; j < dim; j++) ref += g[j] * x[j];
+    if ((ref >= 0.0f) != (fast >= 0.0f)) counts[0]++;
+  }
+}
+
 /* The fib encoder's shortcuts on n vectors (batch numerics): certified normalisation, binary32
  * fused rotation, certified block argmin -- against the exact sequence of fib_encode_one.
  * counts[0] = decided blocks with the wrong index, [1] = flagged blocks, [2] = decided blocks,

@@ -32,6 +32,7 @@ VEC_BAD_NORM = 22
 VEC_NONFINITE_OUTPUT = 23
 VEC_NONFINITE_RESIDUAL = 24
 VEC_NORM_RANGE = 25
+VEC_DEVICE_WAIT = 26
 
 NORM_FP16, NORM_F32 = 0, 1
 ARGMIN_PAIRWISE, ARGMIN_SEQUENTIAL = 0, 1

@@ -136,6 +136,8 @@ struct pkv_turbo_profile {
   uint32_t sign_mask[4];    // bit i set: signs[i] == -1
   int fast_bucket;          // 1: ray table validated, kernels may use the bucket shortcut
   int ray_count;            // 2^polar_bits / 4 + 1, or 0
+  float qjl_thr[64];        // per row: |g_r| * PKV_QJL_REL_BOUND (binary32 sign shortcut)
+  float qjl_thr_tf32[64];   // per row: |g_r| * PKV_QJL_TF32_BOUND (tensor-core sign shortcut)
   float* qjl_dev;           // projections x dim, then one sign-shortcut threshold per row
   float* lut_dev;           // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
   PkvWorkspace ws;

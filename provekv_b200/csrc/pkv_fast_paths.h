@@ -106,6 +106,13 @@ PKV_HD uint32_t pkv_fast_bucket_any(float a, float b, int polar_bits, const floa
  * (turbo-quant/src/qjl.rs:214-217) has the same sign.  The factor below is 2 gamma_129 with
  * 2 % slack for the rounding of the norms themselves. */
 #define PKV_QJL_REL_BOUND (2.0f * 129.0f * 5.9604645e-8f * 1.02f / (1.0f - 129.0f * 5.9604645e-8f))
+/* First tier of the same test for dots taken on the tensor cores in TF32: each operand keeps 10
+ * explicit mantissa bits (relative error below 2^-10, whether the unit truncates or rounds), the
+ * products of the shortened operands are exact and are summed in binary32, so the result differs
+ * from the exact sum by at most (2^-9 + 2^-20) sum|g_j x_j| plus the summation error (below
+ * 2^-17 sum|g_j x_j| for 128 terms).  2.1e-3 leaves 7 % on top of 2^-9 = 1.953e-3.  A dot that fails
+ * this test is retaken in binary32 (bound above) before the exact sequence is used. */
+#define PKV_QJL_TF32_BOUND 2.1e-3f
 /* Absolute floor covering products that underflow to subnormals. */
 #define PKV_QJL_ABS_BOUND 1.0e-35f
 

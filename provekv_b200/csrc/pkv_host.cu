@@ -187,6 +187,7 @@ const char* pkv_status_string(int s) {
     case PKV_VEC_NONFINITE_OUTPUT: return "non-finite decoded value";
     case PKV_VEC_NONFINITE_RESIDUAL: return "non-finite residual";
     case PKV_VEC_NORM_RANGE: return "norm not representable in the wire norm format";
+    case PKV_VEC_DEVICE_WAIT: return "a wait inside a kernel ran out; the output is not valid";
     default: return "unknown status";
   }
 }
@@ -515,6 +516,8 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
       double s2 = 0.0;
       for (int j = 0; j < d; j++) s2 += (double)qjl[r * d + j] * (double)qjl[r * d + j];
       host[(size_t)m * d + r] = (float)(sqrt(s2) * 1.0001) * PKV_QJL_REL_BOUND;
+      p->qjl_thr[r] = host[(size_t)m * d + r];
+      p->qjl_thr_tf32[r] = (float)(sqrt(s2) * 1.0001) * PKV_QJL_TF32_BOUND;
     }
     const size_t bytes = sizeof(float) * (size_t)m * (d + 1);
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->qjl_dev, bytes);

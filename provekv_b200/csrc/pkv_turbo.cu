@@ -33,6 +33,9 @@ TurboParams make_params(const pkv_turbo_profile* p) {
     tp.sgn[i] = neg ? -1.0f : 1.0f;
     tp.sgn_scale[i] = neg ? -p->scale : p->scale;
   }
+  for (int i = 0; i < 64; i++) {
+    tp.qjl_thr_tf32[i] = i < tp.projections ? p->qjl_thr_tf32[i] : 0.0f;
+  }
   tp.fast_bucket = p->fast_bucket;
   tp.ray_count = p->ray_count;
   tp.qjl = p->qjl_dev;
@@ -52,14 +55,14 @@ template <int D, int PB>
 int launch_encode(const TurboParams& tp, const float* x, const PkvGeom& g, uint8_t* payload,
                   uint64_t* err, unsigned grid, cudaStream_t s) {
   const size_t sm = turbo_encode_smem<D>(tp);
-  const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;  // one warp per 32-vector tile
+  const unsigned ctas = (grid + TurboEnc<D>::NWARPS - 1) / TurboEnc<D>::NWARPS;  // one warp per 32-vector tile
   int st;
   if (turbo_encode_direct(tp)) {
     if ((st = set_smem(turbo_encode_kernel<D, PB, true>, sm)) != PKV_OK) return st;
-    turbo_encode_kernel<D, PB, true><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+    turbo_encode_kernel<D, PB, true><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
   } else {
     if ((st = set_smem(turbo_encode_kernel<D, PB, false>, sm)) != PKV_OK) return st;
-    turbo_encode_kernel<D, PB, false><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+    turbo_encode_kernel<D, PB, false><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
   }
   return PKV_OK;
 }

@@ -33,6 +33,7 @@ struct TurboParams {
   uint32_t sign_mask[4];
   float sgn[128];        // the Rademacher signs as +-1.0f and as +-scale: constant-bank operands, so a
   float sgn_scale[128];  // sign flip costs one multiply (or none, merged with the 1/sqrt(d) scaling)
+  float qjl_thr_tf32[64];  // per QJL row: |g| * PKV_QJL_TF32_BOUND (tensor-core tier)
   int fast_bucket;     // ray table present and validated against the exact thresholds
   int ray_count;       // 2^polar_bits / 4 + 1 rays, 0 without the shortcut
   const float* qjl;    // [m][dim] then m sign-shortcut thresholds

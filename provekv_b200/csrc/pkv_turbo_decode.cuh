@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                           float* __restrict__ cache, uint64_t* err) {
   using K = Turbo<D>;
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -6,11 +6,40 @@
 // calls or data-dependent branches, so the compiler can interleave independent pairs; the
 // decisions a shortcut could not certify are collected in bit masks and settled afterwards
 // by out-of-line routines that run the exact operation sequence.
+//
+// Shared-memory tile of the CTA's 128 vectors (4 warps x 32): the tensor cores' K-major layout with
+// the 128-byte swizzle -- one slab of [128 rows][128 bytes] per 32 columns, the eight 16-byte
+// pieces of a row's 128 bytes permuted by (piece ^ (row & 7)) -- so that a 128-byte line of a
+// vector in global memory stays one line in shared memory (efficient staging copies) and the
+// thread-per-row accesses of a quarter warp still fall in eight different bank groups.  The
+// QJL sketch (32 or 64 dot products per vector) is one 128 x m x D TF32 product on the tensor
+// cores (tcgen05.mma, accumulator in tensor memory); its signs are accepted where they clear the
+// TF32 error bound, retaken in binary32 where they do not, and by the exact sequence at last.
 #pragma once
 
+#include "pkv_tcgen05.cuh"
 #include "pkv_turbo_common.cuh"
 
 namespace pkv_turbo {
+
+template <int D>
+struct TurboEnc {
+  static constexpr int NWARPS = 4;  // one CTA = one 128-row tensor-core tile
+  static constexpr int THREADS = 128, ROWS = 128, TV = 32, WS = 33, P = D / 2, LPV = D / 4;
+  static constexpr int SLABS = D / 32;          // 128-byte column blocks per row
+  static constexpr int X_SLAB = ROWS * 128;     // bytes per slab of the vector tile
+  static constexpr int X_BYTES = SLABS * X_SLAB;
+};
+
+// Byte offset of the 16-byte piece c (elements 4c..4c+3) of row r in a swizzled tile whose slabs
+// are slab_bytes apart.
+__device__ __forceinline__ uint32_t sw_piece(int slab_bytes, int r, int c) {
+  return (uint32_t)((c >> 3) * slab_bytes + (r >> 3) * 1024 + (r & 7) * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+// element j of row r
+__device__ __forceinline__ const float* tile_at(const uint8_t* t, int slab_bytes, int r, int j) {
+  return reinterpret_cast<const float*>(t + sw_piece(slab_bytes, r, j >> 2) + (j & 3) * 4);
+}
 
 // Replace angle index i in the shared angle words (LSB-first stream, bitpack.rs:135-143).
 __device__ __forceinline__ void patch_angle(uint32_t* aw, int ws, int i, int pb, uint32_t idx) {
@@ -30,7 +59,7 @@ __device__ __forceinline__ void patch_angle(uint32_t* aw, int ws, int i, int pb,
 // bit-identical to the owner thread's.  Lane l then holds pairs l*D/64 .. and each pending pair
 // takes atan2f + the bucket expression of polar.rs:415-420; lane 0 patches the angle words.
 template <int D>
-__device__ __noinline__ void fix_pairs_warp(const float* xrow, uint4 sign_mask, float scale,
+__device__ __noinline__ void fix_pairs_warp(const uint8_t* xt, int xrow, uint4 sign_mask, float scale,
                                             unsigned long long unc, uint32_t* aw, int ws, int pb,
                                             int lane) {
   constexpr int E = D / 32;  // elements per lane (2 or 4)
@@ -41,7 +70,7 @@ __device__ __noinline__ void fix_pairs_warp(const float* xrow, uint4 sign_mask, 
     const int wi = i >> 5;  // the mask travels by value: a pointer into the kernel parameters would
                             // force a per-thread copy of the whole parameter block
     const uint32_t mw = wi == 0 ? sign_mask.x : wi == 1 ? sign_mask.y : wi == 2 ? sign_mask.z : sign_mask.w;
-    e[k] = __uint_as_float(__float_as_uint(xrow[i]) ^ (((mw >> (i & 31)) & 1u) << 31));
+    e[k] = __uint_as_float(__float_as_uint(*tile_at(xt, TurboEnc<D>::X_SLAB, xrow, i)) ^ (((mw >> (i & 31)) & 1u) << 31));
   }
 #pragma unroll
   for (int step = 1; step < E; step <<= 1)
@@ -88,22 +117,54 @@ __device__ __noinline__ void fix_pairs_warp(const float* xrow, uint4 sign_mask, 
 // Which of the two encode errors applies when some radius came out non-finite: a non-finite
 // input value (turbo.rs:263, checked first by the reference) or an overflow in the butterflies
 // (PolarCode::from_parts, polar.rs:127-133).
-__device__ __noinline__ int classify_bad_vector(const float* xrow, int dim) {
+__device__ __noinline__ int classify_bad_vector(const uint8_t* xt, int slab, int row, int dim) {
   for (int i = 0; i < dim; i++)
-    if (!pkv_finite(xrow[i])) return PKV_VEC_NONFINITE_INPUT;
+    if (!pkv_finite(*tile_at(xt, slab, row, i))) return PKV_VEC_NONFINITE_INPUT;
   return PKV_VEC_BAD_RADIUS;
+}
+
+// Dot of QJL row p with the residual in tile row `row`: binary32 fused in four chains (the second
+// tier of the sign shortcut) and the reference's sequence (qjl.rs:214-217).
+__device__ __noinline__ float fused_dot(const uint8_t* gt, int g_slab, int p, const uint8_t* xt, int x_slab,
+                                        int row, int dim) {
+  float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+  for (int c = 0; c < dim / 4; c++) {
+    const float4 g = *reinterpret_cast<const float4*>(gt + sw_piece(g_slab, p, c));
+    const float4 x = *reinterpret_cast<const float4*>(xt + sw_piece(x_slab, row, c));
+    d0 = fmaf(g.x, x.x, d0);
+    d1 = fmaf(g.y, x.y, d1);
+    d2 = fmaf(g.z, x.z, d2);
+    d3 = fmaf(g.w, x.w, d3);
+  }
+  return (d0 + d1) + (d2 + d3);
+}
+__device__ __noinline__ float sequential_dot(const uint8_t* gt, int g_slab, int p, const uint8_t* xt,
+                                             int x_slab, int row, int dim) {
+  float dot = 0.0f;
+  for (int c = 0; c < dim / 4; c++) {
+    const float4 g = *reinterpret_cast<const float4*>(gt + sw_piece(g_slab, p, c));
+    const float4 x = *reinterpret_cast<const float4*>(xt + sw_piece(x_slab, row, c));
+    dot = __fadd_rn(dot, __fmul_rn(g.x, x.x));
+    dot = __fadd_rn(dot, __fmul_rn(g.y, x.y));
+    dot = __fadd_rn(dot, __fmul_rn(g.z, x.z));
+    dot = __fadd_rn(dot, __fmul_rn(g.w, x.w));
+  }
+  return dot;
 }
 
 template <int D>
 struct TurboEncSmem {
-  using K = Turbo<D>;
-  static __host__ __device__ size_t warp_bytes(int rec_words, int lossy) {
-    const size_t n = sizeof(float) * K::TV * K::XS + sizeof(int64_t) * K::TV +
-                     sizeof(uint32_t) * rec_words * K::WS + (lossy ? sizeof(float) * K::P * K::WS : 0);
+  using K = TurboEnc<D>;
+  // CTA-wide: vector tile, QJL matrix tile, cos/sin + ray tables; then one slice per warp
+  static __host__ __device__ size_t table_bytes(int projections, int levels, int ray_count) {
+    // 1024: the swizzled tiles start on a 1024-byte boundary found at run time
+    const size_t n = 1024 + (size_t)K::X_BYTES + (size_t)K::SLABS * projections * 128 +
+                     sizeof(float) * (2 * levels + 2 * ray_count);
     return (n + 15) & ~(size_t)15;
   }
-  static __host__ __device__ size_t table_bytes(int projections, int levels, int ray_count) {
-    const size_t n = sizeof(float) * (projections * (K::XS + 1) + 2 * levels + 2 * ray_count);
+  static __host__ __device__ size_t warp_bytes(int tile_words, int lossy) {
+    const size_t n = sizeof(int64_t) * K::TV + sizeof(uint32_t) * tile_words * K::WS +
+                     (lossy ? sizeof(float) * K::P * K::WS : 0);
     return (n + 15) & ~(size_t)15;
   }
 };
@@ -114,26 +175,29 @@ struct TurboEncSmem {
 // sit in a small shared tile so that the cooperative fix-up can patch them.  The staged variant
 // handles every other record shape through a word-transposed tile.
 template <int D, int PB, bool DIRECT>
-__global__ void __launch_bounds__(Turbo<D>::THREADS, (D == 64 && DIRECT) ? 4 : 1)
+__global__ void __launch_bounds__(TurboEnc<D>::THREADS, (D == 64 && DIRECT) ? 4 : 1)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                     uint8_t* __restrict__ payload, uint64_t* err) {
-  using K = Turbo<D>;
-  extern __shared__ __align__(16) uint8_t smem[];
+  using K = TurboEnc<D>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t s_bar;  // completion of the tensor-core product
+  __shared__ uint32_t s_tmem;              // base of the CTA's tensor-memory columns
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* s_g = reinterpret_cast<float*>(smem);                 // [m][XS] (padded rows)
-  float* s_lut = s_g + tp.projections * K::XS;                 // (cos, sin)[L], ray_cos, ray_sin
+  const int m = tp.projections;  // 0 without the QJL stage
+  const int g_slab = m * 128;
+  uint8_t* s_xt = smem + ((1024u - (pkv_tc::smem_u32(smem) & 1023u)) & 1023u);  // vector tile, SLABS x [128 rows][128 B]
+  uint8_t* s_gt = s_xt + K::X_BYTES;                                           // QJL matrix, SLABS x [m rows][128 B]
+  float* s_lut = reinterpret_cast<float*>(s_gt + K::SLABS * g_slab);           // (cos, sin)[L], ray_cos, ray_sin
   const int lut_len = 2 * levels + 2 * tp.ray_count;
-  float* s_thr = s_lut + lut_len;                              // [m] sign-shortcut thresholds
   const float* s_ray_cos = s_lut + 2 * levels;
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
   const int rw = DIRECT ? 0 : tp.radii_words;  // radii words present in the shared tile
   const int tile_words = DIRECT ? tp.angle_words + tp.sign_words : tp.rec_words;
-  uint8_t* wbase = smem + TurboEncSmem<D>::table_bytes(tp.projections, levels, tp.ray_count) +
+  uint8_t* wbase = smem + TurboEncSmem<D>::table_bytes(m, levels, tp.ray_count) +
                    warp * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
-  float* s_x = reinterpret_cast<float*>(wbase);                        // [TV][XS]
-  int64_t* s_off = reinterpret_cast<int64_t*>(s_x + K::TV * K::XS);    // [TV]
+  int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                  // [TV]
   uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);          // [tile_words][WS]
   float* s_rad = reinterpret_cast<float*>(s_w + tile_words * K::WS);   // [P][WS], lossy only
 
@@ -144,6 +208,15 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   const int v0 = tile * K::TV;
   const int nv = active ? min(K::TV, g.vpb - v0) : 0;
   const int v = lane;
+  const int row = warp * K::TV + v;  // this thread's row of the CTA tile
+  const uint32_t tmem_cols = m > 32 ? 64u : 32u;
+
+  if (m) {
+    if (warp == 0) pkv_tc::tmem_alloc(&s_tmem, tmem_cols);
+    if (threadIdx.x == 32) pkv_tc::mbar_init(&s_bar, 1);
+  } else if (warp == 0) {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
 
   // the warp's 32 vectors: 16 lanes x 16 bytes per vector, all copies in flight at once
   if (v < nv) s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
@@ -151,266 +224,255 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll 4
   for (int i = lane; i < nv * K::LPV; i += 32) {
     const int vv = i / K::LPV, q = i % K::LPV;
-    pkv_cp_async16(s_x + vv * K::XS + 4 * q, reinterpret_cast<const float4*>(x + s_off[vv]) + q);
+    pkv_cp_async16(s_xt + sw_piece(K::X_SLAB, warp * K::TV + vv, q),
+                   reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
-  for (int i = threadIdx.x; i < tp.projections * K::LPV; i += K::THREADS)
-    pkv_cp_async16(s_g + (i / K::LPV) * K::XS + 4 * (i % K::LPV), reinterpret_cast<const float4*>(tp.qjl) + i);
-  for (int i = threadIdx.x; i < tp.projections; i += K::THREADS)
-    pkv_cp_async4(s_thr + i, tp.qjl + tp.projections * D + i);
+  for (int i = threadIdx.x; i < m * K::LPV; i += K::THREADS)
+    pkv_cp_async16(s_gt + sw_piece(g_slab, i / K::LPV, i % K::LPV), reinterpret_cast<const float4*>(tp.qjl) + i);
   for (int i = threadIdx.x; i < lut_len; i += K::THREADS)  // cos / sin interleaved: one 8-byte read per pair
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : i < 2 * levels ? 2 * (i - levels) + 1 : i), tp.lut + i);
   pkv_cp_async_wait_all();
-  __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
+  if (m) pkv_tc::fence_before_sync();
+  __syncthreads();  // tables, barrier, tensor-memory base; the warp's own rows only need warp-level ordering until the product
+  if (m) pkv_tc::fence_after_sync();
 
   // Every lane runs the per-vector code (lanes beyond nv work on their unused tile rows and
-  // never report or get copied out), so the warp stays converged for the cooperative fix-up.
+  // never report or get copied out), so the warp stays converged for the cooperative steps.
   const bool valid = v < nv;
+  // piece c of this thread's vector sits at s_xt + (c >> 3) * X_SLAB + (xsw ^ ((c & 7) << 4))
+  const uint32_t xsw = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((row & 7) << 4));
+  uint32_t* w = s_w + v;
+  uint32_t* aw = w + rw * K::WS;
+  uint8_t* my_rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)(v0 + v) * g.rec_bytes;
+  int code = 0;
+  float y[D];
+#pragma unroll
+  for (int i = 0; i < D; i += 4) {
+    const float4 t = *reinterpret_cast<const float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)));
+    y[i] = t.x; y[i + 1] = t.y; y[i + 2] = t.z; y[i + 3] = t.w;
+  }
+  // FastHadamardRotation::apply, rotation.rs:202-210.  A non-finite input makes every output of
+  // the transform non-finite, so input finiteness is only looked at when a radius is bad.
+  fwht_forward_signed<D>(y, tp.sgn, tp.scale);
+
+  // Pass 1, encode_pair (polar.rs:413-421): radius exactly, bucket by the shortcut.  Radii go
+  // to the record (f32 codec) or to s_rad (BlockLogU8); undecided pairs are noted in `unc`.
+  float* radp = tp.lossy ? (s_rad + v) : reinterpret_cast<float*>(w);
+  constexpr int NW = PB ? K::P * PB / 32 : 1;
+  unsigned long long unc = 0;
   {
-    float* row = s_x + v * K::XS;
-    uint32_t* w = s_w + v;
-    uint32_t* aw = w + rw * K::WS;
-    uint8_t* my_rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)(v0 + v) * g.rec_bytes;
-    int code = 0;
-    float y[D];
+    uint32_t words[NW];
 #pragma unroll
-    for (int i = 0; i < D; i += 4) {
-      const float4 t = *reinterpret_cast<const float4*>(row + i);
-      y[i] = t.x; y[i + 1] = t.y; y[i + 2] = t.z; y[i + 3] = t.w;
-    }
-    // FastHadamardRotation::apply, rotation.rs:202-210.  A non-finite input makes every output of
-    // the transform non-finite, so input finiteness is only looked at when a radius is bad.
-    fwht_forward_signed<D>(y, tp.sgn, tp.scale);
-
-    // Pass 1, encode_pair (polar.rs:413-421): radius exactly, bucket by the shortcut.  Radii go
-    // to the record (f32 codec) or to s_rad (BlockLogU8); undecided pairs are noted in `unc`.
-    float* radp = tp.lossy ? (s_rad + v) : reinterpret_cast<float*>(w);
-    constexpr int NW = PB ? K::P * PB / 32 : 1;
-    unsigned long long unc = 0;
-    {
-      uint32_t words[NW];
+    for (int k = 0; k < NW; k++) words[k] = 0;
+    uint64_t bitbuf = 0;
+    int nbits = 0, wk = 0;
+    uint32_t rmax = 0;  // radii are >= 0 or NaN: the largest bit pattern tells if any is not finite
 #pragma unroll
-      for (int k = 0; k < NW; k++) words[k] = 0;
-      uint64_t bitbuf = 0;
-      int nbits = 0, wk = 0;
-      uint32_t rmax = 0;  // radii are >= 0 or NaN: the largest bit pattern tells if any is not finite
-#pragma unroll
-      for (int i = 0; i < K::P; i++) {
-        const float a = y[2 * i], b = y[2 * i + 1];
-        const float r = __fsqrt_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
-        int certain = 0;
-        uint32_t idx = 0;
-        if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
-        unc |= (unsigned long long)(certain ? 0u : 1u) << i;
-        rmax = max(rmax, __float_as_uint(r) & 0x7fffffffu);
-        if constexpr (DIRECT) y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
-        else radp[i * K::WS] = r;
-        if constexpr (PB != 0) {
-          const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
-          words[wi] |= idx << sh;
-          if (sh + PB > 32) words[wi + 1] |= idx >> (32 - sh);
-        } else {
-          bitbuf |= (uint64_t)idx << nbits;
-          nbits += pb;
-          if (nbits >= 32) {
-            aw[wk * K::WS] = (uint32_t)bitbuf;
-            wk++;
-            bitbuf >>= 32;
-            nbits -= 32;
-          }
-        }
-      }
+    for (int i = 0; i < K::P; i++) {
+      const float a = y[2 * i], b = y[2 * i + 1];
+      const float r = __fsqrt_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
+      int certain = 0;
+      uint32_t idx = 0;
+      if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
+      unc |= (unsigned long long)(certain ? 0u : 1u) << i;
+      rmax = max(rmax, __float_as_uint(r) & 0x7fffffffu);
+      if constexpr (DIRECT) y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
+      else radp[i * K::WS] = r;
       if constexpr (PB != 0) {
-#pragma unroll
-        for (int k = 0; k < NW; k++) aw[k * K::WS] = words[k];
-      } else if (nbits > 0) {
-        aw[wk * K::WS] = (uint32_t)bitbuf;
-      }
-      if (rmax >= 0x7f800000u) code = classify_bad_vector(row, D);
-    }
-    if (!valid) unc = 0;
-    for (unsigned pending = __ballot_sync(0xffffffffu, unc != 0); pending; pending &= pending - 1) {
-      const int src = __ffs(pending) - 1;  // settle lane src's undecided pairs, all lanes helping
-      const unsigned long long m =
-          ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
-          __shfl_sync(0xffffffffu, (uint32_t)unc, src);
-      fix_pairs_warp<D>(s_x + src * K::XS,
-                        make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]), tp.scale, m,
-                        s_w + src + rw * K::WS, K::WS, pb, lane);
-    }
-    if constexpr (DIRECT) {
-      if (valid) {
-#pragma unroll
-        for (int k = 0; k < K::P / 4; k++)
-          reinterpret_cast<float4*>(my_rec)[k] = make_float4(y[8 * k], y[8 * k + 2], y[8 * k + 4], y[8 * k + 6]);
-      }
-    }
-
-    if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
-      // polar.decode (polar.rs:272-278,306-316): de-quantised pairs from the final indices
-      {
-        const uint32_t mask = (uint32_t)levels - 1u;
-        uint32_t words[NW];
-        uint64_t bitbuf = 0;
-        int nbits = 0, wk = 0;
-        if constexpr (PB != 0) {
-#pragma unroll
-          for (int k = 0; k < NW; k++) words[k] = aw[k * K::WS];
-        }
-#pragma unroll
-        for (int i = 0; i < K::P; i++) {
-          uint32_t idx;
-          if constexpr (PB != 0) {
-            const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
-            idx = words[wi] >> sh;
-            if (sh + PB > 32) idx |= words[wi + 1] << (32 - sh);
-            idx &= mask;
-          } else {
-            if (nbits < pb) {
-              bitbuf |= (uint64_t)aw[wk * K::WS] << nbits;
-              wk++;
-              nbits += 32;
-            }
-            idx = (uint32_t)bitbuf & mask;
-            bitbuf >>= pb;
-            nbits -= pb;
-          }
-          const float r = DIRECT ? y[2 * i] : radp[i * K::WS];
-          const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
-          y[2 * i] = __fmul_rn(r, cs.x);
-          y[2 * i + 1] = __fmul_rn(r, cs.y);
+        const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
+        words[wi] |= idx << sh;
+        if (sh + PB > 32) words[wi + 1] |= idx >> (32 - sh);
+      } else {
+        bitbuf |= (uint64_t)idx << nbits;
+        nbits += pb;
+        if (nbits >= 32) {
+          aw[wk * K::WS] = (uint32_t)bitbuf;
+          wk++;
+          bitbuf >>= 32;
+          nbits -= 32;
         }
       }
-      // inverse rotation (rotation.rs:212-221), residual = vector - reconstruction (turbo.rs:268-273)
-      fwht_inverse_signed<D>(y, tp.sgn_scale);
-      float2 n2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-      for (int i = 0; i < D; i += 4) {
-        const float4 t = *reinterpret_cast<const float4*>(row + i);
-        y[i] = __fsub_rn(t.x, y[i]);
-        y[i + 1] = __fsub_rn(t.y, y[i + 1]);
-        y[i + 2] = __fsub_rn(t.z, y[i + 2]);
-        y[i + 3] = __fsub_rn(t.w, y[i + 3]);
-        n2 = ffma2(make_float2(y[i], y[i + 1]), make_float2(y[i], y[i + 1]), n2);
-        n2 = ffma2(make_float2(y[i + 2], y[i + 3]), make_float2(y[i + 2], y[i + 3]), n2);
-        // the residual replaces x in the tile: the exact dot of an undecided row reads it there
-        *reinterpret_cast<float4*>(row + i) = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
-      }
-      // a non-finite residual element makes the squared norm non-finite (qjl.rs:210)
-      const float nsq = n2.x + n2.y;
-      if (!code && !pkv_finite(nsq)) {
-        bool res_ok = true;
-        for (int i = 0; i < D; i++) res_ok = res_ok && pkv_finite(row[i]);
-        if (!res_ok) code = PKV_VEC_NONFINITE_RESIDUAL;
-      }
-      // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per projection row.
-      // The residual rows now sit in the warp's tile, and the 32 x m dots are taken as a small
-      // register-tiled product from shared memory: lane (vg, pg) owns vectors 4vg..4vg+3 and, per
-      // chunk of 32 projections, rows pg, pg+4, .., pg+28 (rows 4 apart sit in different banks),
-      // with packed fused multiply-adds over even / odd columns.  The sign of such a dot is the
-      // reference's whenever |dot| clears the rounding bound (pkv_fast_paths.h); otherwise the
-      // lane takes the exact sequential dot for that (vector, row).
-      float* s_rn = reinterpret_cast<float*>(s_off);  // the vector offsets are spent
-      s_rn[v] = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
-      __syncwarp();
-      {
-        const int vg = lane >> 2, pg = lane & 3;
-        const float* xr = s_x + (4 * vg) * K::XS;
-        const float4 rn4 = *reinterpret_cast<const float4*>(s_rn + 4 * vg);
-        const float rn[4] = {rn4.x, rn4.y, rn4.z, rn4.w};
-        uint32_t* sw = s_w + (rw + tp.angle_words) * K::WS;
-        for (int c = 0; c < tp.projections; c += 32) {
-          const float* gr = s_g + (c + pg) * K::XS;
-          float2 acc[4][8];
-#pragma unroll
-          for (int i = 0; i < 4; i++)
-#pragma unroll
-            for (int k = 0; k < 8; k++) acc[i][k] = make_float2(0.0f, 0.0f);
-#pragma unroll 2
-          for (int j = 0; j < D; j += 4) {
-            float4 r[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) r[i] = *reinterpret_cast<const float4*>(xr + i * K::XS + j);
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-              const float4 gk = *reinterpret_cast<const float4*>(gr + 4 * k * K::XS + j);
-#pragma unroll
-              for (int i = 0; i < 4; i++) {
-                acc[i][k] = ffma2(make_float2(gk.x, gk.y), make_float2(r[i].x, r[i].y), acc[i][k]);
-                acc[i][k] = ffma2(make_float2(gk.z, gk.w), make_float2(r[i].z, r[i].w), acc[i][k]);
-              }
-            }
-          }
-          uint32_t word[4];
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            word[i] = 0;
-            uint32_t unc8 = 0;  // rows k whose sign the bound does not settle
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-              const float dot = acc[i][k].x + acc[i][k].y;
-              const float tau = fmaf(s_thr[c + pg + 4 * k], rn[i], PKV_QJL_ABS_BOUND);
-              unc8 |= (fabsf(dot) > tau ? 0u : 1u) << k;
-              word[i] |= (dot >= 0.0f ? 1u : 0u) << (pg + 4 * k);
-            }
-            if (4 * vg + i >= nv) unc8 = 0;
-            while (unc8) {
-              const int k = __ffs(unc8) - 1;
-              unc8 &= unc8 - 1;
-              const float dot = exact_dot(s_g + (c + pg + 4 * k) * K::XS, xr + i * K::XS, D);
-              const uint32_t bit = 1u << (pg + 4 * k);
-              word[i] = dot >= 0.0f ? (word[i] | bit) : (word[i] & ~bit);
-            }
-            word[i] |= __shfl_xor_sync(0xffffffffu, word[i], 1);
-            word[i] |= __shfl_xor_sync(0xffffffffu, word[i], 2);
-          }
-          sw[(c >> 5) * K::WS + 4 * vg + pg] = pg == 0 ? word[0] : pg == 1 ? word[1] : pg == 2 ? word[2] : word[3];
-        }
-      }
-      __syncwarp();
     }
-    if (tp.lossy) {
-      // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371)
-      float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
-#pragma unroll 4
-      for (int i = 0; i < K::P; i++) {
-        float r = s_rad[i * K::WS + v];
-        r = (code || !(r > PKV_FLT_MIN)) ? PKV_FLT_MIN : r;
-        const float l = pkv_logf_portable(r);
-        s_rad[i * K::WS + v] = l;
-        mn = l < mn ? l : mn;
-        mx = l > mx ? l : mx;
-      }
-      float span = __fsub_rn(mx, mn);
-      if (!(span > PKV_FLT_EPS)) span = PKV_FLT_EPS;
-#pragma unroll 2
-      for (int k = 0; k < K::P / 4; k++) {
-        uint32_t q4 = 0;
+    if constexpr (PB != 0) {
 #pragma unroll
-        for (int b = 0; b < 4; b++) {
-          float nrm = __fdiv_rn(__fsub_rn(s_rad[(4 * k + b) * K::WS + v], mn), span);
-          nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
-          q4 |= ((uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu) << (8 * b);
-        }
-        w[k * K::WS] = q4;
-      }
-      w[(K::P / 4) * K::WS] = __float_as_uint(mn);
-      w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
+      for (int k = 0; k < NW; k++) aw[k * K::WS] = words[k];
+    } else if (nbits > 0) {
+      aw[wk * K::WS] = (uint32_t)bitbuf;
     }
-    if (valid && code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
-    if constexpr (DIRECT) {
-      if (valid) {  // angle and sign words (patched in place by the fix-ups) follow the radii
-        for (int k = 0; k < tile_words; k += 4)
-          *reinterpret_cast<uint4*>(my_rec + 4 * (K::P + k)) =
-              make_uint4(w[k * K::WS], w[(k + 1) * K::WS], w[(k + 2) * K::WS], w[(k + 3) * K::WS]);
-      }
+    if (rmax >= 0x7f800000u) code = classify_bad_vector(s_xt, K::X_SLAB, row, D);
+  }
+  if (!valid) unc = 0;
+  for (unsigned pending = __ballot_sync(0xffffffffu, unc != 0); pending; pending &= pending - 1) {
+    const int src = __ffs(pending) - 1;  // settle lane src's undecided pairs, all lanes helping
+    const unsigned long long um =
+        ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
+        __shfl_sync(0xffffffffu, (uint32_t)unc, src);
+    fix_pairs_warp<D>(s_xt, warp * K::TV + src,
+                      make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]), tp.scale, um,
+                      s_w + src + rw * K::WS, K::WS, pb, lane);
+  }
+  if constexpr (DIRECT) {
+    if (valid) {
+#pragma unroll
+      for (int k = 0; k < K::P / 4; k++)
+        reinterpret_cast<float4*>(my_rec)[k] = make_float4(y[8 * k], y[8 * k + 2], y[8 * k + 4], y[8 * k + 6]);
     }
   }
-  if constexpr (!DIRECT) {
+
+  if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
+    // polar.decode (polar.rs:272-278,306-316): de-quantised pairs from the final indices
+    {
+      const uint32_t mask = (uint32_t)levels - 1u;
+      uint32_t words[NW];
+      uint64_t bitbuf = 0;
+      int nbits = 0, wk = 0;
+      if constexpr (PB != 0) {
+#pragma unroll
+        for (int k = 0; k < NW; k++) words[k] = aw[k * K::WS];
+      }
+#pragma unroll
+      for (int i = 0; i < K::P; i++) {
+        uint32_t idx;
+        if constexpr (PB != 0) {
+          const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
+          idx = words[wi] >> sh;
+          if (sh + PB > 32) idx |= words[wi + 1] << (32 - sh);
+          idx &= mask;
+        } else {
+          if (nbits < pb) {
+            bitbuf |= (uint64_t)aw[wk * K::WS] << nbits;
+            wk++;
+            nbits += 32;
+          }
+          idx = (uint32_t)bitbuf & mask;
+          bitbuf >>= pb;
+          nbits -= pb;
+        }
+        const float r = DIRECT ? y[2 * i] : radp[i * K::WS];
+        const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
+        y[2 * i] = __fmul_rn(r, cs.x);
+        y[2 * i + 1] = __fmul_rn(r, cs.y);
+      }
+    }
+    // inverse rotation (rotation.rs:212-221), residual = vector - reconstruction (turbo.rs:268-273)
+    fwht_inverse_signed<D>(y, tp.sgn_scale);
+    float2 n2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < D; i += 4) {
+      float4* piece = reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)));
+      const float4 t = *piece;
+      y[i] = __fsub_rn(t.x, y[i]);
+      y[i + 1] = __fsub_rn(t.y, y[i + 1]);
+      y[i + 2] = __fsub_rn(t.z, y[i + 2]);
+      y[i + 3] = __fsub_rn(t.w, y[i + 3]);
+      n2 = ffma2(make_float2(y[i], y[i + 1]), make_float2(y[i], y[i + 1]), n2);
+      n2 = ffma2(make_float2(y[i + 2], y[i + 3]), make_float2(y[i + 2], y[i + 3]), n2);
+      // the residual replaces x in the tile: it is the A operand of the QJL product
+      *piece = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
+    }
+    // a non-finite residual element makes the squared norm non-finite (qjl.rs:210)
+    const float nsq = n2.x + n2.y;
+    if (!code && !pkv_finite(nsq)) {
+      bool res_ok = true;
+      for (int i = 0; i < D; i++) res_ok = res_ok && pkv_finite(*tile_at(s_xt, K::X_SLAB, row, i));
+      if (!res_ok) code = PKV_VEC_NONFINITE_RESIDUAL;
+    }
+    const float rnorm = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
+
+    // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per projection row.
+    // All 128 x m dots come from one TF32 product on the tensor cores: A = the CTA's residual
+    // tile, B = the matrix tile, D in tensor memory with row r in lane r.
+    pkv_tc::fence_smem_to_async();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      pkv_tc::fence_after_sync();
+      const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, m > 32 ? 64 : 32);
+      const uint32_t a0 = pkv_tc::smem_u32(s_xt), b0 = pkv_tc::smem_u32(s_gt);
+#pragma unroll 1
+      for (int k = 0; k < D / 8; k++)  // 8 columns = 32 bytes further along the rows; four steps per slab
+        pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
+                         pkv_tc::smem_desc_sw128(b0 + (k >> 2) * g_slab + (k & 3) * 32), idesc, k > 0);
+      pkv_tc::mma_commit(&s_bar);
+    }
+    const bool done = __all_sync(0xffffffffu, pkv_tc::mbar_wait(&s_bar, 0));
+    pkv_tc::fence_after_sync();
+    uint32_t* sw = w + (rw + tp.angle_words) * K::WS;
+    if (done) {
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {  // unrolled: the thresholds below are read at fixed parameter offsets
+        if (c >= m) break;
+        float dots[32];
+        pkv_tc::tmem_load32(s_tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, dots);
+        uint32_t bits = 0, flagged = 0;
+#pragma unroll
+        for (int p = 0; p < 32; p++) {
+          const float tau = fmaf(tp.qjl_thr_tf32[c + p], rnorm, PKV_QJL_ABS_BOUND);
+          flagged |= (fabsf(dots[p]) > tau ? 0u : 1u) << p;
+          bits |= (dots[p] >= 0.0f ? 1u : 0u) << p;
+        }
+        if (!valid) flagged = 0;
+        while (flagged) {  // second tier in binary32, third the reference's own sequence
+          const int p = __ffs(flagged) - 1;
+          flagged &= flagged - 1;
+          float dot = fused_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
+          // (this threshold is read from memory: indexing the parameter block with a run-time
+          // index would make every thread keep a private copy of the block)
+          const float tau = fmaf(__ldg(tp.qjl + m * D + c + p), rnorm, PKV_QJL_ABS_BOUND);
+          if (!(fabsf(dot) > tau)) dot = sequential_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
+          bits = dot >= 0.0f ? (bits | (1u << p)) : (bits & ~(1u << p));
+        }
+        sw[(c >> 5) * K::WS] = bits;
+      }
+    } else if (threadIdx.x == 0) {
+      pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
+    }
+  }
+  if (tp.lossy) {
+    // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371)
+    float mn = __int_as_float(0x7f800000), mx = __int_as_float(0xff800000);
+#pragma unroll 4
+    for (int i = 0; i < K::P; i++) {
+      float r = s_rad[i * K::WS + v];
+      r = (code || !(r > PKV_FLT_MIN)) ? PKV_FLT_MIN : r;
+      const float l = pkv_logf_portable(r);
+      s_rad[i * K::WS + v] = l;
+      mn = l < mn ? l : mn;
+      mx = l > mx ? l : mx;
+    }
+    float span = __fsub_rn(mx, mn);
+    if (!(span > PKV_FLT_EPS)) span = PKV_FLT_EPS;
+#pragma unroll 2
+    for (int k = 0; k < K::P / 4; k++) {
+      uint32_t q4 = 0;
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        float nrm = __fdiv_rn(__fsub_rn(s_rad[(4 * k + b) * K::WS + v], mn), span);
+        nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
+        q4 |= ((uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu) << (8 * b);
+      }
+      w[k * K::WS] = q4;
+    }
+    w[(K::P / 4) * K::WS] = __float_as_uint(mn);
+    w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
+  }
+  if (valid && code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
+  if constexpr (DIRECT) {
+    if (valid) {  // angle and sign words (patched in place by the fix-ups) follow the radii
+      for (int k = 0; k < tile_words; k += 4)
+        *reinterpret_cast<uint4*>(my_rec + 4 * (K::P + k)) =
+            make_uint4(w[k * K::WS], w[(k + 1) * K::WS], w[(k + 2) * K::WS], w[(k + 3) * K::WS]);
+    }
+  } else {
     __syncwarp();
     stage_records<D, false>(
         s_w, reinterpret_cast<uint32_t*>(payload + (int64_t)batch * g.payload_batch_stride +
                                          (int64_t)v0 * g.rec_bytes),
         nv, tp.rec_words, lane);
+  }
+  if (m) {  // every warp has read its accumulator rows: the columns can go back
+    pkv_tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) pkv_tc::tmem_free(s_tmem, tmem_cols);
   }
 }
 
@@ -422,7 +484,7 @@ template <int D>
 size_t turbo_encode_smem(const TurboParams& tp) {
   const int tile_words = turbo_encode_direct(tp) ? tp.angle_words + tp.sign_words : tp.rec_words;
   return TurboEncSmem<D>::table_bytes(tp.projections, 1 << tp.polar_bits, tp.ray_count) +
-         Turbo<D>::NWARPS * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
+         TurboEnc<D>::NWARPS * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
 }
 
 }  // namespace pkv_turbo

@@ -33,3 +33,15 @@ def test_qjl_sign_shortcut_never_decides_wrong(oracle_mod, dim, scale):
     assert wrong == 0
     assert decided >= 99_000          # ordinary residuals are decided by the fused dot
     assert undecided >= 50_000        # near-orthogonal ones are not
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("variant", [0, 1])  # operand shortening by truncation / by rounding
+@pytest.mark.parametrize("scale", [1.0, 1e-3, 1e15, 1e-15])
+def test_qjl_tf32_tier_never_decides_wrong(oracle_mod, dim, variant, scale):
+    fn = oracle_mod.lib().pkvo_fast_qjl_tf32_check
+    fn.argtypes = [C.c_int, C.c_int64, C.c_uint64, C.c_double, C.c_int, C.POINTER(C.c_int64)]
+    wrong, undecided, decided = _counts(fn, dim, 400_000, dim + 5, scale, variant)
+    assert wrong == 0
+    assert decided >= 190_000         # ordinary residuals: ~98.6 % decided on the tensor cores
+    assert undecided >= 20_000        # dots near the threshold go on to the binary32 tier
