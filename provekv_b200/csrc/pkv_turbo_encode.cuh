@@ -22,6 +22,12 @@
 
 namespace pkv_turbo {
 
+// Entries of the per-warp list of (vector, row) pairs awaiting the second tier (at most 64: the
+// list and the 32 residual norms share the 256 bytes that held the vector offsets).
+#ifndef PKV_QJL_LIST_CAP
+#define PKV_QJL_LIST_CAP 64
+#endif
+
 template <int D>
 struct TurboEnc {
   static constexpr int NWARPS = 4;  // one CTA = one 128-row tensor-core tile
@@ -159,7 +165,7 @@ struct TurboEncSmem {
   static __host__ __device__ size_t table_bytes(int projections, int levels, int ray_count) {
     // 1024: the swizzled tiles start on a 1024-byte boundary found at run time
     const size_t n = 1024 + (size_t)K::X_BYTES + (size_t)K::SLABS * projections * 128 +
-                     sizeof(float) * (2 * levels + 2 * ray_count);
+                     sizeof(float) * (2 * levels + 2 * ray_count + projections);
     return (n + 15) & ~(size_t)15;
   }
   static __host__ __device__ size_t warp_bytes(int tile_words, int lossy) {
@@ -191,6 +197,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   uint8_t* s_gt = s_xt + K::X_BYTES;                                           // QJL matrix, SLABS x [m rows][128 B]
   float* s_lut = reinterpret_cast<float*>(s_gt + K::SLABS * g_slab);           // (cos, sin)[L], ray_cos, ray_sin
   const int lut_len = 2 * levels + 2 * tp.ray_count;
+  float* s_thr = s_lut + lut_len;  // [m] binary32-tier thresholds of the sign shortcut
   const float* s_ray_cos = s_lut + 2 * levels;
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
   const int rw = DIRECT ? 0 : tp.radii_words;  // radii words present in the shared tile
@@ -229,6 +236,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   }
   for (int i = threadIdx.x; i < m * K::LPV; i += K::THREADS)
     pkv_cp_async16(s_gt + sw_piece(g_slab, i / K::LPV, i % K::LPV), reinterpret_cast<const float4*>(tp.qjl) + i);
+  for (int i = threadIdx.x; i < m; i += K::THREADS) pkv_cp_async4(s_thr + i, tp.qjl + m * D + i);
   for (int i = threadIdx.x; i < lut_len; i += K::THREADS)  // cos / sin interleaved: one 8-byte read per pair
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : i < 2 * levels ? 2 * (i - levels) + 1 : i), tp.lut + i);
   pkv_cp_async_wait_all();
@@ -410,16 +418,54 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           flagged |= (fabsf(dots[p]) > tau ? 0u : 1u) << p;
           bits |= (dots[p] >= 0.0f ? 1u : 0u) << p;
         }
-        if (!valid) flagged = 0;
-        while (flagged) {  // second tier in binary32, third the reference's own sequence
-          const int p = __ffs(flagged) - 1;
-          flagged &= flagged - 1;
-          float dot = fused_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
-          // (this threshold is read from memory: indexing the parameter block with a run-time
-          // index would make every thread keep a private copy of the block)
-          const float tau = fmaf(__ldg(tp.qjl + m * D + c + p), rnorm, PKV_QJL_ABS_BOUND);
-          if (!(fabsf(dot) > tau)) dot = sequential_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
-          bits = dot >= 0.0f ? (bits | (1u << p)) : (bits & ~(1u << p));
+        // an all-zero residual gives +-0 for every dot: sign bit 1 without further tests
+        if (!valid || nsq == 0.0f) flagged = 0;
+        // Second tier (binary32 fused dot) and third (the reference's own sequence) for the flagged
+        // (vector, row) pairs of the whole warp, spread over the lanes: each lane lists its pairs
+        // at the position a prefix sum gives it, lane j settles list entry j, the owner reads the
+        // sign back.  Pairs beyond the list's capacity are settled by their owner.
+        const uint32_t cnt = __popc(flagged);
+        uint32_t incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += t;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        if (total) {
+          constexpr uint32_t CAP = PKV_QJL_LIST_CAP;
+          float* s_rn = reinterpret_cast<float*>(s_off);                   // [32] (the offsets are spent)
+          uint16_t* list = reinterpret_cast<uint16_t*>(s_rn + K::TV);      // [CAP]
+          s_rn[v] = rnorm;
+          uint32_t pos = incl - cnt;
+          for (uint32_t f = flagged; f; f &= f - 1, pos++)
+            if (pos < CAP) list[pos] = (uint16_t)((v << 5) | (__ffs(f) - 1));
+          __syncwarp();
+          const uint32_t n_list = min(total, CAP);
+          for (uint32_t e = lane; e < n_list; e += 32) {
+            const uint32_t it = list[e];
+            const int r = warp * K::TV + (int)(it >> 5), p = c + (int)(it & 31u);
+            float dot = fused_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
+            const float tau = fmaf(s_thr[p], s_rn[it >> 5], PKV_QJL_ABS_BOUND);
+            if (!(fabsf(dot) > tau)) dot = sequential_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
+            list[e] = (uint16_t)(it | (dot >= 0.0f ? 0x8000u : 0u));
+          }
+          __syncwarp();
+          pos = incl - cnt;
+          for (uint32_t f = flagged; f; f &= f - 1, pos++) {
+            const int p = __ffs(f) - 1;
+            bool plus;
+            if (pos < CAP) {
+              plus = (list[pos] & 0x8000u) != 0;
+            } else {
+              float dot = fused_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
+              const float tau = fmaf(s_thr[c + p], rnorm, PKV_QJL_ABS_BOUND);
+              if (!(fabsf(dot) > tau)) dot = sequential_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
+              plus = dot >= 0.0f;
+            }
+            bits = plus ? (bits | (1u << p)) : (bits & ~(1u << p));
+          }
+          __syncwarp();
         }
         sw[(c >> 5) * K::WS] = bits;
       }
