@@ -233,3 +233,44 @@ def test_full_size_cold_tier_bytes_and_roundtrip(oracle_mod):
     assert np.array_equal(dec.view(np.uint32), ref.view(np.uint32))
     rel = float(((out - kv) ** 2).sum() / (kv ** 2).sum())
     assert 0.05 < rel < 0.4
+
+
+@pytest.mark.parametrize("kind", ["turbo", "turbo_lossy"])
+def test_full_size_hot_shells_bytes_and_roundtrip(oracle_mod, kind):
+    """C2: 8 agents x 28-token hot shells of a SmolLM2-1.7B shaped cache = 344,064 vectors
+    (88.1 MB f32), turbo b=4: every TQB1 record byte against the multi-threaded oracle (11 M QJL
+    signs, so all three tiers of the sign certification are taken many times), then the decode
+    patched into an 800-token cache at each agent's position."""
+    torch = _torch()
+    shape = pool.SMOLLM2_1_7B
+    A, T, d, cap = 8, 28, 64, 1024
+    prof = _profiles(d)[kind]
+    n = A * shape.vectors(T)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    scale = torch.exp(0.5 * torch.randn((1, 24, 1, 32, 1, d), generator=gen, device="cuda"))
+    kv = (torch.randn((A, 24, 2, 32, T, d), generator=gen, device="cuda") * scale).contiguous()
+    vpb, rec = T * 32, prof.record_bytes
+    stride = pool.payload_batch_stride(vpb, rec)
+    payload = torch.zeros((A * 48, stride), dtype=torch.uint8, device="cuda")
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    prof.encode_dev(kv.data_ptr(), pool.kv_tensor_layout(shape, A, T), payload.data_ptr(), stride,
+                    err.data_ptr())
+    pk.read_error_word(err.data_ptr())
+    got = payload[:, :vpb * rec].cpu().numpy().reshape(n, rec)
+    gathered = kv.permute(0, 1, 2, 4, 3, 5).reshape(n, d).cpu().numpy()
+    want = _oracle_encode(oracle_mod, kind, prof, gathered)
+    assert np.array_equal(got, want)
+    first = pool.agent_patch_position(800, T, 0)
+    cache = torch.full((A, 24, 2, 32, cap, d), 7.0, device="cuda")
+    prof.decode_patch_dev(payload.data_ptr(), stride,
+                          pool.kv_tensor_layout(shape, A, T, token_capacity=cap, first_token=first),
+                          cache.data_ptr(), err.data_ptr())
+    pk.read_error_word(err.data_ptr())
+    patched = cache[:, :, :, :, first:first + T, :]
+    sample = slice(0, n, 53)
+    dec = patched.permute(0, 1, 2, 4, 3, 5).reshape(n, d)[sample].cpu().numpy()
+    ref = _oracle_decode(oracle_mod, kind, prof, want[sample], d)
+    assert np.array_equal(dec.view(np.uint32), ref.view(np.uint32))
+    assert bool((cache[:, :, :, :, :first, :] == 7.0).all()) and bool((cache[:, :, :, :, first + T:, :] == 7.0).all())
+    rel = float(((patched - kv) ** 2).sum() / (kv ** 2).sum())
+    assert 0.01 < rel < 0.4
