@@ -21,6 +21,7 @@
  *   PKVO_LIBM_PORTABLE (1): include/pkv_portable_math.h, the definition the
  *                           GPU kernels implement bit for bit.
  */
+#include <float.h>
 #include <math.h>
 #include <pthread.h>
 #include <stdint.h>
@@ -1022,6 +1023,46 @@ PKVO_API void pkvo_fast_qjl_tf32_check(int dim, int64_t n, uint64_t seed, double
     float ref = 0.0f;
     for (int j = 0; j < dim; j++) ref += g[j] * x[j];
     if ((ref >= 0.0f) != (fast >= 0.0f)) counts[0]++;
+  }
+}
+
+/* BlockLogU8 code shortcut: the fast logarithm is modelled as the exact one displaced by up to
+ * the documented error (max(2^-21.41, 3 ulp)) in either direction; counts as in the other checks. */
+PKVO_API void pkvo_fast_radius_code_check(int64_t n, uint64_t seed, double spread, int64_t* counts) {
+  uint64_t s = seed * 11400714819323198485ull + 7;
+  counts[0] = counts[1] = counts[2] = 0;
+  for (int64_t i = 0; i < n; i++) {
+    float r[32], mn = INFINITY, mx = -INFINITY;
+    const double centre = (unif(&s) - 0.5) * 40.0;
+    for (int j = 0; j < 32; j++) {
+      r[j] = (float)exp(centre + (unif(&s) - 0.5) * spread);
+      if (!(r[j] > FLT_MIN)) r[j] = FLT_MIN;
+      const float l = pkv_logf_portable(r[j]);
+      mn = l < mn ? l : mn;
+      mx = l > mx ? l : mx;
+    }
+    float span = mx - mn;
+    if (!(span > FLT_EPSILON)) span = FLT_EPSILON;
+    const float k = 255.0f / span;
+    for (int j = 0; j < 32; j++) {
+      const float l = pkv_logf_portable(r[j]);
+      float nrm = (l - mn) / span;
+      nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
+      const uint32_t want = (uint32_t)roundf(nrm * 255.0f) & 0xffu;
+      const double exact = log((double)r[j]);
+      const double ulp = ldexp(1.0, ilogb(fabs(exact) > 1e-300 ? fabs(exact) : 1e-300) - 23);
+      double e = 3.0 * ulp;
+      if (e < 3.6e-7) e = 3.6e-7;
+      for (int side = -1; side <= 1; side++) {
+        int certain;
+        const uint32_t got = pkv_fast_radius_code((float)(exact + side * e), mn, k, &certain);
+        if (!certain) counts[1]++;
+        else {
+          counts[2]++;
+          if (got != want) counts[0]++;
+        }
+      }
+    }
   }
 }
 

@@ -116,6 +116,28 @@ PKV_HD uint32_t pkv_fast_bucket_any(float a, float b, int polar_bits, const floa
 /* Absolute floor covering products that underflow to subnormals. */
 #define PKV_QJL_ABS_BOUND 1.0e-35f
 
+/* BlockLogU8 radius code (turbo-quant/src/radius.rs:58-77) from an approximate logarithm.
+ * The reference takes q = round(255 * clamp((ln r - mn) / span)) in binary32.  With l~ within
+ * eps_l of the logarithm the reference uses and k ~ 255 / span, s~ = (l~ - mn) k differs from the
+ * reference's 255 * nrm by at most eps_l * k plus the roundings of both chains (three binary32
+ * roundings each, together below 1.2e-4 code units), so q is the nearest integer of s~ unless s~
+ * lies that close to a half.  eps_l: the fast device logarithm is documented to stay within
+ * 2^-21.41 absolute on [0.5, 2] and 3 ulp elsewhere; 5.4e-7 * max(1, |l~|) is 1.5 times that.
+ * A span too small for the bound to mean anything (delta >= 1/4) is never certain. */
+#define PKV_RADII_LOG_REL 5.4e-7f
+#define PKV_RADII_CHAIN_ABS 3.0e-4f
+PKV_HD uint32_t pkv_fast_radius_code(float l_approx, float mn, float k, int* certain) {
+  float st = PKV_FMUL(PKV_FSUB(l_approx, mn), k);
+  const float al = l_approx < 0.0f ? -l_approx : l_approx;
+  const float delta = PKV_FADD(PKV_FMUL(PKV_FMUL(PKV_RADII_LOG_REL, al > 1.0f ? al : 1.0f), k), PKV_RADII_CHAIN_ABS);
+  st = st < 0.0f ? 0.0f : (st > 255.0f ? 255.0f : st);
+  const uint32_t fl = (uint32_t)st; /* st >= 0: truncation is the floor */
+  const float fr = PKV_FSUB(st, (float)fl);
+  const float d = fr > 0.5f ? PKV_FSUB(fr, 0.5f) : PKV_FSUB(0.5f, fr);
+  *certain = d > delta && delta < 0.25f;
+  return fl + (fr > 0.5f ? 1u : 0u);
+}
+
 /* ------------------------------------------------------------------------------------------
  * fib-quant encoder shortcuts (fib-quant/src/codec.rs:578-729).
  *

@@ -35,6 +35,18 @@ def test_qjl_sign_shortcut_never_decides_wrong(oracle_mod, dim, scale):
     assert undecided >= 50_000        # near-orthogonal ones are not
 
 
+@pytest.mark.parametrize("spread", [6.0, 1.0, 1e-2, 1e-5, 0.0])
+def test_radius_code_shortcut_never_decides_wrong(oracle_mod, spread):
+    fn = oracle_mod.lib().pkvo_fast_radius_code_check
+    fn.argtypes = [C.c_int64, C.c_uint64, C.c_double, C.POINTER(C.c_int64)]
+    wrong, undecided, decided = _counts(fn, 20_000, 11, spread)
+    assert wrong == 0
+    if spread >= 1.0:
+        assert decided > 0.99 * (decided + undecided)   # ordinary blocks: the fast logarithm decides
+    if spread <= 1e-5:
+        assert decided == 0                             # degenerate span: always the exact path
+
+
 @pytest.mark.parametrize("dim", [64, 128])
 @pytest.mark.parametrize("variant", [0, 1])  # operand shortening by truncation / by rounding
 @pytest.mark.parametrize("scale", [1.0, 1e-3, 1e15, 1e-15])
