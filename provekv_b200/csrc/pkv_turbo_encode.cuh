@@ -28,16 +28,10 @@ namespace pkv_turbo {
 #define PKV_QJL_LIST_CAP 64
 #endif
 
-// 128-row groups (4 warps, one tensor-core tile each) per CTA.
-#ifndef PKV_TURBO_ENC_GROUPS
-#define PKV_TURBO_ENC_GROUPS 1
-#endif
-
 template <int D>
 struct TurboEnc {
-  static constexpr int GROUPS = D == 64 ? PKV_TURBO_ENC_GROUPS : 1;
-  static constexpr int NWARPS = 4 * GROUPS;
-  static constexpr int THREADS = 32 * NWARPS, ROWS = 128, TV = 32, WS = 33, P = D / 2, LPV = D / 4;
+  static constexpr int NWARPS = 4;  // one CTA = one 128-row tensor-core tile
+  static constexpr int THREADS = 128, ROWS = 128, TV = 32, WS = 33, P = D / 2, LPV = D / 4;
   static constexpr int SLABS = D / 32;          // 128-byte column blocks per row
   static constexpr int X_SLAB = ROWS * 128;     // bytes per slab of the vector tile
   static constexpr int X_BYTES = SLABS * X_SLAB;
@@ -170,7 +164,7 @@ struct TurboEncSmem {
   // CTA-wide: vector tile, QJL matrix tile, cos/sin + ray tables; then one slice per warp
   static __host__ __device__ size_t table_bytes(int projections, int levels, int ray_count) {
     // 1024: the swizzled tiles start on a 1024-byte boundary found at run time
-    const size_t n = 1024 + (size_t)K::GROUPS * K::X_BYTES + (size_t)K::SLABS * projections * 128 +
+    const size_t n = 1024 + (size_t)K::X_BYTES + (size_t)K::SLABS * projections * 128 +
                      sizeof(float) * (2 * levels + 2 * ray_count + projections);
     return (n + 15) & ~(size_t)15;
   }
@@ -187,23 +181,20 @@ struct TurboEncSmem {
 // sit in a small shared tile so that the cooperative fix-up can patch them.  The staged variant
 // handles every other record shape through a word-transposed tile.
 template <int D, int PB, bool DIRECT>
-__global__ void __launch_bounds__(TurboEnc<D>::THREADS, (D == 64 && DIRECT) ? 4 / TurboEnc<D>::GROUPS : 1)
+__global__ void __launch_bounds__(TurboEnc<D>::THREADS, (D == 64 && DIRECT) ? 4 : 1)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                     uint8_t* __restrict__ payload, uint64_t* err) {
   using K = TurboEnc<D>;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t s_bars[K::GROUPS];  // completion of each group's tensor-core product
-  __shared__ uint32_t s_tmem;                          // base of the CTA's tensor-memory columns
+  __shared__ __align__(8) uint64_t s_bar;  // completion of the tensor-core product
+  __shared__ uint32_t s_tmem;              // base of the CTA's tensor-memory columns
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int grp = warp >> 2, gw = warp & 3;  // 128-row group and the warp's place in it
-  uint64_t& s_bar = s_bars[grp];
   const int m = tp.projections;  // 0 without the QJL stage
   const int g_slab = m * 128;
-  uint8_t* s_x0 = smem + ((1024u - (pkv_tc::smem_u32(smem) & 1023u)) & 1023u);
-  uint8_t* s_xt = s_x0 + grp * K::X_BYTES;               // the group's vector tile, SLABS x [128 rows][128 B]
-  uint8_t* s_gt = s_x0 + K::GROUPS * K::X_BYTES;         // QJL matrix, SLABS x [m rows][128 B]
+  uint8_t* s_xt = smem + ((1024u - (pkv_tc::smem_u32(smem) & 1023u)) & 1023u);  // vector tile, SLABS x [128 rows][128 B]
+  uint8_t* s_gt = s_xt + K::X_BYTES;                                           // QJL matrix, SLABS x [m rows][128 B]
   float* s_lut = reinterpret_cast<float*>(s_gt + K::SLABS * g_slab);           // (cos, sin)[L], ray_cos, ray_sin
   const int lut_len = 2 * levels + 2 * tp.ray_count;
   float* s_thr = s_lut + lut_len;  // [m] binary32-tier thresholds of the sign shortcut
@@ -224,13 +215,12 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   const int v0 = tile * K::TV;
   const int nv = active ? min(K::TV, g.vpb - v0) : 0;
   const int v = lane;
-  const int row = gw * K::TV + v;  // this thread's row of the group's tile
-  const uint32_t grp_cols = m > 32 ? 64u : 32u, tmem_cols = grp_cols * K::GROUPS;
+  const int row = warp * K::TV + v;  // this thread's row of the CTA tile
+  const uint32_t tmem_cols = m > 32 ? 64u : 32u;
 
   if (m) {
     if (warp == 0) pkv_tc::tmem_alloc(&s_tmem, tmem_cols);
-    if (threadIdx.x == 32)
-      for (int i = 0; i < K::GROUPS; i++) pkv_tc::mbar_init(&s_bars[i], 1);
+    if (threadIdx.x == 32) pkv_tc::mbar_init(&s_bar, 1);
   } else if (warp == 0) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -241,7 +231,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll 4
   for (int i = lane; i < nv * K::LPV; i += 32) {
     const int vv = i / K::LPV, q = i % K::LPV;
-    pkv_cp_async16(s_xt + sw_piece(K::X_SLAB, gw * K::TV + vv, q),
+    pkv_cp_async16(s_xt + sw_piece(K::X_SLAB, warp * K::TV + vv, q),
                    reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
   for (int i = threadIdx.x; i < m * K::LPV; i += K::THREADS)
@@ -325,7 +315,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     const unsigned long long um =
         ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
         __shfl_sync(0xffffffffu, (uint32_t)unc, src);
-    fix_pairs_warp<D>(s_xt, gw * K::TV + src,
+    fix_pairs_warp<D>(s_xt, warp * K::TV + src,
                       make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]), tp.scale, um,
                       s_w + src + rw * K::WS, K::WS, pb, lane);
   }
@@ -401,10 +391,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     // All 128 x m dots come from one TF32 product on the tensor cores: A = the CTA's residual
     // tile, B = the matrix tile, D in tensor memory with row r in lane r.
     pkv_tc::fence_smem_to_async();
-    if constexpr (K::GROUPS == 1) __syncthreads();
-    else asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");  // the group's four warps
-    const uint32_t tmem_d = s_tmem + (uint32_t)grp * grp_cols;
-    if ((threadIdx.x & 127) == 0) {
+    __syncthreads();
+    const uint32_t tmem_d = s_tmem;
+    if (threadIdx.x == 0) {
       pkv_tc::fence_after_sync();
       const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, m > 32 ? 64 : 32);
       const uint32_t a0 = pkv_tc::smem_u32(s_xt), b0 = pkv_tc::smem_u32(s_gt);
@@ -422,7 +411,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       for (int c = 0; c < 64; c += 32) {  // unrolled: the thresholds below are read at fixed parameter offsets
         if (c >= m) break;
         float dots[32];
-        pkv_tc::tmem_load32(tmem_d + ((uint32_t)(gw * 32) << 16) + (uint32_t)c, dots);
+        pkv_tc::tmem_load32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, dots);
         uint32_t bits = 0, flagged = 0;
 #pragma unroll
         for (int p = 0; p < 32; p++) {
@@ -456,7 +445,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           const uint32_t n_list = min(total, CAP);
           for (uint32_t e = lane; e < n_list; e += 32) {
             const uint32_t it = list[e];
-            const int r = gw * K::TV + (int)(it >> 5), p = c + (int)(it & 31u);
+            const int r = warp * K::TV + (int)(it >> 5), p = c + (int)(it & 31u);
             float dot = fused_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
             const float tau = fmaf(s_thr[p], s_rn[it >> 5], PKV_QJL_ABS_BOUND);
             if (!(fabsf(dot) > tau)) dot = sequential_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
