@@ -60,6 +60,27 @@ __device__ __forceinline__ void fwht_regs(float (&v)[D], float scale) {
   for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], scale);
 }
 
+// Packed two-lane f32 add / subtract / multiply (sm_100): each lane is the IEEE operation of its
+// own pair of inputs, so a butterfly on two adjacent coordinates costs one issue slot per output
+// pair.  The pair (v[i], v[i + 1]) must sit in an aligned register pair; the arrays below are only
+// ever touched in such pairs once past the first stage.
+__device__ __forceinline__ void add_sub2(float& a0, float& a1, float& b0, float& b1) {
+  unsigned long long pa, pb, ps, pd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pb) : "f"(b0), "f"(b1));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(ps) : "l"(pa), "l"(pb));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(pd) : "l"(pa), "l"(pb));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(ps));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(pd));
+}
+__device__ __forceinline__ void mul2(float& a0, float& a1, float m0, float m1) {
+  unsigned long long pa, pm, pr;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pm) : "f"(m0), "f"(m1));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(pa), "l"(pm));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(pr));
+}
+
 // Forward rotation, FastHadamardRotation::apply (rotation.rs:202-210): signs, butterflies, scale.
 // The sign multiplications are folded into the first butterfly stage: with a' = a * sa (exact),
 // fma(b, sb, a') = RN(a' + sb b) and fma(b, -sb, a') = RN(a' - sb b) are the reference's rounded
@@ -77,15 +98,11 @@ __device__ __forceinline__ void fwht_forward_signed(float (&v)[D], const float (
 #pragma unroll
     for (int start = 0; start < D; start += 2 * step) {
 #pragma unroll
-      for (int o = 0; o < step; o++) {
-        const float a = v[start + o], b = v[start + o + step];
-        v[start + o] = __fadd_rn(a, b);
-        v[start + o + step] = __fsub_rn(a, b);
-      }
+      for (int o = 0; o < step; o += 2) add_sub2(v[start + o], v[start + o + 1], v[start + o + step], v[start + o + step + 1]);
     }
   }
 #pragma unroll
-  for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], scale);
+  for (int i = 0; i < D; i += 2) mul2(v[i], v[i + 1], scale, scale);
 }
 
 // Inverse rotation, FastHadamardRotation::apply_inverse (rotation.rs:212-221): butterflies, scale,
@@ -93,19 +110,21 @@ __device__ __forceinline__ void fwht_forward_signed(float (&v)[D], const float (
 template <int D>
 __device__ __forceinline__ void fwht_inverse_signed(float (&v)[D], const float (&sgn_scale)[128]) {
 #pragma unroll
-  for (int step = 1; step < D; step <<= 1) {
+  for (int i = 0; i < D; i += 2) {
+    const float a = v[i], b = v[i + 1];
+    v[i] = __fadd_rn(a, b);
+    v[i + 1] = __fsub_rn(a, b);
+  }
+#pragma unroll
+  for (int step = 2; step < D; step <<= 1) {
 #pragma unroll
     for (int start = 0; start < D; start += 2 * step) {
 #pragma unroll
-      for (int o = 0; o < step; o++) {
-        const float a = v[start + o], b = v[start + o + step];
-        v[start + o] = __fadd_rn(a, b);
-        v[start + o + step] = __fsub_rn(a, b);
-      }
+      for (int o = 0; o < step; o += 2) add_sub2(v[start + o], v[start + o + 1], v[start + o + step], v[start + o + step + 1]);
     }
   }
 #pragma unroll
-  for (int i = 0; i < D; i++) v[i] = __fmul_rn(v[i], sgn_scale[i]);
+  for (int i = 0; i < D; i += 2) mul2(v[i], v[i + 1], sgn_scale[i], sgn_scale[i + 1]);
 }
 
 // value * sign with sign = +-1.0 is a sign-bit flip (also for zeros and NaNs).
