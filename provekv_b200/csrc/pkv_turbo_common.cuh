@@ -73,6 +73,13 @@ __device__ __forceinline__ void add_sub2(float& a0, float& a1, float& b0, float&
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(ps));
   asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(pd));
 }
+__device__ __forceinline__ void sub2(float& a0, float& a1, float b0, float b1) {  // a -= b
+  unsigned long long pa, pb, pr;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pb) : "f"(b0), "f"(b1));
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(pa), "l"(pb));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(pr));
+}
 __device__ __forceinline__ void mul2(float& a0, float& a1, float m0, float m1) {
   unsigned long long pa, pm, pr;
   asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));

@@ -110,8 +110,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
         idx &= mask;
         const float r = y[2 * i];
         const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
-        y[2 * i] = __fmul_rn(r, cs.x);      // r * theta.cos(), polar.rs:312
-        y[2 * i + 1] = __fmul_rn(r, cs.y);  // r * theta.sin(), polar.rs:313
+        y[2 * i] = cs.x;
+        y[2 * i + 1] = cs.y;
+        mul2(y[2 * i], y[2 * i + 1], r, r);  // (r * theta.cos(), r * theta.sin()), polar.rs:312-313
       }
     } else {
       uint64_t bitbuf = 0;
@@ -128,8 +129,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
         nbits -= pb;
         const float r = y[2 * i];
         const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
-        y[2 * i] = __fmul_rn(r, cs.x);
-        y[2 * i + 1] = __fmul_rn(r, cs.y);
+        y[2 * i] = cs.x;
+        y[2 * i + 1] = cs.y;
+        mul2(y[2 * i], y[2 * i + 1], r, r);
       }
     }
     if (code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);

@@ -278,7 +278,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll
     for (int i = 0; i < K::P; i++) {
       const float a = y[2 * i], b = y[2 * i + 1];
-      const float r = __fsqrt_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
+      float aa = a, bb = b;
+      mul2(aa, bb, a, b);  // (a * a, b * b), each rounded on its own
+      const float r = __fsqrt_rn(__fadd_rn(aa, bb));
       int certain = 0;
       uint32_t idx = 0;
       if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
@@ -358,8 +360,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         }
         const float r = DIRECT ? y[2 * i] : radp[i * K::WS];
         const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
-        y[2 * i] = __fmul_rn(r, cs.x);
-        y[2 * i + 1] = __fmul_rn(r, cs.y);
+        y[2 * i] = cs.x;
+        y[2 * i + 1] = cs.y;
+        mul2(y[2 * i], y[2 * i + 1], r, r);  // (r cos, r sin)
       }
     }
     // inverse rotation (rotation.rs:212-221), residual = vector - reconstruction (turbo.rs:268-273)
@@ -369,10 +372,10 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     for (int i = 0; i < D; i += 4) {
       float4* piece = reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)));
       const float4 t = *piece;
-      y[i] = __fsub_rn(t.x, y[i]);
-      y[i + 1] = __fsub_rn(t.y, y[i + 1]);
-      y[i + 2] = __fsub_rn(t.z, y[i + 2]);
-      y[i + 3] = __fsub_rn(t.w, y[i + 3]);
+      float r0 = t.x, r1 = t.y, r2 = t.z, r3 = t.w;
+      sub2(r0, r1, y[i], y[i + 1]);
+      sub2(r2, r3, y[i + 2], y[i + 3]);
+      y[i] = r0; y[i + 1] = r1; y[i + 2] = r2; y[i + 3] = r3;
       n2 = ffma2(make_float2(y[i], y[i + 1]), make_float2(y[i], y[i + 1]), n2);
       n2 = ffma2(make_float2(y[i + 2], y[i + 3]), make_float2(y[i + 2], y[i + 3]), n2);
       // the residual replaces x in the tile: it is the A operand of the QJL product
