@@ -125,6 +125,8 @@ struct pkv_fib_profile {
   double* rot_dev;      // [r][j] f64 (exact fix-up of undecided blocks)
   float* rot32_t_dev;   // [j][r] = (f32) M[r][j] (shortcut encoder)
   float* half_norm_dev; // |c|^2 / 2 per codeword
+  float* rot_hi_dev;    // [r][j] (f32) M[r][j] with the 13 low significand bits cleared (TF32 operand)
+  float* rot_lo_dev;    // [r][j] (f32) M[r][j] - rot_hi, exact
   PkvWorkspace ws;
 };
 

@@ -18,8 +18,19 @@
 #define PKV_FSUB(a, b) __fsub_rn((a), (b))
 #define PKV_FADD(a, b) __fadd_rn((a), (b))
 #define PKV_FSQRT(a) __fsqrt_rn(a)
+/* An upper bound of the square root for use inside error bounds: the one-instruction approximation
+ * (relative error below 2^-22) scaled up by 1e-5; an argument small enough to be flushed to zero
+ * contributes less than the constant term of every bound it is used in.  The host build uses the
+ * exact root, which is smaller: the device certifies a subset of what the host-side checks cover. */
+static __device__ __forceinline__ float pkv_sqrt_upper(float a) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(a));
+  return __fmul_rn(r, 1.00001f);
+}
+#define PKV_FSQRT_UP(a) pkv_sqrt_upper(a)
 #else
 #define PKV_FSQRT(a) __builtin_sqrtf(a)
+#define PKV_FSQRT_UP(a) __builtin_sqrtf(a)
 #define PKV_FMUL(a, b) ((a) * (b))
 #define PKV_FSUB(a, b) ((a) - (b))
 #define PKV_FADD(a, b) ((a) + (b))
@@ -207,6 +218,31 @@ PKV_HD void pkv_fib_top2(float* best, float* second, float key) {
 #endif
 }
 
+/* (2b) The same rotated value from the tensor cores.  n and M32 are each split into a part with
+ * 11 significant bits (what a TF32 operand keeps) and the exact remainder, and the unit sums
+ * n_hi M_hi + n_hi M_lo + n_lo M_hi with the remainders shortened to 11 bits in turn.  Left out or
+ * cut off: n_lo M_lo and the two shortenings, each below 2^-20 sum|n_j M_rj|, together 2.9e-6.
+ * The vendor does not specify the rounding inside the accumulation of the 24 partial products;
+ * 2^-16 sum|n_j M_rj| = 1.5e-5 is assumed for it (a correctly rounded binary32 accumulation of 24
+ * partial sums would stay below 3e-6).  With |M_r| = |n| = 1:   2.0e-5. */
+#define PKV_FIB_ROT_ERR_TC 2.0e-5f
+
+/* Is the best key's codeword provably the reference's choice when the rotated block is known to
+ * eta per coordinate?  (bound in the comment above with eta for PKV_FIB_ROT_ERR) */
+PKV_HD int pkv_fib_certify_eta(float best, float second, float s0, float s1, float s2, float s3, float eta) {
+  const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
+                            PKV_FADD(PKV_FMUL(s2, s2), PKV_FMUL(s3, s3)));
+  const float d1 = PKV_FADD(PKV_FMUL(2.0f, best), ss), d2 = PKV_FADD(PKV_FMUL(2.0f, second), ss);
+  const float d2p = d2 > 0.0f ? d2 : 0.0f, d1p = d1 > 0.0f ? d1 : 0.0f;
+  const float fb = pkv_f32_from_bits(pkv_f32_bits(best) & 0x7fffffffu);
+  const float fs = pkv_f32_from_bits(pkv_f32_bits(second) & 0x7fffffffu);
+  const float roots = PKV_FADD(PKV_FSQRT_UP(d1p), PKV_FSQRT_UP(d2p));
+  const float bound = PKV_FADD(
+      PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
+      PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(1.0e-5f, PKV_FADD(fb, fs))));
+  return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
+}
+
 /* Is the best key's codeword provably the reference's choice?  (bound in the comment above) */
 PKV_HD int pkv_fib_certify(float best, float second, float s0, float s1, float s2, float s3) {
   const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
@@ -217,7 +253,7 @@ PKV_HD int pkv_fib_certify(float best, float second, float s0, float s1, float s
   const float d2p = d2 > 0.0f ? d2 : 0.0f, d1p = d1 > 0.0f ? d1 : 0.0f;
   const float fb = pkv_f32_from_bits(pkv_f32_bits(best) & 0x7fffffffu);
   const float fs = pkv_f32_from_bits(pkv_f32_bits(second) & 0x7fffffffu);
-  const float roots = PKV_FADD(PKV_FSQRT(d1p), PKV_FSQRT(d2p));
+  const float roots = PKV_FADD(PKV_FSQRT_UP(d1p), PKV_FSQRT_UP(d2p));
   const float bound = PKV_FADD(
       PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
       PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(1.0e-5f, PKV_FADD(fb, fs))));

@@ -76,7 +76,7 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
                         int n_codewords, int idx_bits, int norm_len, float* __restrict__ cache,
                         uint64_t* err, unsigned long long ones) {
   using K = FibDec<D>;
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   float* s_rot = reinterpret_cast<float*>(smem);                 // [D][D]
   float4* s_cb = reinterpret_cast<float4*>(s_rot + D * D);       // [32]
   int64_t* s_dst = reinterpret_cast<int64_t*>(s_cb + 32);        // [TV]
@@ -246,7 +246,7 @@ fib_encode_kernel(PkvGeom g, const float* __restrict__ x, const double* __restri
                   int argmin_order, int batch_numerics, uint8_t* __restrict__ payload,
                   uint64_t* err) {
   using K = FibEnc<D>;
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   double* s_rot = reinterpret_cast<double*>(smem);                 // [j][r]
   double* s_nrm = s_rot + D * D;                                   // [TV][XS]
   double* s_norm = s_nrm + K::TV * K::XS;                          // [TV]
@@ -381,6 +381,7 @@ size_t fib_encode_smem(int rec) {
 }
 
 #include "pkv_fib_encode_fast.cuh"
+#include "pkv_fib_encode_tc.cuh"
 
 template <typename F>
 int set_smem(F kernel, size_t bytes) {
@@ -472,6 +473,24 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
                                             cudaStream_t s) {
   if (cudaMemsetAsync(scratch, 0, sizeof(uint32_t), s) != cudaSuccess) return PKV_ERR_CUDA;
   int st;
+  // the cold-tier default shape takes the tensor-core kernel
+  if (p->cfg.dim == 64 && p->norm_len == 2 && p->idx_bits == 5) {
+    PkvGeom gf = g;
+    gf.tiles_per_batch = (g.vpb + FibTc::TV - 1) / FibTc::TV;
+    const int64_t tiles = (int64_t)g.n_batches * gf.tiles_per_batch;
+    const int64_t grid = (tiles + FibTc::NWARPS - 1) / FibTc::NWARPS;
+    if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+    if ((st = set_smem(fib_encode_tc_kernel, FibTc::SMEM)) != PKV_OK) return st;
+    fib_encode_tc_kernel<<<(unsigned)grid, FibTc::THREADS, FibTc::SMEM, s>>>(
+        gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, payload,
+        err, scratch, scratch + 1);
+    pkv_count_launch();
+    fib_encode_fix_kernel<64><<<148 * 8, kThreads, 0, s>>>(
+        gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
+        p->cfg.argmin_order, payload, scratch, scratch + 1);
+    pkv_count_launch();
+    return pkv_cuda_status(cudaGetLastError());
+  }
 #define PKV_FIB_FAST(DIM)                                                                           \
   {                                                                                                 \
     PkvGeom gf = g;                                                                                 \

@@ -31,7 +31,7 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
                        int n_codewords, int idx_bits, int norm_len, uint8_t* __restrict__ payload,
                        uint64_t* err, uint32_t* flag_count, uint32_t* flag_list) {
   using K = FibFast<D>;
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   float* s_m = reinterpret_cast<float*>(smem);                     // [j][r] = (f32) M[r][j]
   float* s_t = s_m + D * D;                                        // input tile [TV][XS], then n~ [j][TV]
   float4* s_cb = reinterpret_cast<float4*>(s_t + K::tile_floats);  // [32]

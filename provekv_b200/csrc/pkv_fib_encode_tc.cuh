@@ -1,0 +1,297 @@
+// fib-quant encode for the cold-tier default (d = 64, fp16 norm, 5-bit indices): the dense
+// rotation on the tensor cores.  Included by pkv_fib.cu inside its unnamed namespace.
+//
+// One thread per vector, one warp per tile of 32 vectors, one CTA = 4 warps = one 128-row
+// tensor-core tile.  Per vector: exact f64 norm and certified normalisation as in
+// pkv_fib_encode_fast.cuh; the normalised vector n is split into n_hi (11 significant bits, what a
+// TF32 operand keeps) and the exact remainder n_lo, the f32 matrix likewise into M_hi + M_lo (split
+// once on the host), and
+//   y~ = n_lo M_hi^T + n_hi M_hi^T + n_hi M_lo^T        (three 128 x 64 x 64 TF32 products)
+// accumulates in tensor memory (pkv_fast_paths.h gives the error bound PKV_FIB_ROT_ERR_TC).  The
+// thread reads its row back and runs the certified nearest-codeword search on its 16 blocks.
+// Blocks the bound cannot settle are redone by the whole warp in binary32 with fused multiply-adds
+// (bound PKV_FIB_ROT_ERR); what that cannot settle either goes on the list of
+// fib_encode_fix_kernel, which redoes it with the reference's exact f64 sequence.
+#pragma once
+
+#include "pkv_tcgen05.cuh"
+
+struct FibTc {
+  static constexpr int D = 64, B = 16, THREADS = 128, NWARPS = 4, TV = 32, ROWS = 128;
+  static constexpr int X_SLAB = ROWS * 128, X_BYTES = 2 * X_SLAB;  // vector tile: 2 slabs of [128 rows][128 B]
+  static constexpr int M_SLAB = D * 128, M_BYTES = 2 * M_SLAB;     // matrix tile: 2 slabs of [64 rows][128 B]
+  static constexpr int WARP_BYTES = TV * (int)sizeof(int64_t);
+  static constexpr size_t SMEM = 1024 + X_BYTES + 2 * M_BYTES + 32 * sizeof(float4) + 32 * sizeof(float) +
+                                 NWARPS * WARP_BYTES;
+};
+
+__global__ void __launch_bounds__(FibTc::THREADS, 3)
+fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot_hi,
+                     const float* __restrict__ rot_lo, const float* __restrict__ codebook,
+                     const float* __restrict__ half_norm, int n_codewords, uint8_t* __restrict__ payload,
+                     uint64_t* err, uint32_t* flag_count, uint32_t* flag_list) {
+  using K = FibTc;
+  using pkv_tc::sw_piece;
+  using pkv_tc::tile_at;
+  constexpr int D = K::D;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t s_bar;
+  __shared__ uint32_t s_tmem;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint8_t* s_xt = smem + ((1024u - (pkv_tc::smem_u32(smem) & 1023u)) & 1023u);  // x, then n_lo, then n
+  uint8_t* s_mh = s_xt + K::X_BYTES;                                           // M_hi [r][j]
+  uint8_t* s_ml = s_mh + K::M_BYTES;                                           // M_lo [r][j]
+  float4* s_cb = reinterpret_cast<float4*>(s_ml + K::M_BYTES);                 // [32] codewords
+  float* s_hn = reinterpret_cast<float*>(s_cb + 32);                           // [32] |c|^2 / 2
+  uint8_t* wbase = reinterpret_cast<uint8_t*>(s_hn + 32) + warp * K::WARP_BYTES;
+  int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                          // [TV]
+
+  const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
+  const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
+  const int tile = active ? (int)(tile_id % g.tiles_per_batch) : 0;
+  const int batch = active ? (int)(tile_id / g.tiles_per_batch) : 0;
+  const int v0 = tile * K::TV;
+  const int nv = active ? min(K::TV, g.vpb - v0) : 0;
+  const int v = lane, row = warp * K::TV + v;
+  const bool valid = v < nv;
+
+  if (warp == 0) pkv_tc::tmem_alloc(&s_tmem, 64);
+  if (threadIdx.x == 32) pkv_tc::mbar_init(&s_bar, 1);
+
+  s_off[v] = valid ? pkv_vec_offset(g.L, batch, v0 + v) : 0;
+  __syncwarp();
+#pragma unroll 4
+  for (int i = lane; i < nv * 16; i += 32) {
+    const int vv = i >> 4, q = i & 15;
+    pkv_cp_async16(s_xt + sw_piece(K::X_SLAB, warp * K::TV + vv, q),
+                   reinterpret_cast<const float4*>(x + s_off[vv]) + q);
+  }
+  for (int i = threadIdx.x; i < D * 16; i += K::THREADS) {
+    pkv_cp_async16(s_mh + sw_piece(K::M_SLAB, i >> 4, i & 15), reinterpret_cast<const float4*>(rot_hi) + i);
+    pkv_cp_async16(s_ml + sw_piece(K::M_SLAB, i >> 4, i & 15), reinterpret_cast<const float4*>(rot_lo) + i);
+  }
+  if (threadIdx.x < 32) {
+    s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
+    s_hn[threadIdx.x] = __ldg(half_norm + threadIdx.x);
+  }
+  pkv_cp_async_wait_all();
+  pkv_tc::fence_before_sync();
+  __syncthreads();
+  pkv_tc::fence_after_sync();
+
+  // piece c of this thread's row sits at s_xt + (c >> 3) * X_SLAB + (xsw ^ ((c & 7) << 4))
+  const uint32_t xsw = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((row & 7) << 4));
+  float n[D];
+#pragma unroll
+  for (int i = 0; i < D; i += 4) {
+    const float4 t = valid ? *reinterpret_cast<const float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+    n[i] = t.x; n[i + 1] = t.y; n[i + 2] = t.z; n[i + 3] = t.w;
+  }
+
+  // exact norm (codec.rs:1049-1057; the square of a binary32 value is exact in binary64, so the
+  // fused form rounds exactly like the reference's multiply-then-add), certified normalisation
+  bool finite = true;
+  double acc = 0.0;
+#pragma unroll
+  for (int i = 0; i < D; i++) {
+    finite = finite && pkv_finite(n[i]);
+    const double t = (double)n[i];
+    acc = fma(t, t, acc);
+  }
+  double norm = __dsqrt_rn(acc);
+  int bad = 0;
+  if (valid) {
+    if (!finite) bad = PKV_VEC_NONFINITE_INPUT;
+    else if (norm == 0.0) bad = PKV_VEC_ZERO_NORM;
+    if (bad) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, bad);
+  }
+  const bool skip = bad || !valid;
+  if (skip) norm = 1.0;
+  const double inv = __ddiv_rn(1.0, norm);
+  int all_certain = 1;
+#pragma unroll
+  for (int i = 0; i < D; i++) {
+    int certain;
+    const float q = pkv_fib_norm_quotient(n[i], inv, &certain);
+    all_certain &= certain;
+    n[i] = skip ? 0.0f : q;
+  }
+  const bool whole = !all_certain && !skip;  // some element of n is not certain: redo the vector exactly
+
+  // first operand: the exact remainder n_lo = n - n_hi (n_hi = n with its 13 low bits cleared);
+  // one product (M_hi)
+#pragma unroll
+  for (int i = 0; i < D; i += 4) {
+    float lo[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+      lo[k] = __fsub_rn(n[i + k], __uint_as_float(__float_as_uint(n[i + k]) & 0xffffe000u));
+    *reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4))) =
+        make_float4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  pkv_tc::fence_smem_to_async();
+  __syncthreads();
+  const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, D);
+  const uint32_t a0 = pkv_tc::smem_u32(s_xt), bh = pkv_tc::smem_u32(s_mh), bl = pkv_tc::smem_u32(s_ml);
+  if (threadIdx.x == 0) {
+    pkv_tc::fence_after_sync();
+#pragma unroll 1
+    for (int k = 0; k < D / 8; k++)
+      pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
+                       pkv_tc::smem_desc_sw128(bh + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, k > 0);
+    pkv_tc::mma_commit(&s_bar);
+  }
+  bool done = __all_sync(0xffffffffu, pkv_tc::mbar_wait(&s_bar, 0));
+  pkv_tc::fence_after_sync();
+  // second operand: n itself -- the unit reads only its 11 leading bits, i.e. n_hi, and the full
+  // value stays in the tile for the second tier; two products (M_hi, M_lo)
+#pragma unroll
+  for (int i = 0; i < D; i += 4)
+    *reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4))) =
+        make_float4(n[i], n[i + 1], n[i + 2], n[i + 3]);
+  pkv_tc::fence_smem_to_async();
+  pkv_tc::fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    pkv_tc::fence_after_sync();
+#pragma unroll 1
+    for (int k = 0; k < D / 8; k++)
+      pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
+                       pkv_tc::smem_desc_sw128(bh + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, 1u);
+#pragma unroll 1
+    for (int k = 0; k < D / 8; k++)
+      pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
+                       pkv_tc::smem_desc_sw128(bl + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, 1u);
+    pkv_tc::mma_commit(&s_bar);
+  }
+  done = __all_sync(0xffffffffu, done && pkv_tc::mbar_wait(&s_bar, 1));
+  pkv_tc::fence_after_sync();
+
+  uint32_t idx4[4] = {0, 0, 0, 0};  // four 8-bit indices per word
+  uint32_t flagged = 0;             // blocks whose nearest codeword is not settled yet
+  if (done) {
+    float y[D];
+    {
+      float h0[32], h1[32];
+      const uint32_t taddr = s_tmem + ((uint32_t)(warp * 32) << 16);
+      pkv_tc::tmem_load32(taddr, h0);
+      pkv_tc::tmem_load32(taddr + 32, h1);
+#pragma unroll
+      for (int i = 0; i < 32; i++) {
+        y[i] = h0[i];
+        y[32 + i] = h1[i];
+      }
+    }
+    // certified nearest codeword of the 16 blocks (pkv_fast_paths.h)
+    float best[K::B], second[K::B];
+#pragma unroll
+    for (int b = 0; b < K::B; b++) best[b] = second[b] = __int_as_float(0x7f800000);
+#pragma unroll 2
+    for (int c = 0; c < n_codewords; c++) {
+      const float4 w = s_cb[c];
+      const float hn = s_hn[c];
+#pragma unroll
+      for (int b = 0; b < K::B; b++)
+        pkv_fib_top2(&best[b], &second[b],
+                     pkv_fib_key(y[4 * b], y[4 * b + 1], y[4 * b + 2], y[4 * b + 3], w.x, w.y, w.z, w.w, hn,
+                                 (uint32_t)c));
+    }
+#pragma unroll
+    for (int b = 0; b < K::B; b++) {
+      idx4[b >> 2] |= (__float_as_uint(best[b]) & 31u) << (8 * (b & 3));
+      if (!pkv_fib_certify_eta(best[b], second[b], y[4 * b], y[4 * b + 1], y[4 * b + 2], y[4 * b + 3],
+                               PKV_FIB_ROT_ERR_TC))
+        flagged |= 1u << b;
+    }
+    if (skip || whole) flagged = 0;
+  } else if (threadIdx.x == 0) {
+    pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
+  }
+
+  // Second tier: the flagged blocks of one vector at a time, the whole warp on each.  Lane l takes
+  // columns 2l, 2l + 1 of the block's four rows in binary32 (n from the tile, M32 = M_hi + M_lo
+  // exactly) and a butterfly sum gives every lane the block; then lane c scores codeword c, two
+  // butterfly minima give best and second best (keys are distinct: the index rides in them), and
+  // the owner keeps a certified result.
+  for (unsigned pending = __ballot_sync(0xffffffffu, flagged != 0); pending; pending &= pending - 1) {
+    const int src = __ffs(pending) - 1;
+    uint32_t todo = __shfl_sync(0xffffffffu, flagged, src);
+    const float2 nn = *reinterpret_cast<const float2*>(tile_at(s_xt, K::X_SLAB, warp * K::TV + src, 2 * lane));
+    const float4 cw = s_cb[lane];
+    const float hn = s_hn[lane];
+    while (todo) {
+      const int b = __ffs(todo) - 1;
+      todo &= todo - 1;
+      float part[4];
+#pragma unroll
+      for (int rr = 0; rr < 4; rr++) {
+        const int r = 4 * b + rr;
+        const float2 mh = *reinterpret_cast<const float2*>(tile_at(s_mh, K::M_SLAB, r, 2 * lane));
+        const float2 ml = *reinterpret_cast<const float2*>(tile_at(s_ml, K::M_SLAB, r, 2 * lane));
+        part[rr] = fmaf(__fadd_rn(mh.y, ml.y), nn.y, __fmul_rn(__fadd_rn(mh.x, ml.x), nn.x));
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1)
+#pragma unroll
+        for (int rr = 0; rr < 4; rr++) part[rr] = __fadd_rn(part[rr], __shfl_xor_sync(0xffffffffu, part[rr], o));
+      const float inf = __int_as_float(0x7f800000);
+      const float key = lane < n_codewords
+                            ? pkv_fib_key(part[0], part[1], part[2], part[3], cw.x, cw.y, cw.z, cw.w, hn, (uint32_t)lane)
+                            : inf;
+      float best = key;
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) best = fminf(best, __shfl_xor_sync(0xffffffffu, best, o));
+      float second = key == best ? inf : key;
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) second = fminf(second, __shfl_xor_sync(0xffffffffu, second, o));
+      if (lane == src && pkv_fib_certify(best, second, part[0], part[1], part[2], part[3])) {
+        const uint32_t idx = __float_as_uint(best) & 31u;
+        const int wi = b >> 2, sh = 8 * (b & 3);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+          if (k == wi) idx4[k] = (idx4[k] & ~(0xffu << sh)) | (idx << sh);
+        flagged &= ~(1u << b);
+      }
+    }
+  }
+
+  // encode_norm (codec.rs:994-1020), pack_indices (bitpack.rs:4-44): the record is three words
+  if (valid) {
+    uint32_t rec0 = 0, rec1 = 0, rec2 = 0;
+    if (!bad) {
+      const float nf = __double2float_rn(norm);
+      const uint32_t h = pkv_f32_to_f16_bits(nf);
+      if ((h & 0x7fffu) < 0x7c00u && (h & 0x7fffu) != 0) {
+        unsigned long long lo = 0;  // stream bits 0..63
+        uint32_t hi = 0;            // stream bits 64..79
+#pragma unroll
+        for (int b = 0; b < K::B; b++) {
+          const unsigned long long iv = (idx4[b >> 2] >> (8 * (b & 3))) & 31u;
+          const int pos = 5 * b;
+          if (pos < 64) lo |= iv << pos;
+          if (pos + 5 > 64) hi |= (uint32_t)(iv >> (pos < 64 ? 64 - pos : 0)) << (pos < 64 ? 0 : pos - 64);
+        }
+        rec0 = h | ((uint32_t)lo << 16);
+        rec1 = (uint32_t)(lo >> 16);
+        rec2 = (uint32_t)(lo >> 48) | (hi << 16);
+        if (whole || flagged) {
+          const uint32_t which = (whole || (flagged & (flagged - 1))) ? PKV_FIB_ENTRY_ALL
+                                                                       : (uint32_t)(__ffs(flagged) - 1);
+          const uint32_t gvec = (uint32_t)((int64_t)batch * g.vpb + v0 + v);
+          flag_list[atomicAdd(flag_count, 1u)] = (gvec << 5) | which;
+        }
+      } else {
+        pkv_report(err, 1, (int64_t)batch * g.vpb + v0 + v, PKV_VEC_NORM_RANGE);
+      }
+    }
+    uint32_t* dst = reinterpret_cast<uint32_t*>(payload + (int64_t)batch * g.payload_batch_stride +
+                                                (int64_t)(v0 + v) * 12);
+    dst[0] = rec0;
+    dst[1] = rec1;
+    dst[2] = rec2;
+  }
+  pkv_tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) pkv_tc::tmem_free(s_tmem, 64);
+}

@@ -251,6 +251,8 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
   p->rot_dev = nullptr;
   p->rot32_t_dev = nullptr;
   p->half_norm_dev = nullptr;
+  p->rot_hi_dev = nullptr;
+  p->rot_lo_dev = nullptr;
   const int d = cfg->dim;
   cudaError_t e = cudaGetDevice(&p->device);
   double* rt = new double[d * d];
@@ -284,6 +286,24 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
   if (e == cudaSuccess) e = cudaMemcpy(p->rot_dev, rotation, sizeof(double) * d * d, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->rot32_t_dev, r32, sizeof(float) * d * d, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->half_norm_dev, hn, sizeof(hn), cudaMemcpyHostToDevice);
+  {  // split of the f32 matrix for the tensor-core rotation: hi keeps 11 significant bits, lo is exact
+    float* hi = new float[d * d];
+    float* lo = new float[d * d];
+    for (int i = 0; i < d * d; i++) {
+      const float m = (float)rotation[i];
+      uint32_t u;
+      memcpy(&u, &m, 4);
+      u &= 0xffffe000u;
+      memcpy(&hi[i], &u, 4);
+      lo[i] = m - hi[i];
+    }
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot_hi_dev, sizeof(float) * d * d);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot_lo_dev, sizeof(float) * d * d);
+    if (e == cudaSuccess) e = cudaMemcpy(p->rot_hi_dev, hi, sizeof(float) * d * d, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(p->rot_lo_dev, lo, sizeof(float) * d * d, cudaMemcpyHostToDevice);
+    delete[] hi;
+    delete[] lo;
+  }
   delete[] rt;
   delete[] r32;
   if (e != cudaSuccess) {
@@ -302,6 +322,8 @@ int pkv_fib_profile_destroy(pkv_fib_profile* p) {
   if (p->rot_dev) cudaFree(p->rot_dev);
   if (p->rot32_t_dev) cudaFree(p->rot32_t_dev);
   if (p->half_norm_dev) cudaFree(p->half_norm_dev);
+  if (p->rot_hi_dev) cudaFree(p->rot_hi_dev);
+  if (p->rot_lo_dev) cudaFree(p->rot_lo_dev);
   ws_release(&p->ws);
   delete p;
   return PKV_OK;

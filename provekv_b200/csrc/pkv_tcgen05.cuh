@@ -17,6 +17,16 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// Byte offset of the 16-byte piece c (elements 4c..4c+3) of row r in a swizzled tile whose slabs
+// are slab_bytes apart.
+__device__ __forceinline__ uint32_t sw_piece(int slab_bytes, int r, int c) {
+  return (uint32_t)((c >> 3) * slab_bytes + (r >> 3) * 1024 + (r & 7) * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+// element j of row r
+__device__ __forceinline__ const float* tile_at(const uint8_t* t, int slab_bytes, int r, int j) {
+  return reinterpret_cast<const float*>(t + sw_piece(slab_bytes, r, j >> 2) + (j & 3) * 4);
+}
+
 // Shared-memory matrix descriptor (sm_100 format) for that layout: start address in units of 16
 // bytes in bits 0-13, leading offset (unused with a swizzle; 1) in bits 16-29, stride offset
 // between 8-row groups (1024 bytes, in units of 16) in bits 32-45, descriptor version 1 in bits

@@ -37,15 +37,8 @@ struct TurboEnc {
   static constexpr int X_BYTES = SLABS * X_SLAB;
 };
 
-// Byte offset of the 16-byte piece c (elements 4c..4c+3) of row r in a swizzled tile whose slabs
-// are slab_bytes apart.
-__device__ __forceinline__ uint32_t sw_piece(int slab_bytes, int r, int c) {
-  return (uint32_t)((c >> 3) * slab_bytes + (r >> 3) * 1024 + (r & 7) * 128 + (((c & 7) ^ (r & 7)) << 4));
-}
-// element j of row r
-__device__ __forceinline__ const float* tile_at(const uint8_t* t, int slab_bytes, int r, int j) {
-  return reinterpret_cast<const float*>(t + sw_piece(slab_bytes, r, j >> 2) + (j & 3) * 4);
-}
+using pkv_tc::sw_piece;
+using pkv_tc::tile_at;
 
 // Replace angle index i in the shared angle words (LSB-first stream, bitpack.rs:135-143).
 __device__ __forceinline__ void patch_angle(uint32_t* aw, int ws, int i, int pb, uint32_t idx) {
