@@ -478,8 +478,10 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     PkvGeom gf = g;
     gf.tiles_per_batch = (g.vpb + FibTc::TV - 1) / FibTc::TV;
     const int64_t tiles = (int64_t)g.n_batches * gf.tiles_per_batch;
-    const int64_t grid = (tiles + FibTc::NWARPS - 1) / FibTc::NWARPS;
-    if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t quads = (tiles + FibTc::NWARPS - 1) / FibTc::NWARPS;
+    const int64_t grid = quads < (int64_t)sms * 3 ? quads : (int64_t)sms * 3;  // persistent: 3 CTAs per SM
     if ((st = set_smem(fib_encode_tc_kernel, FibTc::SMEM)) != PKV_OK) return st;
     fib_encode_tc_kernel<<<(unsigned)grid, FibTc::THREADS, FibTc::SMEM, s>>>(
         gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, payload,

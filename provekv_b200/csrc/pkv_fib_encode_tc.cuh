@@ -46,17 +46,34 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   uint8_t* wbase = reinterpret_cast<uint8_t*>(s_hn + 32) + warp * K::WARP_BYTES;
   int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                          // [TV]
 
-  const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
-  const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
+  if (warp == 0) pkv_tc::tmem_alloc(&s_tmem, 64);
+  if (threadIdx.x == 32) pkv_tc::mbar_init(&s_bar, 1);
+  for (int i = threadIdx.x; i < D * 16; i += K::THREADS) {
+    pkv_cp_async16(s_mh + sw_piece(K::M_SLAB, i >> 4, i & 15), reinterpret_cast<const float4*>(rot_hi) + i);
+    pkv_cp_async16(s_ml + sw_piece(K::M_SLAB, i >> 4, i & 15), reinterpret_cast<const float4*>(rot_lo) + i);
+  }
+  if (threadIdx.x < 32) {
+    s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
+    s_hn[threadIdx.x] = __ldg(half_norm + threadIdx.x);
+  }
+  const int v = lane, row = warp * K::TV + v;
+  // piece c of this thread's row sits at s_xt + (c >> 3) * X_SLAB + (xsw ^ ((c & 7) << 4))
+  const uint32_t xsw = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((row & 7) << 4));
+  const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, D);
+  const uint32_t a0 = pkv_tc::smem_u32(s_xt), bh = pkv_tc::smem_u32(s_mh), bl = pkv_tc::smem_u32(s_ml);
+  const int64_t n_tiles = (int64_t)g.n_batches * g.tiles_per_batch;
+
+  // The CTA walks over groups of four tiles (one per warp); the matrix tiles, the codebook and the
+  // tensor-memory columns are set up once.  Each round completes the barrier twice, so the phase
+  // parities repeat from round to round.
+  for (int64_t quad = blockIdx.x; quad * K::NWARPS < n_tiles; quad += gridDim.x) {
+  const int64_t tile_id = quad * K::NWARPS + warp;
+  const bool active = tile_id < n_tiles;
   const int tile = active ? (int)(tile_id % g.tiles_per_batch) : 0;
   const int batch = active ? (int)(tile_id / g.tiles_per_batch) : 0;
   const int v0 = tile * K::TV;
   const int nv = active ? min(K::TV, g.vpb - v0) : 0;
-  const int v = lane, row = warp * K::TV + v;
   const bool valid = v < nv;
-
-  if (warp == 0) pkv_tc::tmem_alloc(&s_tmem, 64);
-  if (threadIdx.x == 32) pkv_tc::mbar_init(&s_bar, 1);
 
   s_off[v] = valid ? pkv_vec_offset(g.L, batch, v0 + v) : 0;
   __syncwarp();
@@ -66,21 +83,12 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
     pkv_cp_async16(s_xt + sw_piece(K::X_SLAB, warp * K::TV + vv, q),
                    reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
-  for (int i = threadIdx.x; i < D * 16; i += K::THREADS) {
-    pkv_cp_async16(s_mh + sw_piece(K::M_SLAB, i >> 4, i & 15), reinterpret_cast<const float4*>(rot_hi) + i);
-    pkv_cp_async16(s_ml + sw_piece(K::M_SLAB, i >> 4, i & 15), reinterpret_cast<const float4*>(rot_lo) + i);
-  }
-  if (threadIdx.x < 32) {
-    s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
-    s_hn[threadIdx.x] = __ldg(half_norm + threadIdx.x);
-  }
   pkv_cp_async_wait_all();
   pkv_tc::fence_before_sync();
-  __syncthreads();
+  __syncthreads();  // first round: tables, barrier, tensor-memory base; every round: the previous
+                    // round's accumulator rows have been read by all warps
   pkv_tc::fence_after_sync();
 
-  // piece c of this thread's row sits at s_xt + (c >> 3) * X_SLAB + (xsw ^ ((c & 7) << 4))
-  const uint32_t xsw = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((row & 7) << 4));
   float n[D];
 #pragma unroll
   for (int i = 0; i < D; i += 4) {
@@ -132,8 +140,6 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   }
   pkv_tc::fence_smem_to_async();
   __syncthreads();
-  const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, D);
-  const uint32_t a0 = pkv_tc::smem_u32(s_xt), bh = pkv_tc::smem_u32(s_mh), bl = pkv_tc::smem_u32(s_ml);
   if (threadIdx.x == 0) {
     pkv_tc::fence_after_sync();
 #pragma unroll 1
@@ -291,6 +297,7 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
     dst[1] = rec1;
     dst[2] = rec2;
   }
+  }  // rounds
   pkv_tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) pkv_tc::tmem_free(s_tmem, 64);
