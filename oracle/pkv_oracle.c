@@ -1128,3 +1128,76 @@ PKVO_API void pkvo_fib_fast_check(const float* x, int64_t n, int dim, const doub
   counts[5] = (int64_t)(worst * 1e9);
   free(m32);
 }
+
+/* The same check for the tensor-core rotation of the d = 64 encoder (PKV_FIB_ROT_ERR_TC). */
+PKVO_API void pkvo_fib_tc_check(const float* x, int64_t n, int dim, const double* rot,
+                                  const float* codebook, int n_codewords, int order, int64_t* counts) {
+  const int blocks = dim / 4;
+  float* m32 = (float*)malloc(sizeof(float) * (size_t)dim * dim);
+  float hn[32];
+  for (int i = 0; i < dim * dim; i++) m32[i] = (float)rot[i];
+  for (int c = 0; c < n_codewords; c++) {
+    double s = 0.0;
+    for (int j = 0; j < 4; j++) s += (double)codebook[4 * c + j] * codebook[4 * c + j];
+    hn[c] = (float)(0.5 * s);
+  }
+  for (int k = 0; k < 6; k++) counts[k] = 0;
+  double worst = 0.0;
+  for (int64_t v = 0; v < n; v++) {
+    const float* xv = x + v * dim;
+    double acc = 0.0;
+    for (int i = 0; i < dim; i++) acc += (double)xv[i] * (double)xv[i];
+    const double norm = sqrt(acc);
+    if (!(norm > 0.0)) continue;
+    const double inv = 1.0 / norm;
+    float nf[512], ne[512];
+    for (int i = 0; i < dim; i++) {
+      int certain = 0;
+      nf[i] = pkv_fib_norm_quotient(xv[i], inv, &certain);
+      ne[i] = (float)((double)xv[i] / norm);
+      if (!certain) counts[4]++;
+      else if (pkv_f32_bits(nf[i]) != pkv_f32_bits(ne[i])) counts[3]++;
+    }
+    for (int b = 0; b < blocks; b++) {
+      float yf[4], ye[4];
+      for (int rr = 0; rr < 4; rr++) {
+        const int r = 4 * b + rr;
+        /* n_lo M_hi, n_hi M_hi, n_hi M_lo with every operand cut to 11 significant bits, products
+         * exact, partial sums of 8 terms added to a binary32 accumulator one after another */
+        float a = 0.0f;
+        double s = 0.0;
+        for (int pass = 0; pass < 3; pass++)
+          for (int j0 = 0; j0 < dim; j0 += 8) {
+            double blk8 = 0.0;
+            for (int j = j0; j < j0 + 8; j++) {
+              const float m = m32[(size_t)r * dim + j], mh = tf32_cut(m, 0), ml = tf32_cut(m - mh, 0);
+              const float nh = tf32_cut(ne[j], 0), nl = tf32_cut(ne[j] - nh, 0);
+              blk8 += pass == 0 ? (double)nl * mh : pass == 1 ? (double)nh * mh : (double)nh * ml;
+            }
+            a = (float)((double)a + blk8);
+          }
+        for (int j = 0; j < dim; j++) s += rot[(size_t)r * dim + j] * (double)ne[j];
+        yf[rr] = a;
+        ye[rr] = (float)s;
+        const double e = fabs((double)a - (double)ye[rr]);
+        if (e > worst) worst = e;
+      }
+      int certain = 0;
+      float best = INFINITY, second = INFINITY;
+      for (int c = 0; c < n_codewords; c++)
+        pkv_fib_top2(&best, &second,
+                     pkv_fib_key(yf[0], yf[1], yf[2], yf[3], codebook[4 * c], codebook[4 * c + 1],
+                                 codebook[4 * c + 2], codebook[4 * c + 3], hn[c], (uint32_t)c));
+      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_TC);
+      const uint32_t fast = pkv_f32_bits(best) & 31u;
+      if (!certain) {
+        counts[1]++;
+        continue;
+      }
+      counts[2]++;
+      if ((int)fast != pkvo_nearest_codeword(ye, codebook, n_codewords, 4, order)) counts[0]++;
+    }
+  }
+  counts[5] = (int64_t)(worst * 1e9);
+  free(m32);
+}

@@ -223,9 +223,12 @@ PKV_HD void pkv_fib_top2(float* best, float* second, float key) {
  * n_hi M_hi + n_hi M_lo + n_lo M_hi with the remainders shortened to 11 bits in turn.  Left out or
  * cut off: n_lo M_lo and the two shortenings, each below 2^-20 sum|n_j M_rj|, together 2.9e-6.
  * The vendor does not specify the rounding inside the accumulation of the 24 partial products;
- * 2^-16 sum|n_j M_rj| = 1.5e-5 is assumed for it (a correctly rounded binary32 accumulation of 24
- * partial sums would stay below 3e-6).  With |M_r| = |n| = 1:   2.0e-5. */
-#define PKV_FIB_ROT_ERR_TC 2.0e-5f
+ * 7e-6 sum|n_j M_rj| is assumed for it (a correctly rounded binary32 accumulation of 24 partial
+ * sums stays below 1.4e-6, one that truncates below 2.9e-6).  With |M_r| = |n| = 1:   1.0e-5.
+ * (Measured: with the bound set to 2e-6 the encoder still reproduced every byte of 25 M blocks.) */
+#ifndef PKV_FIB_ROT_ERR_TC
+#define PKV_FIB_ROT_ERR_TC 1.0e-5f
+#endif
 
 /* Is the best key's codeword provably the reference's choice when the rotated block is known to
  * eta per coordinate?  (bound in the comment above with eta for PKV_FIB_ROT_ERR) */

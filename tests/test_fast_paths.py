@@ -57,3 +57,27 @@ def test_qjl_tf32_tier_never_decides_wrong(oracle_mod, dim, variant, scale):
     assert wrong == 0
     assert decided >= 190_000         # ordinary residuals: ~98.6 % decided on the tensor cores
     assert undecided >= 20_000        # dots near the threshold go on to the binary32 tier
+
+
+@pytest.mark.parametrize("check", ["pkvo_fib_fast_check", "pkvo_fib_tc_check"])
+@pytest.mark.parametrize("order", [0, 1])
+def test_fib_rotation_shortcuts_never_decide_wrong(oracle_mod, check, order):
+    """Binary32 fused rotation and the emulated three-product TF32 rotation, each with its own
+    error bound, against the exact f64 sequence: every certified block has the reference's index."""
+    import numpy as np
+    from kvgen import synthetic_kv
+    from provekv_b200 import tables
+    dim, n = 64, 6000
+    rot = np.ascontiguousarray(tables.haar_rotation(dim, 42), dtype=np.float64)
+    cb = np.ascontiguousarray(tables.fib_codebook(dim, seed=42), dtype=np.float32)
+    x = np.ascontiguousarray(synthetic_kv(n, dim, seed=5), dtype=np.float32)
+    fn = getattr(oracle_mod.lib(), check)
+    fn.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                   C.POINTER(C.c_int64)]
+    out = (C.c_int64 * 6)()
+    fn(x.ctypes.data, n, dim, rot.ctypes.data, cb.ctypes.data, 32, order, out)
+    wrong, flagged, decided, quot_wrong, quot_uncertain, worst_e9 = list(out)
+    assert wrong == 0 and quot_wrong == 0
+    assert decided + flagged == n * 16
+    assert flagged < 0.004 * n * 16          # a few per mille of the blocks go to the next tier
+    assert worst_e9 * 1e-9 < (4.0e-6 if check.endswith("fast_check") else 1.0e-5)
