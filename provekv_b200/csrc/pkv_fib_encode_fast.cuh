@@ -233,6 +233,7 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
   constexpr int B = D / 4;
   __shared__ float s_x[kThreads / 32][D];
   __shared__ double s_n[kThreads / 32][D];
+  __shared__ double s_m[kThreads / 32][4 * D];  // the four matrix rows of a single-block entry
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
   const float4* cb4 = reinterpret_cast<const float4*>(codebook);
@@ -260,19 +261,33 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
     for (int k = 0; k < E; k++)
       sn[lane * E + k] = (double)__double2float_rn(__ddiv_rn((double)sx[lane * E + k], norm));
     __syncwarp();
-    // StoredRotation::apply (rotation.rs:104-115): each active lane one row at a time, j ascending
+    // StoredRotation::apply (rotation.rs:104-115): each active lane one row at a time, j ascending.
+    // A single block's four rows (2 KB of f64) are first copied into the warp's slice of shared
+    // memory with coalesced loads, so the sequential sums do not wait on one global load per term.
     const bool whole = blk == PKV_FIB_ENTRY_ALL;
     float yv[RPL];
+    if (!whole) {
+      double* sm = s_m[warp];
+      const double* src = rot + (size_t)(4 * blk) * D;
 #pragma unroll
-    for (int rr = 0; rr < RPL; rr++) {
-      const int r = whole ? lane + 32 * rr : (int)(4 * blk) + (lane & 3);
-      const double* mrow = rot + (size_t)r * D;
+      for (int k = 0; k < 4 * D / 32; k++) sm[lane + 32 * k] = __ldg(src + lane + 32 * k);
+      __syncwarp();
+      const double* mrow = sm + (lane & 3) * D;
       double s = 0.0;
-      if (whole || rr == 0) {
+#pragma unroll 8
+      for (int j = 0; j < D; j++) s = __dadd_rn(s, __dmul_rn(mrow[j], sn[j]));
+      yv[0] = __double2float_rn(s);
+#pragma unroll
+      for (int rr = 1; rr < RPL; rr++) yv[rr] = 0.0f;
+    } else {
+#pragma unroll
+      for (int rr = 0; rr < RPL; rr++) {
+        const double* mrow = rot + (size_t)(lane + 32 * rr) * D;
+        double s = 0.0;
 #pragma unroll 8
         for (int j = 0; j < D; j++) s = __dadd_rn(s, __dmul_rn(__ldg(mrow + j), sn[j]));
+        yv[rr] = __double2float_rn(s);
       }
-      yv[rr] = __double2float_rn(s);
     }
     // nearest codeword per block, reference order; lanes with lane % 4 == 0 own a block
     uint32_t idx[RPL];
