@@ -63,7 +63,8 @@ __device__ __forceinline__ void fwht_regs(float (&v)[D], float scale) {
 // Packed two-lane f32 add / subtract / multiply (sm_100): each lane is the IEEE operation of its
 // own pair of inputs, so a butterfly on two adjacent coordinates costs one issue slot per output
 // pair.  The pair (v[i], v[i + 1]) must sit in an aligned register pair; the arrays below are only
-// ever touched in such pairs once past the first stage.
+// ever touched in such pairs once past the first stage.  A packed multiply must not feed a packed
+// add or subtract directly: the assembler contracts that pair into a fused multiply-add.
 __device__ __forceinline__ void add_sub2(float& a0, float& a1, float& b0, float& b1) {
   unsigned long long pa, pb, ps, pd;
   asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
@@ -72,13 +73,6 @@ __device__ __forceinline__ void add_sub2(float& a0, float& a1, float& b0, float&
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(pd) : "l"(pa), "l"(pb));
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(ps));
   asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(pd));
-}
-__device__ __forceinline__ void sub2(float& a0, float& a1, float b0, float b1) {  // a -= b
-  unsigned long long pa, pb, pr;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(a0), "f"(a1));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(pb) : "f"(b0), "f"(b1));
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(pr) : "l"(pa), "l"(pb));
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(pr));
 }
 __device__ __forceinline__ void mul2(float& a0, float& a1, float m0, float m1) {
   unsigned long long pa, pm, pr;

@@ -365,10 +365,13 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     for (int i = 0; i < D; i += 4) {
       float4* piece = reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)));
       const float4 t = *piece;
-      float r0 = t.x, r1 = t.y, r2 = t.z, r3 = t.w;
-      sub2(r0, r1, y[i], y[i + 1]);
-      sub2(r2, r3, y[i + 2], y[i + 3]);
-      y[i] = r0; y[i + 1] = r1; y[i + 2] = r2; y[i + 3] = r3;
+      // scalar subtractions on purpose: a packed subtraction right after the packed multiply by the
+      // signed scale gets contracted into a fused multiply-add by the assembler (one rounding
+      // instead of two), which moves residual elements by an ulp and, once in ~1e8 dots, a sign
+      y[i] = __fsub_rn(t.x, y[i]);
+      y[i + 1] = __fsub_rn(t.y, y[i + 1]);
+      y[i + 2] = __fsub_rn(t.z, y[i + 2]);
+      y[i + 3] = __fsub_rn(t.w, y[i + 3]);
       n2 = ffma2(make_float2(y[i], y[i + 1]), make_float2(y[i], y[i + 1]), n2);
       n2 = ffma2(make_float2(y[i + 2], y[i + 3]), make_float2(y[i + 2], y[i + 3]), n2);
       // the residual replaces x in the tile: it is the A operand of the QJL product

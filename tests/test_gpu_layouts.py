@@ -274,3 +274,18 @@ def test_full_size_hot_shells_bytes_and_roundtrip(oracle_mod, kind):
     assert bool((cache[:, :, :, :, :first, :] == 7.0).all()) and bool((cache[:, :, :, :, first + T:, :] == 7.0).all())
     rel = float(((patched - kv) ** 2).sum() / (kv ** 2).sum())
     assert 0.01 < rel < 0.4
+
+
+@pytest.mark.parametrize("codec", ["fib", "turbo"])
+def test_scaled_long_context_d128_bytes_and_decode(oracle_mod, codec):
+    """C5 scaled (d=128, 8 KV heads, bf16-valued inputs with 1 % outlier channels x 20): 2 M vectors,
+    every record byte and a 200k-vector sample of the decode against the oracle.  The 67 M QJL signs
+    of the turbo case include dots within 1e-8 of zero relative to their terms, which only come out
+    right if the residual is bit-exact."""
+    import parity_report
+    shape = pool.LLAMA3_8B
+    if codec == "fib":
+        bad = parity_report.run(_torch(), "C5", "fib d=128 scaled", shape, 1, 4096, "fib", seed=6, outliers=True)
+    else:
+        bad = parity_report.run(_torch(), "C5", "turbo d=128 scaled", shape, 16, 256, "turbo", seed=7, outliers=True)
+    assert bad == 0
