@@ -65,9 +65,78 @@ class TurboConfig:
 
 
 @functools.lru_cache(maxsize=16)
-def _fib_profile(dim, k, n, ts, restarts, iters, seed) -> FibProfile:
+def _fib_profile(dim, k, n, ts, restarts, iters, seed, numerics=L.FIB_NUMERICS_AUTO) -> FibProfile:
     return FibProfile.from_seed(dim, seed, k=k, n=n, training_samples=ts, restarts=restarts,
-                                iterations=iters)
+                                iterations=iters, numerics=numerics)
+
+
+# -- per-vector wire formats (host-side framing around the same records) --------------------------
+FB1_MAGIC = b"FB1"       # fib-quant/src/codec.rs:20-21
+FB1_HEADER_BYTES = 11    # magic, version, wire_index_bits, block_count u32, norm_len u16 (codec.rs:81-92)
+TQW1_MAGIC = b"TQW1"     # turbo-quant/src/wire.rs:17
+TQW1_HEADER_BYTES = 46   # wire.rs:74-88
+
+
+def fb1_frame(record: bytes, wire_index_bits: int, block_count: int, norm_len: int) -> bytes:
+    """FibCodeV1::to_compact_bytes (codec.rs:81-92): header, norm payload, packed indices."""
+    return (FB1_MAGIC + bytes([1, wire_index_bits]) + int(block_count).to_bytes(4, "little") +
+            int(norm_len).to_bytes(2, "little") + bytes(record))
+
+
+def fb1_parse(blob: bytes, wire_index_bits: int, block_count: int, norm_len: int) -> bytes:
+    """FibCodeV1::from_compact_bytes (codec.rs:100-152) -> the [norm][indices] record."""
+    if len(blob) < FB1_HEADER_BYTES:
+        raise DecompressionFailed(f"compact FibCodeV1 too short: {len(blob)} bytes (need >= 11)")
+    if blob[0:3] != FB1_MAGIC:
+        raise DecompressionFailed("compact FibCodeV1 bad magic")
+    if blob[3] != 1:
+        raise DecompressionFailed(f"compact FibCodeV1 version {blob[3]} not supported (need 1)")
+    bits, blocks = blob[4], int.from_bytes(blob[5:9], "little")
+    nlen = int.from_bytes(blob[9:11], "little")
+    if len(blob) < FB1_HEADER_BYTES + nlen:
+        raise DecompressionFailed("compact FibCodeV1 truncated")
+    if len(blob) - FB1_HEADER_BYTES - nlen != (blocks * bits + 7) // 8:
+        raise DecompressionFailed("compact FibCodeV1 indices: wrong packed length")
+    if (bits, blocks, nlen) != (wire_index_bits, block_count, norm_len):
+        raise DecompressionFailed("compact FibCodeV1 does not match the quantizer profile")
+    return bytes(blob[FB1_HEADER_BYTES:])
+
+
+def tqw1_frame(record: bytes, dim: int, polar_bits: int, projections: int, seed: int, with_qjl: bool) -> bytes:
+    """TurboCodeWireV1::encode (wire.rs:44-96): f32 radii, packed angle indices, packed signs."""
+    rotation_flag = 1 if dim & (dim - 1) == 0 else 0  # FastHadamard for power-of-two dims (wire.rs:583-589)
+    head = (TQW1_MAGIC + (1).to_bytes(2, "little") + rotation_flag.to_bytes(2, "little") + bytes([1, 0]) +
+            int(dim).to_bytes(4, "little") + bytes([polar_bits, 0, 0, 0]) + int(projections).to_bytes(4, "little") +
+            int(seed).to_bytes(8, "little") + (dim // 2).to_bytes(4, "little") +
+            (projections if with_qjl else 0).to_bytes(4, "little") + len(record).to_bytes(8, "little"))
+    return head + bytes(record)
+
+
+def tqw1_parse(blob: bytes, dim: int, polar_bits: int, projections: int, seed: int, with_qjl: bool) -> bytes:
+    """TurboCodeWireV1::decode header checks (wire.rs:98-214) -> the vector's record."""
+    if len(blob) < TQW1_HEADER_BYTES or blob[0:4] != TQW1_MAGIC:
+        raise DecompressionFailed("wrong TurboQuant wire magic")
+    u = lambda a, n: int.from_bytes(blob[a:a + n], "little")  # noqa: E731
+    if u(4, 2) != 1:
+        raise DecompressionFailed(f"unsupported TurboQuant wire version {u(4, 2)}")
+    if u(6, 2) != (1 if dim & (dim - 1) == 0 else 0):
+        raise DecompressionFailed("wire rotation flag does not match quantizer profile flag")
+    if blob[8] != 1:
+        raise DecompressionFailed(f"unsupported TurboQuant wire variant {blob[8]}")
+    if blob[9] != 0 or blob[15:18] != b"\0\0\0":
+        raise DecompressionFailed("nonzero TurboQuant wire reserved byte")
+    if (u(10, 4), blob[14], u(18, 4)) != (dim, polar_bits, projections):
+        raise DecompressionFailed("wire header does not match quantizer profile")
+    if u(22, 8) != seed:
+        raise DecompressionFailed(f"wire seed {u(22, 8)} does not match quantizer profile seed {seed}")
+    if u(30, 4) != dim // 2:
+        raise DecompressionFailed("wire polar block count does not match dimension")
+    if u(34, 4) != (projections if with_qjl else 0):
+        raise DecompressionFailed("wire sign count does not match expected")
+    expect = 4 * (dim // 2) + ((dim // 2) * polar_bits + 7) // 8 + ((projections + 7) // 8 if with_qjl else 0)
+    if u(38, 8) != expect or len(blob) != TQW1_HEADER_BYTES + expect:
+        raise DecompressionFailed("TurboQuant wire payload length does not match expected")
+    return bytes(blob[TQW1_HEADER_BYTES:])
 
 
 @functools.lru_cache(maxsize=16)
@@ -149,6 +218,53 @@ class FibQuantAdapter(KVecCodec):
         except L.PkvError as e:
             raise DecompressionFailed(f"fib batched wire decode failed: {e}") from e
 
+    # -- per-vector payloads (FB1), codec.rs:581-667 ------------------------------------------
+    def _wire_shape(self, prof: FibProfile):
+        """(wire_index_bits, block_count, norm payload bytes) of the profile's codes."""
+        return (max(1, (prof.codebook_size - 1).bit_length()), self._dim // self.k,
+                2 if prof.norm_format == L.NORM_FP16 else 4)
+
+    def _records(self, prof: FibProfile, x: np.ndarray) -> list[bytes]:
+        fb2 = prof.encode_batch_compact(x)
+        rec = prof.record_bytes
+        bits, blocks, nlen = self._wire_shape(prof)
+        return [fb1_frame(fb2[L.FB2_HEADER_BYTES + i * rec:L.FB2_HEADER_BYTES + (i + 1) * rec], bits, blocks, nlen)
+                for i in range(x.shape[0])]
+
+    def encode(self, vector, seed: int) -> bytes:
+        """codec.rs:581-594: one vector, single-vector numerics, FB1 bytes (23 at d=64)."""
+        x = _as_matrix([vector], self._dim, CompressionFailed)
+        prof = _fib_profile(self._dim, self.k, self.n, self.training_samples, self.lloyd_restarts,
+                            self.lloyd_iterations, seed, L.FIB_NUMERICS_SINGLE)
+        try:
+            return self._records(prof, x)[0]
+        except L.PkvError as e:
+            raise CompressionFailed(f"fib encode failed: {e}") from e
+
+    def encode_batch(self, vectors, seed: int) -> list[bytes]:
+        """codec.rs:596-610: FibQuantizer::encode_batch numerics, one FB1 payload per vector."""
+        x = _as_matrix(vectors, self._dim, CompressionFailed)
+        try:
+            return self._records(self.build_quantizer(seed), x)
+        except L.PkvError as e:
+            raise CompressionFailed(f"fib encode_batch failed: {e}") from e
+
+    def decode_batch(self, payloads, seed: int) -> np.ndarray:
+        """codec.rs:640-667: FB1 payloads through decode_batch_fast -> [n, dim] f32.  (The JSON
+        envelope of older pools is not read here.)"""
+        prof = self.build_quantizer(seed)
+        bits, blocks, nlen = self._wire_shape(prof)
+        recs = [fb1_parse(bytes(p), bits, blocks, nlen) for p in payloads]
+        try:
+            return prof.decode_batch_compact(prof.header(len(recs)) + b"".join(recs))
+        except L.PkvError as e:
+            raise DecompressionFailed(f"fib decode_batch_fast failed: {e}") from e
+
+    def decode(self, payload, seed: int):
+        """codec.rs:612-638 runs the f64 inverse rotation (FibQuantizer::decode), which is not the
+        batched f32 arithmetic this library implements; use decode_batch."""
+        raise NotImplementedError("single-vector fib decode (f64 path) is not provided; use decode_batch")
+
 
 class TurboQuantAdapter(KVecCodec):
     def __init__(self, dim: int, bits: int, projections: int, lossy_radii: bool = False):
@@ -181,6 +297,35 @@ class TurboQuantAdapter(KVecCodec):
             return self.build_quantizer(seed).encode_batch_compact(x)
         except L.PkvError as e:
             raise CompressionFailed(f"turbo encode failed: {e}") from e
+
+    # -- per-vector payloads (TQW1, always f32 radii), codec.rs:341-412 --------------------------
+    def encode_batch(self, vectors, seed: int) -> list[bytes]:
+        x = _as_matrix(vectors, self._dim, CompressionFailed)
+        prof = _turbo_profile(self._dim, self.bits, self.projections, False, seed)
+        try:
+            tqb = prof.encode_batch_compact(x)
+        except L.PkvError as e:
+            raise CompressionFailed(f"turbo encode failed: {e}") from e
+        rec = prof.record_bytes
+        return [tqw1_frame(tqb[L.TQB1_HEADER_BYTES + i * rec:L.TQB1_HEADER_BYTES + (i + 1) * rec], self._dim,
+                           self.bits - 1, self.projections, seed, True) for i in range(x.shape[0])]
+
+    def encode(self, vector, seed: int) -> bytes:
+        """codec.rs:341-368: TurboQuantizer::encode + TurboCodeWireV1::encode (46-byte header)."""
+        return self.encode_batch([vector], seed)[0]
+
+    def decode_batch(self, payloads, seed: int) -> np.ndarray:
+        prof = _turbo_profile(self._dim, self.bits, self.projections, False, seed)
+        recs = [tqw1_parse(bytes(p), self._dim, self.bits - 1, self.projections, seed, True) for p in payloads]
+        try:
+            return prof.decode_batch_compact(prof.header(len(recs)) + b"".join(recs))
+        except L.PkvError as e:
+            raise DecompressionFailed(f"turbo decode failed: {e}") from e
+
+    def decode(self, payload, seed: int) -> np.ndarray:
+        """codec.rs:370-412: the polar reconstruction of one TQW1 payload (the QJL signs are not
+        invertible and are ignored, as in the reference)."""
+        return self.decode_batch([payload], seed)[0]
 
     def decode_batch_compact(self, payload: bytes, seed: int) -> np.ndarray:
         """codec.rs:295-326; the radii codec is taken from byte 15 of the header."""

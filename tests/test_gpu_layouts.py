@@ -289,3 +289,42 @@ def test_scaled_long_context_d128_bytes_and_decode(oracle_mod, codec):
     else:
         bad = parity_report.run(_torch(), "C5", "turbo d=128 scaled", shape, 16, 256, "turbo", seed=7, outliers=True)
     assert bad == 0
+
+
+def test_per_vector_payloads_fb1_and_tqw1(oracle_mod):
+    """KVecCodec::{encode, encode_batch, decode, decode_batch} (proveKV/src/codec.rs:341-412,581-667):
+    the per-vector FB1 / TQW1 payloads carry the same records as the batched formats -- single-vector
+    numerics for fib `encode`, batch numerics for `encode_batch`."""
+    from provekv_b200 import codec as cd
+    d = 64
+    x = synthetic_kv(40, d, seed=21)
+    fib = pk.create_codec(pk.CODEC_FIB_K4_N32, d, fib_config=pk.FibConfig())
+    prof = fib.build_quantizer(SEED)
+    blobs = fib.encode_batch(list(x), SEED)
+    st, want, _, _ = oracle_mod.fib_encode(x, prof.rotation, prof.codebook, numerics=L.FIB_NUMERICS_BATCH)
+    assert st == 0 and len(blobs) == 40 and all(len(b) == 23 for b in blobs)
+    assert b"".join(b[11:] for b in blobs) == want.tobytes()
+    one = fib.encode(x[7], SEED)
+    st, w1, _, _ = oracle_mod.fib_encode(x[7:8], prof.rotation, prof.codebook, numerics=L.FIB_NUMERICS_SINGLE)
+    assert st == 0 and one == cd.fb1_frame(w1.tobytes(), 5, 16, 2)
+    y = fib.decode_batch(blobs, SEED)
+    st, ref, _, _ = oracle_mod.fib_decode(want, d, prof.rotation, prof.codebook)
+    assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
+    with pytest.raises(NotImplementedError):
+        fib.decode(blobs[0], SEED)
+    with pytest.raises(pk.DecompressionFailed):
+        fib.decode_batch([blobs[0][:-1]], SEED)
+
+    tq = pk.create_codec(pk.CODEC_TURBO_8BIT, d, turbo_config=pk.TurboConfig(bits=4, projections=32))
+    tprof = tq.build_quantizer(SEED)
+    tb = tq.encode_batch(list(x), SEED)
+    st, twant, _, _ = oracle_mod.turbo_encode(x, tprof.signs, tprof.qjl, bits=4, mode=1, radii_codec=0)
+    assert st == 0 and all(len(b) == 46 + 144 and b[:4] == b"TQW1" for b in tb)
+    assert b"".join(b[46:] for b in tb) == twant.tobytes()
+    assert tq.encode(x[3], SEED) == tb[3]
+    ty = tq.decode_batch(tb, SEED)
+    st, tref, _, _ = oracle_mod.turbo_decode(twant, d, tprof.signs, bits=4, mode=1, projections=32, radii_codec=0)
+    assert np.array_equal(ty.view(np.uint32), tref.view(np.uint32))
+    assert np.array_equal(tq.decode(tb[5], SEED), ty[5])
+    with pytest.raises(pk.DecompressionFailed):
+        tq.decode(tb[0][:4] + b"\x02" + tb[0][5:], SEED)

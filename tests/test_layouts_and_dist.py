@@ -109,3 +109,28 @@ def test_two_rank_gloo_broadcast_and_sharding():
     assert res[0][1] and res[1][1] and res[0][2] and res[1][2]
     assert res[0][3] == [0, 1, 2, 3] and res[1][3] == [4, 5, 6, 7]
     assert res[0][4] == [2.0, 5.0] and res[1][4] == [2.0, 5.0]
+
+
+def test_per_vector_wire_framing_round_trips_and_rejects():
+    """FB1 (fib-quant/src/codec.rs:81-152) and TQW1 (turbo-quant/src/wire.rs:44-214) framing on the
+    host: sizes from the reference's comments (11 + 12 = 23 bytes; 46-byte header), field checks."""
+    from provekv_b200 import codec as cd
+    rec = bytes(range(12))
+    blob = cd.fb1_frame(rec, 5, 16, 2)
+    assert len(blob) == 23 and blob[:5] == b"FB1\x01\x05" and blob[5:9] == (16).to_bytes(4, "little")
+    assert cd.fb1_parse(blob, 5, 16, 2) == rec
+    for bad in (blob[:10], b"XB1" + blob[3:], blob[:3] + b"\x02" + blob[4:], blob + b"\0", blob[:-1]):
+        with pytest.raises(cd.DecompressionFailed):
+            cd.fb1_parse(bad, 5, 16, 2)
+    with pytest.raises(cd.DecompressionFailed):
+        cd.fb1_parse(blob, 5, 32, 2)
+    trec = bytes(144)
+    tb = cd.tqw1_frame(trec, 64, 3, 32, 42, True)
+    assert len(tb) == 46 + 144 and tb[:4] == b"TQW1" and tb[8] == 1 and tb[14] == 3
+    assert int.from_bytes(tb[38:46], "little") == 144
+    assert cd.tqw1_parse(tb, 64, 3, 32, 42, True) == trec
+    for bad in (tb[:45], b"TQB1" + tb[4:], tb[:8] + b"\x02" + tb[9:], tb + b"\0"):
+        with pytest.raises(cd.DecompressionFailed):
+            cd.tqw1_parse(bad, 64, 3, 32, 42, True)
+    with pytest.raises(cd.DecompressionFailed):
+        cd.tqw1_parse(tb, 64, 3, 32, 43, True)
