@@ -354,8 +354,8 @@ def run_ours(args, w):
                          "decode_patch_achieved": algo_bytes * n_vec / (dec_ms * 1e-3) / 1e9,
                          "traffic": ncu_traffic(f"{args.workload}:{dom}")},
             "e2e": {"value": total_f32 / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": f32_bytes + n_batches * vpb * rec,
-                    "d2h_bytes_per_step": f32_bytes + n_batches * vpb * rec,
+                    "h2d_bytes_per_step": (f32_bytes + n_batches * vpb * rec) * world,
+                    "d2h_bytes_per_step": (f32_bytes + n_batches * vpb * rec) * world,
                     "api": f"pkv_{kind}_{{encode,decode}}_batches_compact, pinned host buffers"},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
