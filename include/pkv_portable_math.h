@@ -177,37 +177,60 @@ PKV_HD double pkv_log_f(float xf) {
 
 PKV_HD float pkv_logf_portable(float x) { return PKV_D2F(pkv_log_f(x)); }
 
-/* expf for a finite binary32 argument: x = k ln2 + r, |r| <= ln2/2,
- * exp(r) by its Taylor series through r^14 (next term < 2^-63), one rounding
- * to binary32 (which also produces subnormals, 0 and +inf correctly). */
+/* expf for a finite binary32 argument: x = k (ln2/32) + r with |r| <= ln2/64, k = 32 e + j,
+ * exp(x) = 2^e * 2^(j/32) * exp(r); 2^(j/32) from a 32-entry table, exp(r) by its Taylor series
+ * through r^7 (next term < 2^-67) evaluated with fused multiply-adds, one rounding to binary32
+ * (which also produces subnormals, 0 and +inf correctly). */
+#define PKV_EXP_INV_C 0x1.71547652b82fep+5 /* 32 / ln2 */
+#define PKV_EXP_C_HI 0x1.62e42fefa0000p-6  /* ln2 / 32, 38 significant bits: k * C_HI is exact */
+#define PKV_EXP_C_LO 0x1.cf79abc9e3b3ap-45
+#define PKV_EXP2_TABLE_INIT                                                                          \
+  {0x1.0000000000000p+0, 0x1.059b0d3158574p+0, 0x1.0b5586cf9890fp+0, 0x1.11301d0125b51p+0,           \
+   0x1.172b83c7d517bp+0, 0x1.1d4873168b9aap+0, 0x1.2387a6e756238p+0, 0x1.29e9df51fdee1p+0,           \
+   0x1.306fe0a31b715p+0, 0x1.371a7373aa9cbp+0, 0x1.3dea64c123422p+0, 0x1.44e086061892dp+0,           \
+   0x1.4bfdad5362a27p+0, 0x1.5342b569d4f82p+0, 0x1.5ab07dd485429p+0, 0x1.6247eb03a5585p+0,           \
+   0x1.6a09e667f3bcdp+0, 0x1.71f75e8ec5f74p+0, 0x1.7a11473eb0187p+0, 0x1.82589994cce13p+0,           \
+   0x1.8ace5422aa0dbp+0, 0x1.93737b0cdc5e5p+0, 0x1.9c49182a3f090p+0, 0x1.a5503b23e255dp+0,           \
+   0x1.ae89f995ad3adp+0, 0x1.b7f76f2fb5e47p+0, 0x1.c199bdd85529cp+0, 0x1.cb720dcef9069p+0,           \
+   0x1.d5818dcfba487p+0, 0x1.dfc97337b9b5fp+0, 0x1.ea4afa2a490dap+0, 0x1.f50765b6e4540p+0}
+#if defined(__CUDACC__)
+/* in global memory (cached loads): the index differs from thread to thread */
+__device__ static const double pkv_exp2_tab_dev[32] = PKV_EXP2_TABLE_INIT;
+#endif
+static const double pkv_exp2_tab_host[32] = PKV_EXP2_TABLE_INIT;
+#if defined(__CUDA_ARCH__)
+#define PKV_DFMA(a, b, c) fma((a), (b), (c))
+#else
+#define PKV_DFMA(a, b, c) __builtin_fma((a), (b), (c))
+#endif
+
 PKV_HD float pkv_expf_portable(float xf) {
   double x = (double)xf;
   if (x > 89.0) return pkv_f32_from_bits(0x7f800000u);
   if (x < -150.0) return 0.0f;
 #if defined(__CUDA_ARCH__)
-  double kd = rint(PKV_DMUL(x, PKV_INV_LN2));
+  double kd = rint(PKV_DMUL(x, PKV_EXP_INV_C));
 #else
-  double kd = __builtin_rint(PKV_DMUL(x, PKV_INV_LN2));
+  double kd = __builtin_rint(PKV_DMUL(x, PKV_EXP_INV_C));
 #endif
-  double r = PKV_DSUB(PKV_DSUB(x, PKV_DMUL(kd, PKV_LN2_HI)), PKV_DMUL(kd, PKV_LN2_LO));
-  double p = 0x1.93974a8c07c9dp-37;                      /* 1/14! */
-  p = PKV_DADD(0x1.6124613a86d09p-33, PKV_DMUL(r, p));   /* 1/13! */
-  p = PKV_DADD(0x1.1eed8eff8d898p-29, PKV_DMUL(r, p));   /* 1/12! */
-  p = PKV_DADD(0x1.ae64567f544e4p-26, PKV_DMUL(r, p));   /* 1/11! */
-  p = PKV_DADD(0x1.27e4fb7789f5cp-22, PKV_DMUL(r, p));   /* 1/10! */
-  p = PKV_DADD(0x1.71de3a556c734p-19, PKV_DMUL(r, p));   /* 1/9! */
-  p = PKV_DADD(0x1.a01a01a01a01ap-16, PKV_DMUL(r, p));   /* 1/8! */
-  p = PKV_DADD(0x1.a01a01a01a01ap-13, PKV_DMUL(r, p));   /* 1/7! */
-  p = PKV_DADD(0x1.6c16c16c16c17p-10, PKV_DMUL(r, p));   /* 1/6! */
-  p = PKV_DADD(0x1.1111111111111p-7, PKV_DMUL(r, p));    /* 1/5! */
-  p = PKV_DADD(0x1.5555555555555p-5, PKV_DMUL(r, p));    /* 1/4! */
-  p = PKV_DADD(0x1.5555555555555p-3, PKV_DMUL(r, p));    /* 1/3! */
-  p = PKV_DADD(0x1.0000000000000p-1, PKV_DMUL(r, p));    /* 1/2! */
-  p = PKV_DADD(1.0, PKV_DMUL(r, p));
-  p = PKV_DADD(1.0, PKV_DMUL(r, p));
+  double r = PKV_DFMA(-kd, PKV_EXP_C_LO, PKV_DFMA(-kd, PKV_EXP_C_HI, x));
+  double p = 0x1.a01a01a01a01ap-13;               /* 1/7! */
+  p = PKV_DFMA(r, p, 0x1.6c16c16c16c17p-10);      /* 1/6! */
+  p = PKV_DFMA(r, p, 0x1.1111111111111p-7);       /* 1/5! */
+  p = PKV_DFMA(r, p, 0x1.5555555555555p-5);       /* 1/4! */
+  p = PKV_DFMA(r, p, 0x1.5555555555555p-3);       /* 1/3! */
+  p = PKV_DFMA(r, p, 0x1.0000000000000p-1);       /* 1/2! */
+  p = PKV_DFMA(r, p, 1.0);
+  p = PKV_DFMA(r, p, 1.0);
   int k = (int)kd;
-  double two_k = pkv_f64_from_bits((uint64_t)(k + 1023) << 52);
-  return PKV_D2F(PKV_DMUL(p, two_k));
+  int j = k & 31, e = k >> 5; /* k = 32 e + j, 0 <= j < 32 (arithmetic shift) */
+#if defined(__CUDA_ARCH__)
+  double t = pkv_exp2_tab_dev[j];
+#else
+  double t = pkv_exp2_tab_host[j];
+#endif
+  double two_e = pkv_f64_from_bits((uint64_t)(e + 1023) << 52);
+  return PKV_D2F(PKV_DMUL(PKV_DMUL(p, t), two_e));
 }
 
 #endif /* PKV_PORTABLE_MATH_H */
