@@ -267,7 +267,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     for (int k = 0; k < NW; k++) words[k] = 0;
     uint64_t bitbuf = 0;
     int nbits = 0, wk = 0;
-    uint32_t rmax = 0;  // radii are >= 0 or NaN: the largest bit pattern tells if any is not finite
+    uint32_t rmax = 0;  // radii are >= +0 or NaN: the largest bit pattern tells if any is not finite
 #pragma unroll
     for (int i = 0; i < K::P; i++) {
       const float a = y[2 * i], b = y[2 * i + 1];
@@ -278,7 +278,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       uint32_t idx = 0;
       if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
       unc |= (unsigned long long)(certain ? 0u : 1u) << i;
-      rmax = max(rmax, __float_as_uint(r) & 0x7fffffffu);
+      rmax = max(rmax, __float_as_uint(r));  // a square root is +x or NaN (either sign): unsigned order works
       if constexpr (DIRECT) y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
       else radp[i * K::WS] = r;
       if constexpr (PB != 0) {
