@@ -473,6 +473,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
     }
   }
+  if constexpr (!DIRECT)  // direct stores imply f32 radii: keep this block out of that kernel's code
   if (tp.lossy) {
     // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371).
     // The logarithm is monotone, so min / max of the logs are the logs of the smallest / largest
