@@ -168,13 +168,14 @@ struct TurboEncSmem {
   }
 };
 
-// DIRECT (f32 radii, record a multiple of 16 bytes, angle + sign words a multiple of 4): the
-// record never passes through shared memory.  Radii stay in the registers of their pairs and are
-// stored by their thread as 16-byte pieces of its own record; only the few angle / sign words
-// sit in a small shared tile so that the cooperative fix-up can patch them.  The staged variant
-// handles every other record shape through a word-transposed tile.
+// f32 radii never pass through shared memory: they stay in the registers of their pairs and are
+// stored by their thread into its own record; only the few angle / sign words sit in a small
+// shared tile so that the cooperative fix-up can patch them.  DIRECT (record a multiple of 16
+// bytes, angle + sign words a multiple of 4) stores 16-byte pieces, the other f32-radii shapes
+// one word at a time (their records are only 4-byte aligned).  BlockLogU8 records are assembled
+// whole in a word-transposed tile and written out by the warp.
 template <int D, int PB, bool DIRECT>
-__global__ void __launch_bounds__(TurboEnc<D>::THREADS, (D == 64 && DIRECT) ? 4 : 1)
+__global__ void __launch_bounds__(TurboEnc<D>::THREADS, D == 64 ? (DIRECT ? 4 : 3) : 2)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                     uint8_t* __restrict__ payload, uint64_t* err) {
   using K = TurboEnc<D>;
@@ -193,8 +194,11 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   float* s_thr = s_lut + lut_len;  // [m] binary32-tier thresholds of the sign shortcut
   const float* s_ray_cos = s_lut + 2 * levels;
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
-  const int rw = DIRECT ? 0 : tp.radii_words;  // radii words present in the shared tile
-  const int tile_words = DIRECT ? tp.angle_words + tp.sign_words : tp.rec_words;
+  // f32 radii never pass through shared memory (16-byte stores in the DIRECT kernel, 4-byte stores
+  // otherwise); BlockLogU8 records are assembled whole in the tile
+  const bool lossy = !DIRECT && tp.lossy;
+  const int rw = lossy ? tp.radii_words : 0;  // radii words present in the shared tile
+  const int tile_words = lossy ? tp.rec_words : tp.angle_words + tp.sign_words;
   uint8_t* wbase = smem + TurboEncSmem<D>::table_bytes(m, levels, tp.ray_count) +
                    warp * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
   int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                  // [TV]
@@ -258,7 +262,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 
   // Pass 1, encode_pair (polar.rs:413-421): radius exactly, bucket by the shortcut.  Radii go
   // to the record (f32 codec) or to s_rad (BlockLogU8); undecided pairs are noted in `unc`.
-  float* radp = tp.lossy ? (s_rad + v) : reinterpret_cast<float*>(w);
+  float* radp = s_rad + v;
   constexpr int NW = PB ? K::P * PB / 32 : 1;
   unsigned long long unc = 0;
   {
@@ -279,8 +283,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
       unc |= (unsigned long long)(certain ? 0u : 1u) << i;
       rmax = max(rmax, __float_as_uint(r));  // a square root is +x or NaN (either sign): unsigned order works
-      if constexpr (DIRECT) y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
-      else radp[i * K::WS] = r;
+      y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
+      if (lossy) radp[i * K::WS] = r;
       if constexpr (PB != 0) {
         const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
         words[wi] |= idx << sh;
@@ -320,6 +324,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       for (int k = 0; k < K::P / 4; k++)
         reinterpret_cast<float4*>(my_rec)[k] = make_float4(y[8 * k], y[8 * k + 2], y[8 * k + 4], y[8 * k + 6]);
     }
+  } else if (!lossy && valid) {  // records that are only 4-byte aligned: one word per store
+#pragma unroll
+    for (int i = 0; i < K::P; i++) reinterpret_cast<float*>(my_rec)[i] = y[2 * i];
   }
 
   if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
@@ -351,7 +358,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           bitbuf >>= pb;
           nbits -= pb;
         }
-        const float r = DIRECT ? y[2 * i] : radp[i * K::WS];
+        const float r = y[2 * i];
         const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
         y[2 * i] = cs.x;
         y[2 * i + 1] = cs.y;
@@ -540,6 +547,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         *reinterpret_cast<uint4*>(my_rec + 4 * (K::P + k)) =
             make_uint4(w[k * K::WS], w[(k + 1) * K::WS], w[(k + 2) * K::WS], w[(k + 3) * K::WS]);
     }
+  } else if (!lossy) {
+    if (valid)
+      for (int k = 0; k < tile_words; k++) reinterpret_cast<uint32_t*>(my_rec)[K::P + k] = w[k * K::WS];
   } else {
     __syncwarp();
     stage_records<D, false>(
@@ -560,7 +570,7 @@ inline bool turbo_encode_direct(const TurboParams& tp) {
 
 template <int D>
 size_t turbo_encode_smem(const TurboParams& tp) {
-  const int tile_words = turbo_encode_direct(tp) ? tp.angle_words + tp.sign_words : tp.rec_words;
+  const int tile_words = tp.lossy ? tp.rec_words : tp.angle_words + tp.sign_words;
   return TurboEncSmem<D>::table_bytes(tp.projections, 1 << tp.polar_bits, tp.ray_count) +
          TurboEnc<D>::NWARPS * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
 }
