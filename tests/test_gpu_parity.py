@@ -134,3 +134,90 @@ def test_turbo_decode_matches_oracle(oracle_mod, dim, case, n):
         err = np.abs(got - plat)
         assert np.all(err.max(axis=1) <= 1e-6 * np.abs(plat).max(axis=1))
         assert np.mean(err > 1e-7 + 1e-6 * np.abs(plat)) < 1e-3
+
+
+def test_turbo_sign_tiers_with_degenerate_projection_rows(oracle_mod):
+    """QJL matrix with all-zero rows, rows of magnitude 1e-30 and rows that are exact copies or
+    negatives of others: every dot with a zero row is exactly 0 (sign bit 1), tiny rows give dots far
+    below any bound relative to nothing -- all of them miss the tensor-core and binary32 tiers and
+    are settled by the exact sequence, for every vector, so the per-warp list overflows as well."""
+    dim, n, m = 64, 3000, 32
+    signs, qjl = _turbo_tables(dim, m)
+    q = np.array(qjl, dtype=np.float32).reshape(m, dim).copy()
+    q[0:6] = 0.0
+    q[6:12] *= np.float32(1e-30)
+    q[12] = q[13]
+    q[14] = -q[15]
+    x = synthetic_kv(n, dim, seed=91)
+    x[5] = 0.0                      # an all-zero vector: zero residual, every sign bit 1
+    x[6] = x[7]
+    prof = pk.TurboProfile(dim, 4, signs, q, mode=L.TURBO_POLAR_WITH_QJL, seed=SEED)
+    got = prof.encode_batch_compact(x)
+    st, payload, _, _ = oracle_mod.turbo_encode(x, signs, q, bits=4, mode=L.TURBO_POLAR_WITH_QJL,
+                                               radii_codec=L.RADII_F32, libm_mode=oracle_mod.LIBM_PORTABLE)
+    assert st == 0
+    want = payload.reshape(n, -1)
+    have = np.frombuffer(got, np.uint8)[L.TQB1_HEADER_BYTES:].reshape(n, -1)
+    assert np.array_equal(have, want)
+    assert np.all(have[5, -4:] == 0xff) and np.all(have[:, -4] & 0x3f == 0x3f)  # zero rows -> bit 1
+
+
+def test_fib_blocks_placed_between_codewords(oracle_mod, fib_tables):
+    """Vectors whose normalised, rotated 4-blocks sit on (and within 1e-7 .. 1e-3 of) the bisector
+    between two codewords: where those two are the nearest, the top-2 gap is at or below every
+    tier's bound, so the decision falls through the tensor-core tier and the binary32 tier to the
+    exact f64 kernel -- whose answer must be the oracle's, including the lowest-index rule."""
+    dim, n, B = 64, 4096, 16
+    rot, cb = fib_tables[dim]
+    c = np.asarray(cb, np.float64)
+    rng = np.random.default_rng(17)
+    i = rng.integers(0, 32, size=(n, B))
+    j = (i + rng.integers(1, 32, size=(n, B))) % 32
+    ci, cj = c[i], c[j]                                   # [n, B, 4]
+    dn = ((ci - cj) ** 2).sum(-1)
+    t = np.full((n, B), 0.5)
+    for _ in range(40):   # the blocks of y / |y| on the bisectors: fixed point in the scale 1 / |y|
+        y = t[..., None] * ci + (1.0 - t[..., None]) * cj
+        s = 1.0 / np.sqrt((y ** 2).sum((1, 2)))[:, None]
+        t = (((ci ** 2).sum(-1) - (cj ** 2).sum(-1)) / (2.0 * s) - (cj * (ci - cj)).sum(-1)) / dn
+    t += rng.choice([0.0, 1e-7, -1e-7, 1e-5, -1e-5, 1e-3, -1e-3], size=(n, B))
+    y = (t[..., None] * ci + (1.0 - t[..., None]) * cj).reshape(n, dim)
+    x = (y @ np.asarray(rot, np.float64)).astype(np.float32) * np.float32(3.0)   # x = M^T y, any norm
+    prof = pk.FibProfile(dim, rot, cb)
+    got = prof.encode_batch_compact(x)
+    st, payload, _, _ = oracle_mod.fib_encode(x, rot, cb)
+    assert st == 0
+    assert got[L.FB2_HEADER_BYTES:] == payload.tobytes()
+
+
+@pytest.mark.parametrize("bits,mode", [(4, L.TURBO_POLAR_WITH_QJL), (4, L.TURBO_POLAR_ONLY), (8, L.TURBO_POLAR_WITH_QJL)])
+def test_turbo_pairs_exactly_on_sector_boundaries(oracle_mod, bits, mode):
+    """Rotated pairs placed exactly on the bucket boundaries (axes, diagonals, zero pairs): with
+    small-integer rotated coordinates the inverse transform is exact in binary32, so the encoder's
+    forward transform lands on the integers again and every such pair is a knife-edge for
+    floor((atan2f(b, a) + pi) / (2 pi) * L): the shortcut must hand all of them to the exact path."""
+    dim, n = 64, 2048
+    m = 32 if mode == L.TURBO_POLAR_WITH_QJL else 0
+    signs, qjl = _turbo_tables(dim, m)
+    rng = np.random.default_rng(5)
+    k = rng.integers(1, 5, size=(n, dim // 2)).astype(np.float64)
+    kind = rng.integers(0, 10, size=(n, dim // 2))
+    a = np.select([kind == 0, kind == 1, kind == 2, kind == 3, kind == 4, kind == 5, kind == 6, kind == 7, kind == 8],
+                  [k, 0 * k, -k, 0 * k, k, -k, -k, k, 0 * k], default=rng.integers(-4, 5, size=k.shape))
+    b = np.select([kind == 0, kind == 1, kind == 2, kind == 3, kind == 4, kind == 5, kind == 6, kind == 7, kind == 8],
+                  [0 * k, k, 0 * k, -k, k, k, -k, -k, 0 * k], default=rng.integers(-4, 5, size=k.shape))
+    y = np.stack([a, b], axis=-1).reshape(n, dim)
+    h = np.array([[1.0]])
+    while h.shape[0] < dim:
+        h = np.block([[h, h], [h, -h]])
+    x = ((y @ h) / 8.0 * np.asarray(signs, np.float64)[None, :]).astype(np.float32)  # exact: x = D H y / sqrt(d)
+    prof = pk.TurboProfile(dim, bits, signs, qjl, mode=mode, seed=SEED)
+    got = prof.encode_batch_compact(x)
+    st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=bits, mode=mode, radii_codec=L.RADII_F32,
+                                               libm_mode=oracle_mod.LIBM_PORTABLE)
+    assert st == 0
+    assert got[L.TQB1_HEADER_BYTES:] == payload.tobytes()
+    # the construction really is exact: the radii on the wire are the integer hypotenuses
+    rec = np.frombuffer(got, np.uint8)[L.TQB1_HEADER_BYTES:].reshape(n, -1)
+    radii = rec[:, :dim * 2].copy().view(np.float32)
+    assert np.array_equal(radii, np.sqrt(a * a + b * b).astype(np.float32))
