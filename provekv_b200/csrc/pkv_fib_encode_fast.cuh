@@ -219,9 +219,10 @@ size_t fib_encode_fast_smem(int rec) {
          K::TV * K::B + (size_t)K::TV * rec + 32;
 }
 
-// One warp per list entry: the reference's exact sequence for one block (4 rows) or for the whole
-// vector, batch numerics (normalised vector rounded to binary32, codec.rs:607-609).
-// rot is the f64 matrix row-major, M[r][j].
+// The reference's exact sequence (batch numerics: normalised vector rounded to binary32,
+// codec.rs:607-609) for the listed entries.  rot is the f64 matrix row-major, M[r][j].
+// Phase A: single-block entries, four lanes per entry (one per row of the block), eight entries
+// per warp.  Phase B: whole-vector entries, one warp per entry.
 template <int D>
 __global__ void __launch_bounds__(kThreads)
 fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __restrict__ rot,
@@ -231,15 +232,71 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
   constexpr int E = D / 32;   // elements of the vector each lane loads
   constexpr int RPL = D / 32; // rows per lane when the whole vector is redone
   constexpr int B = D / 4;
+  constexpr int Q = D / 4;    // phase A: elements of the vector each of an entry's four lanes normalises
   __shared__ float s_x[kThreads / 32][D];
   __shared__ double s_n[kThreads / 32][D];
-  __shared__ double s_m[kThreads / 32][4 * D];  // the four matrix rows of a single-block entry
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
   const float4* cb4 = reinterpret_cast<const float4*>(codebook);
   const uint32_t count = *flag_count;
+
+  for (uint32_t base = (uint32_t)gw * 8u; base < count; base += (uint32_t)nw * 8u) {
+    const int r = lane & 3;
+    const uint32_t e = base + (uint32_t)(lane >> 2);
+    const uint32_t ent = e < count ? flag_list[e] : PKV_FIB_ENTRY_ALL;
+    const uint32_t blk = ent & 31u, gvec = ent >> 5;
+    const bool act = blk != PKV_FIB_ENTRY_ALL;  // idle groups run along on vector 0, block 0, and write nothing
+    const int batch = (int)(gvec / (uint32_t)g.vpb), v = (int)(gvec % (uint32_t)g.vpb);
+    const float4* xv4 = reinterpret_cast<const float4*>(x + pkv_vec_offset(g.L, batch, v));
+    // l2_norm: sequential over j (codec.rs:1049-1057), every lane of the group the same chain
+    double acc = 0.0;
+#pragma unroll 4
+    for (int i = 0; i < D / 4; i++) {
+      const float4 t = __ldg(xv4 + i);
+      acc = __dadd_rn(acc, __dmul_rn((double)t.x, (double)t.x));
+      acc = __dadd_rn(acc, __dmul_rn((double)t.y, (double)t.y));
+      acc = __dadd_rn(acc, __dmul_rn((double)t.z, (double)t.z));
+      acc = __dadd_rn(acc, __dmul_rn((double)t.w, (double)t.w));
+    }
+    double norm = __dsqrt_rn(acc);
+    if (!(norm > 0.0)) norm = 1.0;  // only an idle group's stand-in vector can get here
+    // lane r normalises elements Q r .. Q r + Q - 1
+    float q[Q];
+#pragma unroll
+    for (int k4 = 0; k4 < Q / 4; k4++) {
+      const float4 t = __ldg(xv4 + (Q / 4) * r + k4);
+      q[4 * k4] = __double2float_rn(__ddiv_rn((double)t.x, norm));
+      q[4 * k4 + 1] = __double2float_rn(__ddiv_rn((double)t.y, norm));
+      q[4 * k4 + 2] = __double2float_rn(__ddiv_rn((double)t.z, norm));
+      q[4 * k4 + 3] = __double2float_rn(__ddiv_rn((double)t.w, norm));
+    }
+    // StoredRotation::apply (rotation.rs:104-115): lane r takes row 4 blk + r, j ascending; n_j comes
+    // from the lane of the group that normalised it
+    const double* mrow = rot + (size_t)(4 * (act ? blk : 0u) + (uint32_t)r) * D;
+    double s = 0.0;
+#pragma unroll
+    for (int o = 0; o < 4; o++)
+#pragma unroll
+      for (int k = 0; k < Q; k++) {
+        const float nj = __shfl_sync(0xffffffffu, q[k], o, 4);
+        s = __dadd_rn(s, __dmul_rn(__ldg(mrow + Q * o + k), (double)nj));
+      }
+    const float yv = __double2float_rn(s);
+    const float s0 = __shfl_sync(0xffffffffu, yv, 0, 4), s1 = __shfl_sync(0xffffffffu, yv, 1, 4);
+    const float s2 = __shfl_sync(0xffffffffu, yv, 2, 4), s3 = __shfl_sync(0xffffffffu, yv, 3, 4);
+    if (act && r == 0) {
+      const uint32_t idx = (uint32_t)nearest_codeword(cb4, n_codewords, argmin_order, s0, s1, s2, s3);
+      uint8_t* rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v * g.rec_bytes + norm_len;
+      const int pos = (int)blk * idx_bits;
+      const uint32_t m = ((1u << idx_bits) - 1u) << (pos & 7), val = idx << (pos & 7);
+      rec[pos >> 3] = (uint8_t)((rec[pos >> 3] & ~m) | val);
+      if (m >> 8) rec[(pos >> 3) + 1] = (uint8_t)((rec[(pos >> 3) + 1] & ~(m >> 8)) | (val >> 8));
+    }
+  }
+
   for (uint32_t e = gw; e < count; e += nw) {
     const uint32_t ent = flag_list[e], blk = ent & 31u, gvec = ent >> 5;
+    if (blk != PKV_FIB_ENTRY_ALL) continue;  // settled in phase A
     const int batch = (int)(gvec / (uint32_t)g.vpb), v = (int)(gvec % (uint32_t)g.vpb);
     const float* xv = x + pkv_vec_offset(g.L, batch, v);
     // the vector, then its normalised form, are shared through a per-warp slice of shared memory
@@ -261,33 +318,15 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
     for (int k = 0; k < E; k++)
       sn[lane * E + k] = (double)__double2float_rn(__ddiv_rn((double)sx[lane * E + k], norm));
     __syncwarp();
-    // StoredRotation::apply (rotation.rs:104-115): each active lane one row at a time, j ascending.
-    // A single block's four rows (2 KB of f64) are first copied into the warp's slice of shared
-    // memory with coalesced loads, so the sequential sums do not wait on one global load per term.
-    const bool whole = blk == PKV_FIB_ENTRY_ALL;
+    // StoredRotation::apply (rotation.rs:104-115): lane l takes rows l, l + 32, .., j ascending
     float yv[RPL];
-    if (!whole) {
-      double* sm = s_m[warp];
-      const double* src = rot + (size_t)(4 * blk) * D;
 #pragma unroll
-      for (int k = 0; k < 4 * D / 32; k++) sm[lane + 32 * k] = __ldg(src + lane + 32 * k);
-      __syncwarp();
-      const double* mrow = sm + (lane & 3) * D;
+    for (int rr = 0; rr < RPL; rr++) {
+      const double* mrow = rot + (size_t)(lane + 32 * rr) * D;
       double s = 0.0;
 #pragma unroll 8
-      for (int j = 0; j < D; j++) s = __dadd_rn(s, __dmul_rn(mrow[j], sn[j]));
-      yv[0] = __double2float_rn(s);
-#pragma unroll
-      for (int rr = 1; rr < RPL; rr++) yv[rr] = 0.0f;
-    } else {
-#pragma unroll
-      for (int rr = 0; rr < RPL; rr++) {
-        const double* mrow = rot + (size_t)(lane + 32 * rr) * D;
-        double s = 0.0;
-#pragma unroll 8
-        for (int j = 0; j < D; j++) s = __dadd_rn(s, __dmul_rn(__ldg(mrow + j), sn[j]));
-        yv[rr] = __double2float_rn(s);
-      }
+      for (int j = 0; j < D; j++) s = __dadd_rn(s, __dmul_rn(__ldg(mrow + j), sn[j]));
+      yv[rr] = __double2float_rn(s);
     }
     // nearest codeword per block, reference order; lanes with lane % 4 == 0 own a block
     uint32_t idx[RPL];
@@ -299,7 +338,7 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
       idx[rr] = (uint32_t)nearest_codeword(cb4, n_codewords, argmin_order, yv[rr], s1, s2, s3);
     }
     uint8_t* rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v * g.rec_bytes + norm_len;
-    if (whole) {
+    {
       // block b sits in lane 4 * (b % 8), slot b / 8; lane 0 rebuilds the whole index stream
       uint8_t bytes[(B * 5 + 7) / 8 + 1];
       for (int i = 0; i < (B * idx_bits + 7) / 8; i++) bytes[i] = 0;
@@ -317,11 +356,6 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
       }
       if (lane == 0)
         for (int i = 0; i < (B * idx_bits + 7) / 8; i++) rec[i] = bytes[i];
-    } else if (lane == 0) {
-      const int pos = (int)blk * idx_bits;
-      const uint32_t m = ((1u << idx_bits) - 1u) << (pos & 7), val = idx[0] << (pos & 7);
-      rec[pos >> 3] = (uint8_t)((rec[pos >> 3] & ~m) | val);
-      if (m >> 8) rec[(pos >> 3) + 1] = (uint8_t)((rec[(pos >> 3) + 1] & ~(m >> 8)) | (val >> 8));
     }
     __syncwarp();
   }
