@@ -123,6 +123,15 @@ typedef struct pkv_layout {
   int32_t n_replicas;
 } pkv_layout;
 
+/* Element type of the cache a decode-and-patch call writes.  proveKV/scripts/ppl_validate_multi_agent.py:
+ * 247-262 stores the decoded f32 values with `dtype=k.dtype`, i.e. rounded to nearest-even to the model's
+ * cache type; the *_as calls do the same rounding in the kernel's store (values beyond the half-precision
+ * range become infinities, as in that conversion).  For the 16-bit types the layout's base and strides are
+ * still in elements and must be multiples of 8. */
+#define PKV_DST_F32 0
+#define PKV_DST_F16 1
+#define PKV_DST_BF16 2
+
 typedef struct pkv_fib_profile pkv_fib_profile;
 typedef struct pkv_turbo_profile pkv_turbo_profile;
 
@@ -180,6 +189,11 @@ int pkv_fib_decode_patch_dev(const pkv_fib_profile* p, const uint8_t* payload_de
                              int64_t payload_batch_stride, const pkv_layout* layout,
                              float* cache_dev, uint64_t* err_dev, void* stream);
 
+/* The same decode with the cache element type chosen by the caller (PKV_DST_*). */
+int pkv_fib_decode_patch_dev_as(const pkv_fib_profile* p, const uint8_t* payload_dev,
+                                int64_t payload_batch_stride, const pkv_layout* layout,
+                                void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream);
+
 /* FibQuantAdapter::encode_batch_compact (proveKV/src/codec.rs:513-525): n vectors
  * of dim f32, contiguous, host memory -> FB2 bytes (19-byte header + n records). */
 int pkv_fib_encode_batch_compact(const pkv_fib_profile* p, const float* vectors_host, int64_t n,
@@ -228,6 +242,10 @@ int pkv_turbo_encode_dev(const pkv_turbo_profile* p, const float* x_dev, const p
 int pkv_turbo_decode_patch_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
                                int64_t payload_batch_stride, const pkv_layout* layout,
                                float* cache_dev, uint64_t* err_dev, void* stream);
+
+int pkv_turbo_decode_patch_dev_as(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                                  int64_t payload_batch_stride, const pkv_layout* layout,
+                                  void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream);
 
 /* TurboQuantAdapter::{encode,decode}_batch_compact (proveKV/src/codec.rs:248-326). */
 int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* p, const float* vectors_host, int64_t n,

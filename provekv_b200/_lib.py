@@ -39,6 +39,7 @@ ARGMIN_PAIRWISE, ARGMIN_SEQUENTIAL = 0, 1
 FIB_NUMERICS_AUTO, FIB_NUMERICS_BATCH, FIB_NUMERICS_SINGLE = 0, 1, 2
 TURBO_POLAR_ONLY, TURBO_POLAR_WITH_QJL = 0, 1
 RADII_F32, RADII_BLOCK_LOG_U8 = 0, 1
+DST_F32, DST_F16, DST_BF16 = 0, 1, 2  # PKV_DST_*: element type of the patched cache
 FB2_HEADER_BYTES, TQB1_HEADER_BYTES = 19, 38
 
 
@@ -126,6 +127,8 @@ _SIGS = {
     "pkv_fib_record_bytes": (C.c_int32, [_V]),
     "pkv_fib_encode_dev": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_decode_patch_dev": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, _V]),
+    "pkv_fib_decode_patch_dev_as": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, C.c_int32, _V, _V]),
+    "pkv_turbo_decode_patch_dev_as": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, C.c_int32, _V, _V]),
     "pkv_fib_encode_dev_static": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_encode_batch_compact": (C.c_int, [_V, _V, C.c_int64, _V, C.c_int64, C.POINTER(C.c_int64),
                                                C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),

@@ -2,6 +2,8 @@
 // addressing, the device error word and the profile objects behind the C ABI.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -145,6 +147,23 @@ struct pkv_turbo_profile {
   PkvWorkspace ws;
 };
 
+// Cache element type of a decode kernel and the round-to-nearest-even store conversion.
+template <int DST> struct PkvDst { using type = float; };
+template <> struct PkvDst<PKV_DST_F16> { using type = __half; };
+template <> struct PkvDst<PKV_DST_BF16> { using type = __nv_bfloat16; };
+#ifdef __CUDACC__
+template <int DST>
+__device__ __forceinline__ uint32_t pkv_pack2(float a, float b) {  // a in the low half
+  if constexpr (DST == PKV_DST_F16) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  } else {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+}
+#endif
+
 int pkv_cuda_status(cudaError_t e);
 int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
                   bool encode, PkvGeom* g);
@@ -158,10 +177,10 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
                                             uint8_t* payload, uint64_t* err, uint32_t* scratch,
                                             cudaStream_t s);
 int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
-                          float* cache, uint64_t* err, cudaStream_t s);
+                          void* cache, int dst, uint64_t* err, cudaStream_t s);
 int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const PkvGeom& g,
                             uint8_t* payload, uint64_t* err, cudaStream_t s);
 int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,
-                            float* cache, uint64_t* err, cudaStream_t s);
+                            void* cache, int dst, uint64_t* err, cudaStream_t s);
 int pkv_fib_tile_vectors(int dim, int encode);
 int pkv_turbo_tile_vectors(int dim);

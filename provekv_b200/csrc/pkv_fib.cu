@@ -69,12 +69,13 @@ struct FibDec {
   static constexpr int B = D / 4;
 };
 
-template <int D>
+template <int D, int DST>
 __global__ void __launch_bounds__(kThreads)
 fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
                         const float* __restrict__ rot32, const float* __restrict__ codebook,
-                        int n_codewords, int idx_bits, int norm_len, float* __restrict__ cache,
-                        uint64_t* err, unsigned long long ones) {
+                        int n_codewords, int idx_bits, int norm_len,
+                        typename PkvDst<DST>::type* __restrict__ cache, uint64_t* err,
+                        unsigned long long ones) {
   using K = FibDec<D>;
   extern __shared__ __align__(128) uint8_t smem[];
   float* s_rot = reinterpret_cast<float*>(smem);                 // [D][D]
@@ -180,10 +181,15 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
       ok = ok && pkv_finite(o[c]);
     }
     if (!ok) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, PKV_VEC_NONFINITE_OUTPUT);
-    float* dst = cache + s_dst[v];
+    typename PkvDst<DST>::type* dst = cache + s_dst[v];
     for (int r = 0; r < g.L.n_replicas; r++) {
-      *reinterpret_cast<float4*>(dst + cA) = make_float4(o[0], o[1], o[2], o[3]);
-      *reinterpret_cast<float4*>(dst + cB) = make_float4(o[4], o[5], o[6], o[7]);
+      if constexpr (DST == PKV_DST_F32) {
+        *reinterpret_cast<float4*>(dst + cA) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(dst + cB) = make_float4(o[4], o[5], o[6], o[7]);
+      } else {  // the finite check above is on the f32 values, as in the reference; the cast comes after
+        *reinterpret_cast<uint2*>(dst + cA) = make_uint2(pkv_pack2<DST>(o[0], o[1]), pkv_pack2<DST>(o[2], o[3]));
+        *reinterpret_cast<uint2*>(dst + cB) = make_uint2(pkv_pack2<DST>(o[4], o[5]), pkv_pack2<DST>(o[6], o[7]));
+      }
       dst += g.L.replica_stride;
     }
   }
@@ -518,22 +524,30 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
 }
 
 int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
-                          float* cache, uint64_t* err, cudaStream_t s) {
+                          void* cache, int dst, uint64_t* err, cudaStream_t s) {
   const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
   if (grid == 0) return PKV_OK;
   if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
   int st;
-#define PKV_FIB_DEC(DIM)                                                                          \
+#define PKV_FIB_DEC(DIM, DST)                                                                     \
   {                                                                                               \
     const size_t sm = fib_decode_smem<DIM>(g.rec_bytes);                                          \
-    if ((st = set_smem(fib_decode_patch_kernel<DIM>, sm)) != PKV_OK) return st;                   \
-    fib_decode_patch_kernel<DIM><<<(unsigned)grid, kThreads, sm, s>>>(                            \
+    if ((st = set_smem(fib_decode_patch_kernel<DIM, DST>, sm)) != PKV_OK) return st;              \
+    fib_decode_patch_kernel<DIM, DST><<<(unsigned)grid, kThreads, sm, s>>>(                       \
         g, payload, p->rot32_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits,             \
-        p->norm_len, cache, err, kPackedOnes);                                                    \
+        p->norm_len, static_cast<PkvDst<DST>::type*>(cache), err, kPackedOnes);                   \
   }
-  if (p->cfg.dim == 64) PKV_FIB_DEC(64)
-  else if (p->cfg.dim == 128) PKV_FIB_DEC(128)
+#define PKV_FIB_DEC_DST(DIM)                                                                      \
+  switch (dst) {                                                                                  \
+    case PKV_DST_F32: PKV_FIB_DEC(DIM, PKV_DST_F32) break;                                        \
+    case PKV_DST_F16: PKV_FIB_DEC(DIM, PKV_DST_F16) break;                                        \
+    case PKV_DST_BF16: PKV_FIB_DEC(DIM, PKV_DST_BF16) break;                                      \
+    default: return PKV_ERR_INVALID_ARGUMENT;                                                     \
+  }
+  if (p->cfg.dim == 64) PKV_FIB_DEC_DST(64)
+  else if (p->cfg.dim == 128) PKV_FIB_DEC_DST(128)
   else return PKV_ERR_UNSUPPORTED;
+#undef PKV_FIB_DEC_DST
 #undef PKV_FIB_DEC
   pkv_count_launch();
   return pkv_cuda_status(cudaGetLastError());

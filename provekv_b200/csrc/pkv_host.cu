@@ -82,6 +82,15 @@ int make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, 
   return PKV_OK;
 }
 
+// 16-bit caches are written 16 bytes at a time: offsets in multiples of 8 elements.
+int check_dst(const pkv_layout* L, int dst) {
+  if (dst == PKV_DST_F32) return PKV_OK;
+  if (dst != PKV_DST_F16 && dst != PKV_DST_BF16) return PKV_ERR_INVALID_ARGUMENT;
+  int64_t all = L->base | L->token_stride | L->head_stride | L->replica_stride;
+  for (int i = 0; i < 3; i++) all |= L->batch_stride[i];
+  return (all % 8) ? PKV_ERR_INVALID_ARGUMENT : PKV_OK;
+}
+
 pkv_layout flat_layout(int64_t n, int dim) {
   pkv_layout L;
   memset(&L, 0, sizeof(L));
@@ -353,7 +362,19 @@ int pkv_fib_decode_patch_dev(const pkv_fib_profile* p, const uint8_t* payload_de
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
   if (st != PKV_OK) return st;
-  return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, err_dev, (cudaStream_t)stream);
+  return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, PKV_DST_F32, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_fib_decode_patch_dev_as(const pkv_fib_profile* p, const uint8_t* payload_dev,
+                                int64_t payload_batch_stride, const pkv_layout* layout,
+                                void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream) {
+  if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
+  if (st == PKV_OK) st = check_dst(layout, dst_dtype);
+  if (st != PKV_OK) return st;
+  return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
 }
 
 int pkv_fb2_header_write(const pkv_fib_profile* p, uint32_t n_vectors, uint8_t* out) {
@@ -585,7 +606,19 @@ int pkv_turbo_decode_patch_dev(const pkv_turbo_profile* p, const uint8_t* payloa
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
   if (st != PKV_OK) return st;
-  return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, err_dev, (cudaStream_t)stream);
+  return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, PKV_DST_F32, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_turbo_decode_patch_dev_as(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                                  int64_t payload_batch_stride, const pkv_layout* layout,
+                                  void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream) {
+  if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
+  if (st == PKV_OK) st = check_dst(layout, dst_dtype);
+  if (st != PKV_OK) return st;
+  return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
 }
 
 int pkv_tqb1_header_write(const pkv_turbo_profile* p, uint32_t n_vectors, uint8_t* out) {

@@ -67,15 +67,27 @@ int launch_encode(const TurboParams& tp, const float* x, const PkvGeom& g, uint8
   return PKV_OK;
 }
 
-template <int D, int PB>
-int launch_decode(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g, float* cache,
-                  uint64_t* err, unsigned grid, cudaStream_t s) {
+template <int D, int PB, int DST>
+int launch_decode_as(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g, void* cache,
+                     uint64_t* err, unsigned grid, cudaStream_t s) {
   const size_t sm = turbo_decode_smem<D>(tp);
-  int st = set_smem(turbo_decode_patch_kernel<D, PB>, sm);
+  int st = set_smem(turbo_decode_patch_kernel<D, PB, DST>, sm);
   if (st != PKV_OK) return st;
   const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
-  turbo_decode_patch_kernel<D, PB><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, cache, err);
+  turbo_decode_patch_kernel<D, PB, DST><<<ctas, Turbo<D>::THREADS, sm, s>>>(
+      g, tp, payload, static_cast<typename PkvDst<DST>::type*>(cache), err);
   return PKV_OK;
+}
+
+template <int D, int PB>
+int launch_decode(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g, void* cache, int dst,
+                  uint64_t* err, unsigned grid, cudaStream_t s) {
+  switch (dst) {
+    case PKV_DST_F32: return launch_decode_as<D, PB, PKV_DST_F32>(tp, payload, g, cache, err, grid, s);
+    case PKV_DST_F16: return launch_decode_as<D, PB, PKV_DST_F16>(tp, payload, g, cache, err, grid, s);
+    case PKV_DST_BF16: return launch_decode_as<D, PB, PKV_DST_BF16>(tp, payload, g, cache, err, grid, s);
+    default: return PKV_ERR_INVALID_ARGUMENT;
+  }
 }
 
 }  // namespace
@@ -110,16 +122,16 @@ int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const Pk
 }
 
 int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,
-                            float* cache, uint64_t* err, cudaStream_t s) {
+                            void* cache, int dst, uint64_t* err, cudaStream_t s) {
   const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
   if (grid == 0) return PKV_OK;
   if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
   const TurboParams tp = make_params(p);
   int st;
   if (p->cfg.dim == 64) {
-    PKV_DISPATCH_PB(launch_decode, 64, tp, payload, g, cache, err, (unsigned)grid, s)
+    PKV_DISPATCH_PB(launch_decode, 64, tp, payload, g, cache, dst, err, (unsigned)grid, s)
   } else if (p->cfg.dim == 128) {
-    PKV_DISPATCH_PB(launch_decode, 128, tp, payload, g, cache, err, (unsigned)grid, s)
+    PKV_DISPATCH_PB(launch_decode, 128, tp, payload, g, cache, dst, err, (unsigned)grid, s)
   } else {
     return PKV_ERR_UNSUPPORTED;
   }

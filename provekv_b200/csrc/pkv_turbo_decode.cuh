@@ -19,10 +19,10 @@ struct TurboDecSmem {  // per-warp slices follow the CTA-wide tables
   static __host__ __device__ size_t table_bytes(int levels) { return sizeof(float) * (256 + 2 * levels); }
 };
 
-template <int D, int PB>
+template <int D, int PB, int DST>
 __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
-                          float* __restrict__ cache, uint64_t* err) {
+                          typename PkvDst<DST>::type* __restrict__ cache, uint64_t* err) {
   using K = Turbo<D>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int pb = PB ? PB : tp.polar_bits;
@@ -147,15 +147,33 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   }
   __syncwarp();
 
-  // coalesced write-out: D/4 lanes per vector, one float4 each, every replica
+  if constexpr (DST == PKV_DST_F32) {
+    // coalesced write-out: D/4 lanes per vector, one float4 each, every replica
 #pragma unroll 4
-  for (int i = lane; i < nv * K::LPV; i += 32) {
-    const int vv = i / K::LPV, q = i % K::LPV;
-    const float4 val = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 4 * q);
-    float* dst = cache + s_off[vv] + 4 * q;
-    for (int r = 0; r < g.L.n_replicas; r++) {
-      *reinterpret_cast<float4*>(dst) = val;
-      dst += g.L.replica_stride;
+    for (int i = lane; i < nv * K::LPV; i += 32) {
+      const int vv = i / K::LPV, q = i % K::LPV;
+      const float4 val = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 4 * q);
+      float* dst = cache + s_off[vv] + 4 * q;
+      for (int r = 0; r < g.L.n_replicas; r++) {
+        *reinterpret_cast<float4*>(dst) = val;
+        dst += g.L.replica_stride;
+      }
+    }
+  } else {
+    // 16-bit cache: D/8 lanes per vector, eight values rounded to nearest-even and stored as 16 bytes
+    constexpr int LPH = D / 8;
+#pragma unroll 4
+    for (int i = lane; i < nv * LPH; i += 32) {
+      const int vv = i / LPH, q = i % LPH;
+      const float4 a = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 8 * q);
+      const float4 b = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 8 * q + 4);
+      const uint4 val = make_uint4(pkv_pack2<DST>(a.x, a.y), pkv_pack2<DST>(a.z, a.w),
+                                   pkv_pack2<DST>(b.x, b.y), pkv_pack2<DST>(b.z, b.w));
+      typename PkvDst<DST>::type* dst = cache + s_off[vv] + 8 * q;
+      for (int r = 0; r < g.L.n_replicas; r++) {
+        *reinterpret_cast<uint4*>(dst) = val;
+        dst += g.L.replica_stride;
+      }
     }
   }
 }

@@ -110,9 +110,11 @@ class FibProfile(_ProfileBase):
                                                   payload_batch_stride, err_ptr, stream))
 
     def decode_patch_dev(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
-                         cache_ptr: int, err_ptr: int, stream: int = 0) -> None:
-        L.check(L.lib().pkv_fib_decode_patch_dev(self.handle, payload_ptr, payload_batch_stride,
-                                                 C.byref(layout), cache_ptr, err_ptr, stream))
+                         cache_ptr: int, err_ptr: int, stream: int = 0, dst_dtype: int = L.DST_F32) -> None:
+        """dst_dtype: element type of the cache (L.DST_F32 / DST_F16 / DST_BF16); the 16-bit types
+        are rounded to nearest-even in the store and need strides in multiples of 8 elements."""
+        L.check(L.lib().pkv_fib_decode_patch_dev_as(self.handle, payload_ptr, payload_batch_stride,
+                                                    C.byref(layout), cache_ptr, dst_dtype, err_ptr, stream))
 
 
 class TurboProfile(_ProfileBase):
@@ -175,9 +177,9 @@ class TurboProfile(_ProfileBase):
                                              payload_batch_stride, err_ptr, stream))
 
     def decode_patch_dev(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
-                         cache_ptr: int, err_ptr: int, stream: int = 0) -> None:
-        L.check(L.lib().pkv_turbo_decode_patch_dev(self.handle, payload_ptr, payload_batch_stride,
-                                                   C.byref(layout), cache_ptr, err_ptr, stream))
+                         cache_ptr: int, err_ptr: int, stream: int = 0, dst_dtype: int = L.DST_F32) -> None:
+        L.check(L.lib().pkv_turbo_decode_patch_dev_as(self.handle, payload_ptr, payload_batch_stride,
+                                                      C.byref(layout), cache_ptr, dst_dtype, err_ptr, stream))
 
 
 def read_error_word(err_ptr: int, stream: int = 0) -> None:

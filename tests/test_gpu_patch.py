@@ -1,0 +1,150 @@
+"""Decode-and-patch into a framework's per-layer caches: fp16 / bf16 / f32 cache tensors, one
+allocation per (layer, K|V) as in a transformers DynamicCache, replicas, and the value flow
+kv-binary file -> cache of proveKV/scripts/ppl_validate_multi_agent.py:202-293."""
+import numpy as np
+import pytest
+
+import provekv_b200 as pk
+from provekv_b200 import _lib as L
+from provekv_b200 import patch, pool
+
+from kvgen import synthetic_kv
+from test_gpu_layouts import _oracle_decode, _oracle_encode, _profiles
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits16(t):
+    import torch
+    return t.contiguous().view(torch.int16).cpu().numpy()
+
+
+def _reference_patch(torch, dec, layers, heads, T, d, dtype, cap, pos0, fill):
+    """patch_cache_with_multi_agent_kv, ppl_validate_multi_agent.py:247-262: per token,
+    `k[0, :, pos, :] = torch.tensor(flat[t*stride:(t+1)*stride], dtype=k.dtype).view(H, d)`."""
+    out = []
+    for li in range(layers):
+        pair = []
+        for side in range(2):
+            c = torch.full((1, heads, cap, d), fill, dtype=dtype)
+            flat = dec[li, side].reshape(T, heads * d)
+            for t in range(T):
+                c[0, :, pos0 + t, :] = torch.tensor(flat[t].tolist(), dtype=dtype).view(heads, d)
+            pair.append(c)
+        out.append(pair)
+    return out
+
+
+@pytest.mark.parametrize("kind", ["fib", "turbo", "turbo_lossy"])
+@pytest.mark.parametrize("dtype_name", ["float16", "bfloat16", "float32"])
+@pytest.mark.parametrize("d,heads,T", [(64, 4, 21), (128, 2, 9)])
+def test_patch_per_layer_caches_of_every_dtype(oracle_mod, kind, dtype_name, d, heads, T):
+    import torch
+    dtype = getattr(torch, dtype_name)
+    layers, cap, pos0 = 3, T + 11, 6
+    prof = _profiles(d)[kind]
+    vpb, rec = T * heads, prof.record_bytes
+    x = synthetic_kv(layers * 2 * vpb, d, seed=d + T).reshape(layers * 2, vpb, d)
+    if dtype_name == "float16" and kind != "fib":  # (a fib norm that large does not fit its fp16 field)
+        x[0, 0, :] *= 3.0e4  # decoded values beyond the fp16 range must become infinities
+    stride = pool.payload_batch_stride(vpb, rec)
+    want = [_oracle_encode(oracle_mod, kind, prof, x[b]) for b in range(layers * 2)]
+    host = np.zeros((layers, 2, stride), np.uint8)
+    for b, p in enumerate(want):
+        host[b // 2, b % 2, :vpb * rec] = p.reshape(-1)
+    payload = torch.from_numpy(host).cuda()
+    dec = np.stack([_oracle_decode(oracle_mod, kind, prof, p, d) for p in want]).reshape(layers, 2, T, heads, d)
+
+    try:  # the reference installs the tensors in a DynamicCache (ppl_validate_multi_agent.py:282-293)
+        from transformers import DynamicCache, DynamicLayer
+        cache = DynamicCache()
+        while len(cache.layers) < layers:
+            cache.layers.append(DynamicLayer())
+        for layer in cache.layers:
+            layer.keys = torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda")
+            layer.values = torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda")
+    except Exception:
+        cache = [(torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda"),
+                  torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda")) for _ in range(layers)]
+
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    before = L.lib().pkv_launch_count()
+    n = patch.patch_cache(prof, payload, cache, T, pos0, err)
+    pk.read_error_word(err.data_ptr())
+    assert n == 2 * layers and L.lib().pkv_launch_count() - before == n
+
+    ref = _reference_patch(torch, dec, layers, heads, T, d, dtype, cap, pos0, 7.0)
+    for li, (k, v) in enumerate(patch.cache_layers(cache)):
+        for side, got in enumerate((k, v)):
+            exp = ref[li][side]
+            if dtype == torch.float32:
+                assert np.array_equal(got.cpu().numpy().view(np.uint32), exp.numpy().view(np.uint32))
+            else:
+                assert np.array_equal(_bits16(got), _bits16(exp)), (kind, dtype_name, li, side)
+    if dtype_name == "float16" and kind != "fib":
+        assert torch.isinf(patch.cache_layers(cache)[0][0][0, :, pos0, :].float()).any()
+
+
+@pytest.mark.parametrize("kind", ["fib", "turbo"])
+def test_half_precision_replicas_and_alignment_rule(oracle_mod, kind):
+    import torch
+    d, heads, T, reps, cap = 64, 8, 13, 3, 16
+    prof = _profiles(d)[kind]
+    vpb, rec = T * heads, prof.record_bytes
+    x = synthetic_kv(vpb, d, seed=5)
+    p = _oracle_encode(oracle_mod, kind, prof, x)
+    stride = pool.payload_batch_stride(vpb, rec)
+    host = np.zeros(stride, np.uint8)
+    host[:vpb * rec] = p.reshape(-1)
+    payload = torch.from_numpy(host).cuda()
+    dec = torch.from_numpy(_oracle_decode(oracle_mod, kind, prof, p, d).reshape(T, heads, d)).to(torch.bfloat16)
+    caches = torch.zeros((reps, heads, cap, d), dtype=torch.bfloat16, device="cuda")
+    lay = patch.cache_tensor_layout(caches[0], T, 2)
+    lay.n_replicas, lay.replica_stride = reps, caches.stride(0)
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    prof.decode_patch_dev(payload.data_ptr(), stride, lay, caches.data_ptr(), err.data_ptr(),
+                          dst_dtype=L.DST_BF16)
+    pk.read_error_word(err.data_ptr())
+    for r in range(reps):
+        assert np.array_equal(_bits16(caches[r, :, 2:2 + T, :]), _bits16(dec.permute(1, 0, 2)))
+        assert float(caches[r, :, :2, :].abs().max()) == 0.0 and float(caches[r, :, 2 + T:, :].abs().max()) == 0.0
+    # 16-bit caches need offsets in multiples of 8 elements; an unknown type code is refused
+    lay.base += 4
+    with pytest.raises(pk.PkvError):
+        prof.decode_patch_dev(payload.data_ptr(), stride, lay, caches.data_ptr(), err.data_ptr(),
+                              dst_dtype=L.DST_BF16)
+    lay.base -= 4
+    with pytest.raises(pk.PkvError):
+        prof.decode_patch_dev(payload.data_ptr(), stride, lay, caches.data_ptr(), err.data_ptr(), dst_dtype=3)
+
+
+def test_kv_binary_file_to_cache(oracle_mod, tmp_path):
+    """encode on the GPU -> decode to the flat [token][head][dim] lists the reference writes to a
+    kv binary file -> read it back -> the values a cache patched from that file would hold equal
+    the cache patched by the fused kernel."""
+    import torch
+    d, heads, T, layers = 64, 4, 12, 2
+    prof = _profiles(d)["turbo"]
+    x = synthetic_kv(layers * 2 * T * heads, d, seed=77).reshape(layers * 2, T * heads, d)
+    blobs = [prof.encode_batch_compact(x[b]) for b in range(layers * 2)]
+    flat = [prof.decode_batch_compact(b).reshape(-1) for b in blobs]
+    path = tmp_path / "agent.kv.bin"
+    patch.write_kv_binary(path, {"num_layers": layers, "num_kv_heads": heads, "head_dim": d, "num_tokens": T},
+                          [(flat[2 * i], flat[2 * i + 1]) for i in range(layers)])
+    manifest, from_file, nl, nh, hd = patch.read_kv_binary(path)
+    assert (nl, nh, hd, manifest["num_tokens"]) == (layers, heads, d, T)
+
+    rec, vpb = prof.record_bytes, T * heads
+    stride = pool.payload_batch_stride(vpb, rec)
+    host = np.zeros((layers, 2, stride), np.uint8)
+    for b, blob in enumerate(blobs):
+        host[b // 2, b % 2, :vpb * rec] = np.frombuffer(blob, np.uint8)[L.TQB1_HEADER_BYTES:]
+    cache = {i: {"k": torch.zeros((1, heads, T, d), dtype=torch.float16, device="cuda"),
+                 "v": torch.zeros((1, heads, T, d), dtype=torch.float16, device="cuda")} for i in range(layers)}
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    patch.patch_cache(prof, torch.from_numpy(host).cuda(), cache, T, 0, err)
+    pk.read_error_word(err.data_ptr())
+    for i in range(layers):
+        for side, name in enumerate("kv"):
+            exp = torch.from_numpy(from_file[i][side].reshape(T, heads, d)).to(torch.float16).permute(1, 0, 2)
+            assert np.array_equal(_bits16(cache[i][name][0]), _bits16(exp))

@@ -134,3 +134,46 @@ def test_per_vector_wire_framing_round_trips_and_rejects():
             cd.tqw1_parse(bad, 64, 3, 32, 42, True)
     with pytest.raises(cd.DecompressionFailed):
         cd.tqw1_parse(tb, 64, 3, 32, 43, True)
+
+
+def test_kv_binary_round_trip_and_layout(tmp_path):
+    """The kv binary container of prove_kv_multi_agent_shell.rs:106-122, read the way
+    ppl_validate_multi_agent.py:202-224 reads it, and the patch layout of a cache tensor."""
+    import json
+    import struct
+
+    import torch
+
+    from provekv_b200 import _lib as L
+    from provekv_b200 import patch
+
+    rng = np.random.default_rng(3)
+    layers = [(rng.standard_normal(48).astype(np.float32), rng.standard_normal(48).astype(np.float32))
+              for _ in range(2)]
+    manifest = {"num_layers": 2, "num_kv_heads": 2, "head_dim": 8, "num_tokens": 3, "agent_id": "a0"}
+    path = tmp_path / "x.kv.bin"
+    patch.write_kv_binary(path, manifest, layers)
+    raw = path.read_bytes()
+    (mlen,) = struct.unpack_from("<Q", raw, 0)
+    assert json.loads(raw[8:8 + mlen].decode()) == manifest
+    (klen,) = struct.unpack_from("<I", raw, 8 + mlen)
+    assert klen == 48 and struct.unpack_from("<48f", raw, 12 + mlen) == tuple(layers[0][0].tolist())
+    assert len(raw) == 8 + mlen + 4 * (4 + 4 * 48)
+    m, got, nl, nh, hd = patch.read_kv_binary(path)
+    assert (m, nl, nh, hd) == (manifest, 2, 2, 8)
+    for i in range(2):
+        assert np.array_equal(got[i][0], layers[i][0]) and np.array_equal(got[i][1], layers[i][1])
+    (tmp_path / "cut.kv.bin").write_bytes(raw[:-5])
+    with pytest.raises(ValueError):
+        patch.read_kv_binary(tmp_path / "cut.kv.bin")
+
+    cache = torch.zeros((1, 4, 32, 64), dtype=torch.bfloat16)
+    lay = patch.cache_tensor_layout(cache, 5, 7)
+    assert (lay.base, lay.token_stride, lay.head_stride, lay.n_tokens, lay.n_heads) == (7 * 64, 64, 32 * 64, 5, 4)
+    assert patch.dst_dtype_of(cache) == L.DST_BF16 and patch.dst_dtype_of(cache.float()) == L.DST_F32
+    with pytest.raises(ValueError):
+        patch.cache_tensor_layout(cache, 30, 7)
+    with pytest.raises(TypeError):
+        patch.dst_dtype_of(cache.to(torch.float64))
+    pairs = patch.cache_layers({1: {"k": 3, "v": 4}, 0: {"k": 1, "v": 2}})
+    assert pairs == [(1, 2), (3, 4)]
