@@ -507,7 +507,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;                                              \
     const size_t sm = fib_encode_fast_smem<DIM>(g.rec_bytes);                                       \
     if ((st = set_smem(fib_encode_fast_kernel<DIM>, sm)) != PKV_OK) return st;                      \
-    fib_encode_fast_kernel<DIM><<<(unsigned)grid, kThreads, sm, s>>>(                               \
+    fib_encode_fast_kernel<DIM><<<(unsigned)grid, FibFast<DIM>::THREADS, sm, s>>>(                             \
         gf, x, p->rot32_t_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->idx_bits, \
         p->norm_len, payload, err, scratch, scratch + 1);                                           \
     pkv_count_launch();                                                                             \

@@ -17,15 +17,19 @@
 template <int D>
 struct FibFast {
   static constexpr int B = D / 4;
-  static constexpr int RG = D / 8;            // threads along the rows (8 rows = 2 blocks each)
-  static constexpr int VG = kThreads / RG;    // threads along the vectors (8 vectors each)
-  static constexpr int TV = VG * 8;           // 128 vectors (D = 64), 64 (D = 128)
-  static constexpr int XS = D + 4;            // row stride of the staged input tile
+  static constexpr int THREADS = 128;
+  static constexpr int VPT = 8;  // vectors per thread in the product
+  static constexpr int RG = D / 8;              // threads along the rows (2 blocks each)
+  static constexpr int VG = THREADS / RG;       // threads along the vectors (VPT vectors each)
+  static constexpr int TV = VG * VPT;           // 128 vectors (D = 64), 64 (D = 128)
+  static constexpr int SPLIT = THREADS / TV;    // threads sharing one vector's normalisation
+  static constexpr int EPT = D / SPLIT;         // elements each of them normalises
+  static constexpr int XS = D + 4;              // row stride of the staged input tile
   static constexpr size_t tile_floats = (size_t)TV * XS > (size_t)D * TV ? (size_t)TV * XS : (size_t)D * TV;
 };
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(FibFast<D>::THREADS, D == 128 ? 2 : 3)
 fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot32_t,
                        const float* __restrict__ codebook, const float* __restrict__ half_norm,
                        int n_codewords, int idx_bits, int norm_len, uint8_t* __restrict__ payload,
@@ -51,106 +55,114 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
   const int rec = g.rec_bytes;
   const int tid = threadIdx.x;
 
-  for (int v = tid; v < K::TV; v += kThreads) {
+  for (int v = tid; v < K::TV; v += K::THREADS) {
     s_off[v] = v < nv ? pkv_vec_offset(g.L, batch, v0 + v) : 0;
     s_flag[v] = 0;
   }
-  for (int i = tid; i < D * D / 4; i += kThreads)
+  for (int i = tid; i < D * D / 4; i += K::THREADS)
     pkv_cp_async16(reinterpret_cast<float4*>(s_m) + i, reinterpret_cast<const float4*>(rot32_t) + i);
   if (tid < 32) {
     s_cb[tid] = __ldg(reinterpret_cast<const float4*>(codebook) + tid);
     s_hn[tid] = __ldg(half_norm + tid);
   }
   __syncthreads();
-  for (int i = tid; i < nv * (D / 4); i += kThreads) {
+  for (int i = tid; i < nv * (D / 4); i += K::THREADS) {
     const int v = i / (D / 4), q = i % (D / 4);
     pkv_cp_async16(s_t + v * K::XS + 4 * q, reinterpret_cast<const float4*>(x + s_off[v]) + q);
   }
   pkv_cp_async_wait_all();
   __syncthreads();
 
-  // (A) one thread per vector: exact norm (codec.rs:1049-1057; the square of a binary32 value is
-  // exact in binary64, so the fused form rounds exactly like the reference's multiply-then-add),
-  // then the certified normalised vector written transposed, n~[j][v], over the input tile.
-  for (int vb = 0; vb < K::TV; vb += kThreads) {
-    const int v = vb + tid;
-    float xr[D];
-    if (v < K::TV) {
-      const float* row = s_t + v * K::XS;
-#pragma unroll
-      for (int i = 0; i < D; i += 4) {
-        const float4 t = v < nv ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        xr[i] = t.x; xr[i + 1] = t.y; xr[i + 2] = t.z; xr[i + 3] = t.w;
-      }
+  // (A) exact norm (codec.rs:1049-1057; the square of a binary32 value is exact in binary64, so
+  // the fused form rounds exactly like the reference's multiply-then-add), then the certified
+  // normalised vector written transposed, n~[j][v], over the input tile.  SPLIT threads share a
+  // vector: each runs the whole norm chain from the tile and normalises its own EPT elements.
+  {
+    const int v = tid % K::TV, part = tid / K::TV;
+    const float* row = s_t + v * K::XS;
+    bool finite = true;
+    double acc = 0.0;
+#pragma unroll 8
+    for (int i = 0; i < D; i += 4) {
+      const float4 t = v < nv ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      finite = finite && pkv_finite(t.x) && pkv_finite(t.y) && pkv_finite(t.z) && pkv_finite(t.w);
+      acc = fma((double)t.x, (double)t.x, acc);
+      acc = fma((double)t.y, (double)t.y, acc);
+      acc = fma((double)t.z, (double)t.z, acc);
+      acc = fma((double)t.w, (double)t.w, acc);
     }
-    __syncthreads();  // every row is in registers: the tile may now be overwritten
-    if (v < K::TV) {
-      bool finite = true;
-      double acc = 0.0;
+    float xr[K::EPT];
 #pragma unroll
-      for (int i = 0; i < D; i++) {
-        finite = finite && pkv_finite(xr[i]);
-        const double t = (double)xr[i];
-        acc = fma(t, t, acc);
-      }
-      double norm = __dsqrt_rn(acc);
-      int bad = 0;
-      if (v < nv) {
-        if (!finite) bad = PKV_VEC_NONFINITE_INPUT;
-        else if (norm == 0.0) bad = PKV_VEC_ZERO_NORM;
-        if (bad) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, bad);
-      }
-      const bool skip = bad || v >= nv;
-      if (skip) norm = 1.0;
+    for (int i = 0; i < K::EPT; i += 4) {
+      const float4 t = v < nv ? *reinterpret_cast<const float4*>(row + part * K::EPT + i)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+      xr[i] = t.x; xr[i + 1] = t.y; xr[i + 2] = t.z; xr[i + 3] = t.w;
+    }
+    __syncthreads();  // every row has been read: the tile may now be overwritten
+    double norm = __dsqrt_rn(acc);
+    int bad = 0;
+    if (v < nv) {
+      if (!finite) bad = PKV_VEC_NONFINITE_INPUT;
+      else if (norm == 0.0) bad = PKV_VEC_ZERO_NORM;
+      if (bad && part == 0) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, bad);
+    }
+    const bool skip = bad || v >= nv;
+    if (skip) norm = 1.0;
+    if (part == 0) {
       s_norm[v] = norm;
       s_bad[v] = (uint8_t)skip;
-      const double inv = __ddiv_rn(1.0, norm);
-      int all_certain = 1;
-#pragma unroll
-      for (int i = 0; i < D; i++) {
-        int certain;
-        const float q = pkv_fib_norm_quotient(xr[i], inv, &certain);
-        all_certain &= certain;
-        s_t[i * K::TV + v] = skip ? 0.0f : q;
-      }
-      if (!all_certain && !skip) s_flag[v] = 1u << 31;  // redo the whole vector exactly
     }
+    const double inv = __ddiv_rn(1.0, norm);
+    int all_certain = 1;
+#pragma unroll
+    for (int i = 0; i < K::EPT; i++) {
+      int certain;
+      const float q = pkv_fib_norm_quotient(xr[i], inv, &certain);
+      all_certain &= certain;
+      s_t[(part * K::EPT + i) * K::TV + v] = skip ? 0.0f : q;
+    }
+    if (!all_certain && !skip) atomicOr(&s_flag[v], 1u << 31);  // redo the whole vector exactly
   }
   __syncthreads();
 
-  // (B) y~ = M32 n~ as a register-tiled product: thread (rg, vg) owns rows 8rg..8rg+7 (two
-  // 4-blocks) of vectors 8vg..8vg+7 and accumulates over j with fused multiply-adds.
+  // (B) y~ = M32 n~ as a register-tiled product: thread (rg, vg) owns the blocks rg and B/2 + rg
+  // (rows 4rg..4rg+3 and D/2+4rg..: a warp's matrix reads are then contiguous, free of bank
+  // conflicts) of vectors VPT*vg.. and accumulates over j with fused multiply-adds.
   const int rg = tid % K::RG, vg = tid / K::RG;
-  float acc[8][8];
+  constexpr int VPT = K::VPT;
+  float acc[VPT][8];
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < VPT; i++)
 #pragma unroll
     for (int r = 0; r < 8; r++) acc[i][r] = 0.0f;
 #pragma unroll 2
   for (int j = 0; j < D; j++) {
-    const float4 m0 = *reinterpret_cast<const float4*>(s_m + j * D + 8 * rg);
-    const float4 m1 = *reinterpret_cast<const float4*>(s_m + j * D + 8 * rg + 4);
-    const float4 n0 = *reinterpret_cast<const float4*>(s_t + j * K::TV + 8 * vg);
-    const float4 n1 = *reinterpret_cast<const float4*>(s_t + j * K::TV + 8 * vg + 4);
+    const float4 m0 = *reinterpret_cast<const float4*>(s_m + j * D + 4 * rg);
+    const float4 m1 = *reinterpret_cast<const float4*>(s_m + j * D + D / 2 + 4 * rg);
     const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-    const float nn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+    float nn[VPT];
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < VPT; i += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(s_t + j * K::TV + VPT * vg + i);
+      nn[i] = t.x; nn[i + 1] = t.y; nn[i + 2] = t.z; nn[i + 3] = t.w;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; i++)
 #pragma unroll
       for (int r = 0; r < 8; r++) acc[i][r] = fmaf(mm[r], nn[i], acc[i][r]);
   }
 
-  // (C) certified nearest codeword of the 16 (vector, block) pairs this thread holds
+  // (C) certified nearest codeword of the 2 * VPT (vector, block) pairs this thread holds
   {
-    float best[16], second[16];
+    float best[2 * VPT], second[2 * VPT];
 #pragma unroll
-    for (int k = 0; k < 16; k++) best[k] = second[k] = __int_as_float(0x7f800000);
+    for (int k = 0; k < 2 * VPT; k++) best[k] = second[k] = __int_as_float(0x7f800000);
 #pragma unroll 2
     for (int c = 0; c < n_codewords; c++) {
       const float4 w = s_cb[c];
       const float hn = s_hn[c];
 #pragma unroll
-      for (int i = 0; i < 8; i++)
+      for (int i = 0; i < VPT; i++)
 #pragma unroll
         for (int h = 0; h < 2; h++)
           pkv_fib_top2(&best[2 * i + h], &second[2 * i + h],
@@ -158,10 +170,10 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
                                    w.x, w.y, w.z, w.w, hn, (uint32_t)c));
     }
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < VPT; i++)
 #pragma unroll
       for (int h = 0; h < 2; h++) {
-        const int v = 8 * vg + i, b = 2 * rg + h;
+        const int v = VPT * vg + i, b = h * (K::B / 2) + rg;
         s_idx[v * K::B + b] = (uint8_t)(__float_as_uint(best[2 * i + h]) & 31u);
         if (!pkv_fib_certify(best[2 * i + h], second[2 * i + h], acc[i][4 * h], acc[i][4 * h + 1],
                              acc[i][4 * h + 2], acc[i][4 * h + 3]))
@@ -171,7 +183,7 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
   __syncthreads();
 
   // (D) encode_norm (:994-1020) + pack_indices (bitpack.rs:4-44); undecided work goes to the list
-  for (int v = tid; v < nv; v += kThreads) {
+  for (int v = tid; v < nv; v += K::THREADS) {
     uint8_t* r = s_rec + v * rec;
     for (int i = 0; i < rec; i++) r[i] = 0;
     if (s_bad[v]) continue;

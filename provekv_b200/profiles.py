@@ -140,10 +140,16 @@ class TurboProfile(_ProfileBase):
 
     @classmethod
     def from_seed(cls, dim: int, bits: int, projections: int, seed: int, *,
-                  mode: int = L.TURBO_POLAR_WITH_QJL, radii_codec: int = L.RADII_F32) -> "TurboProfile":
+                  mode: int = L.TURBO_POLAR_WITH_QJL, radii_codec: int = L.RADII_F32,
+                  sign_stream: str = "pcg64") -> "TurboProfile":
+        """sign_stream "chacha8": the Hadamard signs come from the reference's own ChaCha8 bool
+        stream (tables.reference_hadamard_signs), which is all a polar-only profile needs from the
+        seed; the QJL matrix is NumPy-seeded either way."""
         qjl = tables.qjl_matrix(dim, projections, seed) if mode == L.TURBO_POLAR_WITH_QJL else None
-        return cls(dim, bits, tables.rademacher_signs(dim, seed), qjl, mode=mode,
-                   radii_codec=radii_codec, seed=seed)
+        if sign_stream not in ("pcg64", "chacha8"):
+            raise ValueError("sign_stream must be 'pcg64' or 'chacha8'")
+        signs = (tables.reference_hadamard_signs if sign_stream == "chacha8" else tables.rademacher_signs)(dim, seed)
+        return cls(dim, bits, signs, qjl, mode=mode, radii_codec=radii_codec, seed=seed)
 
     def encode_batch_compact(self, vectors: np.ndarray) -> bytes:
         x = np.ascontiguousarray(vectors, dtype=np.float32).reshape(-1, self.dim)

@@ -2,7 +2,8 @@
 
 The reference derives its tables from a seed with ``rand_chacha`` (ChaCha8),
 ``rand_distr`` (ziggurat normal, gamma), ``nalgebra`` (Householder QR) and
-``statrs`` (inverse CDFs).  None of those streams is reproduced here: these
+``statrs`` (inverse CDFs).  Apart from `reference_hadamard_signs` (the ChaCha8
+bool stream, restated below) those streams are not reproduced here: the
 generators follow the same *algorithms* with NumPy's PCG64 as the random
 source, so a table built here is a valid table of the same distribution but is
 not the table the Rust crate builds for the same seed.  Bit-exactness of the
@@ -51,6 +52,79 @@ def rademacher_signs(dim: int, seed: int) -> np.ndarray:
     """dim values of +-1.0 (f32); seed offset as turbo-quant/src/rotation.rs:152."""
     bits = _rng((seed + 0xA11CE55ED5A5EED5) & _MASK64).integers(0, 2, size=dim)
     return np.where(bits == 1, 1.0, -1.0).astype(np.float32)
+
+
+# --- the reference's own random stream (rand_chacha 0.3.1 ChaCha8Rng, rand_core 0.6.4, rand 0.8) ----
+# Restated from the published algorithms (the crates are not vendored with the reference): the ChaCha
+# block function with 8 rounds, 64-bit block counter in words 12-13 and stream id 0 in words 14-15,
+# output words consumed in order; SeedableRng::seed_from_u64 fills the 32-byte key from a PCG32
+# sequence; Standard's bool is the top bit of next_u32().  The block function is checked against
+# the published zero-key ChaCha8 and ChaCha20 keystreams (tests/test_oracle_pins.py); no output of
+# the Rust crate for a given seed exists here to compare with, so seed-level equality with the
+# crate is unverified.
+_M32 = 0xFFFFFFFF
+
+
+def _rotl32(x: int, n: int) -> int:
+    return ((x << n) & _M32) | (x >> (32 - n))
+
+
+def _quarter_round(s: list, a: int, b: int, c: int, d: int) -> None:
+    s[a] = (s[a] + s[b]) & _M32
+    s[d] = _rotl32(s[d] ^ s[a], 16)
+    s[c] = (s[c] + s[d]) & _M32
+    s[b] = _rotl32(s[b] ^ s[c], 12)
+    s[a] = (s[a] + s[b]) & _M32
+    s[d] = _rotl32(s[d] ^ s[a], 8)
+    s[c] = (s[c] + s[d]) & _M32
+    s[b] = _rotl32(s[b] ^ s[c], 7)
+
+
+def chacha_block(key_words, counter: int, stream: int = 0, rounds: int = 8) -> list:
+    """One 16-word ChaCha block (original variant: 64-bit counter, 64-bit stream id)."""
+    init = [0x61707865, 0x3320646E, 0x79622D32, 0x6B206574, *key_words,
+            counter & _M32, (counter >> 32) & _M32, stream & _M32, (stream >> 32) & _M32]
+    s = list(init)
+    for _ in range(rounds // 2):
+        _quarter_round(s, 0, 4, 8, 12)
+        _quarter_round(s, 1, 5, 9, 13)
+        _quarter_round(s, 2, 6, 10, 14)
+        _quarter_round(s, 3, 7, 11, 15)
+        _quarter_round(s, 0, 5, 10, 15)
+        _quarter_round(s, 1, 6, 11, 12)
+        _quarter_round(s, 2, 7, 8, 13)
+        _quarter_round(s, 3, 4, 9, 14)
+    return [(a + b) & _M32 for a, b in zip(s, init)]
+
+
+def seed_from_u64_key(state: int) -> list:
+    """The eight key words SeedableRng::seed_from_u64 derives from a u64: PCG32 steps
+    (multiplier 6364136223846793005, increment 11634580027462260723, XSH-RR output), the state
+    advanced before each output."""
+    words = []
+    for _ in range(8):
+        state = (state * 6364136223846793005 + 11634580027462260723) & _MASK64
+        xorshifted = (((state >> 18) ^ state) >> 27) & _M32
+        rot = state >> 59
+        words.append(((xorshifted >> rot) | (xorshifted << ((32 - rot) & 31))) & _M32)
+    return words
+
+
+def chacha8_next_u32(seed: int, n: int) -> list:
+    """The first n next_u32() outputs of ChaCha8Rng::seed_from_u64(seed)."""
+    key, out, counter = seed_from_u64_key(seed & _MASK64), [], 0
+    while len(out) < n:
+        out.extend(chacha_block(key, counter, 0, 8))
+        counter += 1
+    return out[:n]
+
+
+def reference_hadamard_signs(dim: int, seed: int) -> np.ndarray:
+    """FastHadamardRotation::new (turbo-quant/src/rotation.rs:152-155) on the reference's own
+    stream: ChaCha8Rng::seed_from_u64(seed + 0xA11CE55ED5A5EED5), one gen::<bool>() per
+    coordinate, true -> +1.0."""
+    words = chacha8_next_u32((seed + 0xA11CE55ED5A5EED5) & _MASK64, dim)
+    return np.array([1.0 if w >> 31 else -1.0 for w in words], dtype=np.float32)
 
 
 def qjl_matrix(dim: int, projections: int, seed: int) -> np.ndarray:

@@ -221,3 +221,22 @@ def test_turbo_pairs_exactly_on_sector_boundaries(oracle_mod, bits, mode):
     rec = np.frombuffer(got, np.uint8)[L.TQB1_HEADER_BYTES:].reshape(n, -1)
     radii = rec[:, :dim * 2].copy().view(np.float32)
     assert np.array_equal(radii, np.sqrt(a * a + b * b).astype(np.float32))
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_polar_only_profile_on_the_reference_sign_stream(oracle_mod, dim):
+    """A polar-only quantizer needs nothing from the seed but the Hadamard signs; with
+    sign_stream="chacha8" they come from the reference's own generator stream."""
+    n = 700
+    prof = pk.TurboProfile.from_seed(dim, 4, 0, SEED, mode=L.TURBO_POLAR_ONLY, sign_stream="chacha8")
+    signs = tables.reference_hadamard_signs(dim, SEED)
+    assert np.array_equal(prof.signs, signs) and not np.array_equal(signs, tables.rademacher_signs(dim, SEED))
+    x = synthetic_kv(n, dim, seed=dim)
+    got = prof.encode_batch_compact(x)
+    st, payload, _, _ = oracle_mod.turbo_encode(x, signs, None, bits=4, mode=L.TURBO_POLAR_ONLY,
+                                               radii_codec=L.RADII_F32, libm_mode=oracle_mod.LIBM_PORTABLE)
+    assert st == 0
+    assert got == oracle_mod.tqb1_header(dim, 4, L.TURBO_POLAR_ONLY, 0, L.RADII_F32, SEED, n) + payload.tobytes()
+    st, want, _, _ = oracle_mod.turbo_decode(payload, dim, signs, bits=4, mode=L.TURBO_POLAR_ONLY, projections=0,
+                                            radii_codec=L.RADII_F32, libm_mode=oracle_mod.LIBM_PORTABLE)
+    assert np.array_equal(prof.decode_batch_compact(got).view(np.uint32), want.view(np.uint32))

@@ -211,3 +211,28 @@ def test_turbo_decode_is_deterministic_and_thread_invariant(oracle_mod):
     assert np.array_equal(a.view(np.uint32), one_by_one.view(np.uint32))
     other = tables.rademacher_signs(d, 1)
     assert not np.array_equal(signs, other)
+
+
+def test_chacha_stream_of_the_reference_sign_generator():
+    """turbo-quant/src/rotation.rs:152-155 draws its signs from ChaCha8Rng.  The block function is
+    pinned by the published zero-key keystreams of ChaCha8 and ChaCha20 (same code, 8 / 20 rounds);
+    the seeding and the bool rule are checked for their stated structure only."""
+    import struct
+
+    from provekv_b200 import tables
+
+    ks8 = struct.pack("<16I", *tables.chacha_block([0] * 8, 0, 0, 8)).hex()
+    ks20 = struct.pack("<16I", *tables.chacha_block([0] * 8, 0, 0, 20)).hex()
+    assert ks8.startswith("3e00ef2f895f40d67f5bb8e81f09a5a12c840ec3ce9a7f3b181be188ef711a1e")
+    assert ks20.startswith("76b8e0ada0f13d90405d6ae55386bd28bdd219b8a08ded1aa836efcc8b770dc7")
+    # successive blocks only differ through the counter words
+    assert tables.chacha_block([0] * 8, 1) != tables.chacha_block([0] * 8, 0)
+    key = tables.seed_from_u64_key(42)
+    assert len(key) == 8 and all(0 <= w < 1 << 32 for w in key) and key != tables.seed_from_u64_key(43)
+    words = tables.chacha8_next_u32(42, 40)
+    assert words[:16] == tables.chacha_block(key, 0) and words[16:32] == tables.chacha_block(key, 1)
+    s = tables.reference_hadamard_signs(128, 42)
+    assert s.dtype == np.float32 and set(np.unique(s)) == {-1.0, 1.0}
+    expect = tables.chacha8_next_u32((42 + 0xA11CE55ED5A5EED5) & (2 ** 64 - 1), 128)
+    assert [v > 0 for v in s] == [w >= 1 << 31 for w in expect]
+    assert np.array_equal(s[:64], tables.reference_hadamard_signs(64, 42))  # a prefix of one stream
