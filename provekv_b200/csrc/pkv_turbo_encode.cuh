@@ -162,8 +162,8 @@ struct TurboEncSmem {
     return (n + 15) & ~(size_t)15;
   }
   static __host__ __device__ size_t warp_bytes(int tile_words, int lossy) {
-    const size_t n = sizeof(int64_t) * K::TV + sizeof(uint32_t) * tile_words * K::WS +
-                     (lossy ? sizeof(float) * K::P * K::WS : 0);
+    const size_t n = sizeof(int64_t) * K::TV + sizeof(uint32_t) * tile_words * K::WS;
+    (void)lossy;
     return (n + 15) & ~(size_t)15;
   }
 };
@@ -203,7 +203,6 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                    warp * TurboEncSmem<D>::warp_bytes(tile_words, tp.lossy);
   int64_t* s_off = reinterpret_cast<int64_t*>(wbase);                  // [TV]
   uint32_t* s_w = reinterpret_cast<uint32_t*>(s_off + K::TV);          // [tile_words][WS]
-  float* s_rad = reinterpret_cast<float*>(s_w + tile_words * K::WS);   // [P][WS], lossy only
 
   const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
   const bool active = tile_id < (int64_t)g.n_batches * g.tiles_per_batch;
@@ -260,9 +259,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   // the transform non-finite, so input finiteness is only looked at when a radius is bad.
   fwht_forward_signed<D>(y, tp.sgn, tp.scale);
 
-  // Pass 1, encode_pair (polar.rs:413-421): radius exactly, bucket by the shortcut.  Radii go
-  // to the record (f32 codec) or to s_rad (BlockLogU8); undecided pairs are noted in `unc`.
-  float* radp = s_rad + v;
+  // Pass 1, encode_pair (polar.rs:413-421): radius exactly, bucket by the shortcut.  Radii stay in
+  // the registers of their pairs; undecided pairs are noted in `unc`.
   constexpr int NW = PB ? K::P * PB / 32 : 1;
   unsigned long long unc = 0;
   {
@@ -284,7 +282,6 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       unc |= (unsigned long long)(certain ? 0u : 1u) << i;
       rmax = max(rmax, __float_as_uint(r));  // a square root is +x or NaN (either sign): unsigned order works
       y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
-      if (lossy) radp[i * K::WS] = r;
       if constexpr (PB != 0) {
         const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
         words[wi] |= idx << sh;
@@ -327,6 +324,75 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   } else if (!lossy && valid) {  // records that are only 4-byte aligned: one word per store
 #pragma unroll
     for (int i = 0; i < K::P; i++) reinterpret_cast<float*>(my_rec)[i] = y[2 * i];
+  }
+  if constexpr (!DIRECT)  // direct stores imply f32 radii: keep this block out of that kernel's code
+  if (tp.lossy) {
+    // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371),
+    // straight from the radii in the registers (y[2i]; the reconstruction below still uses them).
+    // The logarithm is monotone, so min / max of the logs are the logs of the smallest / largest
+    // radius: two exact logarithms per vector (radii within 1e-5 of an extreme are taken exactly
+    // too, in case the rounded logarithm is not monotone to the last bit there).  The 8-bit codes
+    // come from the fast logarithm where that provably gives the reference's code
+    // (pkv_fast_radius_code); the rare others are redone with the exact one from a copy of the
+    // radii in local memory.
+    float rmin = __int_as_float(0x7f800000), rmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < K::P; i++) {
+      const float r = (code || !(y[2 * i] > PKV_FLT_MIN)) ? PKV_FLT_MIN : y[2 * i];
+      rmin = fminf(rmin, r);
+      rmax = fmaxf(rmax, r);
+    }
+    float mn = pkv_logf_portable(rmin), mx = pkv_logf_portable(rmax);
+    const float near_min = __fmul_rn(rmin, 1.00001f), near_max = __fmul_rn(rmax, 0.99999f);
+    bool ties = false;
+#pragma unroll
+    for (int i = 0; i < K::P; i++) {
+      const float r = (code || !(y[2 * i] > PKV_FLT_MIN)) ? PKV_FLT_MIN : y[2 * i];
+      ties = ties || (r != rmin && r <= near_min) || (r != rmax && r >= near_max);
+    }
+    float rl[K::P];  // local-memory copy, touched only on the rare paths
+    if (ties) {
+#pragma unroll
+      for (int i = 0; i < K::P; i++) rl[i] = (code || !(y[2 * i] > PKV_FLT_MIN)) ? PKV_FLT_MIN : y[2 * i];
+#pragma unroll 1
+      for (int i = 0; i < K::P; i++) {
+        const float r = rl[i];
+        if (r <= near_min) mn = fminf(mn, pkv_logf_portable(r));
+        if (r >= near_max) mx = fmaxf(mx, pkv_logf_portable(r));
+      }
+    }
+    float span = __fsub_rn(mx, mn);
+    if (!(span > PKV_FLT_EPS)) span = PKV_FLT_EPS;
+    const float k = __fdiv_rn(255.0f, span);
+    unsigned long long unsure = 0;
+#pragma unroll
+    for (int q = 0; q < K::P / 4; q++) {
+      uint32_t q4 = 0;
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        const int i = 4 * q + b;
+        const float r = (code || !(y[2 * i] > PKV_FLT_MIN)) ? PKV_FLT_MIN : y[2 * i];
+        int certain;
+        q4 |= pkv_fast_radius_code(__logf(r), mn, k, &certain) << (8 * b);
+        unsure |= (unsigned long long)(certain ? 0u : 1u) << i;
+      }
+      w[q * K::WS] = q4;
+    }
+    if (unsure) {
+#pragma unroll
+      for (int i = 0; i < K::P; i++) rl[i] = (code || !(y[2 * i] > PKV_FLT_MIN)) ? PKV_FLT_MIN : y[2 * i];
+      while (unsure) {
+        const int i = __ffsll((long long)unsure) - 1;
+        unsure &= unsure - 1;
+        float nrm = __fdiv_rn(__fsub_rn(pkv_logf_portable(rl[i]), mn), span);
+        nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
+        const uint32_t c8 = (uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu;
+        const int sh = 8 * (i & 3);
+        w[(i >> 2) * K::WS] = (w[(i >> 2) * K::WS] & ~(0xffu << sh)) | (c8 << sh);
+      }
+    }
+    w[(K::P / 4) * K::WS] = __float_as_uint(mn);
+    w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
   }
 
   if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
@@ -479,66 +545,6 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     } else if (threadIdx.x == 0) {
       pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
     }
-  }
-  if constexpr (!DIRECT)  // direct stores imply f32 radii: keep this block out of that kernel's code
-  if (tp.lossy) {
-    // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371).
-    // The logarithm is monotone, so min / max of the logs are the logs of the smallest / largest
-    // radius: two exact logarithms per vector (radii within 1e-5 of an extreme are taken exactly
-    // too, in case the rounded logarithm is not monotone to the last bit there).  The 8-bit codes
-    // come from the fast logarithm where that provably gives the reference's code
-    // (pkv_fast_radius_code), from the exact one otherwise.
-    float rmin = __int_as_float(0x7f800000), rmax = 0.0f;
-#pragma unroll 8
-    for (int i = 0; i < K::P; i++) {
-      float r = s_rad[i * K::WS + v];
-      r = (code || !(r > PKV_FLT_MIN)) ? PKV_FLT_MIN : r;
-      s_rad[i * K::WS + v] = r;
-      rmin = fminf(rmin, r);
-      rmax = fmaxf(rmax, r);
-    }
-    float mn = pkv_logf_portable(rmin), mx = pkv_logf_portable(rmax);
-    const float near_min = __fmul_rn(rmin, 1.00001f), near_max = __fmul_rn(rmax, 0.99999f);
-    float span, k;
-    {
-      bool ties = false;
-#pragma unroll 8
-      for (int i = 0; i < K::P; i++) {
-        const float r = s_rad[i * K::WS + v];
-        ties = ties || (r != rmin && r <= near_min) || (r != rmax && r >= near_max);
-      }
-      if (ties) {
-        for (int i = 0; i < K::P; i++) {
-          const float r = s_rad[i * K::WS + v];
-          if (r <= near_min) mn = fminf(mn, pkv_logf_portable(r));
-          if (r >= near_max) mx = fmaxf(mx, pkv_logf_portable(r));
-        }
-      }
-      span = __fsub_rn(mx, mn);
-      if (!(span > PKV_FLT_EPS)) span = PKV_FLT_EPS;
-      k = __fdiv_rn(255.0f, span);
-    }
-#pragma unroll 2
-    for (int q = 0; q < K::P / 4; q++) {
-      uint32_t q4 = 0, unsure = 0;
-#pragma unroll
-      for (int b = 0; b < 4; b++) {
-        int certain;
-        const uint32_t c8 = pkv_fast_radius_code(__logf(s_rad[(4 * q + b) * K::WS + v]), mn, k, &certain);
-        q4 |= c8 << (8 * b);
-        unsure |= (certain ? 0u : 1u) << b;
-      }
-      while (unsure) {
-        const int b = __ffs(unsure) - 1;
-        unsure &= unsure - 1;
-        float nrm = __fdiv_rn(__fsub_rn(pkv_logf_portable(s_rad[(4 * q + b) * K::WS + v]), mn), span);
-        nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
-        q4 = (q4 & ~(0xffu << (8 * b))) | (((uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu) << (8 * b));
-      }
-      w[q * K::WS] = q4;
-    }
-    w[(K::P / 4) * K::WS] = __float_as_uint(mn);
-    w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
   }
   if (valid && code) pkv_report(err, 0, (int64_t)batch * g.vpb + v0 + v, code);
   if constexpr (DIRECT) {
