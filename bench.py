@@ -45,6 +45,16 @@ WORKLOADS = {
     # cold tier: one whole SmolLM2-1.7B cache, fib k4_n32
     "c1": dict(agents=1, layers=24, heads=32, tokens=1024, dim=64, cache_tokens=1024, n_shared=0,
                codec="fib", desc="C1 fib k4_n32 cold tier: 24x{K,V}x32 heads x 1024 tokens x 64"),
+    # d = 128 (Llama-3-8B shape, 32 layers x 8 KV heads), the long-context configuration cut to a size
+    # one launch finishes in milliseconds: 1,048,576 vectors (537 MB f32) per launch
+    "c5s_fib": dict(agents=1, layers=32, heads=8, tokens=2048, dim=128, cache_tokens=2048, n_shared=0,
+                    codec="fib", desc="C5 scaled, fib k4_n32 prefix: 32x{K,V}x8 heads x 2048 tokens x 128"),
+    "c5s_turbo": dict(agents=4, layers=32, heads=8, tokens=512, dim=128, cache_tokens=1024, n_shared=512,
+                      codec="turbo", bits=4, mode=1, lossy=False,
+                      desc="C5 scaled, turbo b=4 shells (f32 radii): 4 agents x 512 tokens, 32x{K,V}x8x128"),
+    "c5s_turbo_lossy": dict(agents=4, layers=32, heads=8, tokens=512, dim=128, cache_tokens=1024, n_shared=512,
+                            codec="turbo", bits=4, mode=1, lossy=True,
+                            desc="C5 scaled, turbo b=4 shells (BlockLogU8 radii): 4 agents x 512 tokens, 32x{K,V}x8x128"),
 }
 TURBO_PROJ = 32
 
