@@ -116,6 +116,9 @@ __device__ __noinline__ void fix_pairs_warp(const uint8_t* xt, int xrow, uint4 s
 // Which of the two encode errors applies when some radius came out non-finite: a non-finite
 // input value (turbo.rs:263, checked first by the reference) or an overflow in the butterflies
 // (PolarCode::from_parts, polar.rs:127-133).
+// The exact logarithm of the BlockLogU8 coder, kept out of line: four call sites, two of them rare.
+__device__ __noinline__ float exact_logf(float r) { return pkv_logf_portable(r); }
+
 __device__ __noinline__ int classify_bad_vector(const uint8_t* xt, int slab, int row, int dim) {
   for (int i = 0; i < dim; i++)
     if (!pkv_finite(*tile_at(xt, slab, row, i))) return PKV_VEC_NONFINITE_INPUT;
@@ -342,7 +345,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       rmin = fminf(rmin, r);
       rmax = fmaxf(rmax, r);
     }
-    float mn = pkv_logf_portable(rmin), mx = pkv_logf_portable(rmax);
+    float mn = exact_logf(rmin), mx = exact_logf(rmax);
     const float near_min = __fmul_rn(rmin, 1.00001f), near_max = __fmul_rn(rmax, 0.99999f);
     bool ties = false;
 #pragma unroll
@@ -357,8 +360,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll 1
       for (int i = 0; i < K::P; i++) {
         const float r = rl[i];
-        if (r <= near_min) mn = fminf(mn, pkv_logf_portable(r));
-        if (r >= near_max) mx = fmaxf(mx, pkv_logf_portable(r));
+        if (r <= near_min) mn = fminf(mn, exact_logf(r));
+        if (r >= near_max) mx = fmaxf(mx, exact_logf(r));
       }
     }
     float span = __fsub_rn(mx, mn);
@@ -384,7 +387,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       while (unsure) {
         const int i = __ffsll((long long)unsure) - 1;
         unsure &= unsure - 1;
-        float nrm = __fdiv_rn(__fsub_rn(pkv_logf_portable(rl[i]), mn), span);
+        float nrm = __fdiv_rn(__fsub_rn(exact_logf(rl[i]), mn), span);
         nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
         const uint32_t c8 = (uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu;
         const int sh = 8 * (i & 3);
