@@ -58,7 +58,8 @@ enum {
   PKV_VEC_NONFINITE_OUTPUT = 23,  /* fib-quant/src/codec.rs:840 */
   PKV_VEC_NONFINITE_RESIDUAL = 24,/* turbo-quant/src/qjl.rs:210 */
   PKV_VEC_NORM_RANGE = 25,        /* fib-quant/src/codec.rs:1003 (second pass of encode_batch) */
-  PKV_VEC_DEVICE_WAIT = 26        /* no counterpart: a bounded wait inside a kernel ran out (the payload is not valid) */
+  PKV_VEC_DEVICE_WAIT = 26,
+  PKV_VEC_MISALIGNED_DST = 27        /* no counterpart: a bounded wait inside a kernel ran out (the payload is not valid) */
 };
 
 const char* pkv_status_string(int status);
@@ -194,6 +195,18 @@ int pkv_fib_decode_patch_dev_as(const pkv_fib_profile* p, const uint8_t* payload
                                 int64_t payload_batch_stride, const pkv_layout* layout,
                                 void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream);
 
+/* One launch for a cache made of separately allocated tensors (a framework's per-layer K and V
+ * tensors, proveKV/scripts/ppl_validate_multi_agent.py:282-293): batch b of the launch (flattened
+ * n_batches index) is written at cache_dev + batch_offsets_dev[b] elements, plus the layout's base,
+ * token and head terms; the layout's batch_stride values are ignored.  batch_offsets_dev is device
+ * memory holding one int64 per batch; an offset must be non-negative and a multiple of 4 elements
+ * (8 for the 16-bit types).  The kernel checks that: a violating batch is skipped and reported
+ * through the error word as PKV_VEC_MISALIGNED_DST. */
+int pkv_fib_decode_patch_dev_multi(const pkv_fib_profile* p, const uint8_t* payload_dev,
+                                   int64_t payload_batch_stride, const pkv_layout* layout,
+                                   void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
+                                   uint64_t* err_dev, void* stream);
+
 /* FibQuantAdapter::encode_batch_compact (proveKV/src/codec.rs:513-525): n vectors
  * of dim f32, contiguous, host memory -> FB2 bytes (19-byte header + n records). */
 int pkv_fib_encode_batch_compact(const pkv_fib_profile* p, const float* vectors_host, int64_t n,
@@ -246,6 +259,11 @@ int pkv_turbo_decode_patch_dev(const pkv_turbo_profile* p, const uint8_t* payloa
 int pkv_turbo_decode_patch_dev_as(const pkv_turbo_profile* p, const uint8_t* payload_dev,
                                   int64_t payload_batch_stride, const pkv_layout* layout,
                                   void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream);
+
+int pkv_turbo_decode_patch_dev_multi(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                                     int64_t payload_batch_stride, const pkv_layout* layout,
+                                     void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
+                                     uint64_t* err_dev, void* stream);
 
 /* TurboQuantAdapter::{encode,decode}_batch_compact (proveKV/src/codec.rs:248-326). */
 int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* p, const float* vectors_host, int64_t n,

@@ -33,6 +33,7 @@ VEC_NONFINITE_OUTPUT = 23
 VEC_NONFINITE_RESIDUAL = 24
 VEC_NORM_RANGE = 25
 VEC_DEVICE_WAIT = 26
+VEC_MISALIGNED_DST = 27
 
 NORM_FP16, NORM_F32 = 0, 1
 ARGMIN_PAIRWISE, ARGMIN_SEQUENTIAL = 0, 1
@@ -129,6 +130,8 @@ _SIGS = {
     "pkv_fib_decode_patch_dev": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, _V]),
     "pkv_fib_decode_patch_dev_as": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, C.c_int32, _V, _V]),
     "pkv_turbo_decode_patch_dev_as": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, C.c_int32, _V, _V]),
+    "pkv_fib_decode_patch_dev_multi": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, C.c_int32, _V, _V]),
+    "pkv_turbo_decode_patch_dev_multi": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, C.c_int32, _V, _V]),
     "pkv_fib_encode_dev_static": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_encode_batch_compact": (C.c_int, [_V, _V, C.c_int64, _V, C.c_int64, C.POINTER(C.c_int64),
                                                C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),

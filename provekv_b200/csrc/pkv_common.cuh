@@ -21,6 +21,9 @@ struct PkvGeom {
   int32_t tiles_per_batch;       // ceil(vpb / tile vectors)
   int32_t n_batches;             // n_batches[0] * [1] * [2]
   int32_t rec_bytes;             // bytes per vector record
+  // Decode only, may be null.  Element offset of each batch's tensor from the cache pointer, for
+  // caches made of separately allocated tensors; replaces the batch_stride terms of the layout.
+  const int64_t* batch_offsets;
 };
 
 // Element offset of vector v of batch `batch` (see pkv_layout in the C header).
@@ -36,12 +39,31 @@ __device__ __forceinline__ int64_t pkv_vec_offset(const pkv_layout& L, int batch
          (int64_t)head * L.head_stride;
 }
 
+// Destination of vector v of batch `batch` in a decode kernel.  With a table of per-batch tensor
+// offsets the alignment cannot be checked on the host: a batch whose offset is negative or not a
+// multiple of `align` elements (16 bytes) is reported and skipped (PKV_SKIP_DST).
+#define PKV_SKIP_DST ((int64_t)0x8000000000000000ll)
+__device__ __forceinline__ int64_t pkv_dst_offset(const PkvGeom& g, int batch, int v, int align,
+                                                  uint64_t* err);
+
 // Error word: the smallest (pass << 56 | global vector index << 8 | code) wins,
 // which is the error the reference's sequential loops would hit first.
 __device__ __forceinline__ void pkv_report(uint64_t* err, int pass, int64_t gvec, int code) {
   unsigned long long w = ((unsigned long long)pass << 56) | ((unsigned long long)gvec << 8) |
                          (unsigned long long)code;
   atomicMin((unsigned long long*)err, w);
+}
+
+__device__ __forceinline__ int64_t pkv_dst_offset(const PkvGeom& g, int batch, int v, int align,
+                                                  uint64_t* err) {
+  if (g.batch_offsets == nullptr) return pkv_vec_offset(g.L, batch, v);
+  const int64_t off = g.batch_offsets[batch];
+  if (off < 0 || off % align) {
+    pkv_report(err, 0, (int64_t)batch * g.vpb + v, PKV_VEC_MISALIGNED_DST);
+    return PKV_SKIP_DST;
+  }
+  const int token = v / g.L.n_heads, head = v - token * g.L.n_heads;
+  return off + g.L.base + (int64_t)token * g.L.token_stride + (int64_t)head * g.L.head_stride;
 }
 
 __device__ __forceinline__ bool pkv_finite(float x) {
@@ -177,7 +199,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
                                             uint8_t* payload, uint64_t* err, uint32_t* scratch,
                                             cudaStream_t s);
 int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
-                          void* cache, int dst, uint64_t* err, cudaStream_t s);
+                          void* cache, int dst, uint64_t* err, cudaStream_t s);  // g.batch_offsets honoured
 int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const PkvGeom& g,
                             uint8_t* payload, uint64_t* err, cudaStream_t s);
 int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,

@@ -126,7 +126,7 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
         if (!code) code = PKV_VEC_BAD_NORM;
       }
       if (code) pkv_report(err, 0, gvec, code);
-      s_dst[v] = pkv_vec_offset(g.L, batch, v0 + v);
+      s_dst[v] = pkv_dst_offset(g, batch, v0 + v, DST == PKV_DST_F32 ? 4 : 8, err);
     } else {
       for (int b = 0; b < K::B; b++) s_idx[v * K::B + b] = 0;
       s_dst[v] = 0;
@@ -170,7 +170,7 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const int v = vg * 8 + i;
-    if (v >= nv) continue;
+    if (v >= nv || s_dst[v] == PKV_SKIP_DST) continue;
     const float nf = s_norm[v];
     float o[8];
     bool ok = true;

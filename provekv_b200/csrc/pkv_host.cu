@@ -79,6 +79,7 @@ int make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, 
   g->tiles_per_batch = (int32_t)((vpb + tile - 1) / tile);
   g->n_batches = (int32_t)nb;
   g->rec_bytes = rec_bytes;
+  g->batch_offsets = nullptr;
   return PKV_OK;
 }
 
@@ -186,6 +187,8 @@ const char* pkv_status_string(int s) {
     case PKV_ERR_BUFFER_TOO_SMALL: return "output buffer too small";
     case PKV_ERR_STATIC_SCRATCH_TOO_SMALL:
       return "too many vectors for the fixed scratch array of pkv_fib_encode_dev_static";
+    case PKV_VEC_MISALIGNED_DST:
+      return "cache tensor offset is negative or not a multiple of 16 bytes";
     case PKV_VEC_NONFINITE_INPUT: return "non-finite input value";
     case PKV_VEC_ZERO_NORM: return "zero-norm vector";
     case PKV_VEC_BAD_RADIUS: return "radius is not finite and non-negative";
@@ -374,6 +377,20 @@ int pkv_fib_decode_patch_dev_as(const pkv_fib_profile* p, const uint8_t* payload
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
   if (st == PKV_OK) st = check_dst(layout, dst_dtype);
   if (st != PKV_OK) return st;
+  return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_fib_decode_patch_dev_multi(const pkv_fib_profile* p, const uint8_t* payload_dev,
+                                   int64_t payload_batch_stride, const pkv_layout* layout,
+                                   void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
+                                   uint64_t* err_dev, void* stream) {
+  if (!p || !cache_dev || !payload_dev || !err_dev || !batch_offsets_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
+  if (st == PKV_OK) st = check_dst(layout, dst_dtype);
+  if (st != PKV_OK) return st;
+  g.batch_offsets = batch_offsets_dev;
   return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
 }
 
@@ -618,6 +635,20 @@ int pkv_turbo_decode_patch_dev_as(const pkv_turbo_profile* p, const uint8_t* pay
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
   if (st == PKV_OK) st = check_dst(layout, dst_dtype);
   if (st != PKV_OK) return st;
+  return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
+}
+
+int pkv_turbo_decode_patch_dev_multi(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                                     int64_t payload_batch_stride, const pkv_layout* layout,
+                                     void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
+                                     uint64_t* err_dev, void* stream) {
+  if (!p || !cache_dev || !payload_dev || !err_dev || !batch_offsets_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
+  if (st == PKV_OK) st = check_dst(layout, dst_dtype);
+  if (st != PKV_OK) return st;
+  g.batch_offsets = batch_offsets_dev;
   return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
 }
 

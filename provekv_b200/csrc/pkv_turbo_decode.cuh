@@ -51,7 +51,7 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : 2 * (i - levels) + 1), tp.lut + i);
   if (tp.lossy)  // `*value as f32 / u8::MAX as f32`, radius.rs:143
     for (int i = threadIdx.x; i < 256; i += K::THREADS) s_q255[i] = __fdiv_rn((float)i, 255.0f);
-  if (v < nv) s_off[v] = pkv_vec_offset(g.L, batch, v0 + v);
+  if (v < nv) s_off[v] = pkv_dst_offset(g, batch, v0 + v, DST == PKV_DST_F32 ? 4 : 8, err);
   pkv_cp_async_wait_all();
   __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
 
@@ -152,6 +152,7 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
 #pragma unroll 4
     for (int i = lane; i < nv * K::LPV; i += 32) {
       const int vv = i / K::LPV, q = i % K::LPV;
+      if (s_off[vv] == PKV_SKIP_DST) continue;
       const float4 val = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 4 * q);
       float* dst = cache + s_off[vv] + 4 * q;
       for (int r = 0; r < g.L.n_replicas; r++) {
@@ -165,6 +166,7 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
 #pragma unroll 4
     for (int i = lane; i < nv * LPH; i += 32) {
       const int vv = i / LPH, q = i % LPH;
+      if (s_off[vv] == PKV_SKIP_DST) continue;
       const float4 a = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 8 * q);
       const float4 b = *reinterpret_cast<const float4*>(s_x + vv * K::XS + 8 * q + 4);
       const uint4 val = make_uint4(pkv_pack2<DST>(a.x, a.y), pkv_pack2<DST>(a.z, a.w),

@@ -22,7 +22,7 @@ from . import _lib as L
 from .pool import payload_batch_stride
 
 __all__ = ["write_kv_binary", "read_kv_binary", "dst_dtype_of", "cache_tensor_layout", "cache_layers",
-           "patch_cache"]
+           "CachePlan", "plan_cache", "patch_cache"]
 
 
 def write_kv_binary(path, manifest: dict, layers: Sequence[tuple[np.ndarray, np.ndarray]]) -> None:
@@ -118,8 +118,46 @@ def cache_layers(cache) -> list[tuple]:
     return [tuple(pair) for pair in cache]
 
 
-def patch_cache(profile, payload, cache, n_tokens: int, pos0: int, err, stream: int = 0) -> int:
-    """Decode ``payload`` into the cache in place.
+class CachePlan:
+    """Where the tensors of a cache sit relative to the lowest one: what one decode-and-patch launch
+    over all of them needs.  Build it once per cache (`plan_cache`) and pass it to `patch_cache`;
+    it stays valid while the cache's tensors are not reallocated."""
+
+    def __init__(self, base_ptr: int, offsets, dst_dtype: int, heads: int, token_stride: int,
+                 head_stride: int, capacity: int, n_layers: int):
+        self.base_ptr, self.offsets, self.dst_dtype = base_ptr, offsets, dst_dtype
+        self.heads, self.token_stride, self.head_stride = heads, token_stride, head_stride
+        self.capacity, self.n_layers = capacity, n_layers
+
+
+def plan_cache(cache) -> CachePlan | None:
+    """A `CachePlan` if every tensor of the cache has the same shape, strides, element type and
+    device and the distances between them are whole multiples of 16 bytes; otherwise None (then
+    `patch_cache` launches once per tensor)."""
+    import torch
+    layers = cache_layers(cache)
+    tensors = [t for pair in layers for t in pair]
+    first = tensors[0]
+    if any(t.shape != first.shape or t.stride() != first.stride() or t.dtype != first.dtype or
+           t.device != first.device for t in tensors):
+        return None
+    view = first[0] if first.dim() == 4 else first
+    if view.dim() != 3 or view.stride(2) != 1:
+        return None
+    esize = first.element_size()
+    base = min(t.data_ptr() for t in tensors)
+    if base % 16 or any((t.data_ptr() - base) % 16 for t in tensors):
+        return None
+    offsets = torch.tensor([(t.data_ptr() - base) // esize for t in tensors], dtype=torch.int64,
+                           device=first.device)
+    return CachePlan(base, offsets, dst_dtype_of(first), view.shape[0], view.stride(1), view.stride(0),
+                     view.shape[1], len(layers))
+
+
+def patch_cache(profile, payload, cache, n_tokens: int, pos0: int, err, stream: int = 0,
+                plan: CachePlan | None = None) -> int:
+    """Decode ``payload`` into the cache in place: one launch for the whole cache when its tensors
+    are alike (``plan``, or `plan_cache(cache)` when none is given), else one per tensor.
 
     ``payload``: uint8 device tensor ``[layers][2][stride]`` of records without wire headers, batch
     (layer, side) at ``stride = payload_batch_stride(n_tokens * H, record_bytes)``.  ``cache``: see
@@ -132,6 +170,22 @@ def patch_cache(profile, payload, cache, n_tokens: int, pos0: int, err, stream: 
     stride = payload_batch_stride(n_tokens * heads, rec)
     if payload.dim() != 3 or payload.shape[0] != len(layers) or payload.shape[1] != 2 or payload.shape[2] != stride:
         raise ValueError(f"payload must be [layers={len(layers)}][2][{stride}] bytes")
+    if plan is None:
+        plan = plan_cache(cache)
+    if plan is not None:
+        if plan.n_layers != len(layers) or plan.heads != heads:
+            raise ValueError("the plan was made for another cache")
+        if pos0 < 0 or pos0 + n_tokens > plan.capacity:
+            raise ValueError(f"positions {pos0}..{pos0 + n_tokens} do not fit a cache of {plan.capacity} tokens")
+        lay = L.Layout()
+        lay.base = pos0 * plan.token_stride
+        lay.batch_stride[0] = lay.batch_stride[1] = lay.batch_stride[2] = 0
+        lay.n_batches[0], lay.n_batches[1], lay.n_batches[2] = len(layers), 2, 1
+        lay.token_stride, lay.head_stride, lay.replica_stride = plan.token_stride, plan.head_stride, 0
+        lay.n_tokens, lay.n_heads, lay.n_replicas = n_tokens, heads, 1
+        profile.decode_patch_dev_multi(payload.data_ptr(), stride, lay, plan.base_ptr, plan.offsets.data_ptr(),
+                                       err.data_ptr(), stream, dst_dtype=plan.dst_dtype)
+        return 1
     launches = 0
     for li, pair in enumerate(layers):
         for side, tensor in enumerate(pair):

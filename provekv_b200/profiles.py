@@ -117,6 +117,16 @@ class FibProfile(_ProfileBase):
                                                     C.byref(layout), cache_ptr, dst_dtype, err_ptr, stream))
 
 
+    def decode_patch_dev_multi(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
+                               cache_ptr: int, batch_offsets_ptr: int, err_ptr: int, stream: int = 0,
+                               dst_dtype: int = L.DST_F32) -> None:
+        """One launch over separately allocated cache tensors: batch b goes to
+        cache_ptr + offsets[b] elements (device int64 table, non-negative multiples of 16 bytes)."""
+        L.check(L.lib().pkv_fib_decode_patch_dev_multi(self.handle, payload_ptr, payload_batch_stride,
+                                                       C.byref(layout), cache_ptr, batch_offsets_ptr,
+                                                       dst_dtype, err_ptr, stream))
+
+
 class TurboProfile(_ProfileBase):
     """turbo-quant profile: Rademacher signs, optional QJL matrix, angle LUT."""
     _destroy = "pkv_turbo_profile_destroy"
@@ -186,6 +196,14 @@ class TurboProfile(_ProfileBase):
                          cache_ptr: int, err_ptr: int, stream: int = 0, dst_dtype: int = L.DST_F32) -> None:
         L.check(L.lib().pkv_turbo_decode_patch_dev_as(self.handle, payload_ptr, payload_batch_stride,
                                                       C.byref(layout), cache_ptr, dst_dtype, err_ptr, stream))
+
+
+    def decode_patch_dev_multi(self, payload_ptr: int, payload_batch_stride: int, layout: L.Layout,
+                               cache_ptr: int, batch_offsets_ptr: int, err_ptr: int, stream: int = 0,
+                               dst_dtype: int = L.DST_F32) -> None:
+        L.check(L.lib().pkv_turbo_decode_patch_dev_multi(self.handle, payload_ptr, payload_batch_stride,
+                                                         C.byref(layout), cache_ptr, batch_offsets_ptr,
+                                                         dst_dtype, err_ptr, stream))
 
 
 def read_error_word(err_ptr: int, stream: int = 0) -> None:

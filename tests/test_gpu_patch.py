@@ -19,14 +19,14 @@ def _bits16(t):
     return t.contiguous().view(torch.int16).cpu().numpy()
 
 
-def _reference_patch(torch, dec, layers, heads, T, d, dtype, cap, pos0, fill):
+def _reference_patch(torch, dec, layers, heads, T, d, dtype, caps, pos0, fill):
     """patch_cache_with_multi_agent_kv, ppl_validate_multi_agent.py:247-262: per token,
     `k[0, :, pos, :] = torch.tensor(flat[t*stride:(t+1)*stride], dtype=k.dtype).view(H, d)`."""
     out = []
     for li in range(layers):
         pair = []
         for side in range(2):
-            c = torch.full((1, heads, cap, d), fill, dtype=dtype)
+            c = torch.full((1, heads, caps[li], d), fill, dtype=dtype)
             flat = dec[li, side].reshape(T, heads * d)
             for t in range(T):
                 c[0, :, pos0 + t, :] = torch.tensor(flat[t].tolist(), dtype=dtype).view(heads, d)
@@ -37,8 +37,8 @@ def _reference_patch(torch, dec, layers, heads, T, d, dtype, cap, pos0, fill):
 
 @pytest.mark.parametrize("kind", ["fib", "turbo", "turbo_lossy"])
 @pytest.mark.parametrize("dtype_name", ["float16", "bfloat16", "float32"])
-@pytest.mark.parametrize("d,heads,T", [(64, 4, 21), (128, 2, 9)])
-def test_patch_per_layer_caches_of_every_dtype(oracle_mod, kind, dtype_name, d, heads, T):
+@pytest.mark.parametrize("d,heads,T,alike", [(64, 4, 21, True), (128, 2, 9, True), (64, 4, 21, False)])
+def test_patch_per_layer_caches_of_every_dtype(oracle_mod, kind, dtype_name, d, heads, T, alike):
     import torch
     dtype = getattr(torch, dtype_name)
     layers, cap, pos0 = 3, T + 11, 6
@@ -55,25 +55,28 @@ def test_patch_per_layer_caches_of_every_dtype(oracle_mod, kind, dtype_name, d, 
     payload = torch.from_numpy(host).cuda()
     dec = np.stack([_oracle_decode(oracle_mod, kind, prof, p, d) for p in want]).reshape(layers, 2, T, heads, d)
 
+    # alike tensors take one launch for the whole cache; layers of different capacity one per tensor
+    caps = [cap if alike else cap + li for li in range(layers)]
     try:  # the reference installs the tensors in a DynamicCache (ppl_validate_multi_agent.py:282-293)
         from transformers import DynamicCache, DynamicLayer
         cache = DynamicCache()
         while len(cache.layers) < layers:
             cache.layers.append(DynamicLayer())
-        for layer in cache.layers:
-            layer.keys = torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda")
-            layer.values = torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda")
+        for li, layer in enumerate(cache.layers):
+            layer.keys = torch.full((1, heads, caps[li], d), 7.0, dtype=dtype, device="cuda")
+            layer.values = torch.full((1, heads, caps[li], d), 7.0, dtype=dtype, device="cuda")
     except Exception:
-        cache = [(torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda"),
-                  torch.full((1, heads, cap, d), 7.0, dtype=dtype, device="cuda")) for _ in range(layers)]
+        cache = [(torch.full((1, heads, caps[li], d), 7.0, dtype=dtype, device="cuda"),
+                  torch.full((1, heads, caps[li], d), 7.0, dtype=dtype, device="cuda")) for li in range(layers)]
+    assert (patch.plan_cache(cache) is not None) == alike
 
     err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
     before = L.lib().pkv_launch_count()
     n = patch.patch_cache(prof, payload, cache, T, pos0, err)
     pk.read_error_word(err.data_ptr())
-    assert n == 2 * layers and L.lib().pkv_launch_count() - before == n
+    assert n == (1 if alike else 2 * layers) and L.lib().pkv_launch_count() - before == n
 
-    ref = _reference_patch(torch, dec, layers, heads, T, d, dtype, cap, pos0, 7.0)
+    ref = _reference_patch(torch, dec, layers, heads, T, d, dtype, caps, pos0, 7.0)
     for li, (k, v) in enumerate(patch.cache_layers(cache)):
         for side, got in enumerate((k, v)):
             exp = ref[li][side]
@@ -148,3 +151,48 @@ def test_kv_binary_file_to_cache(oracle_mod, tmp_path):
         for side, name in enumerate("kv"):
             exp = torch.from_numpy(from_file[i][side].reshape(T, heads, d)).to(torch.float16).permute(1, 0, 2)
             assert np.array_equal(_bits16(cache[i][name][0]), _bits16(exp))
+
+
+@pytest.mark.parametrize("kind", ["fib", "turbo"])
+def test_multi_tensor_launch_checks_offsets_on_the_device(oracle_mod, kind):
+    """A tensor offset that is not a multiple of 16 bytes is reported (PKV_VEC_MISALIGNED_DST, with
+    the batch's first vector) and that batch is skipped; the other batches are written."""
+    import torch
+    d, heads, T, nb = 64, 4, 8, 3
+    prof = _profiles(d)[kind]
+    vpb, rec = T * heads, prof.record_bytes
+    x = synthetic_kv(nb * vpb, d, seed=9).reshape(nb, vpb, d)
+    stride = pool.payload_batch_stride(vpb, rec)
+    host = np.zeros((nb, stride), np.uint8)
+    want = [_oracle_encode(oracle_mod, kind, prof, x[b]) for b in range(nb)]
+    for b in range(nb):
+        host[b, :vpb * rec] = want[b].reshape(-1)
+    payload = torch.from_numpy(host).cuda()
+    arena = torch.zeros(nb * heads * T * d + 64, dtype=torch.float32, device="cuda")
+    per = heads * T * d
+    lay = patch.cache_tensor_layout(arena[:per].view(heads, T, d), T, 0)
+    lay.n_batches[0] = nb
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    for bad in (None, 1):
+        arena.zero_()
+        err.fill_(-1)
+        offs = [b * per for b in range(nb)]
+        if bad is not None:
+            offs[bad] += 2
+        table = torch.tensor(offs, dtype=torch.int64, device="cuda")
+        prof.decode_patch_dev_multi(payload.data_ptr(), stride, lay, arena.data_ptr(), table.data_ptr(),
+                                    err.data_ptr())
+        if bad is None:
+            pk.read_error_word(err.data_ptr())
+        else:
+            with pytest.raises(pk.PkvError) as e:
+                pk.read_error_word(err.data_ptr())
+            assert e.value.status == L.VEC_MISALIGNED_DST and e.value.vector_index == bad * vpb
+        out = arena.cpu().numpy()
+        for b in range(nb):
+            got = out[b * per:(b + 1) * per].reshape(heads, T, d)
+            if b == bad:
+                assert not out[b * per:(b + 1) * per].any()
+            else:
+                exp = _oracle_decode(oracle_mod, kind, prof, want[b], d).reshape(T, heads, d).transpose(1, 0, 2)
+                assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(exp).view(np.uint32))
