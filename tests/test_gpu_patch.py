@@ -196,3 +196,26 @@ def test_multi_tensor_launch_checks_offsets_on_the_device(oracle_mod, kind):
             else:
                 exp = _oracle_decode(oracle_mod, kind, prof, want[b], d).reshape(T, heads, d).transpose(1, 0, 2)
                 assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(exp).view(np.uint32))
+
+
+def test_shared_pool_built_on_the_gpu_from_the_reference_corpus_layout(oracle_mod):
+    """build_shared_pool encodes every (layer, K|V) batch of a [token][layer][head][K|V][dim] corpus
+    in one launch; the blobs must equal the per-batch encode_batch_compact results of
+    proveKV/src/pool.rs:246-266 and the digests must chain as in pool.rs:83-103,329-343."""
+    from provekv_b200 import manifest as M
+    d, H, Lc, T = 64, 4, 3, 37
+    prof = _profiles(d)["fib"]
+    corpus = synthetic_kv(T * Lc * H * 2, d, seed=21).reshape(T, Lc * H * 2 * d)
+    shape = M.KvTensorShape("mha", Lc, H, H, d, H * d)
+    before = L.lib().pkv_launch_count()
+    pool_ = M.build_shared_pool(prof, corpus, shape, 42, "cb-digest", "rot-digest")
+    assert L.lib().pkv_launch_count() - before == 2  # the encoder and its exact fix-up pass
+    x = corpus.reshape(T, Lc, H, 2, d)
+    for li, layer in enumerate(pool_["layers"]):
+        for side, block in enumerate((layer.key_blocks[0], layer.value_blocks[0])):
+            vectors = np.ascontiguousarray(x[:, li, :, side, :]).reshape(T * H, d)  # token-major, head-minor
+            want = oracle_mod.fb2_header(d, T * H) + _oracle_encode(oracle_mod, "fib", prof, vectors).tobytes()
+            assert block.encoded_payload == want and block.original_dim == d
+        assert layer.block_digest == layer.compute_digest() == pool_["layer_digests"][li]
+    assert pool_["pool_id"] == M.pool_id(pool_["layer_digests"], "cb-digest", "rot-digest", shape, 42)
+    assert pool_["pool_size_bytes"] == Lc * 2 * (19 + T * H * 12) and pool_["raw_size_bytes"] == corpus.size * 4
