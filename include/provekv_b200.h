@@ -265,6 +265,19 @@ int pkv_turbo_decode_patch_dev_multi(const pkv_turbo_profile* p, const uint8_t* 
                                      void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
                                      uint64_t* err_dev, void* stream);
 
+/* Compressed-domain scoring, TurboQuantizer::score_batch_prepared (turbo-quant/src/turbo.rs:340-381):
+ * scores_dev[b * vectors_per_batch + v] = polar inner-product estimate (polar.rs:346-370) plus the
+ * QJL correction (qjl.rs:294-330) of record v of batch b against one prepared query, computed from
+ * the records without reconstructing the vectors.  rotated_query_dev: dim values, the query after
+ * FastHadamardRotation::apply (polar.rs:336-343); projected_query_dev: `projections` values G * query
+ * (qjl.rs:266-281), ignored for polar-only profiles; both are what TurboQuantizer::prepare_query
+ * (turbo.rs:322-337) returns, in device memory.  Records are validated as in the decode call; a
+ * non-finite score is reported as PKV_VEC_NONFINITE_OUTPUT. */
+int pkv_turbo_score_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                        int64_t payload_batch_stride, int64_t n_batches, int64_t vectors_per_batch,
+                        const float* rotated_query_dev, const float* projected_query_dev,
+                        float* scores_dev, uint64_t* err_dev, void* stream);
+
 /* TurboQuantAdapter::{encode,decode}_batch_compact (proveKV/src/codec.rs:248-326). */
 int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* p, const float* vectors_host, int64_t n,
                                    uint8_t* out_host, int64_t out_capacity, int64_t* out_len,

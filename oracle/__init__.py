@@ -139,6 +139,39 @@ def turbo_decode(payload, dim, signs, *, bits=4, mode=1, projections=32, radii_c
     return st, out, code.value, idx.value
 
 
+def turbo_prepare_query(query, signs, qjl=None):
+    """(rotated, projected) as TurboQuantizer::prepare_query returns them (turbo.rs:322-337)."""
+    q, signs = _f32(query), _f32(signs)
+    dim = q.size
+    rotated = np.zeros(dim, np.float32)
+    m = 0 if qjl is None else np.asarray(qjl).shape[0]
+    projected = np.zeros(max(m, 1), np.float32)
+    g = None if qjl is None else _f32(qjl)
+    st = lib().pkvo_turbo_prepare_query(_p(q, C.c_float), dim, m, _p(signs, C.c_float),
+                                        None if g is None else _p(g, C.c_float), _p(rotated, C.c_float),
+                                        _p(projected, C.c_float))
+    return st, rotated, projected[:m]
+
+
+def turbo_score(payload, dim, rotated, projected, *, bits=4, mode=1, projections=32, radii_codec=0,
+                libm_mode=LIBM_PORTABLE):
+    """TurboQuantizer::score_batch_prepared over wire records (turbo.rs:340-381)."""
+    rec = turbo_record_bytes(dim, bits, mode, projections, radii_codec)
+    payload = np.ascontiguousarray(payload, np.uint8).reshape(-1, rec)
+    n = payload.shape[0]
+    pb = bits - 1 if mode == 1 else bits
+    cl, sl = polar_lut(pb)
+    rotated = _f32(rotated)
+    projected = _f32(projected) if mode == 1 else np.zeros(1, np.float32)
+    scores = np.zeros(n, np.float32)
+    code, idx = C.c_int32(0), C.c_int64(-1)
+    st = lib().pkvo_turbo_score_batch(_p(payload, C.c_uint8), C.c_int64(n), dim, bits, mode, projections,
+                                      radii_codec, libm_mode, _p(cl, C.c_float), _p(sl, C.c_float),
+                                      _p(rotated, C.c_float), _p(projected, C.c_float), _p(scores, C.c_float),
+                                      C.byref(code), C.byref(idx))
+    return st, scores, code.value, idx.value
+
+
 def fb2_header(dim, n_vectors, k=4, n_codewords=32, norm_format=0) -> bytes:
     buf = (C.c_uint8 * 19)()
     lib().pkvo_fb2_header_write(dim, k, n_codewords, norm_format, C.c_uint32(n_vectors), buf)

@@ -746,6 +746,97 @@ static void turbo_dec_range(void* p, int64_t lo, int64_t hi) {
   }
 }
 
+/* TurboQuantizer::prepare_query (turbo.rs:322-337): the query after FastHadamardRotation::apply
+ * (polar.rs:336-343, rotation.rs:202-210) and after the QJL matrix (qjl.rs:266-281: per row the
+ * products g * q summed in order).  projected may be NULL for polar-only. */
+PKVO_API int pkvo_turbo_prepare_query(const float* query, int dim, int projections, const float* signs,
+                                      const float* qjl, float* rotated, float* projected) {
+  if (dim <= 0 || dim > 512 || (dim & (dim - 1))) return PKV_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < dim; i++)
+    if (!is_finite_f32(query[i])) return PKV_VEC_NONFINITE_INPUT;
+  for (int i = 0; i < dim; i++) rotated[i] = query[i] * signs[i];
+  fwht_normalized(rotated, dim);
+  for (int i = 0; i < dim; i++)
+    if (!is_finite_f32(rotated[i])) return PKV_VEC_NONFINITE_INPUT;
+  if (projected && qjl) {
+    for (int j = 0; j < projections; j++) {
+      volatile float sum = 0.0f;
+      for (int k = 0; k < dim; k++) {
+        volatile float prod = qjl[(size_t)j * dim + k] * query[k];
+        sum = sum + prod;
+      }
+      projected[j] = sum;
+      if (!is_finite_f32(projected[j])) return PKV_VEC_NONFINITE_INPUT;
+    }
+  }
+  return 0;
+}
+
+/* TurboQuantizer::inner_product_estimate_prepared for one wire record (turbo.rs:340-369): record
+ * parsed and validated as in turbo_decode_one, polar estimate polar.rs:346-370, QJL correction
+ * qjl.rs:294-330 with source_norm 1. */
+static int turbo_score_one(const turbo_job* J, const uint8_t* rec, const float* rotated,
+                           const float* projected, float* score) {
+  const int d = J->dim, pairs = d / 2;
+  const int pb = pkvo_turbo_polar_bits(J->bits, J->mode);
+  float radii[256];
+  uint32_t aidx[256], sg[64];
+  const uint8_t* r = rec;
+  *score = 0.0f;
+  if (J->radii_codec == PKV_RADII_F32) {
+    memcpy(radii, r, (size_t)pairs * 4);
+    r += pairs * 4;
+    for (int i = 0; i < pairs; i++)
+      if (!is_finite_f32(radii[i]) || radii[i] < 0.0f) return PKV_VEC_BAD_RADIUS;
+  } else {
+    float mn, mx;
+    memcpy(&mn, r + pairs, 4);
+    memcpy(&mx, r + pairs + 4, 4);
+    if (!is_finite_f32(mn) || !is_finite_f32(mx) || mn > mx) return PKV_VEC_BAD_RADIUS_RANGE;
+    float span = mx - mn;
+    for (int i = 0; i < pairs; i++)
+      radii[i] = expf_mode(mn + span * ((float)r[i] / 255.0f), J->libm_mode);
+    r += pairs + 8;
+  }
+  if (!unpack_bits(r, pairs, pb, aidx)) return PKV_VEC_PADDING_BITS;
+  r += (pairs * pb + 7) / 8;
+  if (J->mode == PKV_TURBO_POLAR_WITH_QJL && !unpack_bits(r, J->projections, 1, sg)) return PKV_VEC_PADDING_BITS;
+  for (int i = 0; i < pairs; i++)
+    if (!is_finite_f32(radii[i]) || radii[i] < 0.0f) return PKV_VEC_BAD_RADIUS;
+  volatile float estimate = 0.0f;
+  for (int i = 0; i < pairs; i++) {
+    volatile float qa = rotated[2 * i] * J->cos_lut[aidx[i]];
+    volatile float qb = rotated[2 * i + 1] * J->sin_lut[aidx[i]];
+    volatile float inner = qa + qb;
+    volatile float term = radii[i] * inner;
+    estimate = estimate + term;
+  }
+  if (!is_finite_f32(estimate)) return PKV_VEC_NONFINITE_OUTPUT;
+  float total = estimate;
+  if (J->mode == PKV_TURBO_POLAR_WITH_QJL) {
+    const float pi = 3.14159274101257324f;
+    volatile float root = sqrtf(pi / 2.0f);
+    volatile float scale = (root * 1.0f) / (float)J->projections;
+    volatile float sum = 0.0f;
+    for (int j = 0; j < J->projections; j++) {
+      volatile float term = (sg[j] ? 1.0f : -1.0f) * projected[j];
+      sum = sum + term;
+    }
+    volatile float corr = scale * sum;
+    if (!is_finite_f32(corr)) return PKV_VEC_NONFINITE_OUTPUT;
+    total = estimate + corr;
+    if (!is_finite_f32(total)) return PKV_VEC_NONFINITE_OUTPUT;
+  }
+  *score = total;
+  return 0;
+}
+
+/* TurboQuantizer::score_batch_prepared (turbo.rs:372-381): the first failing record ends the batch. */
+PKVO_API int pkvo_turbo_score_batch(const uint8_t* payload, int64_t n, int dim, int bits, int mode,
+                                    int projections, int radii_codec, int libm_mode, const float* cos_lut,
+                                    const float* sin_lut, const float* rotated, const float* projected,
+                                    float* scores, int32_t* vec_code, int64_t* vec_index);
+
 static int turbo_job_init(turbo_job* J, int64_t n, int dim, int bits, int mode, int projections,
                           int radii_codec, int libm_mode, const float* signs, const float* qjl,
                           const float* cos_lut, const float* sin_lut) {
@@ -768,6 +859,29 @@ static int turbo_job_init(turbo_job* J, int64_t n, int dim, int bits, int mode, 
   J->code = 0;
   J->index = -1;
   pthread_mutex_init(&J->mu, NULL);
+  return 0;
+}
+
+PKVO_API int pkvo_turbo_score_batch(const uint8_t* payload, int64_t n, int dim, int bits, int mode,
+                                    int projections, int radii_codec, int libm_mode, const float* cos_lut,
+                                    const float* sin_lut, const float* rotated, const float* projected,
+                                    float* scores, int32_t* vec_code, int64_t* vec_index) {
+  turbo_job J;
+  int st = turbo_job_init(&J, n, dim, bits, mode, projections, radii_codec, libm_mode, NULL, NULL, cos_lut,
+                          sin_lut);
+  if (st) return st;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  for (int64_t v = 0; v < n; v++) {
+    int code = turbo_score_one(&J, payload + v * J.rec_bytes, rotated, projected, scores + v);
+    if (code) {
+      if (vec_code) *vec_code = code;
+      if (vec_index) *vec_index = v;
+      pthread_mutex_destroy(&J.mu);
+      return code;
+    }
+  }
+  pthread_mutex_destroy(&J.mu);
   return 0;
 }
 

@@ -10,6 +10,7 @@
 // dimension and on the angle width: 3, 4 and 7 bits are compiled with static bit
 // positions, any other width runs the generic variant (PB = 0).
 #include "pkv_turbo_decode.cuh"
+#include "pkv_turbo_score.cuh"
 #include "pkv_turbo_encode.cuh"
 
 using namespace pkv_turbo;
@@ -90,6 +91,19 @@ int launch_decode(const TurboParams& tp, const uint8_t* payload, const PkvGeom& 
   }
 }
 
+template <int D, int PB>
+int launch_score(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g, const float* rotated,
+                 const float* projected, float qjl_scale, float* scores, uint64_t* err, unsigned grid,
+                 cudaStream_t s) {
+  const size_t sm = turbo_score_smem<D>(tp);
+  int st = set_smem(turbo_score_kernel<D, PB>, sm);
+  if (st != PKV_OK) return st;
+  const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
+  turbo_score_kernel<D, PB><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected, qjl_scale,
+                                                               scores, err);
+  return PKV_OK;
+}
+
 }  // namespace
 
 int pkv_turbo_tile_vectors(int dim) { return (dim == 64 || dim == 128) ? 32 : 0; }
@@ -132,6 +146,29 @@ int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, 
     PKV_DISPATCH_PB(launch_decode, 64, tp, payload, g, cache, dst, err, (unsigned)grid, s)
   } else if (p->cfg.dim == 128) {
     PKV_DISPATCH_PB(launch_decode, 128, tp, payload, g, cache, dst, err, (unsigned)grid, s)
+  } else {
+    return PKV_ERR_UNSUPPORTED;
+  }
+  if (st != PKV_OK) return st;
+  pkv_count_launch();
+  return pkv_cuda_status(cudaGetLastError());
+}
+
+int pkv_launch_turbo_score(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,
+                           const float* rotated, const float* projected, float* scores, uint64_t* err,
+                           cudaStream_t s) {
+  const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
+  if (grid == 0) return PKV_OK;
+  if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  const TurboParams tp = make_params(p);
+  // (PI / 2.0).sqrt() * source_norm / m with source_norm = 1, turbo-quant/src/qjl.rs:316-317
+  volatile float half_pi_root = sqrtf(3.14159274101257324f / 2.0f);
+  const float qjl_scale = p->cfg.projections > 0 ? (half_pi_root * 1.0f) / (float)p->cfg.projections : 0.0f;
+  int st;
+  if (p->cfg.dim == 64) {
+    PKV_DISPATCH_PB(launch_score, 64, tp, payload, g, rotated, projected, qjl_scale, scores, err, (unsigned)grid, s)
+  } else if (p->cfg.dim == 128) {
+    PKV_DISPATCH_PB(launch_score, 128, tp, payload, g, rotated, projected, qjl_scale, scores, err, (unsigned)grid, s)
   } else {
     return PKV_ERR_UNSUPPORTED;
   }

@@ -206,6 +206,39 @@ class TurboProfile(_ProfileBase):
                                                          dst_dtype, err_ptr, stream))
 
 
+    def prepare_query(self, query) -> tuple[np.ndarray, np.ndarray]:
+        """TurboQuantizer::prepare_query (turbo-quant/src/turbo.rs:322-337) on the host, in the
+        reference's binary32 operation order: (rotated, projected) = (FastHadamardRotation::apply(q),
+        G q).  `projected` is empty for a polar-only profile."""
+        q = np.ascontiguousarray(query, dtype=np.float32).reshape(-1)
+        if q.size != self.dim:
+            raise ValueError(f"query has {q.size} values, expected {self.dim}")
+        if not np.all(np.isfinite(q)):
+            raise ValueError("query is not finite")
+        v = (q * self.signs).astype(np.float32)
+        step = 1
+        while step < self.dim:  # butterflies (a, b) -> (a + b, a - b) on (i, i + step), rotation.rs:379-398
+            w = v.reshape(-1, 2, step)
+            v = np.stack([w[:, 0, :] + w[:, 1, :], w[:, 0, :] - w[:, 1, :]], axis=1).astype(np.float32).reshape(-1)
+            step *= 2
+        rotated = (v * (np.float32(1.0) / np.sqrt(np.float32(self.dim)))).astype(np.float32)
+        if self.qjl is None:
+            return rotated, np.zeros(0, np.float32)
+        prod = (self.qjl * q[None, :]).astype(np.float32)  # g * q, each rounded
+        acc = np.zeros(self.qjl.shape[0], np.float32)
+        for k in range(self.dim):  # summed in order, qjl.rs:277
+            acc = (acc + prod[:, k]).astype(np.float32)
+        return rotated, acc
+
+    def score_dev(self, payload_ptr: int, payload_batch_stride: int, n_batches: int, vectors_per_batch: int,
+                  rotated_ptr: int, projected_ptr: int, scores_ptr: int, err_ptr: int, stream: int = 0) -> None:
+        """Inner-product estimates of one prepared query against every record of the launch
+        (TurboQuantizer::score_batch_prepared, turbo.rs:340-381), read straight from the records."""
+        L.check(L.lib().pkv_turbo_score_dev(self.handle, payload_ptr, payload_batch_stride, n_batches,
+                                            vectors_per_batch, rotated_ptr, projected_ptr, scores_ptr,
+                                            err_ptr, stream))
+
+
 def read_error_word(err_ptr: int, stream: int = 0) -> None:
     """Synchronise the stream and raise PkvError if a kernel reported a vector."""
     code, idx = C.c_int32(0), C.c_int64(-1)

@@ -172,3 +172,37 @@ def test_lossy_radii_within_five_percent(oracle_mod, turbo64):
     mx = lossy[:, 36:40].copy().view(np.float32)
     back = np.exp(mn + (mx - mn) * (q / 255.0))
     assert np.max(np.abs(back - r) / np.maximum(r, 1e-6)) < 0.05
+
+
+def test_oracle_scoring_against_reconstruction_and_host_mirror(oracle_mod):
+    """Compressed-domain scores (turbo.rs:340-381): the polar part equals the inner product with the
+    reconstruction (the rotation is orthonormal), the QJL part adds sqrt(pi/2)/m * sum of +-p_j, and
+    the package's host-side prepare_query reproduces the oracle's rotated / projected query bits."""
+    import provekv_b200 as pk
+    from provekv_b200 import tables
+
+    d, n = 64, 500
+    signs, qjl = tables.rademacher_signs(d, 42), tables.qjl_matrix(d, 32, 42)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    q = rng.standard_normal(d).astype(np.float32)
+    st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=4, mode=1, radii_codec=0)
+    assert st == 0
+    st, rotated, projected = oracle_mod.turbo_prepare_query(q, signs, qjl)
+    assert st == 0
+
+    class _Stub:  # prepare_query only reads these fields; no GPU library needed
+        dim, signs, qjl = d, None, None
+    stub = _Stub()
+    stub.signs, stub.qjl = signs, qjl
+    r2, p2 = pk.TurboProfile.prepare_query(stub, q)
+    assert np.array_equal(r2.view(np.uint32), rotated.view(np.uint32))
+    assert np.array_equal(p2.view(np.uint32), projected.view(np.uint32))
+
+    st, full, _, _ = oracle_mod.turbo_score(payload, d, rotated, projected)
+    st, polar, _, _ = oracle_mod.turbo_score(payload, d, rotated, np.zeros(32, np.float32))
+    st, dec, _, _ = oracle_mod.turbo_decode(payload, d, signs)
+    assert np.allclose(polar, dec @ q, rtol=1e-5, atol=1e-4)
+    sign_bits = np.unpackbits(payload.reshape(n, -1)[:, -4:], axis=1, bitorder="little").astype(np.float32) * 2 - 1
+    corr = np.float32(np.sqrt(np.float32(np.pi) / np.float32(2))) / np.float32(32) * (sign_bits @ projected)
+    assert np.allclose(full - polar, corr, rtol=1e-4, atol=1e-4)
