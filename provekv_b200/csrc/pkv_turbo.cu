@@ -96,11 +96,19 @@ int launch_score(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g
                  const float* projected, float qjl_scale, float* scores, uint64_t* err, unsigned grid,
                  cudaStream_t s) {
   const size_t sm = turbo_score_smem<D>(tp);
-  int st = set_smem(turbo_score_kernel<D, PB>, sm);
-  if (st != PKV_OK) return st;
   const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
-  turbo_score_kernel<D, PB><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected, qjl_scale,
-                                                               scores, err);
+  int st;
+  if constexpr (PB != 0) {
+    if (turbo_score_raw(tp, PB)) {
+      if ((st = set_smem(turbo_score_kernel<D, PB, true>, sm)) != PKV_OK) return st;
+      turbo_score_kernel<D, PB, true><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
+                                                                         qjl_scale, scores, err);
+      return PKV_OK;
+    }
+  }
+  if ((st = set_smem(turbo_score_kernel<D, PB, false>, sm)) != PKV_OK) return st;
+  turbo_score_kernel<D, PB, false><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
+                                                                      qjl_scale, scores, err);
   return PKV_OK;
 }
 

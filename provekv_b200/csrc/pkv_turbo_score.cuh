@@ -18,10 +18,128 @@ struct TurboScoreSmem {
   static __host__ __device__ size_t warp_bytes(int rec_words) {
     return ((sizeof(uint32_t) * rec_words * K::WS) + 15) & ~(size_t)15;
   }
-  static __host__ __device__ size_t table_bytes(int levels) { return sizeof(float) * (256 + 2 * levels + D + 64); }
+  // the per-pair table of q_a cos_k + q_b sin_k is kept for up to 128 angle levels (16 KB at d = 64)
+  static __host__ __device__ bool has_inner_table(int levels) { return levels <= 128; }
+  static __host__ __device__ size_t table_bytes(int levels) {
+    return sizeof(float) * (256 + 2 * levels + D + 64 + (has_inner_table(levels) ? (D / 2) * levels : 0));
+  }
 };
 
-template <int D, int PB>
+// One record -> score.  W(k) returns word k of the record.  FIXED: f32 radii and a compile-time angle
+// width, so every k is a compile-time constant after unrolling and W may index registers.
+template <int D, int PB, bool FIXED, typename W>
+__device__ __forceinline__ float score_record(const W& w, const TurboParams& tp, int pb, int levels,
+                                              const float* s_q255, const float* s_lut, const float* s_q,
+                                              const float* s_p, const float* s_inner, bool inner_table,
+                                              float qjl_scale, int& code) {
+  using K = Turbo<D>;
+  bool lossy = false;
+  if constexpr (!FIXED) lossy = tp.lossy;
+  // radius i: f32 word i (finite and non-negative, radius.rs:98-103: sign clear and exponent not all
+  // ones; -0.0 is looked at again below), or the BlockLogU8 byte i through expf (radius.rs:128-145)
+  uint32_t bad = 0;
+  float mn = 0.0f, span = 0.0f;
+  if (lossy) {
+    if constexpr (!FIXED) {
+      mn = __uint_as_float(w(K::P / 4));
+      const float mx = __uint_as_float(w(K::P / 4 + 1));
+      if (!pkv_finite(mn) || !pkv_finite(mx) || mn > mx) code = PKV_VEC_BAD_RADIUS_RANGE;
+      span = __fsub_rn(mx, mn);
+    }
+  }
+  auto radius = [&](int i) -> float {
+    if (!lossy) {
+      const uint32_t u = w(i);
+      bad |= (u >> 31) | (uint32_t)((u & 0x7f800000u) == 0x7f800000u);
+      return __uint_as_float(u);
+    }
+    float r = 0.0f;
+    if constexpr (!FIXED) {
+      const float t = __fadd_rn(mn, __fmul_rn(span, s_q255[(w(i >> 2) >> (8 * (i & 3))) & 0xffu]));
+      r = code ? 0.0f : pkv_expf_portable(t);
+      if (!code && !pkv_finite(r)) code = PKV_VEC_BAD_RADIUS;  // polar.rs:127-133
+    }
+    return r;
+  };
+  // polar estimate, polar.rs:355-362: estimate += r * (q_a * cos + q_b * sin)
+  const int a0 = FIXED ? K::P : tp.radii_words;  // first angle word
+  const uint32_t mask = (uint32_t)levels - 1u;
+  float est = 0.0f;
+  auto add_pair = [&](int i, uint32_t idx) {
+    float inner;
+    if (inner_table) {
+      inner = s_inner[i * levels + idx];
+    } else {
+      const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
+      const float2 q = *reinterpret_cast<const float2*>(s_q + 2 * i);
+      inner = __fadd_rn(__fmul_rn(q.x, cs.x), __fmul_rn(q.y, cs.y));
+    }
+    est = __fadd_rn(est, __fmul_rn(radius(i), inner));
+  };
+  if constexpr (PB != 0) {
+    constexpr int NW = K::P * PB / 32;
+    uint32_t words[NW];
+#pragma unroll
+    for (int k = 0; k < NW; k++) words[k] = w(a0 + k);
+#pragma unroll
+    for (int i = 0; i < K::P; i++) {
+      const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
+      uint32_t idx = words[wi] >> sh;
+      if (sh + PB > 32) idx |= words[wi + 1] << (32 - sh);
+      add_pair(i, idx & mask);
+    }
+  } else {
+    uint64_t bitbuf = 0;
+    int nbits = 0, wk = 0;
+#pragma unroll
+    for (int i = 0; i < K::P; i++) {
+      if (nbits < pb) {
+        bitbuf |= (uint64_t)w(a0 + wk) << nbits;
+        wk++;
+        nbits += 32;
+      }
+      const uint32_t idx = (uint32_t)bitbuf & mask;
+      bitbuf >>= pb;
+      nbits -= pb;
+      add_pair(i, idx);
+    }
+  }
+  if (bad) {  // a set sign bit or an all-ones exponent: decide exactly (-0.0 passes `value < 0.0`)
+#pragma unroll
+    for (int i = 0; i < K::P; i++) {
+      const float r = __uint_as_float(w(i));
+      if (!code && (!pkv_finite(r) || r < 0.0f)) code = PKV_VEC_BAD_RADIUS;
+    }
+  }
+  if (!code && !pkv_finite(est)) code = PKV_VEC_NONFINITE_OUTPUT;  // "polar score is not finite"
+  float score = est;
+  if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
+    // qjl.rs:316-330: sum of sign_j * p_j in order, then the scale
+    const int s0 = FIXED ? K::P + K::P * (PB ? PB : 1) / 32 : a0 + tp.angle_words;
+    float sum = 0.0f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {  // projections is 32 or 64
+      if (h * 32 < tp.projections) {
+        const uint32_t flip = ~w(s0 + h);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 p4 = *reinterpret_cast<const float4*>(s_p + h * 32 + j);
+          const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+          for (int t = 0; t < 4; t++)  // sign as f32 * p is exactly +-p
+            sum = __fadd_rn(sum, __uint_as_float(__float_as_uint(pv[t]) ^ (((flip >> (j + t)) & 1u) << 31)));
+        }
+      }
+    }
+    const float corr = __fmul_rn(qjl_scale, sum);
+    if (!code && !pkv_finite(corr)) code = PKV_VEC_NONFINITE_OUTPUT;  // "qjl score is not finite"
+    score = __fadd_rn(est, corr);
+    if (!code && !pkv_finite(score)) code = PKV_VEC_NONFINITE_OUTPUT;  // "turbo score is not finite"
+  }
+  return score;
+}
+
+template <int D, int PB, bool RAW>
 __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                    const float* __restrict__ rotated_query, const float* __restrict__ projected_query,
@@ -35,6 +153,8 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
   float* s_lut = s_q255 + 256;                     // (cos, sin)[L]
   float* s_q = s_lut + 2 * levels;                 // [D] rotated query
   float* s_p = s_q + D;                            // [64] projected query
+  float* s_inner = s_p + 64;                       // [P][L]: q_a cos_k + q_b sin_k, the same for every record
+  const bool inner_table = TurboScoreSmem<D>::has_inner_table(levels);
   uint32_t* s_w = reinterpret_cast<uint32_t*>(smem + TurboScoreSmem<D>::table_bytes(levels) +
                                               warp * TurboScoreSmem<D>::warp_bytes(tp.rec_words));
 
@@ -46,10 +166,19 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
   const int nv = active ? min(K::TV, g.vpb - v0) : 0;
   const int v = lane;
 
-  stage_records<D, true>(
-      s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(
-               payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes)),
-      nv, tp.rec_words, lane);
+  // f32 radii in records that are a multiple of 16 bytes (fixed angle width): the warp's run of records
+  // is copied as it lies, 16 bytes per copy, and every lane reads its own record with 16-byte loads
+  // (conflict-free: consecutive records start an odd number of 16-byte units apart or the quarter-warps
+  // cover distinct bank groups); otherwise the word-transposed tile of the decode kernel.
+  constexpr bool raw = RAW;  // the launcher checks: PB != 0, f32 radii, rec_words % 4 == 0
+  const uint8_t* src = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes;
+  if constexpr (raw) {
+    const int n16 = nv * (tp.rec_words / 4);
+    for (int i = lane; i < n16; i += 32)
+      pkv_cp_async16(reinterpret_cast<uint4*>(s_w) + i, reinterpret_cast<const uint4*>(src) + i);
+  } else {
+    stage_records<D, true>(s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(src)), nv, tp.rec_words, lane);
+  }
   for (int i = threadIdx.x; i < 2 * levels; i += K::THREADS)
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : 2 * (i - levels) + 1), tp.lut + i);
   for (int i = threadIdx.x; i < D; i += K::THREADS) pkv_cp_async4(s_q + i, rotated_query + i);
@@ -58,72 +187,34 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
     for (int i = threadIdx.x; i < 256; i += K::THREADS) s_q255[i] = __fdiv_rn((float)i, 255.0f);
   pkv_cp_async_wait_all();
   __syncthreads();
+  if (inner_table) {  // polar.rs:361: (q_a * theta.cos() + q_b * theta.sin()), the record-independent part
+    for (int e = threadIdx.x; e < K::P * levels; e += K::THREADS) {
+      const int i = e / levels, k = e - i * levels;
+      s_inner[e] = __fadd_rn(__fmul_rn(s_q[2 * i], s_lut[2 * k]), __fmul_rn(s_q[2 * i + 1], s_lut[2 * k + 1]));
+    }
+    __syncthreads();
+  }
 
   if (v >= nv) return;
-  const uint32_t* w = s_w + v;
   int code = 0;
-  float rad[K::P];
-  if (!tp.lossy) {
+  float score;
+  if constexpr (raw) {
+    // the record in registers: RW words loaded 16 bytes at a time from this lane's run of the raw tile
+    constexpr int NWT = K::P * (PB ? PB : 1) / 32 + 2;  // angle words + up to two sign words
+    constexpr int RW = (K::P + NWT + 3) & ~3;
+    uint32_t rw[RW];
+    const uint4* w4 = reinterpret_cast<const uint4*>(s_w + v * tp.rec_words);
 #pragma unroll
-    for (int i = 0; i < K::P; i++) {
-      rad[i] = __uint_as_float(w[i * K::WS]);
-      if (!code && (!pkv_finite(rad[i]) || rad[i] < 0.0f)) code = PKV_VEC_BAD_RADIUS;  // radius.rs:98-103
+    for (int k = 0; k < RW / 4; k++) {
+      const uint4 u = 4 * k < tp.rec_words ? w4[k] : make_uint4(0u, 0u, 0u, 0u);
+      rw[4 * k] = u.x; rw[4 * k + 1] = u.y; rw[4 * k + 2] = u.z; rw[4 * k + 3] = u.w;
     }
+    score = score_record<D, PB, true>([&](int k) { return rw[k]; }, tp, pb, levels, s_q255, s_lut, s_q, s_p, s_inner,
+                                inner_table, qjl_scale, code);
   } else {
-    const float mn = __uint_as_float(w[(K::P / 4) * K::WS]);
-    const float mx = __uint_as_float(w[(K::P / 4 + 1) * K::WS]);
-    if (!pkv_finite(mn) || !pkv_finite(mx) || mn > mx) code = PKV_VEC_BAD_RADIUS_RANGE;
-    const float span = __fsub_rn(mx, mn);
-#pragma unroll
-    for (int k = 0; k < K::P / 4; k++) {
-      const uint32_t q4 = w[k * K::WS];
-#pragma unroll
-      for (int b = 0; b < 4; b++) {
-        const float t = __fadd_rn(mn, __fmul_rn(span, s_q255[(q4 >> (8 * b)) & 0xffu]));
-        const float r = code ? 0.0f : pkv_expf_portable(t);
-        if (!code && !pkv_finite(r)) code = PKV_VEC_BAD_RADIUS;  // polar.rs:127-133
-        rad[4 * k + b] = r;
-      }
-    }
-  }
-  // polar estimate, polar.rs:355-362: estimate += r * (q_a * cos + q_b * sin)
-  const uint32_t* aw = w + tp.radii_words * K::WS;
-  const uint32_t mask = (uint32_t)levels - 1u;
-  float est = 0.0f;
-  {
-    uint64_t bitbuf = 0;
-    int nbits = 0, wk = 0;
-#pragma unroll
-    for (int i = 0; i < K::P; i++) {
-      if (nbits < pb) {
-        bitbuf |= (uint64_t)aw[wk * K::WS] << nbits;
-        wk++;
-        nbits += 32;
-      }
-      const uint32_t idx = (uint32_t)bitbuf & mask;
-      bitbuf >>= pb;
-      nbits -= pb;
-      const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
-      const float2 q = *reinterpret_cast<const float2*>(s_q + 2 * i);
-      const float inner = __fadd_rn(__fmul_rn(q.x, cs.x), __fmul_rn(q.y, cs.y));
-      est = __fadd_rn(est, __fmul_rn(rad[i], inner));
-    }
-  }
-  if (!code && !pkv_finite(est)) code = PKV_VEC_NONFINITE_OUTPUT;  // "polar score is not finite"
-  float score = est;
-  if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
-    // qjl.rs:316-330: sum of sign_j * p_j in order, then the scale
-    const uint32_t* sw = aw + tp.angle_words * K::WS;
-    float sum = 0.0f;
-    for (int j = 0; j < tp.projections; j++) {
-      const uint32_t bit = (sw[(j >> 5) * K::WS] >> (j & 31)) & 1u;
-      const float p = s_p[j];
-      sum = __fadd_rn(sum, bit ? p : -p);
-    }
-    const float corr = __fmul_rn(qjl_scale, sum);
-    if (!code && !pkv_finite(corr)) code = PKV_VEC_NONFINITE_OUTPUT;  // "qjl score is not finite"
-    score = __fadd_rn(est, corr);
-    if (!code && !pkv_finite(score)) code = PKV_VEC_NONFINITE_OUTPUT;  // "turbo score is not finite"
+    const uint32_t* w = s_w + v;
+    score = score_record<D, PB, false>([&](int k) { return w[k * K::WS]; }, tp, pb, levels, s_q255, s_lut, s_q, s_p,
+                                s_inner, inner_table, qjl_scale, code);
   }
   const int64_t gvec = (int64_t)batch * g.vpb + v0 + v;
   if (code) pkv_report(err, 0, gvec, code);
@@ -136,4 +227,10 @@ size_t turbo_score_smem(const TurboParams& tp) {
          Turbo<D>::NWARPS * TurboScoreSmem<D>::warp_bytes(tp.rec_words);
 }
 
+}  // namespace pkv_turbo
+
+namespace pkv_turbo {
+inline bool turbo_score_raw(const TurboParams& tp, int pb_template) {
+  return pb_template != 0 && !tp.lossy && (tp.rec_words % 4) == 0;
+}
 }  // namespace pkv_turbo
