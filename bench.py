@@ -313,6 +313,31 @@ def run_ours(args, w):
     dec_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in events]))
     step_ms = float(np.mean([e[0].elapsed_time(e[2]) for e in events]))
 
+    # compressed-domain scoring of one query against the records just written (turbo only); outside
+    # the timed region of the metric, reported beside it
+    score = None
+    if kind == "turbo":
+        rq, pq = prof.prepare_query(np.random.default_rng(SEED).standard_normal(d).astype(np.float32))
+        rq_dev = torch.from_numpy(rq).to(dev)
+        pq_dev = torch.from_numpy(pq if pq.size else np.zeros(1, np.float32)).to(dev)
+        scores = torch.empty(n_vec, dtype=torch.float32, device=dev)
+        sev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(10)]
+        for i in range(13):
+            if not big:
+                flush.zero_()
+            if i >= 3:
+                sev[i - 3][0].record()
+            prof.score_dev(payload.data_ptr(), pstride, n_batches, vpb, rq_dev.data_ptr(), pq_dev.data_ptr(),
+                           scores.data_ptr(), err[1:].data_ptr(), stream)
+            if i >= 3:
+                sev[i - 3][1].record()
+        torch.cuda.synchronize()
+        assert int(err[1]) == -1, "the score kernel reported a record"
+        score_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in sev]))
+        score = {"ms": score_ms, "records_per_s": n_vec / (score_ms * 1e-3),
+                 "achieved_gbs": n_vec * (rec + 4) / (score_ms * 1e-3) / 1e9,
+                 "api": "pkv_turbo_score_dev, one query against every record"}
+
     # end to end through the host-buffer C ABI: pinned host f32 -> TQB1 blobs -> pinned host f32
     blob = (L.FB2_HEADER_BYTES if kind == "fib" else L.TQB1_HEADER_BYTES) + vpb * rec
     x_host = torch.empty((n_batches, vpb, d), dtype=torch.float32).pin_memory()
@@ -376,6 +401,9 @@ def run_ours(args, w):
             "clocks": clocks.summary(),
             "wall_ms_timed_region": t_wall * 1e3,
         }
+        if score is not None:
+            score["frac_of_peak"] = score["achieved_gbs"] / peak
+            line["score"] = score
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             gbs, t, sample = cpu_codec_rate(w, 8.0, cores)
