@@ -72,10 +72,18 @@ template <int D, int PB, int DST>
 int launch_decode_as(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g, void* cache,
                      uint64_t* err, unsigned grid, cudaStream_t s) {
   const size_t sm = turbo_decode_smem<D>(tp);
-  int st = set_smem(turbo_decode_patch_kernel<D, PB, DST>, sm);
-  if (st != PKV_OK) return st;
   const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
-  turbo_decode_patch_kernel<D, PB, DST><<<ctas, Turbo<D>::THREADS, sm, s>>>(
+  int st;
+  if constexpr (PB != 0) {
+    if (turbo_decode_raw(tp, PB)) {
+      if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, true>, sm)) != PKV_OK) return st;
+      turbo_decode_patch_kernel<D, PB, DST, true><<<ctas, Turbo<D>::THREADS, sm, s>>>(
+          g, tp, payload, static_cast<typename PkvDst<DST>::type*>(cache), err);
+      return PKV_OK;
+    }
+  }
+  if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, false>, sm)) != PKV_OK) return st;
+  turbo_decode_patch_kernel<D, PB, DST, false><<<ctas, Turbo<D>::THREADS, sm, s>>>(
       g, tp, payload, static_cast<typename PkvDst<DST>::type*>(cache), err);
   return PKV_OK;
 }

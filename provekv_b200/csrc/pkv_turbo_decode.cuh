@@ -19,7 +19,11 @@ struct TurboDecSmem {  // per-warp slices follow the CTA-wide tables
   static __host__ __device__ size_t table_bytes(int levels) { return sizeof(float) * (256 + 2 * levels); }
 };
 
-template <int D, int PB, int DST>
+// RAW (f32 radii, fixed angle width, records a multiple of 16 bytes): the warp's run of records is
+// copied as it lies with 16-byte copies and every lane reads its own record with 16-byte loads
+// (consecutive 144-byte records start 9 sixteen-byte units apart: the lanes of a quarter-warp hit
+// distinct bank groups); otherwise the records go through a word-transposed tile, 4 bytes per copy.
+template <int D, int PB, int DST, bool RAW>
 __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                           typename PkvDst<DST>::type* __restrict__ cache, uint64_t* err) {
@@ -43,10 +47,14 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   const int nv = active ? min(K::TV, g.vpb - v0) : 0;
   const int v = lane;
 
-  stage_records<D, true>(
-      s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(
-               payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes)),
-      nv, tp.rec_words, lane);
+  const uint8_t* src = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes;
+  if constexpr (RAW) {
+    const int n16 = nv * (tp.rec_words / 4);
+    for (int i = lane; i < n16; i += 32)
+      pkv_cp_async16(reinterpret_cast<uint4*>(s_w) + i, reinterpret_cast<const uint4*>(src) + i);
+  } else {
+    stage_records<D, true>(s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(src)), nv, tp.rec_words, lane);
+  }
   for (int i = threadIdx.x; i < 2 * levels; i += K::THREADS)  // interleaved: one 8-byte read per pair
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : 2 * (i - levels) + 1), tp.lut + i);
   if (tp.lossy)  // `*value as f32 / u8::MAX as f32`, radius.rs:143
@@ -57,34 +65,49 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
 
   float y[D];
   if (v < nv) {
-    const uint32_t* w = s_w + v;
+    // word k of this lane's record (k is a compile-time constant wherever RAW is used)
+    constexpr int RW = RAW ? ((K::P + K::P * (PB ? PB : 1) / 32 + 3) & ~3) : 4;
+    uint32_t rw[RW];
+    if constexpr (RAW) {
+      const uint4* w4 = reinterpret_cast<const uint4*>(s_w + v * tp.rec_words);
+#pragma unroll
+      for (int k = 0; k < RW / 4; k++) {
+        const uint4 u = w4[k];  // the last piece may reach into the sign words, which decode ignores
+        rw[4 * k] = u.x; rw[4 * k + 1] = u.y; rw[4 * k + 2] = u.z; rw[4 * k + 3] = u.w;
+      }
+    }
+    const uint32_t* wt = s_w + v;
+    auto w = [&](int k) -> uint32_t {
+      if constexpr (RAW) return rw[k];
+      else return wt[k * K::WS];
+    };
     int code = 0;
     // radii -> y[2i] (temporarily)
     if (!tp.lossy) {
       uint32_t bad = 0;
 #pragma unroll
       for (int i = 0; i < K::P; i++) {
-        const uint32_t u = w[i * K::WS];
+        const uint32_t u = w(i);
         // finite and non-negative (radius.rs:98-103): sign clear and exponent not all ones
         bad |= (u >> 31) | (uint32_t)((u & 0x7f800000u) == 0x7f800000u);
         y[2 * i] = __uint_as_float(u);
       }
       // -0.0 has the sign bit set but passes `value < 0.0`; re-check exactly when flagged
       if (bad) {
-#pragma unroll 4
+#pragma unroll
         for (int i = 0; i < K::P; i++) {
-          const float r = __uint_as_float(w[i * K::WS]);
+          const float r = __uint_as_float(w(i));
           if (!code && (!pkv_finite(r) || r < 0.0f)) code = PKV_VEC_BAD_RADIUS;
         }
       }
     } else {
-      const float mn = __uint_as_float(w[(K::P / 4) * K::WS]);
-      const float mx = __uint_as_float(w[(K::P / 4 + 1) * K::WS]);
+      const float mn = __uint_as_float(wt[(K::P / 4) * K::WS]);
+      const float mx = __uint_as_float(wt[(K::P / 4 + 1) * K::WS]);
       if (!pkv_finite(mn) || !pkv_finite(mx) || mn > mx) code = PKV_VEC_BAD_RADIUS_RANGE;
       const float span = __fsub_rn(mx, mn);
 #pragma unroll
       for (int k = 0; k < K::P / 4; k++) {
-        const uint32_t q4 = w[k * K::WS];
+        const uint32_t q4 = wt[k * K::WS];
 #pragma unroll
         for (int b = 0; b < 4; b++) {
           const float t = __fadd_rn(mn, __fmul_rn(span, s_q255[(q4 >> (8 * b)) & 0xffu]));
@@ -95,13 +118,13 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
       }
     }
     // angle indices (LSB-first stream, bitpack.rs:135-153) and the polar -> cartesian step
-    const uint32_t* aw = w + tp.radii_words * K::WS;
+    const uint32_t* aw = wt + tp.radii_words * K::WS;
     const uint32_t mask = (uint32_t)levels - 1u;
     if constexpr (PB != 0) {
       constexpr int NW = K::P * PB / 32;
       uint32_t words[NW];
 #pragma unroll
-      for (int k = 0; k < NW; k++) words[k] = aw[k * K::WS];
+      for (int k = 0; k < NW; k++) words[k] = RAW ? w(K::P + k) : aw[k * K::WS];
 #pragma unroll
       for (int i = 0; i < K::P; i++) {
         const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
@@ -178,6 +201,10 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
       }
     }
   }
+}
+
+inline bool turbo_decode_raw(const TurboParams& tp, int pb_template) {
+  return pb_template != 0 && !tp.lossy && (tp.rec_words % 4) == 0;
 }
 
 template <int D>
