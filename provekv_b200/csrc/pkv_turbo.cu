@@ -75,15 +75,22 @@ int launch_decode_as(const TurboParams& tp, const uint8_t* payload, const PkvGeo
   const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
   int st;
   if constexpr (PB != 0) {
-    if (turbo_decode_raw(tp, PB)) {
-      if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, true>, sm)) != PKV_OK) return st;
-      turbo_decode_patch_kernel<D, PB, DST, true><<<ctas, Turbo<D>::THREADS, sm, s>>>(
+    const int raw = turbo_decode_raw(tp, PB);
+    if (raw == 1) {
+      if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, 1>, sm)) != PKV_OK) return st;
+      turbo_decode_patch_kernel<D, PB, DST, 1><<<ctas, Turbo<D>::THREADS, sm, s>>>(
+          g, tp, payload, static_cast<typename PkvDst<DST>::type*>(cache), err);
+      return PKV_OK;
+    }
+    if (raw == 2) {
+      if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, 2>, sm)) != PKV_OK) return st;
+      turbo_decode_patch_kernel<D, PB, DST, 2><<<ctas, Turbo<D>::THREADS, sm, s>>>(
           g, tp, payload, static_cast<typename PkvDst<DST>::type*>(cache), err);
       return PKV_OK;
     }
   }
-  if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, false>, sm)) != PKV_OK) return st;
-  turbo_decode_patch_kernel<D, PB, DST, false><<<ctas, Turbo<D>::THREADS, sm, s>>>(
+  if ((st = set_smem(turbo_decode_patch_kernel<D, PB, DST, 0>, sm)) != PKV_OK) return st;
+  turbo_decode_patch_kernel<D, PB, DST, 0><<<ctas, Turbo<D>::THREADS, sm, s>>>(
       g, tp, payload, static_cast<typename PkvDst<DST>::type*>(cache), err);
   return PKV_OK;
 }
@@ -107,16 +114,23 @@ int launch_score(const TurboParams& tp, const uint8_t* payload, const PkvGeom& g
   const unsigned ctas = (grid + Turbo<D>::NWARPS - 1) / Turbo<D>::NWARPS;
   int st;
   if constexpr (PB != 0) {
-    if (turbo_score_raw(tp, PB)) {
-      if ((st = set_smem(turbo_score_kernel<D, PB, true>, sm)) != PKV_OK) return st;
-      turbo_score_kernel<D, PB, true><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
-                                                                         qjl_scale, scores, err);
+    const int raw = turbo_score_raw(tp, PB);
+    if (raw == 1) {
+      if ((st = set_smem(turbo_score_kernel<D, PB, 1>, sm)) != PKV_OK) return st;
+      turbo_score_kernel<D, PB, 1><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
+                                                                      qjl_scale, scores, err);
+      return PKV_OK;
+    }
+    if (raw == 2) {
+      if ((st = set_smem(turbo_score_kernel<D, PB, 2>, sm)) != PKV_OK) return st;
+      turbo_score_kernel<D, PB, 2><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
+                                                                      qjl_scale, scores, err);
       return PKV_OK;
     }
   }
-  if ((st = set_smem(turbo_score_kernel<D, PB, false>, sm)) != PKV_OK) return st;
-  turbo_score_kernel<D, PB, false><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
-                                                                      qjl_scale, scores, err);
+  if ((st = set_smem(turbo_score_kernel<D, PB, 0>, sm)) != PKV_OK) return st;
+  turbo_score_kernel<D, PB, 0><<<ctas, Turbo<D>::THREADS, sm, s>>>(g, tp, payload, rotated, projected,
+                                                                  qjl_scale, scores, err);
   return PKV_OK;
 }
 

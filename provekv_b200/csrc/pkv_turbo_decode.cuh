@@ -19,11 +19,13 @@ struct TurboDecSmem {  // per-warp slices follow the CTA-wide tables
   static __host__ __device__ size_t table_bytes(int levels) { return sizeof(float) * (256 + 2 * levels); }
 };
 
-// RAW (f32 radii, fixed angle width, records a multiple of 16 bytes): the warp's run of records is
-// copied as it lies with 16-byte copies and every lane reads its own record with 16-byte loads
-// (consecutive 144-byte records start 9 sixteen-byte units apart: the lanes of a quarter-warp hit
-// distinct bank groups); otherwise the records go through a word-transposed tile, 4 bytes per copy.
-template <int D, int PB, int DST, bool RAW>
+// RAW != 0 (f32 radii, fixed angle width): the warp's run of records is copied as it lies with 16-byte
+// copies.  RAW == 1 (records a multiple of 16 bytes): every lane reads its own record with 16-byte
+// loads into registers (consecutive 144-byte records start 9 sixteen-byte units apart: the lanes of a
+// quarter-warp hit distinct bank groups).  RAW == 2 (an odd number of words per record, e.g. 71): the
+// lane reads its words one by one, conflict-free because the record stride is odd.  RAW == 0: the
+// records go through a word-transposed tile, 4 bytes per copy.
+template <int D, int PB, int DST, int RAW>
 __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                           typename PkvDst<DST>::type* __restrict__ cache, uint64_t* err) {
@@ -48,10 +50,11 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   const int v = lane;
 
   const uint8_t* src = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes;
-  if constexpr (RAW) {
-    const int n16 = nv * (tp.rec_words / 4);
+  if constexpr (RAW != 0) {
+    const int nw = nv * tp.rec_words, n16 = nw / 4;  // a full tile of 32 records is a multiple of 16 bytes
     for (int i = lane; i < n16; i += 32)
       pkv_cp_async16(reinterpret_cast<uint4*>(s_w) + i, reinterpret_cast<const uint4*>(src) + i);
+    for (int i = 4 * n16 + lane; i < nw; i += 32) pkv_cp_async4(s_w + i, reinterpret_cast<const uint32_t*>(src) + i);
   } else {
     stage_records<D, true>(s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(src)), nv, tp.rec_words, lane);
   }
@@ -66,9 +69,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   float y[D];
   if (v < nv) {
     // word k of this lane's record (k is a compile-time constant wherever RAW is used)
-    constexpr int RW = RAW ? ((K::P + K::P * (PB ? PB : 1) / 32 + 3) & ~3) : 4;
+    constexpr int RW = RAW == 1 ? ((K::P + K::P * (PB ? PB : 1) / 32 + 3) & ~3) : 4;
     uint32_t rw[RW];
-    if constexpr (RAW) {
+    if constexpr (RAW == 1) {
       const uint4* w4 = reinterpret_cast<const uint4*>(s_w + v * tp.rec_words);
 #pragma unroll
       for (int k = 0; k < RW / 4; k++) {
@@ -77,8 +80,10 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
       }
     }
     const uint32_t* wt = s_w + v;
+    const uint32_t* wr = s_w + v * tp.rec_words;
     auto w = [&](int k) -> uint32_t {
-      if constexpr (RAW) return rw[k];
+      if constexpr (RAW == 1) return rw[k];
+      else if constexpr (RAW == 2) return wr[k];
       else return wt[k * K::WS];
     };
     int code = 0;
@@ -124,7 +129,7 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
       constexpr int NW = K::P * PB / 32;
       uint32_t words[NW];
 #pragma unroll
-      for (int k = 0; k < NW; k++) words[k] = RAW ? w(K::P + k) : aw[k * K::WS];
+      for (int k = 0; k < NW; k++) words[k] = RAW != 0 ? w(K::P + k) : aw[k * K::WS];
 #pragma unroll
       for (int i = 0; i < K::P; i++) {
         const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
@@ -203,8 +208,9 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   }
 }
 
-inline bool turbo_decode_raw(const TurboParams& tp, int pb_template) {
-  return pb_template != 0 && !tp.lossy && (tp.rec_words % 4) == 0;
+inline int turbo_decode_raw(const TurboParams& tp, int pb_template) {
+  if (pb_template == 0 || tp.lossy) return 0;
+  return (tp.rec_words % 4) == 0 ? 1 : (tp.rec_words & 1) ? 2 : 0;
 }
 
 template <int D>

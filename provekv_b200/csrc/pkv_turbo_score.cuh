@@ -139,7 +139,7 @@ __device__ __forceinline__ float score_record(const W& w, const TurboParams& tp,
   return score;
 }
 
-template <int D, int PB, bool RAW>
+template <int D, int PB, int RAW>
 __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                    const float* __restrict__ rotated_query, const float* __restrict__ projected_query,
@@ -170,12 +170,14 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
   // is copied as it lies, 16 bytes per copy, and every lane reads its own record with 16-byte loads
   // (conflict-free: consecutive records start an odd number of 16-byte units apart or the quarter-warps
   // cover distinct bank groups); otherwise the word-transposed tile of the decode kernel.
-  constexpr bool raw = RAW;  // the launcher checks: PB != 0, f32 radii, rec_words % 4 == 0
+  // the launcher checks: PB != 0, f32 radii; RAW 1: rec_words % 4 == 0 (register loads), 2: rec_words odd
+  constexpr int raw = RAW;
   const uint8_t* src = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes;
-  if constexpr (raw) {
-    const int n16 = nv * (tp.rec_words / 4);
+  if constexpr (raw != 0) {
+    const int nw = nv * tp.rec_words, n16 = nw / 4;  // a full tile of 32 records is a multiple of 16 bytes
     for (int i = lane; i < n16; i += 32)
       pkv_cp_async16(reinterpret_cast<uint4*>(s_w) + i, reinterpret_cast<const uint4*>(src) + i);
+    for (int i = 4 * n16 + lane; i < nw; i += 32) pkv_cp_async4(s_w + i, reinterpret_cast<const uint32_t*>(src) + i);
   } else {
     stage_records<D, true>(s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(src)), nv, tp.rec_words, lane);
   }
@@ -198,7 +200,11 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
   if (v >= nv) return;
   int code = 0;
   float score;
-  if constexpr (raw) {
+  if constexpr (raw == 2) {  // odd record stride: word reads of the raw tile are conflict-free
+    const uint32_t* wr = s_w + v * tp.rec_words;
+    score = score_record<D, PB, true>([&](int k) { return wr[k]; }, tp, pb, levels, s_q255, s_lut, s_q, s_p,
+                                      s_inner, inner_table, qjl_scale, code);
+  } else if constexpr (raw == 1) {
     // the record in registers: RW words loaded 16 bytes at a time from this lane's run of the raw tile
     constexpr int NWT = K::P * (PB ? PB : 1) / 32 + 2;  // angle words + up to two sign words
     constexpr int RW = (K::P + NWT + 3) & ~3;
@@ -230,7 +236,8 @@ size_t turbo_score_smem(const TurboParams& tp) {
 }  // namespace pkv_turbo
 
 namespace pkv_turbo {
-inline bool turbo_score_raw(const TurboParams& tp, int pb_template) {
-  return pb_template != 0 && !tp.lossy && (tp.rec_words % 4) == 0;
+inline int turbo_score_raw(const TurboParams& tp, int pb_template) {
+  if (pb_template == 0 || tp.lossy) return 0;
+  return (tp.rec_words % 4) == 0 ? 1 : (tp.rec_words & 1) ? 2 : 0;
 }
 }  // namespace pkv_turbo
