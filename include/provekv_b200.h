@@ -58,8 +58,9 @@ enum {
   PKV_VEC_NONFINITE_OUTPUT = 23,  /* fib-quant/src/codec.rs:840 */
   PKV_VEC_NONFINITE_RESIDUAL = 24,/* turbo-quant/src/qjl.rs:210 */
   PKV_VEC_NORM_RANGE = 25,        /* fib-quant/src/codec.rs:1003 (second pass of encode_batch) */
-  PKV_VEC_DEVICE_WAIT = 26,
-  PKV_VEC_MISALIGNED_DST = 27        /* no counterpart: a bounded wait inside a kernel ran out (the payload is not valid) */
+  PKV_VEC_DEVICE_WAIT = 26,       /* no counterpart: a bounded wait inside a kernel ran out (the payload is not valid) */
+  PKV_VEC_MISALIGNED_DST = 27     /* no counterpart: a per-tensor cache offset of a *_multi call is negative or not
+                                     a multiple of 16 bytes (that batch is skipped) */
 };
 
 const char* pkv_status_string(int status);
@@ -148,15 +149,40 @@ int pkv_memcpy_h2d(void* dst_dev, const void* src_host, int64_t bytes, void* str
 int pkv_memcpy_d2h(void* dst_host, const void* src_dev, int64_t bytes, void* stream);
 int pkv_stream_synchronize(void* stream);
 
+/* Wire blobs on the host <-> a device payload buffer, headers skipped: blob b lies at
+ * blobs_host + b * blob_bytes with its records after header_bytes (PKV_FB2_HEADER_BYTES /
+ * PKV_TQB1_HEADER_BYTES; fib-quant/src/codec.rs:195-220, turbo-quant/src/wire.rs:276-290), batch b of
+ * the payload at payload_dev + b * payload_batch_stride.  One strided asynchronous copy on `stream`;
+ * pinned host memory keeps it asynchronous.  The download leaves the header bytes of each blob
+ * untouched (write them with pkv_fb2_header_write / pkv_tqb1_header_write). */
+int pkv_payload_upload(const uint8_t* blobs_host, int64_t blob_bytes, int32_t header_bytes, int64_t n_batches,
+                       int64_t record_bytes_per_batch, uint8_t* payload_dev, int64_t payload_batch_stride,
+                       void* stream);
+int pkv_payload_download(const uint8_t* payload_dev, int64_t payload_batch_stride, int64_t n_batches,
+                         int64_t record_bytes_per_batch, uint8_t* blobs_host, int64_t blob_bytes,
+                         int32_t header_bytes, void* stream);
+
 /* The device error word: 0xFFFF...F = no error; otherwise the smallest
- * (pass << 56 | vector_index << 8 | code) any thread reported.  Reset before a
- * launch, read (synchronising the stream) after it. */
+ * (pass << 56 | vector_index << 8 | code) any thread reported, vector_index counted over the
+ * whole launch.  Within one batch this is the error the reference's loops reach first (fib
+ * encode checks every vector for finiteness / zero norm in a first pass and the norm range in a
+ * second, fib-quant/src/codec.rs:593-608,695-708).  Across the batches of one launch the order
+ * is by pass, then by vector: a first-pass error of a later batch is reported in preference to a
+ * second-pass error of an earlier one (the reference issues one call per batch from a parallel
+ * loop and reports whichever batch fails).  Reset before a launch, read (synchronising the
+ * stream) after it. */
 int pkv_error_word_reset(uint64_t* err_dev, void* stream);
 int pkv_error_word_read(const uint64_t* err_dev, void* stream, int32_t* code, int64_t* vector_index);
 
 /* ---- fib-quant --------------------------------------------------------- */
 /* rotation: dim x dim f64 row-major (StoredRotation.matrix, fib-quant/src/rotation.rs:51-56);
- * codebook: codebook_size x block_dim f32 row-major (fib-quant/src/codebook.rs:28-29). */
+ * codebook: codebook_size x block_dim f32 row-major (fib-quant/src/codebook.rs:28-29).
+ * A profile (fib or turbo) belongs to the CUDA device that is current when it is created: its
+ * tables are uploaded there, and every call that takes the profile returns
+ * PKV_ERR_INVALID_ARGUMENT, before launching or copying anything, when another device is
+ * current.  The shortcut encoders' error bounds assume an orthonormal rotation; the matrix is
+ * checked here (rows of unit length, M M^T = I to 1e-6) and a profile whose matrix fails the check
+ * encodes with the exact f64 kernel only. */
 int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, const float* codebook,
                            pkv_fib_profile** out);
 int pkv_fib_profile_destroy(pkv_fib_profile* p);
@@ -175,7 +201,8 @@ int pkv_fib_encode_dev(const pkv_fib_profile* p, const float* x_dev, const pkv_l
  * from the stream's memory pool, this call keeps it in a fixed array inside the library image
  * and calls no allocating routine.  Limits: at most PKV_FIB_STATIC_MAX_VECTORS vectors per call
  * (PKV_ERR_STATIC_SCRATCH_TOO_SMALL beyond), batches of at least 4 vectors (PKV_ERR_UNSUPPORTED
- * below, unless the profile forces batch numerics).  The array (4 MiB on every GPU that loads the
+ * below, unless the profile forces batch numerics; also for a profile whose matrix is not
+ * orthonormal, which only the exact kernel encodes).  The array (4 MiB on every GPU that loads the
  * library) is shared by all calls on a device: calls that can overlap on the GPU race.  The first
  * call on each device looks the array's address up; make that call before any stream capture. */
 #define PKV_FIB_STATIC_MAX_VECTORS (1 << 20)
@@ -303,6 +330,13 @@ int pkv_tqb1_header_parse(const pkv_turbo_profile* p, const uint8_t* bytes, int6
 
 /* Number of kernel launches this process has issued through the library. */
 int64_t pkv_launch_count(void);
+
+/* Test hook, no counterpart in the reference.  While switched on, the encoders that use the tensor
+ * cores (turbo with QJL, fib d = 64) do not issue their products, so the bounded wait on the
+ * completion barrier runs out after a few hundred polls: the launch reports PKV_VEC_DEVICE_WAIT
+ * through the error word, releases its tensor memory and returns, with nothing outstanding on the
+ * GPU.  The payload of such a launch is not valid.  Process-wide; switch it off again after use. */
+int pkv_test_skip_tensor_issue(int on);
 
 #ifdef __cplusplus
 }

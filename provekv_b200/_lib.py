@@ -121,6 +121,8 @@ _SIGS = {
     "pkv_memcpy_h2d": (C.c_int, [_V, _V, C.c_int64, _V]),
     "pkv_memcpy_d2h": (C.c_int, [_V, _V, C.c_int64, _V]),
     "pkv_stream_synchronize": (C.c_int, [_V]),
+    "pkv_payload_upload": (C.c_int, [_V, C.c_int64, C.c_int32, C.c_int64, C.c_int64, _V, C.c_int64, _V]),
+    "pkv_payload_download": (C.c_int, [_V, C.c_int64, C.c_int64, C.c_int64, _V, C.c_int64, C.c_int32, _V]),
     "pkv_error_word_reset": (C.c_int, [_V, _V]),
     "pkv_error_word_read": (C.c_int, [_V, _V, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_fib_profile_create": (C.c_int, [C.POINTER(FibConfigC), _V, _V, C.POINTER(_V)]),
@@ -152,6 +154,7 @@ _SIGS = {
     "pkv_tqb1_header_write": (C.c_int, [_V, C.c_uint32, _V]),
     "pkv_tqb1_header_parse": (C.c_int, [_V, _V, C.c_int64, C.POINTER(C.c_uint32)]),
     "pkv_launch_count": (C.c_int64, []),
+    "pkv_test_skip_tensor_issue": (C.c_int, [C.c_int]),
     "pkv_fib_encode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
                                                  C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_fib_decode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/pkv_portable_math.h"
 #include "../../include/provekv_b200.h"
 
@@ -46,8 +48,9 @@ __device__ __forceinline__ int64_t pkv_vec_offset(const pkv_layout& L, int batch
 __device__ __forceinline__ int64_t pkv_dst_offset(const PkvGeom& g, int batch, int v, int align,
                                                   uint64_t* err);
 
-// Error word: the smallest (pass << 56 | global vector index << 8 | code) wins,
-// which is the error the reference's sequential loops would hit first.
+// Error word: the smallest (pass << 56 | global vector index << 8 | code) wins: within a batch
+// the error the reference's sequential loops hit first; across the batches of a launch the
+// order is by pass, then by vector.
 __device__ __forceinline__ void pkv_report(uint64_t* err, int pass, int64_t gvec, int code) {
   unsigned long long w = ((unsigned long long)pass << 56) | ((unsigned long long)gvec << 8) |
                          (unsigned long long)code;
@@ -143,6 +146,7 @@ struct pkv_fib_profile {
   pkv_fib_config cfg;
   int device;
   int idx_bits, norm_len, idx_len, rec_bytes, blocks;
+  int orthonormal;      // 1: rows of unit length and M M^T = I to 1e-6, the premise of the shortcut bounds
   double* rot_t_dev;    // [j][r]  = M[r][j], f64 (encode: lanes read consecutive rows)
   float* rot32_dev;     // [row][col] = (f32) M[row][col] (decode, fib-quant/src/rotation.rs:139)
   float* codebook_dev;  // 32 x 4 f32, rows >= N zero-filled
@@ -152,6 +156,7 @@ struct pkv_fib_profile {
   float* rot_hi_dev;    // [r][j] (f32) M[r][j] with the 13 low significand bits cleared (TF32 operand)
   float* rot_lo_dev;    // [r][j] (f32) M[r][j] - rot_hi, exact
   PkvWorkspace ws;
+  std::mutex ws_mutex;  // the host-buffer calls of one profile share ws; other profiles run alongside
 };
 
 struct pkv_turbo_profile {
@@ -167,6 +172,7 @@ struct pkv_turbo_profile {
   float* qjl_dev;           // projections x dim, then one sign-shortcut threshold per row
   float* lut_dev;           // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
   PkvWorkspace ws;
+  std::mutex ws_mutex;
 };
 
 // Cache element type of a decode kernel and the round-to-nearest-even store conversion.
@@ -187,10 +193,12 @@ __device__ __forceinline__ uint32_t pkv_pack2(float a, float b) {  // a in the l
 #endif
 
 int pkv_cuda_status(cudaError_t e);
+int pkv_check_device(int profile_device);
 int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
                   bool encode, PkvGeom* g);
 int pkv_ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes);
 void pkv_count_launch();
+int pkv_skip_tensor_issue();  // test hook, see pkv_test_skip_tensor_issue
 
 // launchers implemented in pkv_fib.cu / pkv_turbo.cu
 int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeom& g,

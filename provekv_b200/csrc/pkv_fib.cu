@@ -451,7 +451,7 @@ int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeo
   if (grid == 0) return PKV_OK;
   if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
   // The shortcuts are proven for the batch numerics; list entries hold 27-bit vector indices.
-  if (batch_numerics && (int64_t)g.n_batches * g.vpb <= ((int64_t)1 << 27)) {
+  if (batch_numerics && p->orthonormal && (int64_t)g.n_batches * g.vpb <= ((int64_t)1 << 27)) {
     if (p->cfg.dim == 64) return launch_fib_encode_fast<64>(p, x, g, payload, err, s);
     if (p->cfg.dim == 128) return launch_fib_encode_fast<128>(p, x, g, payload, err, s);
     return PKV_ERR_UNSUPPORTED;
@@ -491,7 +491,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     if ((st = set_smem(fib_encode_tc_kernel, FibTc::SMEM)) != PKV_OK) return st;
     fib_encode_tc_kernel<<<(unsigned)grid, FibTc::THREADS, FibTc::SMEM, s>>>(
         gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, payload,
-        err, scratch, scratch + 1);
+        err, scratch, scratch + 1, pkv_skip_tensor_issue());
     pkv_count_launch();
     fib_encode_fix_kernel<64><<<148 * 8, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
@@ -581,6 +581,7 @@ extern "C" int pkv_fib_encode_dev_static(const pkv_fib_profile* p, const float* 
                                          void* stream) {
   if (!p || !x_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
   if (((uintptr_t)x_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   PkvGeom g;
   int st = pkv_make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 1),
                          true, &g);
@@ -589,7 +590,7 @@ extern "C" int pkv_fib_encode_dev_static(const pkv_fib_profile* p, const float* 
   // the shortcut encoder implements the batch numerics only (fib-quant/src/codec.rs:586-589)
   const bool batch_numerics = p->cfg.numerics == PKV_FIB_NUMERICS_BATCH ||
                               (p->cfg.numerics == PKV_FIB_NUMERICS_AUTO && g.vpb >= 4);
-  if (!batch_numerics) return PKV_ERR_UNSUPPORTED;
+  if (!batch_numerics || !p->orthonormal) return PKV_ERR_UNSUPPORTED;
   if ((int64_t)g.n_batches * g.vpb > PKV_FIB_STATIC_MAX_VECTORS) return PKV_ERR_STATIC_SCRATCH_TOO_SMALL;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PKV_ERR_CUDA;

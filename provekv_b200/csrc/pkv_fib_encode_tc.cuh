@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(FibTc::THREADS, 3)
 fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot_hi,
                      const float* __restrict__ rot_lo, const float* __restrict__ codebook,
                      const float* __restrict__ half_norm, int n_codewords, uint8_t* __restrict__ payload,
-                     uint64_t* err, uint32_t* flag_count, uint32_t* flag_list) {
+                     uint64_t* err, uint32_t* flag_count, uint32_t* flag_list, int skip_issue) {
   using K = FibTc;
   using pkv_tc::sw_piece;
   using pkv_tc::tile_at;
@@ -62,6 +62,11 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, D);
   const uint32_t a0 = pkv_tc::smem_u32(s_xt), bh = pkv_tc::smem_u32(s_mh), bl = pkv_tc::smem_u32(s_ml);
   const int64_t n_tiles = (int64_t)g.n_batches * g.tiles_per_batch;
+  // skip_issue (test hook): the products are never issued, so the first wait runs out after a
+  // short limit and the kernel takes its failure exit with nothing outstanding
+  const int wait_limit = skip_issue ? 256 : pkv_tc::kWaitPolls;
+  bool failed = false;
+  uint32_t pending_parity = 0;  // phase the CTA was waiting for when it gave up
 
   // The CTA walks over groups of four tiles (one per warp); the matrix tiles, the codebook and the
   // tensor-memory columns are set up once.  Each round completes the barrier twice, so the phase
@@ -140,7 +145,7 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   }
   pkv_tc::fence_smem_to_async();
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && !skip_issue) {
     pkv_tc::fence_after_sync();
 #pragma unroll 1
     for (int k = 0; k < D / 8; k++)
@@ -148,7 +153,13 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
                        pkv_tc::smem_desc_sw128(bh + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, k > 0);
     pkv_tc::mma_commit(&s_bar);
   }
-  bool done = __all_sync(0xffffffffu, pkv_tc::mbar_wait(&s_bar, 0));
+  // The outcome of a wait is made uniform over the CTA: when it ran out for any thread, every
+  // warp leaves the loop together, no further product is issued and no accumulator is read.
+  if (!__syncthreads_and(pkv_tc::mbar_wait(&s_bar, 0, wait_limit))) {
+    failed = true;
+    pending_parity = 0;
+    break;
+  }
   pkv_tc::fence_after_sync();
   // second operand: n itself -- the unit reads only its 11 leading bits, i.e. n_hi, and the full
   // value stays in the tile for the second tier; two products (M_hi, M_lo)
@@ -171,12 +182,16 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
                        pkv_tc::smem_desc_sw128(bl + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, 1u);
     pkv_tc::mma_commit(&s_bar);
   }
-  done = __all_sync(0xffffffffu, done && pkv_tc::mbar_wait(&s_bar, 1));
+  if (!__syncthreads_and(pkv_tc::mbar_wait(&s_bar, 1, wait_limit))) {
+    failed = true;
+    pending_parity = 1;
+    break;
+  }
   pkv_tc::fence_after_sync();
 
   uint32_t idx4[4] = {0, 0, 0, 0};  // four 8-bit indices per word
   uint32_t flagged = 0;             // blocks whose nearest codeword is not settled yet
-  if (done) {
+  {
     float y[D];
     {
       float h0[32], h1[32];
@@ -211,8 +226,6 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
         flagged |= 1u << b;
     }
     if (skip || whole) flagged = 0;
-  } else if (threadIdx.x == 0) {
-    pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
   }
 
   // Second tier: the flagged blocks of one vector at a time, the whole warp on each.  Lane l takes
@@ -298,6 +311,12 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
     dst[2] = rec2;
   }
   }  // rounds
+  if (failed) {
+    // the launch's payload is declared invalid; give products that may still be in flight one
+    // more bounded wait before the columns go back
+    if (threadIdx.x == 0) pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
+    if (!skip_issue) pkv_tc::mbar_wait(&s_bar, pending_parity, wait_limit);
+  }
   pkv_tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) pkv_tc::tmem_free(s_tmem, 64);

@@ -13,6 +13,7 @@
 namespace {
 
 std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_skip_tensor_issue{0};
 
 int grow(void** ptr, int64_t* cap, int64_t need) {
   if (need <= *cap) return PKV_OK;
@@ -50,10 +51,6 @@ void ws_release(PkvWorkspace* ws) {
   *ws = PkvWorkspace();
 }
 
-std::mutex g_compact_mutex;  // the compact calls share each profile's staging buffers
-}  // namespace
-std::mutex& pkv_compact_mutex() { return g_compact_mutex; }
-namespace {
 
 // Validate a layout and derive the launch geometry for tiles of `tile` vectors.
 int make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
@@ -165,15 +162,28 @@ int fib_index_bits(int n) {  // fib-quant/src/profile.rs:268-274
 }  // namespace
 
 int pkv_cuda_status(cudaError_t e) { return e == cudaSuccess ? PKV_OK : PKV_ERR_CUDA; }
+// A profile's tables live on the device that was current when it was created; a launch from another
+// device would hand that device's kernels pointers they cannot reach.  Checked before anything is
+// launched or copied.
+int pkv_check_device(int profile_device) {
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) return PKV_ERR_CUDA;
+  return cur == profile_device ? PKV_OK : PKV_ERR_INVALID_ARGUMENT;
+}
 int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
                   bool encode, PkvGeom* g) {
   return make_geom(L, rec_bytes, payload_batch_stride, tile, encode, g);
 }
 void pkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int pkv_skip_tensor_issue() { return g_skip_tensor_issue.load(std::memory_order_relaxed); }
 
 extern "C" {
 
 int64_t pkv_launch_count(void) { return g_launches.load(); }
+int pkv_test_skip_tensor_issue(int on) {
+  g_skip_tensor_issue.store(on ? 1 : 0);
+  return PKV_OK;
+}
 int pkv_version(void) { return 100; }
 
 const char* pkv_status_string(int s) {
@@ -223,6 +233,31 @@ int pkv_memcpy_d2h(void* d, const void* s, int64_t n, void* stream) {
 }
 int pkv_stream_synchronize(void* stream) { return pkv_cuda_status(cudaStreamSynchronize((cudaStream_t)stream)); }
 
+// Records of `n_batches` wire blobs between host memory (blob b at blobs_host + b * blob_bytes, its
+// records after header_bytes) and a device payload buffer (batch b at payload_dev + b * stride).
+int pkv_payload_upload(const uint8_t* blobs_host, int64_t blob_bytes, int32_t header_bytes, int64_t n_batches,
+                       int64_t record_bytes_per_batch, uint8_t* payload_dev, int64_t payload_batch_stride,
+                       void* stream) {
+  if (!blobs_host || !payload_dev || n_batches < 0 || header_bytes < 0 || record_bytes_per_batch < 0 ||
+      blob_bytes < header_bytes + record_bytes_per_batch || payload_batch_stride < record_bytes_per_batch)
+    return PKV_ERR_INVALID_ARGUMENT;
+  if (n_batches == 0 || record_bytes_per_batch == 0) return PKV_OK;
+  return pkv_cuda_status(cudaMemcpy2DAsync(payload_dev, (size_t)payload_batch_stride, blobs_host + header_bytes,
+                                           (size_t)blob_bytes, (size_t)record_bytes_per_batch, (size_t)n_batches,
+                                           cudaMemcpyHostToDevice, (cudaStream_t)stream));
+}
+int pkv_payload_download(const uint8_t* payload_dev, int64_t payload_batch_stride, int64_t n_batches,
+                         int64_t record_bytes_per_batch, uint8_t* blobs_host, int64_t blob_bytes,
+                         int32_t header_bytes, void* stream) {
+  if (!blobs_host || !payload_dev || n_batches < 0 || header_bytes < 0 || record_bytes_per_batch < 0 ||
+      blob_bytes < header_bytes + record_bytes_per_batch || payload_batch_stride < record_bytes_per_batch)
+    return PKV_ERR_INVALID_ARGUMENT;
+  if (n_batches == 0 || record_bytes_per_batch == 0) return PKV_OK;
+  return pkv_cuda_status(cudaMemcpy2DAsync(blobs_host + header_bytes, (size_t)blob_bytes, payload_dev,
+                                           (size_t)payload_batch_stride, (size_t)record_bytes_per_batch,
+                                           (size_t)n_batches, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+}
+
 int pkv_error_word_reset(uint64_t* err_dev, void* stream) {
   return pkv_cuda_status(cudaMemsetAsync(err_dev, 0xFF, sizeof(uint64_t), (cudaStream_t)stream));
 }
@@ -266,6 +301,19 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
   p->rot_hi_dev = nullptr;
   p->rot_lo_dev = nullptr;
   const int d = cfg->dim;
+  // The error bounds of the shortcut encoders (pkv_fast_paths.h) take |M_r|_2 = 1 and an orthogonal
+  // M.  A table that is not (scaled, truncated, not a rotation at all) is still a valid input of the
+  // reference's arithmetic, so the profile is kept but encodes with the exact f64 kernel only.
+  p->orthonormal = 1;
+  for (int r = 0; r < d && p->orthonormal; r++)
+    for (int q = r; q < d; q++) {
+      double dot = 0.0;
+      for (int j = 0; j < d; j++) dot += rotation[r * d + j] * rotation[q * d + j];
+      if (!(fabs(dot - (r == q ? 1.0 : 0.0)) < 1.0e-6)) {  // also catches NaN
+        p->orthonormal = 0;
+        break;
+      }
+    }
   cudaError_t e = cudaGetDevice(&p->device);
   double* rt = new double[d * d];
   float* r32 = new float[d * d];
@@ -347,6 +395,7 @@ int pkv_fib_encode_dev(const pkv_fib_profile* p, const float* x_dev, const pkv_l
                        uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
                        void* stream) {
   if (!p || !x_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)x_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 1), true, &g);
@@ -361,6 +410,7 @@ int pkv_fib_decode_patch_dev(const pkv_fib_profile* p, const uint8_t* payload_de
                              int64_t payload_batch_stride, const pkv_layout* layout,
                              float* cache_dev, uint64_t* err_dev, void* stream) {
   if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
@@ -372,6 +422,7 @@ int pkv_fib_decode_patch_dev_as(const pkv_fib_profile* p, const uint8_t* payload
                                 int64_t payload_batch_stride, const pkv_layout* layout,
                                 void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream) {
   if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
@@ -385,6 +436,7 @@ int pkv_fib_decode_patch_dev_multi(const pkv_fib_profile* p, const uint8_t* payl
                                    void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
                                    uint64_t* err_dev, void* stream) {
   if (!p || !cache_dev || !payload_dev || !err_dev || !batch_offsets_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
@@ -432,6 +484,7 @@ int pkv_fib_encode_batch_compact(const pkv_fib_profile* cp, const float* vectors
                                  int32_t* vec_code, int64_t* vec_index) {
   pkv_fib_profile* p = const_cast<pkv_fib_profile*>(cp);
   if (!p || !out_host || !out_len || n < 0 || (n > 0 && !vectors_host)) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (vec_code) *vec_code = 0;
   if (vec_index) *vec_index = -1;
   *out_len = 0;
@@ -440,7 +493,7 @@ int pkv_fib_encode_batch_compact(const pkv_fib_profile* cp, const float* vectors
   const int d = p->cfg.dim;
   const int64_t total = PKV_FB2_HEADER_BYTES + n * p->rec_bytes;
   if (out_capacity < total) return PKV_ERR_BUFFER_TOO_SMALL;
-  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  std::lock_guard<std::mutex> lock(p->ws_mutex);
   int st = pkv_ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
@@ -466,6 +519,7 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* cp, const uint8_t* bytes
                                  int32_t* vec_code, int64_t* vec_index) {
   pkv_fib_profile* p = const_cast<pkv_fib_profile*>(cp);
   if (!p || !bytes_host || !n_vectors) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (vec_code) *vec_code = 0;
   if (vec_index) *vec_index = -1;
   *n_vectors = 0;
@@ -476,7 +530,7 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* cp, const uint8_t* bytes
   const int d = p->cfg.dim;
   if (n == 0) return PKV_OK;  // decode_batch_fast of no codes, fib-quant/src/codec.rs:798
   if (!out_host || out_capacity_floats < n * d) return PKV_ERR_BUFFER_TOO_SMALL;
-  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  std::lock_guard<std::mutex> lock(p->ws_mutex);
   st = pkv_ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
@@ -607,6 +661,7 @@ int pkv_turbo_encode_dev(const pkv_turbo_profile* p, const float* x_dev, const p
                          uint8_t* payload_dev, int64_t payload_batch_stride, uint64_t* err_dev,
                          void* stream) {
   if (!p || !x_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)x_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), true, &g);
@@ -619,6 +674,7 @@ int pkv_turbo_decode_patch_dev(const pkv_turbo_profile* p, const uint8_t* payloa
                                int64_t payload_batch_stride, const pkv_layout* layout,
                                float* cache_dev, uint64_t* err_dev, void* stream) {
   if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
@@ -630,6 +686,7 @@ int pkv_turbo_decode_patch_dev_as(const pkv_turbo_profile* p, const uint8_t* pay
                                   int64_t payload_batch_stride, const pkv_layout* layout,
                                   void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream) {
   if (!p || !cache_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
@@ -643,6 +700,7 @@ int pkv_turbo_decode_patch_dev_multi(const pkv_turbo_profile* p, const uint8_t* 
                                      void* cache_dev, const int64_t* batch_offsets_dev, int32_t dst_dtype,
                                      uint64_t* err_dev, void* stream) {
   if (!p || !cache_dev || !payload_dev || !err_dev || !batch_offsets_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (((uintptr_t)cache_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
   PkvGeom g;
   int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
@@ -657,6 +715,7 @@ int pkv_turbo_score_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
                         const float* rotated_query_dev, const float* projected_query_dev,
                         float* scores_dev, uint64_t* err_dev, void* stream) {
   if (!p || !payload_dev || !rotated_query_dev || !scores_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (p->cfg.mode == PKV_TURBO_POLAR_WITH_QJL && !projected_query_dev) return PKV_ERR_INVALID_ARGUMENT;
   if (((uintptr_t)payload_dev & 15) || ((uintptr_t)rotated_query_dev & 3) || ((uintptr_t)scores_dev & 3))
     return PKV_ERR_INVALID_ARGUMENT;
@@ -727,6 +786,7 @@ int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* cp, const float* vec
                                    int32_t* vec_code, int64_t* vec_index) {
   pkv_turbo_profile* p = const_cast<pkv_turbo_profile*>(cp);
   if (!p || !out_host || !out_len || n < 0 || (n > 0 && !vectors_host)) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (vec_code) *vec_code = 0;
   if (vec_index) *vec_index = -1;
   *out_len = 0;
@@ -735,7 +795,7 @@ int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* cp, const float* vec
   const int d = p->cfg.dim;
   const int64_t total = PKV_TQB1_HEADER_BYTES + n * p->rec_bytes;
   if (out_capacity < total) return PKV_ERR_BUFFER_TOO_SMALL;
-  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  std::lock_guard<std::mutex> lock(p->ws_mutex);
   int st = pkv_ws_prepare(&p->ws, n * d * 4, n * p->rec_bytes + 16);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;
@@ -761,6 +821,7 @@ int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* cp, const uint8_t* b
                                    int64_t* n_vectors, int32_t* vec_code, int64_t* vec_index) {
   pkv_turbo_profile* p = const_cast<pkv_turbo_profile*>(cp);
   if (!p || !bytes_host || !n_vectors) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
   if (vec_code) *vec_code = 0;
   if (vec_index) *vec_index = -1;
   *n_vectors = 0;
@@ -771,7 +832,7 @@ int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* cp, const uint8_t* b
   const int d = p->cfg.dim;
   if (n == 0) return PKV_OK;
   if (!out_host || out_capacity_floats < n * d) return PKV_ERR_BUFFER_TOO_SMALL;
-  std::lock_guard<std::mutex> lock(g_compact_mutex);
+  std::lock_guard<std::mutex> lock(p->ws_mutex);
   st = pkv_ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
   if (st != PKV_OK) return st;
   cudaStream_t s = 0;

@@ -10,15 +10,28 @@
 
 #include "pkv_common.cuh"
 
-std::mutex& pkv_compact_mutex();
-
 namespace {
 
 struct BulkCodec {
   PkvWorkspace* ws;
+  std::mutex* mu;  // the profile's staging lock
+  int device;      // the device the profile's tables live on
   int dim, rec, hdr;
   const void* profile;
   bool turbo;
+};
+
+// On an error exit copies of earlier chunks may still be reading or writing the caller's host
+// buffers and the staging area: wait for them before the caller gets control back.  The status
+// of the wait itself is dropped; the caller sees the original error.
+struct StreamDrain {
+  PkvWorkspace* ws;
+  bool armed = true;
+  ~StreamDrain() {
+    if (!armed) return;
+    for (int i = 0; i < PKV_WS_STREAMS; i++)
+      if (ws->streams[i]) cudaStreamSynchronize(ws->streams[i]);
+  }
 };
 
 int dev_encode(const BulkCodec& c, const float* x, const pkv_layout* L, uint8_t* pay, int64_t stride,
@@ -108,10 +121,12 @@ int bulk_encode(const BulkCodec& c, const float* x_host, int64_t n_batches, int6
   const int64_t blob = c.hdr + vpb * c.rec;
   if (out_capacity < n_batches * blob) return PKV_ERR_BUFFER_TOO_SMALL;
   const int64_t pstride = (vpb * c.rec + 15) / 16 * 16;
-  std::lock_guard<std::mutex> lock(pkv_compact_mutex());
+  if (int ds = pkv_check_device(c.device)) return ds;
+  std::lock_guard<std::mutex> lock(*c.mu);
   int st = pkv_ws_prepare(c.ws, n_batches * vpb * c.dim * 4, n_batches * pstride);
   if (st != PKV_OK) return st;
   if ((st = prepare_streams(c.ws)) != PKV_OK) return st;
+  StreamDrain drain{c.ws};
   const int n_chunks = chunk_count(n_batches, n_batches * vpb * c.dim * 4, n_batches * vpb * c.rec);
   int64_t chunk_b0[PKV_WS_ERR_WORDS];
   for (int k = 0; k < n_chunks; k++) {
@@ -133,6 +148,7 @@ int bulk_encode(const BulkCodec& c, const float* x_host, int64_t n_batches, int6
       return PKV_ERR_CUDA;
   }
   for (int64_t b = 0; b < n_batches; b++) write_header(c, (uint32_t)vpb, out_host + b * blob);
+  drain.armed = false;  // finish() waits for the streams itself
   return finish(c, n_chunks, chunk_b0, vpb, vec_code, vec_index);
 }
 
@@ -152,10 +168,12 @@ int bulk_decode(const BulkCodec& c, const uint8_t* bytes_host, int64_t n_batches
     if (n != (uint32_t)vpb) return PKV_ERR_CORRUPT_HEADER;
   }
   const int64_t pstride = (vpb * c.rec + 15) / 16 * 16;
-  std::lock_guard<std::mutex> lock(pkv_compact_mutex());
+  if (int ds = pkv_check_device(c.device)) return ds;
+  std::lock_guard<std::mutex> lock(*c.mu);
   int st = pkv_ws_prepare(c.ws, n_batches * pstride, n_batches * vpb * c.dim * 4);
   if (st != PKV_OK) return st;
   if ((st = prepare_streams(c.ws)) != PKV_OK) return st;
+  StreamDrain drain{c.ws};
   const int n_chunks = chunk_count(n_batches, n_batches * vpb * c.rec, n_batches * vpb * c.dim * 4);
   int64_t chunk_b0[PKV_WS_ERR_WORDS];
   for (int k = 0; k < n_chunks; k++) {
@@ -176,16 +194,17 @@ int bulk_decode(const BulkCodec& c, const uint8_t* bytes_host, int64_t n_batches
                         cudaMemcpyDeviceToHost, s) != cudaSuccess)
       return PKV_ERR_CUDA;
   }
+  drain.armed = false;
   return finish(c, n_chunks, chunk_b0, vpb, vec_code, vec_index);
 }
 
 BulkCodec fib_codec(const pkv_fib_profile* p) {
   pkv_fib_profile* q = const_cast<pkv_fib_profile*>(p);
-  return BulkCodec{&q->ws, q->cfg.dim, q->rec_bytes, PKV_FB2_HEADER_BYTES, q, false};
+  return BulkCodec{&q->ws, &q->ws_mutex, q->device, q->cfg.dim, q->rec_bytes, PKV_FB2_HEADER_BYTES, q, false};
 }
 BulkCodec turbo_codec(const pkv_turbo_profile* p) {
   pkv_turbo_profile* q = const_cast<pkv_turbo_profile*>(p);
-  return BulkCodec{&q->ws, q->cfg.dim, q->rec_bytes, PKV_TQB1_HEADER_BYTES, q, true};
+  return BulkCodec{&q->ws, &q->ws_mutex, q->device, q->cfg.dim, q->rec_bytes, PKV_TQB1_HEADER_BYTES, q, true};
 }
 
 }  // namespace

@@ -82,10 +82,11 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// Bounded wait for the barrier phase `parity`; false if it never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait for the barrier phase `parity`; false if it never completed within `limit` polls.
+constexpr int kWaitPolls = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = kWaitPolls) {
   const uint32_t a = smem_u32(bar);
-  for (int it = 0; it < (1 << 20); it++) {
+  for (int it = 0; it < limit; it++) {
     uint32_t ok;
     asm volatile(
         "{\n\t"

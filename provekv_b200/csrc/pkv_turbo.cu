@@ -39,6 +39,7 @@ TurboParams make_params(const pkv_turbo_profile* p) {
   }
   tp.fast_bucket = p->fast_bucket;
   tp.ray_count = p->ray_count;
+  tp.skip_issue = pkv_skip_tensor_issue();
   tp.qjl = p->qjl_dev;
   tp.lut = p->lut_dev;
   return tp;

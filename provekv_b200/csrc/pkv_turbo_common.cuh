@@ -36,6 +36,7 @@ struct TurboParams {
   float qjl_thr_tf32[64];  // per QJL row: |g| * PKV_QJL_TF32_BOUND (tensor-core tier)
   int fast_bucket;     // ray table present and validated against the exact thresholds
   int ray_count;       // 2^polar_bits / 4 + 1 rays, 0 without the shortcut
+  int skip_issue;      // test hook: the tensor-core product is not issued, so its bounded wait runs out
   const float* qjl;    // [m][dim] then m sign-shortcut thresholds
   const float* lut;    // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
 };

@@ -437,6 +437,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     // inverse rotation (rotation.rs:212-221), residual = vector - reconstruction (turbo.rs:268-273)
     fwht_inverse_signed<D>(y, tp.sgn_scale);
     float2 n2 = make_float2(0.0f, 0.0f);
+    uint32_t res_any = 0;  // OR of the residual's magnitude bits: zero only for an all-zero residual
 #pragma unroll
     for (int i = 0; i < D; i += 4) {
       float4* piece = reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)));
@@ -450,6 +451,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       y[i + 3] = __fsub_rn(t.w, y[i + 3]);
       n2 = ffma2(make_float2(y[i], y[i + 1]), make_float2(y[i], y[i + 1]), n2);
       n2 = ffma2(make_float2(y[i + 2], y[i + 3]), make_float2(y[i + 2], y[i + 3]), n2);
+      res_any |= (__float_as_uint(y[i]) | __float_as_uint(y[i + 1]) | __float_as_uint(y[i + 2]) |
+                  __float_as_uint(y[i + 3])) & 0x7fffffffu;
       // the residual replaces x in the tile: it is the A operand of the QJL product
       *piece = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
     }
@@ -468,7 +471,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     pkv_tc::fence_smem_to_async();
     __syncthreads();
     const uint32_t tmem_d = s_tmem;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && !tp.skip_issue) {
       pkv_tc::fence_after_sync();
       const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, m > 32 ? 64 : 32);
       const uint32_t a0 = pkv_tc::smem_u32(s_xt), b0 = pkv_tc::smem_u32(s_gt);
@@ -478,7 +481,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                          pkv_tc::smem_desc_sw128(b0 + (k >> 2) * g_slab + (k & 3) * 32), idesc, k > 0);
       pkv_tc::mma_commit(&s_bar);
     }
-    const bool done = __all_sync(0xffffffffu, pkv_tc::mbar_wait(&s_bar, 0));
+    const bool done =
+        __all_sync(0xffffffffu, pkv_tc::mbar_wait(&s_bar, 0, tp.skip_issue ? 256 : pkv_tc::kWaitPolls));
     pkv_tc::fence_after_sync();
     uint32_t* sw = w + (rw + tp.angle_words) * K::WS;
     if (done) {
@@ -494,8 +498,10 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           flagged |= (fabsf(dots[p]) > tau ? 0u : 1u) << p;
           bits |= (dots[p] >= 0.0f ? 1u : 0u) << p;
         }
-        // an all-zero residual gives +-0 for every dot: sign bit 1 without further tests
-        if (!valid || nsq == 0.0f) flagged = 0;
+        // an all-zero residual gives +-0 for every dot: sign bit 1 without further tests.  The test
+        // is on the bits: a squared norm that merely underflowed to zero (elements below ~1e-23)
+        // stays flagged, falls under the absolute bound and takes the exact sequence.
+        if (!valid || res_any == 0u) flagged = 0;
         // Second tier (binary32 fused dot) and third (the reference's own sequence) for the flagged
         // (vector, row) pairs of the whole warp, spread over the lanes: each lane lists its pairs
         // at the position a prefix sum gives it, lane j settles list entry j, the owner reads the

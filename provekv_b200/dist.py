@@ -58,6 +58,65 @@ def gather_layer_shards(local_payload, world_size: int, group=None):
     return out
 
 
+def all_gather_pool(local_payload, pool_payload, group=None):
+    """Layer-sharded pool build: every rank has encoded an equal, contiguous block of the pool's
+    batches (``local_payload``); afterwards ``pool_payload`` (world_size times as large, rank order
+    = layer order) holds the whole pool in every rank's own memory.  With one rank the local block
+    is the pool and is copied unless both arguments are the same tensor."""
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        if pool_payload.numel() != local_payload.numel() * dist.get_world_size(group):
+            raise ValueError("the pool must be world_size equal blocks")
+        dist.all_gather_into_tensor(pool_payload.view(-1), local_payload.view(-1), group=group)
+    elif pool_payload.data_ptr() != local_payload.data_ptr():
+        pool_payload.view(-1).copy_(local_payload.view(-1))
+    return pool_payload
+
+
+def gpu_numa_cpus(pci_bus_id: str, sysfs: str = "/sys/bus/pci/devices"):
+    """CPUs of the NUMA node a GPU hangs off, from sysfs (``local_cpulist`` of the PCI device);
+    an empty list when the platform does not say (virtual machines often report node -1)."""
+    import os
+
+    dev = os.path.join(sysfs, pci_bus_id.lower())
+    try:
+        with open(os.path.join(dev, "numa_node")) as f:
+            if int(f.read().strip()) < 0:
+                return []
+        with open(os.path.join(dev, "local_cpulist")) as f:
+            text = f.read().strip()
+    except (OSError, ValueError):
+        return []
+    cpus = []
+    for part in text.split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus += list(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_rank_to_gpu_numa(device_index: int):
+    """Pin the calling process (its copy-issuing threads and the pages of the pinned buffers it
+    allocates afterwards) to the CPUs next to its GPU, so that several ranks on one host do not
+    pull their host<->device copies through one socket.  Returns the CPU list used ([] = left
+    unchanged: no NUMA information, or the intersection with the allowed CPUs is empty)."""
+    import os
+
+    import torch
+
+    props = torch.cuda.get_device_properties(device_index)
+    try:
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+    except AttributeError:
+        return []
+    cpus = sorted(set(gpu_numa_cpus(bus)) & set(os.sched_getaffinity(0)))
+    if cpus:
+        os.sched_setaffinity(0, cpus)
+    return cpus
+
+
 def max_over_ranks(values: Sequence[float], device=None) -> List[float]:
     """Element-wise max of per-rank timings (the reported time is the slowest rank's)."""
     import torch

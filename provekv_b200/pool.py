@@ -64,3 +64,97 @@ def agent_patch_position(n_shared: int, n_unique: int, agent: int) -> int:
     """First cache position of an agent's unique tokens
     (proveKV/scripts/ppl_validate_multi_agent.py:258)."""
     return n_shared + agent * n_unique
+
+
+@dataclass(frozen=True)
+class TwoTierPlan:
+    """Where one rank's part of the two-tier pool lives and which kernel launch covers it.
+
+    The reference builds one cold pool of the shared prefix (fib-quant, one batch per (layer, K|V),
+    proveKV/src/pool.rs:246-309), one hot shell per agent (turbo-quant, proveKV/src/shell.rs:250-311,
+    examples/prove_kv_multi_agent_shell.rs:272-331) and patches both into the agents' caches
+    (proveKV/scripts/ppl_validate_multi_agent.py:226-271): prefix token t at position t of every
+    cache, agent a's token t at ``n_shared + a * n_unique + t`` of its own cache, each cache holding
+    ``n_shared + n_agents * n_unique`` positions.
+
+    ``shard = "agent"``: the rank owns a block of agents (their shells and caches) and encodes a block
+    of the prefix's layers; the FB2 payload of the other layers arrives by an all-gather, and the
+    rank decodes the whole pool into its agents' caches.  ``shard = "layer"``: the rank owns a block
+    of layers of everything; nothing is exchanged.
+
+    Tensors (f32, contiguous): prefix ``[enc_layers][2][H][n_shared][d]``, shells
+    ``[agents][dec_layers][2][H][n_unique][d]``, caches ``[agents][dec_layers][2][H][cache_tokens][d]``.
+    """
+    shape: KvShape
+    n_agents: int
+    n_shared: int
+    n_unique: int
+    world_size: int = 1
+    rank: int = 0
+    shard: str = "agent"
+
+    def __post_init__(self):
+        if self.shard not in ("agent", "layer"):
+            raise ValueError("shard must be 'agent' or 'layer'")
+        if not 0 <= self.rank < self.world_size:
+            raise ValueError("bad rank / world_size")
+
+    @staticmethod
+    def _block(n: int, world: int, rank: int) -> range:
+        return range(n * rank // world, n * (rank + 1) // world)
+
+    @property
+    def cache_tokens(self) -> int:
+        return self.n_shared + self.n_agents * self.n_unique
+
+    @property
+    def agents(self) -> range:
+        if self.shard == "agent":
+            return self._block(self.n_agents, self.world_size, self.rank)
+        return range(self.n_agents)
+
+    @property
+    def enc_layers(self) -> range:
+        """Prefix layers this rank encodes."""
+        return self._block(self.shape.num_layers, self.world_size, self.rank)
+
+    @property
+    def dec_layers(self) -> range:
+        """Layers present in this rank's shells and caches."""
+        return range(self.shape.num_layers) if self.shard == "agent" else self.enc_layers
+
+    def _sub(self, layers: range) -> KvShape:
+        return KvShape(len(layers), self.shape.num_kv_heads, self.shape.head_dim)
+
+    @property
+    def agent_cache_elems(self) -> int:
+        s = self.shape
+        return len(self.dec_layers) * 2 * s.num_kv_heads * self.cache_tokens * s.head_dim
+
+    def prefix_vectors(self, layers: range) -> int:
+        return self._sub(layers).vectors(self.n_shared)
+
+    def shell_vectors(self) -> int:
+        return self._sub(self.dec_layers).vectors(self.n_unique, len(self.agents))
+
+    def prefix_encode_layout(self) -> Layout:
+        return kv_tensor_layout(self._sub(self.enc_layers), 1, self.n_shared)
+
+    def prefix_decode_layout(self) -> Layout:
+        """One decode of the pool's dec_layers, written into every owned agent's cache."""
+        return kv_tensor_layout(self._sub(self.dec_layers), 1, self.n_shared,
+                                token_capacity=self.cache_tokens, first_token=0,
+                                n_replicas=len(self.agents), replica_stride=self.agent_cache_elems)
+
+    def shell_encode_layout(self) -> Layout:
+        return kv_tensor_layout(self._sub(self.dec_layers), len(self.agents), self.n_unique)
+
+    def shell_decode_layout(self) -> Layout:
+        """Agent a (global index) lands at position n_shared + a * n_unique of its own cache: the
+        step from one agent's batches to the next is one cache plus n_unique positions."""
+        s, d = self._sub(self.dec_layers), self.shape.head_dim
+        L = kv_tensor_layout(s, len(self.agents), self.n_unique, token_capacity=self.cache_tokens,
+                             first_token=agent_patch_position(self.n_shared, self.n_unique, self.agents.start)
+                             if len(self.agents) else 0)
+        L.batch_stride[0] = self.agent_cache_elems + self.n_unique * d
+        return L

@@ -1,0 +1,182 @@
+"""Failure paths and guard rails of the CUDA library, exercised without faulting the GPU:
+a bounded wait that runs out, a profile used from the wrong device, a rotation table that is
+not orthonormal, residuals too small for binary32 norms, and the error word's order when one
+launch covers several batches.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import provekv_b200 as pk
+from provekv_b200 import _lib as L
+from provekv_b200 import tables
+
+from kvgen import synthetic_kv
+
+pytestmark = pytest.mark.gpu
+
+SEED = 42
+
+
+def _flat_layout(n_batches, vpb, dim):
+    return L.Layout.make(n_batches=(n_batches, 1, 1), batch_stride=(vpb * dim, 0, 0), n_tokens=vpb,
+                         n_heads=1, token_stride=dim, head_stride=dim)
+
+
+@pytest.mark.parametrize("codec", ["turbo", "fib"])
+def test_bounded_wait_runs_out_and_the_context_stays_usable(oracle_mod, codec):
+    """With the tensor-core products withheld (test hook) the completion barrier never flips: the
+    kernels poll it a few hundred times, report PKV_VEC_DEVICE_WAIT, give their tensor memory back
+    and return.  Afterwards the same profile encodes normally and matches the oracle."""
+    dim, n = 64, 5000
+    x = synthetic_kv(n, dim, seed=3)
+    if codec == "turbo":
+        signs, qjl = tables.rademacher_signs(dim, SEED), tables.qjl_matrix(dim, 32, SEED)
+        prof = pk.TurboProfile(dim, 4, signs, qjl, seed=SEED)
+    else:
+        rot, cb = tables.haar_rotation(dim, SEED), tables.fib_codebook(dim, seed=SEED)
+        prof = pk.FibProfile(dim, rot, cb)
+    lib = L.lib()
+    assert lib.pkv_test_skip_tensor_issue(1) == L.OK
+    try:
+        with pytest.raises(L.PkvError) as ei:
+            prof.encode_batch_compact(x)
+        assert ei.value.status == L.VEC_DEVICE_WAIT
+    finally:
+        lib.pkv_test_skip_tensor_issue(0)
+    got = prof.encode_batch_compact(x)
+    if codec == "turbo":
+        st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=4, mode=1, radii_codec=0,
+                                                   libm_mode=oracle_mod.LIBM_PORTABLE)
+        assert st == 0 and got[L.TQB1_HEADER_BYTES:] == payload.tobytes()
+    else:
+        st, payload, _, _ = oracle_mod.fib_encode(x, rot, cb)
+        assert st == 0 and got[L.FB2_HEADER_BYTES:] == payload.tobytes()
+
+
+def test_profile_is_bound_to_its_device():
+    """A profile's tables live on the device it was created on; calls made with another device
+    current are refused before anything is launched or copied."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    lib = L.lib()
+    dim, n = 64, 256
+    L.check(lib.pkv_set_device(0))
+    fib = pk.FibProfile(dim, tables.haar_rotation(dim, 1), tables.fib_codebook(dim, seed=1))
+    tq = pk.TurboProfile(dim, 4, tables.rademacher_signs(dim, 1), tables.qjl_matrix(dim, 32, 1), seed=1)
+    x = synthetic_kv(n, dim, seed=1)
+    fib_wire, tq_wire = fib.encode_batch_compact(x), tq.encode_batch_compact(x)
+    L.check(lib.pkv_set_device(1))
+    try:
+        launches = lib.pkv_launch_count()
+        with torch.cuda.device(1):
+            xd = torch.from_numpy(x).cuda()
+            out = torch.zeros(n * 256, dtype=torch.uint8, device="cuda")
+            err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+            lay = _flat_layout(1, n, dim)
+            for prof in (fib, tq):
+                with pytest.raises(L.PkvError) as ei:
+                    prof.encode_dev(xd.data_ptr(), lay, out.data_ptr(), n * 256, err.data_ptr())
+                assert ei.value.status == L.ERR_INVALID_ARGUMENT
+                with pytest.raises(L.PkvError) as ei:
+                    prof.decode_patch_dev(out.data_ptr(), n * 256, lay, xd.data_ptr(), err.data_ptr())
+                assert ei.value.status == L.ERR_INVALID_ARGUMENT
+                with pytest.raises(L.PkvError) as ei:
+                    prof.encode_batch_compact(x)
+                assert ei.value.status == L.ERR_INVALID_ARGUMENT
+            st = lib.pkv_fib_encode_dev_static(fib.handle, xd.data_ptr(), C.byref(lay), out.data_ptr(),
+                                               n * 256, err.data_ptr(), None)
+            assert st == L.ERR_INVALID_ARGUMENT
+            with pytest.raises(L.PkvError):
+                fib.decode_batch_compact(fib_wire)
+            with pytest.raises(L.PkvError):
+                tq.decode_batch_compact(tq_wire)
+            torch.cuda.synchronize()
+            assert int(err[0]) == -1
+        assert lib.pkv_launch_count() == launches
+    finally:
+        L.check(lib.pkv_set_device(0))
+    assert fib.encode_batch_compact(x) == fib_wire
+
+
+@pytest.mark.parametrize("kind", ["scaled", "sheared"])
+def test_fib_matrix_that_is_not_orthonormal_takes_the_exact_kernel(oracle_mod, kind):
+    """The shortcut encoders' bounds assume an orthonormal rotation.  A scaled or sheared matrix is
+    still a valid table for the reference's arithmetic: such a profile encodes with the exact f64
+    kernel and the bytes equal the oracle's; the no-allocation entry point refuses it."""
+    import torch
+    dim, n = 64, 3000
+    rot, cb = tables.haar_rotation(dim, 9), tables.fib_codebook(dim, seed=9)
+    rot = np.array(rot, np.float64)
+    if kind == "scaled":
+        rot = rot * 1.37
+    else:
+        rot[3] += 0.25 * rot[11]
+    x = synthetic_kv(n, dim, seed=77)
+    prof = pk.FibProfile(dim, rot, cb)
+    got = prof.encode_batch_compact(x)
+    st, payload, _, _ = oracle_mod.fib_encode(x, rot, cb)
+    assert st == 0 and got[L.FB2_HEADER_BYTES:] == payload.tobytes()
+    dec = prof.decode_batch_compact(got)
+    st, want, _, _ = oracle_mod.fib_decode(payload, dim, rot, cb)
+    assert st == 0 and np.array_equal(dec.view(np.uint32), want.view(np.uint32))
+    xd = torch.from_numpy(x).cuda()
+    out = torch.zeros(n * 16, dtype=torch.uint8, device="cuda")
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    lay = _flat_layout(1, n, dim)
+    st = L.lib().pkv_fib_encode_dev_static(prof.handle, xd.data_ptr(), C.byref(lay), out.data_ptr(), n * 16,
+                                           err.data_ptr(), None)
+    assert st == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("scale", [1e-25, 3e-33])
+def test_turbo_residuals_below_the_binary32_norm_range(oracle_mod, dim, scale):
+    """Inputs so small that the residual's squared norm underflows to zero in binary32 while the
+    residual itself is not zero: the tensor-core dots flush, no bound certifies anything, and every
+    sign has to come from the exact sequential dot."""
+    n, m = 700, 32
+    signs, qjl = tables.rademacher_signs(dim, SEED), tables.qjl_matrix(dim, m, SEED)
+    x = (synthetic_kv(n, dim, seed=12).astype(np.float64) * scale).astype(np.float32)
+    x[17] = 0.0
+    for rc in (L.RADII_F32, L.RADII_BLOCK_LOG_U8):
+        prof = pk.TurboProfile(dim, 4, signs, qjl, radii_codec=rc, seed=SEED)
+        got = prof.encode_batch_compact(x)
+        st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=4, mode=1, radii_codec=rc,
+                                                   libm_mode=oracle_mod.LIBM_PORTABLE)
+        assert st == 0
+        have = np.frombuffer(got, np.uint8)[L.TQB1_HEADER_BYTES:].reshape(n, -1)
+        want = payload.reshape(n, -1)
+        assert np.array_equal(have, want), f"{(have != want).any(axis=1).sum()} records differ"
+
+
+def test_error_word_order_over_two_batches():
+    """One launch over two batches: batch 0 holds a vector whose norm overflows fp16 (found by the
+    encoder's second pass), batch 1 a NaN (first pass).  Encoded one batch per call, as the reference
+    does, each batch reports its own error; in one launch the word orders by pass before vector, so
+    the first-pass error of the later batch is the one reported."""
+    import torch
+    dim, vpb = 64, 500
+    rot, cb = tables.haar_rotation(dim, 5), tables.fib_codebook(dim, seed=5)
+    prof = pk.FibProfile(dim, rot, cb)
+    x = synthetic_kv(2 * vpb, dim, seed=8).reshape(2, vpb, dim)
+    x[0, 123] *= np.float32(1e5)       # norm ~ 8e5 > 65504
+    x[1, 45, 7] = np.float32("nan")
+    xd = torch.from_numpy(x).cuda()
+    stride = (vpb * prof.record_bytes + 15) // 16 * 16
+    out = torch.zeros((2, stride), dtype=torch.uint8, device="cuda")
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+
+    def run(first, count):
+        err.fill_(-1)
+        lay = _flat_layout(count, vpb, dim)
+        prof.encode_dev(xd[first:].data_ptr(), lay, out.data_ptr(), stride, err.data_ptr())
+        with pytest.raises(L.PkvError) as ei:
+            pk.read_error_word(err.data_ptr())
+        return ei.value.status, ei.value.vector_index
+
+    assert run(0, 1) == (L.VEC_NORM_RANGE, 123)
+    assert run(1, 1) == (L.VEC_NONFINITE_INPUT, 45)
+    assert run(0, 2) == (L.VEC_NONFINITE_INPUT, vpb + 45)

@@ -49,6 +49,51 @@ def test_patch_positions_and_strides():
     assert pool.LLAMA3_8B.vectors(131072) == 67_108_864
 
 
+def test_two_tier_plan_addresses_match_numpy_indexing():
+    """Every (replica, batch, vector) of the four launches of a rank lands on the element the
+    reference's patch loop writes (ppl_validate_multi_agent.py:247-262)."""
+    shape = pool.KvShape(4, 2, 8)
+    A, ns, nu = 6, 5, 3
+    for shard, world in (("agent", 1), ("agent", 2), ("layer", 2), ("agent", 3)):
+        seen_prefix_layers, seen_agents = [], []
+        for rank in range(world):
+            plan = pool.TwoTierPlan(shape, A, ns, nu, world, rank, shard)
+            assert plan.cache_tokens == ns + A * nu
+            ag, dl, el = plan.agents, plan.dec_layers, plan.enc_layers
+            seen_prefix_layers += list(el)
+            seen_agents += list(ag)
+            cache = np.arange(len(ag) * len(dl) * 2 * 2 * plan.cache_tokens * 8).reshape(
+                len(ag), len(dl), 2, 2, plan.cache_tokens, 8)
+            assert plan.agent_cache_elems == cache[0].size
+            L = plan.prefix_decode_layout()
+            assert L.n_replicas == len(ag) and L.batch_count == len(dl) * 2
+            for r in range(L.n_replicas):
+                for batch in range(L.batch_count):
+                    layer, side = divmod(batch, 2)
+                    for v in range(L.vectors_per_batch):
+                        t, h = divmod(v, 2)
+                        assert vec_offset(L, batch, v) + r * L.replica_stride == cache[r, layer, side, h, t, 0]
+            L = plan.shell_decode_layout()
+            assert L.batch_count == len(ag) * len(dl) * 2 and L.n_replicas == 1
+            for batch in range(L.batch_count):
+                a, rem = divmod(batch, len(dl) * 2)
+                layer, side = divmod(rem, 2)
+                for v in range(L.vectors_per_batch):
+                    t, h = divmod(v, 2)
+                    pos = pool.agent_patch_position(ns, nu, ag[a]) + t
+                    assert vec_offset(L, batch, v) == cache[a, layer, side, h, pos, 0]
+            src = np.arange(len(el) * 2 * 2 * ns * 8).reshape(len(el), 2, 2, ns, 8)
+            L = plan.prefix_encode_layout()
+            for batch in range(L.batch_count):
+                layer, side = divmod(batch, 2)
+                for v in range(L.vectors_per_batch):
+                    t, h = divmod(v, 2)
+                    assert vec_offset(L, batch, v) == src[layer, side, h, t, 0]
+            assert plan.shell_vectors() == len(ag) * len(dl) * 2 * 2 * nu
+        assert seen_prefix_layers == list(range(4))
+        assert seen_agents == (list(range(A)) if shard == "agent" else list(range(A)) * world)
+
+
 def test_sharding_covers_everything_once():
     for n, w in [(8, 1), (8, 2), (8, 8), (64, 8), (32, 8), (7, 4), (3, 8)]:
         shards = pdist.all_shards(n, w)
@@ -87,6 +132,13 @@ def _gloo_worker(rank, world, port, q):
         local = torch.full((hi - lo, 16), rank + 1, dtype=torch.uint8)
         parts = pdist.gather_layer_shards(local, world)
         ok_gather = [int(p[0, 0]) for p in parts] == list(range(1, world + 1))
+        # the pool build of the two-tier plan: equal layer blocks gathered into every rank's pool
+        plan = pool.TwoTierPlan(pool.KvShape(6, 2, 8), 4, 5, 3, world, rank, "agent")
+        mine = torch.tensor([[10 * layer + side] * 16 for layer in plan.enc_layers for side in (0, 1)],
+                            dtype=torch.uint8)
+        whole = torch.zeros((12, 16), dtype=torch.uint8)
+        pdist.all_gather_pool(mine, whole)
+        ok_gather = ok_gather and [int(v) for v in whole[:, 0]] == [10 * l + s for l in range(6) for s in (0, 1)]
         agents = list(pdist.shard_agents(8, world, rank))
         slow = pdist.max_over_ranks([1.0 + rank, 5.0 - rank])
         q.put((rank, ok_bcast, ok_gather, agents, slow))
@@ -109,6 +161,17 @@ def test_two_rank_gloo_broadcast_and_sharding():
     assert res[0][1] and res[1][1] and res[0][2] and res[1][2]
     assert res[0][3] == [0, 1, 2, 3] and res[1][3] == [4, 5, 6, 7]
     assert res[0][4] == [2.0, 5.0] and res[1][4] == [2.0, 5.0]
+
+
+def test_gpu_numa_cpu_list_from_sysfs(tmp_path):
+    dev = tmp_path / "0000:1b:00.0"
+    dev.mkdir()
+    (dev / "numa_node").write_text("1\n")
+    (dev / "local_cpulist").write_text("32-35,96,98-99\n")
+    assert pdist.gpu_numa_cpus("0000:1B:00.0", str(tmp_path)) == [32, 33, 34, 35, 96, 98, 99]
+    (dev / "numa_node").write_text("-1\n")
+    assert pdist.gpu_numa_cpus("0000:1b:00.0", str(tmp_path)) == []
+    assert pdist.gpu_numa_cpus("0000:ff:00.0", str(tmp_path)) == []
 
 
 def test_per_vector_wire_framing_round_trips_and_rejects():

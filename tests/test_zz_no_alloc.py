@@ -4,8 +4,9 @@ under an allocator it must not re-enter).  It keeps the encoder's undecided-bloc
 array inside the library image instead of borrowing it from the stream's memory pool.
 
 The test calls it through the C ABI twice in a row on different inputs and checks every record
-byte against pkv_fib_encode_dev; the second call also proves that the previous call's leftover
-list does not leak into the next one.  The file name sorts last so a `-x` run has already
+byte against pkv_fib_encode_dev and against the CPU oracle (so the comparison is not only the
+library with itself); the second call also proves that the previous call's leftover list does not
+leak into the next one.  The file name sorts last so a `-x` run has already
 executed every other test when it gets here.
 """
 import ctypes as C
@@ -29,8 +30,11 @@ def test_static_scratch_encode_matches_pool_backed_encode(dim):
     from provekv_b200 import _lib as L
     from provekv_b200 import tables
 
+    import oracle
+
     lib = L.lib()
-    prof = pk.FibProfile(dim, tables.haar_rotation(dim, 7), tables.fib_codebook(dim, seed=7))
+    rot, cb = tables.haar_rotation(dim, 7), tables.fib_codebook(dim, seed=7)
+    prof = pk.FibProfile(dim, rot, cb)
     rec = prof.record_bytes
     for call, (n_batches, vpb, seed) in enumerate([(5, 3001, 1), (3, 777, 2)]):
         gen = torch.Generator(device="cuda").manual_seed(seed)
@@ -52,6 +56,10 @@ def test_static_scratch_encode_matches_pool_backed_encode(dim):
         b = got.cpu().numpy()[:, :vpb * rec]
         assert np.array_equal(a, b), f"call {call}: {(a != b).sum()} differing bytes"
         assert a.any()
+        st, ref, _, _ = oracle.fib_encode(x.cpu().numpy().reshape(-1, dim), rot, cb)
+        assert st == 0
+        ref = ref.reshape(n_batches, vpb * rec)
+        assert np.array_equal(b, ref), f"call {call}: {(b != ref).sum()} bytes differ from the oracle"
 
     # sizes beyond the fixed array are refused with their own status, nothing is launched
     big = L.Layout.make(n_batches=(1, 1, 1), n_tokens=(1 << 20) + 4, n_heads=1, token_stride=dim,
