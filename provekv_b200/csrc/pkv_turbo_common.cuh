@@ -145,13 +145,13 @@ __device__ __forceinline__ uint32_t angle_bucket(float theta, uint32_t levels) {
 }
 
 // The exact (slow) forms, kept out of line: taken only by undecided pairs / projections.
-__device__ __noinline__ uint32_t exact_bucket(float b, float a, uint32_t levels) {
+static __device__ __noinline__ uint32_t exact_bucket(float b, float a, uint32_t levels) {
   return angle_bucket(pkv_atan2f_portable(b, a), levels);
 }
 
 // QjlQuantizer::sketch's dot (qjl.rs:214-217): sequential, separately rounded * and +.
 // `res` is the thread's residual vector in shared memory (its row of the f32 tile).
-__device__ __noinline__ float exact_dot(const float* g, const float* res, int dim) {
+static __device__ __noinline__ float exact_dot(const float* g, const float* res, int dim) {
   float dot = 0.0f;
   for (int j = 0; j < dim; j++) dot = __fadd_rn(dot, __fmul_rn(g[j], res[j]));
   return dot;

@@ -1,0 +1,57 @@
+// turbo-quant hot-shell kernels for sm_100a: randomised Hadamard transform
+// (Rademacher signs, FWHT held in registers), polar decomposition with b-bit
+// angle buckets, f32 or BlockLogU8 radii, optional QJL residual sign sketch,
+// and the inverse fused with the write into the KV cache.
+//
+// One thread owns one vector and one warp owns a tile of 32 vectors, staged through its own
+// slice of shared memory (f32 tile with padded rows; records word-transposed, so record word k
+// of vector v sits at [k][v]) so that every global access is coalesced.
+// The kernels (pkv_turbo_encode.cuh, pkv_turbo_decode.cuh) are templated on the
+// dimension and on the angle width: 3, 4 and 7 bits are compiled with static bit
+// positions, any other width runs the generic variant (PB = 0).
+#include "pkv_turbo_encode.cuh"
+#include "pkv_turbo_launch.cuh"
+
+using namespace pkv_turbo;
+
+namespace {
+
+template <int D, int PB>
+int launch_encode(const TurboParams& tp, const float* x, const PkvGeom& g, uint8_t* payload,
+                  uint64_t* err, unsigned grid, cudaStream_t s) {
+  const size_t sm = turbo_encode_smem<D>(tp);
+  const unsigned ctas = (grid + TurboEnc<D>::NWARPS - 1) / TurboEnc<D>::NWARPS;  // one warp per 32-vector tile
+  int st;
+  if (turbo_encode_direct(tp)) {
+    if ((st = set_smem(turbo_encode_kernel<D, PB, true>, sm)) != PKV_OK) return st;
+    turbo_encode_kernel<D, PB, true><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+  } else {
+    if ((st = set_smem(turbo_encode_kernel<D, PB, false>, sm)) != PKV_OK) return st;
+    turbo_encode_kernel<D, PB, false><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+  }
+  return PKV_OK;
+}
+
+}  // namespace
+
+int pkv_turbo_tile_vectors(int dim) { return (dim == 64 || dim == 128) ? 32 : 0; }
+
+int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const PkvGeom& g,
+                            uint8_t* payload, uint64_t* err, cudaStream_t s) {
+  const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
+  if (grid == 0) return PKV_OK;
+  if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  const TurboParams tp = make_params(p);
+  int st;
+  if (p->cfg.dim == 64) {
+    PKV_DISPATCH_PB(launch_encode, 64, tp, x, g, payload, err, (unsigned)grid, s)
+  } else if (p->cfg.dim == 128) {
+    PKV_DISPATCH_PB(launch_encode, 128, tp, x, g, payload, err, (unsigned)grid, s)
+  } else {
+    return PKV_ERR_UNSUPPORTED;
+  }
+  if (st != PKV_OK) return st;
+  pkv_count_launch();
+  return pkv_cuda_status(cudaGetLastError());
+}
+

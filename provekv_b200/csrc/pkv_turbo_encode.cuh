@@ -463,7 +463,11 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       for (int i = 0; i < D; i++) res_ok = res_ok && pkv_finite(*tile_at(s_xt, K::X_SLAB, row, i));
       if (!res_ok) code = PKV_VEC_NONFINITE_RESIDUAL;
     }
-    const float rnorm = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
+    // |residual| rounded up, the yardstick of both sign shortcuts.  Squares of elements below ~1e-19
+    // underflow, so a sum under 1e-30 says nothing about the norm: such a vector is treated as
+    // having an unbounded one (no shortcut certifies, every sign comes from the exact sequence).
+    // Above that, underflowed squares change the sum by less than 1e-6 of it (the 1.0001 covers it).
+    const float rnorm = nsq < 1.0e-30f ? __int_as_float(0x7f800000) : __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
 
     // QjlQuantizer::sketch, qjl.rs:214-217: sign of the sequential f32 dot per projection row.
     // All 128 x m dots come from one TF32 product on the tensor cores: A = the CTA's residual
