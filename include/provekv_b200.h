@@ -65,6 +65,8 @@ enum {
 
 const char* pkv_status_string(int status);
 int pkv_version(void);
+/* Text of the CUDA runtime error behind the calling thread's most recent PKV_ERR_CUDA ("" if none). */
+const char* pkv_last_cuda_error(void);
 
 /* ---- configuration ----------------------------------------------------- */
 #define PKV_NORM_FP16 0 /* NormFormat::Fp16Paper, fib-quant/src/codec.rs:1001 */
@@ -337,6 +339,12 @@ int64_t pkv_launch_count(void);
  * through the error word, releases its tensor memory and returns, with nothing outstanding on the
  * GPU.  The payload of such a launch is not valid.  Process-wide; switch it off again after use. */
 int pkv_test_skip_tensor_issue(int on);
+
+/* Test hook, no counterpart in the reference.  For PolarWithQjl profiles with f32 radii the turbo
+ * encoder takes the QJL sketch in the rotated domain (no inverse transform in the common case); while
+ * this is switched on it takes the sketch of the residual, as every other profile does, so that tests
+ * can compare the two routes byte for byte.  Process-wide. */
+int pkv_test_turbo_encode_legacy(int on);
 
 #ifdef __cplusplus
 }

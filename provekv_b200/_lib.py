@@ -112,6 +112,7 @@ _V = C.c_void_p
 _SIGS = {
     "pkv_status_string": (C.c_char_p, [C.c_int]),
     "pkv_version": (C.c_int, []),
+    "pkv_last_cuda_error": (C.c_char_p, []),
     "pkv_device_count": (C.c_int, [C.POINTER(C.c_int)]),
     "pkv_set_device": (C.c_int, [C.c_int]),
     "pkv_host_alloc": (C.c_int, [C.POINTER(_V), C.c_int64]),
@@ -155,6 +156,7 @@ _SIGS = {
     "pkv_tqb1_header_parse": (C.c_int, [_V, _V, C.c_int64, C.POINTER(C.c_uint32)]),
     "pkv_launch_count": (C.c_int64, []),
     "pkv_test_skip_tensor_issue": (C.c_int, [C.c_int]),
+    "pkv_test_turbo_encode_legacy": (C.c_int, [C.c_int]),
     "pkv_fib_encode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
                                                  C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_fib_decode_batches_compact": (C.c_int, [_V, _V, C.c_int64, C.c_int64, _V, C.c_int64,
@@ -186,7 +188,12 @@ def lib() -> C.CDLL:
 
 
 def status_string(status: int) -> str:
-    return lib().pkv_status_string(status).decode()
+    text = lib().pkv_status_string(status).decode()
+    if status == ERR_CUDA:
+        detail = lib().pkv_last_cuda_error().decode()
+        if detail:
+            text += f": {detail}"
+    return text
 
 
 def check(status: int, vector_index: int = -1) -> None:

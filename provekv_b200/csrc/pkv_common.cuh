@@ -170,6 +170,7 @@ struct pkv_turbo_profile {
   float qjl_thr[64];        // per row: |g_r| * PKV_QJL_REL_BOUND (binary32 sign shortcut)
   float qjl_thr_tf32[64];   // per row: |g_r| * PKV_QJL_TF32_BOUND (tensor-core sign shortcut)
   float* qjl_dev;           // projections x dim, then one sign-shortcut threshold per row
+  float* qjl_rot_dev;       // projections x dim: G S H~ with unit-length rows (the rotated-domain sketch)
   float* lut_dev;           // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
   PkvWorkspace ws;
   std::mutex ws_mutex;
@@ -198,7 +199,9 @@ int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stri
                   bool encode, PkvGeom* g);
 int pkv_ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes);
 void pkv_count_launch();
+cudaMemPool_t pkv_scratch_pool();  // the library's stream-ordered pool of the current device (scratch lists)
 int pkv_skip_tensor_issue();  // test hook, see pkv_test_skip_tensor_issue
+int pkv_turbo_encode_legacy();  // test hook, see pkv_test_turbo_encode_legacy
 
 // launchers implemented in pkv_fib.cu / pkv_turbo.cu
 int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeom& g,

@@ -404,30 +404,6 @@ int pkv_fib_tile_vectors(int dim, int encode) {
   return 0;
 }
 
-// The library's own stream-ordered memory pool, one per device, created on first use.  Its
-// release threshold is unlimited, so the scratch of one call is recycled by the next instead
-// of being returned to the driver at every synchronisation.
-cudaMemPool_t scratch_pool() {
-  static std::mutex mu;
-  static cudaMemPool_t pools[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!pools[dev]) {
-    cudaMemPoolProps props = {};
-    props.allocType = cudaMemAllocationTypePinned;
-    props.handleTypes = cudaMemHandleTypeNone;
-    props.location.type = cudaMemLocationTypeDevice;
-    props.location.id = dev;
-    cudaMemPool_t pool = nullptr;
-    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) return nullptr;
-    uint64_t keep = ~0ull;
-    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
-    pools[dev] = pool;
-  }
-  return pools[dev];
-}
-
 // Shortcut path: fast kernel over all vectors, then the exact fix-up of the listed entries.  The
 // list (one counter + at most one entry per vector) is scratch memory taken from the pool above,
 // ordered on the caller's stream, for the duration of the two launches.
@@ -435,11 +411,10 @@ template <int D>
 int launch_fib_encode_fast(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
                            uint8_t* payload, uint64_t* err, cudaStream_t s) {
   const int64_t n = (int64_t)g.n_batches * g.vpb;
-  cudaMemPool_t pool = scratch_pool();
+  cudaMemPool_t pool = pkv_scratch_pool();
   if (!pool) return PKV_ERR_CUDA;
   uint32_t* scratch = nullptr;
-  if (cudaMallocFromPoolAsync((void**)&scratch, sizeof(uint32_t) * (size_t)(n + 1), pool, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMallocFromPoolAsync((void**)&scratch, sizeof(uint32_t) * (size_t)(n + 1), pool, s)) return pkv_cuda_status(ce);
   int st = pkv_launch_fib_encode_fast_with_scratch(p, x, g, payload, err, scratch, s);
   if (cudaFreeAsync(scratch, s) != cudaSuccess && st == PKV_OK) st = PKV_ERR_CUDA;
   return st;
@@ -477,7 +452,7 @@ int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeo
 int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const float* x, const PkvGeom& g,
                                             uint8_t* payload, uint64_t* err, uint32_t* scratch,
                                             cudaStream_t s) {
-  if (cudaMemsetAsync(scratch, 0, sizeof(uint32_t), s) != cudaSuccess) return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemsetAsync(scratch, 0, sizeof(uint32_t), s)) return pkv_cuda_status(ce);
   int st;
   // the cold-tier default shape takes the tensor-core kernel
   if (p->cfg.dim == 64 && p->norm_len == 2 && p->idx_bits == 5) {

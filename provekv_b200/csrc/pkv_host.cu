@@ -14,6 +14,7 @@ namespace {
 
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_skip_tensor_issue{0};
+std::atomic<int> g_turbo_encode_legacy{0};
 
 int grow(void** ptr, int64_t* cap, int64_t need) {
   if (need <= *cap) return PKV_OK;
@@ -161,13 +162,44 @@ int fib_index_bits(int n) {  // fib-quant/src/profile.rs:268-274
 
 }  // namespace
 
-int pkv_cuda_status(cudaError_t e) { return e == cudaSuccess ? PKV_OK : PKV_ERR_CUDA; }
+namespace {
+thread_local cudaError_t t_last_cuda_error = cudaSuccess;
+}
+// The library's own stream-ordered memory pool, one per device, created on first use.  Its
+// release threshold is unlimited, so the scratch of one call is recycled by the next instead
+// of being returned to the driver at every synchronisation.
+cudaMemPool_t pkv_scratch_pool() {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) return nullptr;
+    uint64_t keep = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    pools[dev] = pool;
+  }
+  return pools[dev];
+}
+
+int pkv_cuda_status(cudaError_t e) {
+  if (e == cudaSuccess) return PKV_OK;
+  t_last_cuda_error = e;
+  return PKV_ERR_CUDA;
+}
 // A profile's tables live on the device that was current when it was created; a launch from another
 // device would hand that device's kernels pointers they cannot reach.  Checked before anything is
 // launched or copied.
 int pkv_check_device(int profile_device) {
   int cur = -1;
-  if (cudaGetDevice(&cur) != cudaSuccess) return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaGetDevice(&cur)) return pkv_cuda_status(ce);
   return cur == profile_device ? PKV_OK : PKV_ERR_INVALID_ARGUMENT;
 }
 int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stride, int tile,
@@ -176,10 +208,18 @@ int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stri
 }
 void pkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 int pkv_skip_tensor_issue() { return g_skip_tensor_issue.load(std::memory_order_relaxed); }
+int pkv_turbo_encode_legacy() { return g_turbo_encode_legacy.load(std::memory_order_relaxed); }
 
 extern "C" {
 
 int64_t pkv_launch_count(void) { return g_launches.load(); }
+const char* pkv_last_cuda_error(void) {
+  return t_last_cuda_error == cudaSuccess ? "" : cudaGetErrorString(t_last_cuda_error);
+}
+int pkv_test_turbo_encode_legacy(int on) {
+  g_turbo_encode_legacy.store(on ? 1 : 0);
+  return PKV_OK;
+}
 int pkv_test_skip_tensor_issue(int on) {
   g_skip_tensor_issue.store(on ? 1 : 0);
   return PKV_OK;
@@ -265,7 +305,7 @@ int pkv_error_word_read(const uint64_t* err_dev, void* stream, int32_t* code, in
   uint64_t w = 0;
   cudaError_t e = cudaMemcpyAsync(&w, err_dev, sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
-  if (e != cudaSuccess) return PKV_ERR_CUDA;
+  if (e != cudaSuccess) return pkv_cuda_status(e);
   return decode_err_word(w, code, index);
 }
 
@@ -499,14 +539,12 @@ int pkv_fib_encode_batch_compact(const pkv_fib_profile* cp, const float* vectors
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
   const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
-  if (cudaMemcpyAsync(p->ws.in, vectors_host, (size_t)n * d * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(p->ws.in, vectors_host, (size_t)n * d * 4, cudaMemcpyHostToDevice, s)) return pkv_cuda_status(ce);
   pkv_error_word_reset(p->ws.err, s);
   st = pkv_fib_encode_dev(p, (const float*)p->ws.in, &L, (uint8_t*)p->ws.out, stride, p->ws.err, s);
   if (st != PKV_OK) return st;
-  if (cudaMemcpyAsync(out_host + PKV_FB2_HEADER_BYTES, p->ws.out, (size_t)n * p->rec_bytes,
-                      cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(out_host + PKV_FB2_HEADER_BYTES, p->ws.out, (size_t)n * p->rec_bytes,
+                      cudaMemcpyDeviceToHost, s)) return pkv_cuda_status(ce);
   st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
   if (st != PKV_OK) return st;
   pkv_fb2_header_write(p, (uint32_t)n, out_host);
@@ -536,14 +574,12 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* cp, const uint8_t* bytes
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
   const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
-  if (cudaMemcpyAsync(p->ws.in, bytes_host + PKV_FB2_HEADER_BYTES, (size_t)n * p->rec_bytes,
-                      cudaMemcpyHostToDevice, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(p->ws.in, bytes_host + PKV_FB2_HEADER_BYTES, (size_t)n * p->rec_bytes,
+                      cudaMemcpyHostToDevice, s)) return pkv_cuda_status(ce);
   pkv_error_word_reset(p->ws.err, s);
   st = pkv_fib_decode_patch_dev(p, (const uint8_t*)p->ws.in, stride, &L, (float*)p->ws.out, p->ws.err, s);
   if (st != PKV_OK) return st;
-  if (cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s)) return pkv_cuda_status(ce);
   st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
   if (st != PKV_OK) return st;
   *n_vectors = n;
@@ -593,6 +629,7 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
   for (int i = 0; i < d; i++)
     if (signs[i] < 0.0f) p->sign_mask[i >> 5] |= 1u << (i & 31);
   p->qjl_dev = nullptr;
+  p->qjl_rot_dev = nullptr;
   p->lut_dev = nullptr;
   const int levels = 1 << pb;
   float lut[1024];
@@ -637,6 +674,29 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->qjl_dev, bytes);
     if (e == cudaSuccess) e = cudaMemcpy(p->qjl_dev, host, bytes, cudaMemcpyHostToDevice);
     delete[] host;
+    {
+      // The sketch in the rotated domain: g . (S H~ z) = (g S H~) . z with H~ = scale * H, H the natural-order
+      // Walsh-Hadamard matrix the butterflies of turbo-quant/src/rotation.rs:379-398 apply, S the signs.
+      // Row r of the table is g_r S H~ / (|g_r| * 1.0001), computed in binary64 and rounded once, so that
+      // one bound serves every projection.  A zero row stays zero (its signs come from the exact sequence).
+      float* rot = new float[(size_t)m * d];
+      for (int r = 0; r < m; r++) {
+        double s2 = 0.0;
+        for (int j = 0; j < d; j++) s2 += (double)qjl[r * d + j] * (double)qjl[r * d + j];
+        const double denom = sqrt(s2) * 1.0001;
+        for (int k = 0; k < d; k++) {
+          double acc = 0.0;
+          for (int j = 0; j < d; j++) {
+            const double term = (double)qjl[r * d + j] * (double)signs[j];
+            acc += (__builtin_popcount((unsigned)(j & k)) & 1) ? -term : term;
+          }
+          rot[r * d + k] = denom > 0.0 ? (float)(acc * (double)p->scale / denom) : 0.0f;
+        }
+      }
+      if (e == cudaSuccess) e = cudaMalloc((void**)&p->qjl_rot_dev, sizeof(float) * (size_t)m * d);
+      if (e == cudaSuccess) e = cudaMemcpy(p->qjl_rot_dev, rot, sizeof(float) * (size_t)m * d, cudaMemcpyHostToDevice);
+      delete[] rot;
+    }
   }
   if (e != cudaSuccess) {
     pkv_turbo_profile_destroy(p);
@@ -649,6 +709,7 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
 int pkv_turbo_profile_destroy(pkv_turbo_profile* p) {
   if (!p) return PKV_OK;
   if (p->qjl_dev) cudaFree(p->qjl_dev);
+  if (p->qjl_rot_dev) cudaFree(p->qjl_rot_dev);
   if (p->lut_dev) cudaFree(p->lut_dev);
   ws_release(&p->ws);
   delete p;
@@ -801,14 +862,12 @@ int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* cp, const float* vec
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
   const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
-  if (cudaMemcpyAsync(p->ws.in, vectors_host, (size_t)n * d * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(p->ws.in, vectors_host, (size_t)n * d * 4, cudaMemcpyHostToDevice, s)) return pkv_cuda_status(ce);
   pkv_error_word_reset(p->ws.err, s);
   st = pkv_turbo_encode_dev(p, (const float*)p->ws.in, &L, (uint8_t*)p->ws.out, stride, p->ws.err, s);
   if (st != PKV_OK) return st;
-  if (cudaMemcpyAsync(out_host + PKV_TQB1_HEADER_BYTES, p->ws.out, (size_t)n * p->rec_bytes,
-                      cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(out_host + PKV_TQB1_HEADER_BYTES, p->ws.out, (size_t)n * p->rec_bytes,
+                      cudaMemcpyDeviceToHost, s)) return pkv_cuda_status(ce);
   st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
   if (st != PKV_OK) return st;
   pkv_tqb1_header_write(p, (uint32_t)n, out_host);
@@ -838,14 +897,12 @@ int pkv_turbo_decode_batch_compact(const pkv_turbo_profile* cp, const uint8_t* b
   cudaStream_t s = 0;
   pkv_layout L = flat_layout(n, d);
   const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
-  if (cudaMemcpyAsync(p->ws.in, bytes_host + PKV_TQB1_HEADER_BYTES, (size_t)n * p->rec_bytes,
-                      cudaMemcpyHostToDevice, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(p->ws.in, bytes_host + PKV_TQB1_HEADER_BYTES, (size_t)n * p->rec_bytes,
+                      cudaMemcpyHostToDevice, s)) return pkv_cuda_status(ce);
   pkv_error_word_reset(p->ws.err, s);
   st = pkv_turbo_decode_patch_dev(p, (const uint8_t*)p->ws.in, stride, &L, (float*)p->ws.out, p->ws.err, s);
   if (st != PKV_OK) return st;
-  if (cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    return PKV_ERR_CUDA;
+  if (cudaError_t ce = cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s)) return pkv_cuda_status(ce);
   st = pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
   if (st != PKV_OK) return st;
   *n_vectors = n;

@@ -93,9 +93,8 @@ int finish(const BulkCodec& c, int n_chunks, const int64_t* chunk_b0, int64_t vp
            int64_t* vec_index) {
   uint64_t words[PKV_WS_ERR_WORDS];
   for (int i = 0; i < PKV_WS_STREAMS; i++)
-    if (cudaStreamSynchronize(c.ws->streams[i]) != cudaSuccess) return PKV_ERR_CUDA;
-  if (cudaMemcpy(words, c.ws->err, sizeof(uint64_t) * n_chunks, cudaMemcpyDeviceToHost) != cudaSuccess)
-    return PKV_ERR_CUDA;
+    if (cudaError_t ce = cudaStreamSynchronize(c.ws->streams[i])) return pkv_cuda_status(ce);
+  if (cudaError_t ce = cudaMemcpy(words, c.ws->err, sizeof(uint64_t) * n_chunks, cudaMemcpyDeviceToHost)) return pkv_cuda_status(ce);
   uint64_t best = PKV_ERR_NONE;
   for (int k = 0; k < n_chunks; k++) {
     if (words[k] == PKV_ERR_NONE) continue;
@@ -135,17 +134,15 @@ int bulk_encode(const BulkCodec& c, const float* x_host, int64_t n_batches, int6
     cudaStream_t s = c.ws->streams[k % PKV_WS_STREAMS];
     if (pkv_error_word_reset(c.ws->err + k, s) != PKV_OK) return PKV_ERR_CUDA;
     const int64_t xoff = b0 * vpb * c.dim;
-    if (cudaMemcpyAsync((float*)c.ws->in + xoff, x_host + xoff, (size_t)(nb * vpb * c.dim) * 4,
-                        cudaMemcpyHostToDevice, s) != cudaSuccess)
-      return PKV_ERR_CUDA;
+    if (cudaError_t ce = cudaMemcpyAsync((float*)c.ws->in + xoff, x_host + xoff, (size_t)(nb * vpb * c.dim) * 4,
+                        cudaMemcpyHostToDevice, s)) return pkv_cuda_status(ce);
     pkv_layout L = chunk_layout(b0, nb, vpb, c.dim);
     st = dev_encode(c, (const float*)c.ws->in, &L, (uint8_t*)c.ws->out + b0 * pstride, pstride,
                     c.ws->err + k, s);
     if (st != PKV_OK) return st;
-    if (cudaMemcpy2DAsync(out_host + b0 * blob + c.hdr, (size_t)blob, (uint8_t*)c.ws->out + b0 * pstride,
+    if (cudaError_t ce = cudaMemcpy2DAsync(out_host + b0 * blob + c.hdr, (size_t)blob, (uint8_t*)c.ws->out + b0 * pstride,
                           (size_t)pstride, (size_t)(vpb * c.rec), (size_t)nb, cudaMemcpyDeviceToHost,
-                          s) != cudaSuccess)
-      return PKV_ERR_CUDA;
+                          s)) return pkv_cuda_status(ce);
   }
   for (int64_t b = 0; b < n_batches; b++) write_header(c, (uint32_t)vpb, out_host + b * blob);
   drain.armed = false;  // finish() waits for the streams itself
@@ -181,18 +178,16 @@ int bulk_decode(const BulkCodec& c, const uint8_t* bytes_host, int64_t n_batches
     chunk_b0[k] = b0;
     cudaStream_t s = c.ws->streams[k % PKV_WS_STREAMS];
     if (pkv_error_word_reset(c.ws->err + k, s) != PKV_OK) return PKV_ERR_CUDA;
-    if (cudaMemcpy2DAsync((uint8_t*)c.ws->in + b0 * pstride, (size_t)pstride,
+    if (cudaError_t ce = cudaMemcpy2DAsync((uint8_t*)c.ws->in + b0 * pstride, (size_t)pstride,
                           bytes_host + b0 * blob + c.hdr, (size_t)blob, (size_t)(vpb * c.rec), (size_t)nb,
-                          cudaMemcpyHostToDevice, s) != cudaSuccess)
-      return PKV_ERR_CUDA;
+                          cudaMemcpyHostToDevice, s)) return pkv_cuda_status(ce);
     pkv_layout L = chunk_layout(b0, nb, vpb, c.dim);
     st = dev_decode(c, (const uint8_t*)c.ws->in + b0 * pstride, pstride, &L, (float*)c.ws->out,
                     c.ws->err + k, s);
     if (st != PKV_OK) return st;
     const int64_t xoff = b0 * vpb * c.dim;
-    if (cudaMemcpyAsync(out_host + xoff, (float*)c.ws->out + xoff, (size_t)(nb * vpb * c.dim) * 4,
-                        cudaMemcpyDeviceToHost, s) != cudaSuccess)
-      return PKV_ERR_CUDA;
+    if (cudaError_t ce = cudaMemcpyAsync(out_host + xoff, (float*)c.ws->out + xoff, (size_t)(nb * vpb * c.dim) * 4,
+                        cudaMemcpyDeviceToHost, s)) return pkv_cuda_status(ce);
   }
   drain.armed = false;
   return finish(c, n_chunks, chunk_b0, vpb, vec_code, vec_index);

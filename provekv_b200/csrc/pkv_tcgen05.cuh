@@ -125,4 +125,29 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&d)[32]) {
   for (int i = 0; i < 32; i++) d[i] = __uint_as_float(r[i]);
 }
 
+// N = 4 or 8 consecutive accumulator columns of this thread's tensor-memory lane; whole-warp call.
+template <int N>
+__device__ __forceinline__ void tmem_load(uint32_t taddr, float (&d)[N]) {
+  static_assert(N == 4 || N == 8, "column count");
+  uint32_t r[N];
+  if constexpr (N == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]) : : "memory");
+  }
+#pragma unroll
+  for (int i = 0; i < N; i++) d[i] = __uint_as_float(r[i]);
+}
+
 }  // namespace pkv_tc

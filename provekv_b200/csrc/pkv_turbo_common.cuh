@@ -38,6 +38,7 @@ struct TurboParams {
   int ray_count;       // 2^polar_bits / 4 + 1 rays, 0 without the shortcut
   int skip_issue;      // test hook: the tensor-core product is not issued, so its bounded wait runs out
   const float* qjl;    // [m][dim] then m sign-shortcut thresholds
+  const float* qjl_rot;  // [m][dim]: rows of G S H~ scaled to unit length (the rotated-domain sketch)
   const float* lut;    // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
 };
 

@@ -16,19 +16,46 @@ using namespace pkv_turbo;
 
 namespace {
 
+// ROT: the sketch in the rotated domain (PolarWithQjl, f32 radii, validated ray table, G'' present).
 template <int D, int PB>
 int launch_encode(const TurboParams& tp, const float* x, const PkvGeom& g, uint8_t* payload,
                   uint64_t* err, unsigned grid, cudaStream_t s) {
   const size_t sm = turbo_encode_smem<D>(tp);
   const unsigned ctas = (grid + TurboEnc<D>::NWARPS - 1) / TurboEnc<D>::NWARPS;  // one warp per 32-vector tile
+  const bool rot = tp.mode == PKV_TURBO_POLAR_WITH_QJL && !tp.lossy && tp.fast_bucket && tp.qjl_rot != nullptr &&
+                   !pkv_turbo_encode_legacy();
   int st;
-  if (turbo_encode_direct(tp)) {
-    if ((st = set_smem(turbo_encode_kernel<D, PB, true>, sm)) != PKV_OK) return st;
-    turbo_encode_kernel<D, PB, true><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
-  } else {
-    if ((st = set_smem(turbo_encode_kernel<D, PB, false>, sm)) != PKV_OK) return st;
-    turbo_encode_kernel<D, PB, false><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err);
+  uint32_t* fix = nullptr;  // rot: counter + one entry per (vector, block of 32 projections), from the stream's pool
+  const int64_t entries = (int64_t)g.n_batches * g.vpb * ((tp.projections + 31) / 32);
+  if (rot) {
+    cudaMemPool_t pool = pkv_scratch_pool();
+    if (!pool) return PKV_ERR_CUDA;
+    if (cudaError_t ce = cudaMallocFromPoolAsync((void**)&fix, sizeof(uint2) * (size_t)(entries + 1), pool, s))
+      return pkv_cuda_status(ce);
+    if (cudaError_t ce = cudaMemsetAsync(fix, 0, sizeof(uint32_t), s)) {
+      cudaFreeAsync(fix, s);
+      return pkv_cuda_status(ce);
+    }
   }
+  uint2* fix_list = reinterpret_cast<uint2*>(fix) + 1;
+#define PKV_TURBO_ENC(DIRECT, ROT)                                                                        \
+  {                                                                                                       \
+    if ((st = set_smem(turbo_encode_kernel<D, PB, DIRECT, ROT>, sm)) != PKV_OK) return st;                \
+    turbo_encode_kernel<D, PB, DIRECT, ROT><<<ctas, TurboEnc<D>::THREADS, sm, s>>>(g, tp, x, payload, err, fix, \
+                                                                                    fix_list);             \
+  }
+  if (turbo_encode_direct(tp)) {
+    if (rot) PKV_TURBO_ENC(true, true) else PKV_TURBO_ENC(true, false)
+  } else {
+    if (rot) PKV_TURBO_ENC(false, true) else PKV_TURBO_ENC(false, false)
+  }
+  if (rot) {
+    const size_t fsm = sizeof(float) * ((size_t)tp.projections * (D + 1) + 2 * (1u << tp.polar_bits) + 4 * D);
+    turbo_encode_fix_kernel<D><<<148 * 4, 128, fsm, s>>>(g, tp, x, payload, err, fix, fix_list);
+    pkv_count_launch();
+    if (cudaError_t ce = cudaFreeAsync(fix, s)) return pkv_cuda_status(ce);
+  }
+#undef PKV_TURBO_ENC
   return PKV_OK;
 }
 

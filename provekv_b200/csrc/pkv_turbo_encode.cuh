@@ -51,14 +51,23 @@ __device__ __forceinline__ void patch_angle(uint32_t* aw, int ws, int i, int pb,
   }
 }
 
+// Angle index i of the shared angle words.
+__device__ __forceinline__ uint32_t read_angle(const uint32_t* aw, int ws, int i, int pb) {
+  const int pos = i * pb, wi = pos >> 5, sh = pos & 31;
+  uint32_t idx = aw[wi * ws] >> sh;
+  if (sh + pb > 32) idx |= aw[(wi + 1) * ws] << (32 - sh);
+  return idx & ((1u << pb) - 1u);
+}
+
 // Exact angle buckets for the undecided pairs `unc` of ONE vector, computed by the whole warp
 // (all 32 lanes call this together).  The rotated vector is rebuilt from the input row with
 // D/32 elements per lane: the butterflies pair the same elements in the same order as
 // fwht_normalized (in-lane for step < D/32, by lane-xor shuffles above), so every value is
 // bit-identical to the owner thread's.  Lane l then holds pairs l*D/64 .. and each pending pair
 // takes atan2f + the bucket expression of polar.rs:415-420; lane 0 patches the angle words.
+// Returns (to every lane) whether an index differs from the one the shortcut had guessed.
 template <int D>
-__device__ __noinline__ void fix_pairs_warp(const uint8_t* xt, int xrow, uint4 sign_mask, float scale,
+__device__ __noinline__ bool fix_pairs_warp(const uint8_t* xt, int xrow, uint4 sign_mask, float scale,
                                             unsigned long long unc, uint32_t* aw, int ws, int pb,
                                             int lane) {
   constexpr int E = D / 32;  // elements per lane (2 or 4)
@@ -99,6 +108,7 @@ __device__ __noinline__ void fix_pairs_warp(const uint8_t* xt, int xrow, uint4 s
     if ((unc >> i) & 1ull)
       mine[j] = exact_bucket(__fmul_rn(e[2 * j + 1], scale), __fmul_rn(e[2 * j], scale), 1u << pb);
   }
+  bool changed = false;
   while (unc) {
     const int i = __ffsll((long long)unc) - 1;
     unc &= unc - 1;
@@ -108,9 +118,13 @@ __device__ __noinline__ void fix_pairs_warp(const uint8_t* xt, int xrow, uint4 s
       const uint32_t t = __shfl_sync(0xffffffffu, mine[j], i / (E / 2));
       if (j == i % (E / 2)) val = t;
     }
-    if (lane == 0) patch_angle(aw, ws, i, pb, val);
+    if (lane == 0) {
+      changed = changed || read_angle(aw, ws, i, pb) != val;
+      patch_angle(aw, ws, i, pb, val);
+    }
   }
   __syncwarp();
+  return __shfl_sync(0xffffffffu, (int)changed, 0) != 0;
 }
 
 // Which of the two encode errors applies when some radius came out non-finite: a non-finite
@@ -140,6 +154,24 @@ __device__ __noinline__ float fused_dot(const uint8_t* gt, int g_slab, int p, co
   }
   return (d0 + d1) + (d2 + d3);
 }
+// The same dot in binary64 (second tier of the rotated-domain sketch): the products of binary32
+// values are exact, the sum is good to 1e-14, so what is left between this value and the reference's
+// sequential binary32 dot is that dot's own rounding and the model's error.
+template <int D>
+__device__ __noinline__ double fused_dot64(const uint8_t* gt, int g_slab, int p, const uint8_t* xt, int x_slab,
+                                           int row) {
+  double d0 = 0.0, d1 = 0.0, d2 = 0.0, d3 = 0.0;
+#pragma unroll 4
+  for (int c = 0; c < D / 4; c++) {
+    const float4 g = *reinterpret_cast<const float4*>(gt + sw_piece(g_slab, p, c));
+    const float4 x = *reinterpret_cast<const float4*>(xt + sw_piece(x_slab, row, c));
+    d0 = fma((double)g.x, (double)x.x, d0);
+    d1 = fma((double)g.y, (double)x.y, d1);
+    d2 = fma((double)g.z, (double)x.z, d2);
+    d3 = fma((double)g.w, (double)x.w, d3);
+  }
+  return (d0 + d1) + (d2 + d3);
+}
 __device__ __noinline__ float sequential_dot(const uint8_t* gt, int g_slab, int p, const uint8_t* xt,
                                              int x_slab, int row, int dim) {
   float dot = 0.0f;
@@ -152,6 +184,128 @@ __device__ __noinline__ float sequential_dot(const uint8_t* gt, int g_slab, int 
     dot = __fadd_rn(dot, __fmul_rn(g.w, x.w));
   }
   return dot;
+}
+
+// The reference's own sequence for one vector, by one warp (all 32 lanes call this together), used by
+// the rotated-domain sketch for what its shortcuts leave open: forward rotation and radii recomputed
+// from the input row (bit-identical to the encoder thread's), polar.decode with the final angle indices
+// read from the finished record (polar.rs:272-278,306-316), FastHadamardRotation::apply_inverse
+// (rotation.rs:212-221), residual (turbo.rs:268-273) and QjlQuantizer::sketch's sequential dots
+// (qjl.rs:214-217), lane t taking row c0 + t of the matrix `g` ([m][D], shared memory).  Lane t holds
+// coordinates t E .. t E + E - 1 (E = D/32); the residual passes through `scratch` (D floats, shared).
+// Returns the 32 sign bits; *bad is set for a residual that is not finite (qjl.rs:210).  A zero input
+// has a zero residual: every dot is +0, every bit 1.
+template <int D>
+__device__ __forceinline__ uint32_t exact_signs_warp(const float* __restrict__ xrow, const uint32_t* aw, int pb,
+                                                     uint4 sign_mask, float scale, const float* s_lut,
+                                                     const float* g, int c0, float* scratch, int lane, int* bad) {
+  constexpr int E = D / 32;
+  float xv[E], e[E];
+  bool zero_x = true;
+#pragma unroll
+  for (int k = 0; k < E; k++) {
+    const int i = lane * E + k;
+    const uint32_t mw = (i >> 5) == 0 ? sign_mask.x : (i >> 5) == 1 ? sign_mask.y : (i >> 5) == 2 ? sign_mask.z : sign_mask.w;
+    xv[k] = __ldg(xrow + i);
+    zero_x = zero_x && (__float_as_uint(xv[k]) & 0x7fffffffu) == 0u;
+    e[k] = __uint_as_float(__float_as_uint(xv[k]) ^ (((mw >> (i & 31)) & 1u) << 31));
+  }
+  if (__all_sync(0xffffffffu, zero_x)) return 0xffffffffu;
+  auto butterflies = [&]() {
+#pragma unroll
+    for (int step = 1; step < E; step <<= 1)
+#pragma unroll
+      for (int start = 0; start < E; start += 2 * step)
+#pragma unroll
+        for (int o = 0; o < step; o++) {
+          const float a = e[start + o], b = e[start + o + step];
+          e[start + o] = __fadd_rn(a, b);
+          e[start + o + step] = __fsub_rn(a, b);
+        }
+#pragma unroll
+    for (int step = E; step < D; step <<= 1) {
+      const int lm = step / E;
+      const bool upper = (lane & lm) != 0;
+#pragma unroll
+      for (int k = 0; k < E; k++) {
+        const float p = __shfl_xor_sync(0xffffffffu, e[k], lm);
+        e[k] = upper ? __fsub_rn(p, e[k]) : __fadd_rn(e[k], p);
+      }
+    }
+  };
+  butterflies();
+#pragma unroll
+  for (int j = 0; j < E / 2; j++) {  // encode_pair's radius, then the de-quantised pair
+    const float a = __fmul_rn(e[2 * j], scale), b = __fmul_rn(e[2 * j + 1], scale);
+    const float r = __fsqrt_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
+    const uint32_t idx = read_angle(aw, 1, lane * (E / 2) + j, pb);
+    e[2 * j] = __fmul_rn(r, s_lut[2 * idx]);
+    e[2 * j + 1] = __fmul_rn(r, s_lut[2 * idx + 1]);
+  }
+  butterflies();
+  bool finite_res = true;
+#pragma unroll
+  for (int k = 0; k < E; k++) {
+    const int i = lane * E + k;
+    const uint32_t mw = (i >> 5) == 0 ? sign_mask.x : (i >> 5) == 1 ? sign_mask.y : (i >> 5) == 2 ? sign_mask.z : sign_mask.w;
+    const float z = __fmul_rn(e[k], scale);
+    const float rec = __uint_as_float(__float_as_uint(z) ^ (((mw >> (i & 31)) & 1u) << 31));
+    const float res = __fsub_rn(xv[k], rec);
+    finite_res = finite_res && pkv_finite(res);
+    scratch[i] = res;
+  }
+  if (!__all_sync(0xffffffffu, finite_res)) *bad = PKV_VEC_NONFINITE_RESIDUAL;
+  __syncwarp();
+  // row c0 + lane of g, read with a rotation so that the 32 lanes hit 32 different banks
+  const float* gr = g + (size_t)(c0 + lane) * (D + 1);
+  float dot = 0.0f;
+#pragma unroll 8
+  for (int j = 0; j < D; j++) dot = __fadd_rn(dot, __fmul_rn(gr[j], scratch[j]));
+  const uint32_t word = __ballot_sync(0xffffffffu, dot >= 0.0f);
+  __syncwarp();
+  return word;
+}
+
+// Second kernel of the rotated-domain sketch: the exact sequence for the (vector, block of 32
+// projections) entries the encoder listed, one warp per entry, patching the sign bits named by the
+// entry's mask in the finished record.  Entry: x = global vector index | block << 31, y = mask.
+template <int D>
+__global__ void __launch_bounds__(128)
+turbo_encode_fix_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x, uint8_t* __restrict__ payload,
+                        uint64_t* err, const uint32_t* __restrict__ count, const uint2* __restrict__ list) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int m = tp.projections;
+  float* s_g = reinterpret_cast<float*>(smem);   // [m][D + 1]
+  float* s_lut = s_g + m * (D + 1);              // (cos, sin)[levels]
+  float* s_scr = s_lut + 2 * (1 << tp.polar_bits);  // [4][D]
+  const uint32_t n = *count;
+  if ((uint32_t)blockIdx.x * 4u >= n) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int levels = 1 << tp.polar_bits;
+  for (int i = threadIdx.x; i < m * D; i += 128) s_g[(i / D) * (D + 1) + (i % D)] = __ldg(tp.qjl + i);
+  for (int i = threadIdx.x; i < levels; i += 128) {
+    s_lut[2 * i] = __ldg(tp.lut + i);
+    s_lut[2 * i + 1] = __ldg(tp.lut + levels + i);
+  }
+  __syncthreads();
+  const uint4 smask = make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]);
+  const int sign_off = 4 * (D / 2) + 4 * tp.angle_words;
+  for (uint32_t it = blockIdx.x * 4u + warp; it < n; it += gridDim.x * 4u) {
+    const uint2 e = list[it];
+    const int64_t gvec = (int64_t)(e.x & 0x7fffffffu);
+    const int c0 = (int)(e.x >> 31) * 32;
+    const int batch = (int)(gvec / g.vpb), v = (int)(gvec % g.vpb);
+    uint8_t* rec = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v * g.rec_bytes;
+    int bad = 0;
+    const uint32_t word = exact_signs_warp<D>(x + pkv_vec_offset(g.L, batch, v),
+                                              reinterpret_cast<const uint32_t*>(rec + 4 * (D / 2)), tp.polar_bits, smask,
+                                              tp.scale, s_lut, s_g, c0, s_scr + warp * D, lane, &bad);
+    if (lane == 0) {
+      uint32_t* sw = reinterpret_cast<uint32_t*>(rec + sign_off) + (c0 >> 5);
+      *sw = (*sw & ~e.y) | (word & e.y);
+      if (bad) pkv_report(err, 0, gvec, bad);
+    }
+  }
 }
 
 template <int D>
@@ -177,10 +331,32 @@ struct TurboEncSmem {
 // bytes, angle + sign words a multiple of 4) stores 16-byte pieces, the other f32-radii shapes
 // one word at a time (their records are only 4-byte aligned).  BlockLogU8 records are assembled
 // whole in a word-transposed tile and written out by the warp.
-template <int D, int PB, bool DIRECT>
+//
+// ROT (PolarWithQjl with f32 radii): the QJL sketch is taken in the rotated domain.  The reference
+// signs g . res with res = x - rec, rec = S H~ p (p the de-quantised pairs, H~ = scale * H, S the signs).
+// With y the rotated vector this is (g S H~) . (y - p) up to a modelling error bounded below, so the
+// thread forms q = y - p pair by pair as it quantises, and the sketch is one TF32 product of the q
+// tile with G'' = G S H~ (rows scaled to unit length, prepared on the host in binary64): no inverse
+// butterflies and no residual in the common case.  A sign is accepted when |dot| clears the tier's
+// bound; the rest are retaken in binary32 (fused dot of q with G''), and what is still open, or
+// belongs to a vector the model does not cover (an index corrected after q was formed, radii beyond
+// 1e30, norms lost to underflow), is listed for turbo_encode_fix_kernel, which runs the reference's own
+// sequence for those vectors after this kernel (global vector indices below 2^31 fit the entries).
+// Error of the model relative to |g|:  |G'' . q - g . res| / |g| <=
+//   eta |y| + c_f (|x| + |p|) + u (|p| + |q|) + 2 u |q|,
+// eta = |d scale^2 - 1| <= 4 u (scale = fl(1 / fl(sqrt d)); zero for d = 64), c_f = (log2 d + 1) u the
+// 2-norm error of a rounded transform, u = 2^-24; the u terms are the roundings of r cos / r sin, of q,
+// of G'' and of res.  With |p|, |x| <= |y| (1 + 1e-6) that is below 21 u |y| + 3 u |q| for d <= 128;
+// the kernel adds PKV_QJL_MODEL_BOUND times an upper bound of |y| to both tiers' bounds.
+// d = 64: eta = 0, c_f = 6 u (the scale 1/8 is exact): 13 u |y| = 7.8e-7 |y|;  d = 128: 21 u |y| = 1.25e-6 |y|.
+// The binary64 tier's own bound is the rounding of the reference's sequential dot, (d + 1) u |g| |res|,
+// plus the 3 u |q| above.
+#define PKV_QJL_MODEL_BOUND(D) ((D) == 64 ? 9.0e-7f : 1.45e-6f)
+#define PKV_QJL_SEQ_BOUND(D) ((float)((D) + 4) * 5.9604645e-8f * 1.05f)
+template <int D, int PB, bool DIRECT, bool ROT>
 __global__ void __launch_bounds__(TurboEnc<D>::THREADS, D == 64 ? (DIRECT ? 4 : 3) : 2)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
-                    uint8_t* __restrict__ payload, uint64_t* err) {
+                    uint8_t* __restrict__ payload, uint64_t* err, uint32_t* fix_count, uint2* fix_list) {
   using K = TurboEnc<D>;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_bar;  // completion of the tensor-core product
@@ -199,7 +375,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   const float* s_ray_sin = s_ray_cos + tp.ray_count;
   // f32 radii never pass through shared memory (16-byte stores in the DIRECT kernel, 4-byte stores
   // otherwise); BlockLogU8 records are assembled whole in the tile
-  const bool lossy = !DIRECT && tp.lossy;
+  const bool lossy = !DIRECT && !ROT && tp.lossy;
   const int rw = lossy ? tp.radii_words : 0;  // radii words present in the shared tile
   const int tile_words = lossy ? tp.rec_words : tp.angle_words + tp.sign_words;
   uint8_t* wbase = smem + TurboEncSmem<D>::table_bytes(m, levels, tp.ray_count) +
@@ -234,7 +410,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
                    reinterpret_cast<const float4*>(x + s_off[vv]) + q);
   }
   for (int i = threadIdx.x; i < m * K::LPV; i += K::THREADS)
-    pkv_cp_async16(s_gt + sw_piece(g_slab, i / K::LPV, i % K::LPV), reinterpret_cast<const float4*>(tp.qjl) + i);
+    pkv_cp_async16(s_gt + sw_piece(g_slab, i / K::LPV, i % K::LPV),
+                   reinterpret_cast<const float4*>(ROT ? tp.qjl_rot : tp.qjl) + i);
   for (int i = threadIdx.x; i < m; i += K::THREADS) pkv_cp_async4(s_thr + i, tp.qjl + m * D + i);
   for (int i = threadIdx.x; i < lut_len; i += K::THREADS)  // cos / sin interleaved: one 8-byte read per pair
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : i < 2 * levels ? 2 * (i - levels) + 1 : i), tp.lut + i);
@@ -266,6 +443,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
   // the registers of their pairs; undecided pairs are noted in `unc`.
   constexpr int NW = PB ? K::P * PB / 32 : 1;
   unsigned long long unc = 0;
+  [[maybe_unused]] float ysq = 0.0f;   // ROT: |y|^2 from the squared radii
+  [[maybe_unused]] bool force = false;  // ROT: every sign of this vector comes from the exact sequence
   {
     uint32_t words[NW];
 #pragma unroll
@@ -273,18 +452,35 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     uint64_t bitbuf = 0;
     int nbits = 0, wk = 0;
     uint32_t rmax = 0;  // radii are >= +0 or NaN: the largest bit pattern tells if any is not finite
+    [[maybe_unused]] float rq[4];
 #pragma unroll
     for (int i = 0; i < K::P; i++) {
       const float a = y[2 * i], b = y[2 * i + 1];
       float aa = a, bb = b;
       mul2(aa, bb, a, b);  // (a * a, b * b), each rounded on its own
-      const float r = __fsqrt_rn(__fadd_rn(aa, bb));
+      const float r2 = __fadd_rn(aa, bb);
+      const float r = __fsqrt_rn(r2);
       int certain = 0;
       uint32_t idx = 0;
       if (tp.fast_bucket) idx = pkv_fast_bucket_any(a, b, pb, s_ray_cos, s_ray_sin, &certain);
       unc |= (unsigned long long)(certain ? 0u : 1u) << i;
       rmax = max(rmax, __float_as_uint(r));  // a square root is +x or NaN (either sign): unsigned order works
-      y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
+      if constexpr (ROT) {
+        // the radius leaves for the record at once; the pair's registers take q = (a, b) - r (cos, sin)
+        // of the guessed bucket (a vector whose guess is corrected later takes the exact sequence)
+        ysq = __fadd_rn(ysq, r2);
+        const float2 cs = *reinterpret_cast<const float2*>(s_lut + 2 * idx);
+        y[2 * i] = __fmaf_rn(-r, cs.x, a);
+        y[2 * i + 1] = __fmaf_rn(-r, cs.y, b);
+        if constexpr (DIRECT) {
+          rq[i & 3] = r;
+          if ((i & 3) == 3 && valid) reinterpret_cast<float4*>(my_rec)[i >> 2] = make_float4(rq[0], rq[1], rq[2], rq[3]);
+        } else {
+          if (valid) reinterpret_cast<float*>(my_rec)[i] = r;
+        }
+      } else {
+        y[2 * i] = r;  // a and b are spent: the pair's first register keeps r
+      }
       if constexpr (PB != 0) {
         const int pos = i * PB, wi = pos >> 5, sh = pos & 31;
         words[wi] |= idx << sh;
@@ -307,6 +503,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       aw[wk * K::WS] = (uint32_t)bitbuf;
     }
     if (rmax >= 0x7f800000u) code = classify_bad_vector(s_xt, K::X_SLAB, row, D);
+    if constexpr (ROT) force = rmax >= 0x7149f2cau;  // radii beyond 1e30: the residual might overflow
   }
   if (!valid) unc = 0;
   for (unsigned pending = __ballot_sync(0xffffffffu, unc != 0); pending; pending &= pending - 1) {
@@ -314,11 +511,14 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     const unsigned long long um =
         ((unsigned long long)__shfl_sync(0xffffffffu, (uint32_t)(unc >> 32), src) << 32) |
         __shfl_sync(0xffffffffu, (uint32_t)unc, src);
-    fix_pairs_warp<D>(s_xt, warp * K::TV + src,
-                      make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]), tp.scale, um,
-                      s_w + src + rw * K::WS, K::WS, pb, lane);
+    const bool changed = fix_pairs_warp<D>(
+        s_xt, warp * K::TV + src, make_uint4(tp.sign_mask[0], tp.sign_mask[1], tp.sign_mask[2], tp.sign_mask[3]),
+        tp.scale, um, s_w + src + rw * K::WS, K::WS, pb, lane);
+    if constexpr (ROT) force = force || (changed && lane == src);
   }
-  if constexpr (DIRECT) {
+  if constexpr (ROT) {
+    // radii already stored
+  } else if constexpr (DIRECT) {
     if (valid) {
 #pragma unroll
       for (int k = 0; k < K::P / 4; k++)
@@ -328,7 +528,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll
     for (int i = 0; i < K::P; i++) reinterpret_cast<float*>(my_rec)[i] = y[2 * i];
   }
-  if constexpr (!DIRECT)  // direct stores imply f32 radii: keep this block out of that kernel's code
+  if constexpr (!DIRECT && !ROT)  // direct stores and the rotated-domain sketch imply f32 radii
   if (tp.lossy) {
     // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371),
     // straight from the radii in the registers (y[2i]; the reconstruction below still uses them).
@@ -398,7 +598,115 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     w[(K::P / 4 + 1) * K::WS] = __float_as_uint(mx);
   }
 
-  if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
+  if constexpr (ROT) {
+   if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
+    // q replaces x in the tile: it is the A operand of the sketch
+    float2 n2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < D; i += 4) {
+      n2 = ffma2(make_float2(y[i], y[i + 1]), make_float2(y[i], y[i + 1]), n2);
+      n2 = ffma2(make_float2(y[i + 2], y[i + 3]), make_float2(y[i + 2], y[i + 3]), n2);
+      *reinterpret_cast<float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4))) =
+          make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
+    }
+    // upper bounds of |q| and |y|; sums under 1e-30 have lost squares to underflow and bound nothing
+    // (this also catches the all-zero vector): such vectors take the exact sequence
+    const float nsq = n2.x + n2.y;
+    if (!(nsq >= 1.0e-30f) || !(ysq >= 1.0e-30f)) force = true;
+    const float nq = __fmul_rn(__fsqrt_rn(nsq), 1.0001f);
+    const float model = __fmul_rn(PKV_QJL_MODEL_BOUND(D), __fmul_rn(__fsqrt_rn(ysq), 1.0001f));
+    const float tau1 = fmaf(PKV_QJL_TF32_BOUND, nq, model) + PKV_QJL_ABS_BOUND;
+    const float tau2 = fmaf(PKV_QJL_SEQ_BOUND(D), nq, model) + PKV_QJL_ABS_BOUND;
+
+    pkv_tc::fence_smem_to_async();
+    __syncthreads();
+    const uint32_t tmem_d = s_tmem;
+    if (threadIdx.x == 0 && !tp.skip_issue) {
+      pkv_tc::fence_after_sync();
+      const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, m > 32 ? 64 : 32);
+      const uint32_t a0 = pkv_tc::smem_u32(s_xt), b0 = pkv_tc::smem_u32(s_gt);
+#pragma unroll 1
+      for (int k = 0; k < D / 8; k++)
+        pkv_tc::mma_tf32(tmem_d, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
+                         pkv_tc::smem_desc_sw128(b0 + (k >> 2) * g_slab + (k & 3) * 32), idesc, k > 0);
+      pkv_tc::mma_commit(&s_bar);
+    }
+    const bool done =
+        __all_sync(0xffffffffu, pkv_tc::mbar_wait(&s_bar, 0, tp.skip_issue ? 256 : pkv_tc::kWaitPolls));
+    pkv_tc::fence_after_sync();
+    uint32_t* sw = w + (rw + tp.angle_words) * K::WS;
+    float* s_bound = reinterpret_cast<float*>(s_off);                      // [32] (the offsets are spent)
+    uint16_t* s_items = reinterpret_cast<uint16_t*>(s_bound + K::TV);      // [PKV_QJL_LIST_CAP]
+    const bool settle = valid && !code;  // this vector's signs matter
+    if (done) {
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        if (c >= m) break;
+        float dots[32];
+        pkv_tc::tmem_load32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, dots);
+        uint32_t bits = 0, flagged = 0;
+#pragma unroll
+        for (int p = 0; p < 32; p++) {  // rows of G'' have unit length: one bound for all of them
+          flagged |= (fabsf(dots[p]) > tau1 ? 0u : 1u) << p;
+          bits |= (dots[p] >= 0.0f ? 1u : 0u) << p;
+        }
+        if (!settle || force) flagged = 0;
+        // Binary64 tier for the flagged (vector, row) pairs of the whole warp, spread over the lanes
+        // through a prefix-summed list; pairs beyond the list's capacity are taken by their owner.
+        // What this tier leaves open is noted in `open`.
+        uint32_t open = 0;
+        const uint32_t cnt = __popc(flagged);
+        uint32_t incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += t;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        if (total) {
+          constexpr uint32_t CAP = PKV_QJL_LIST_CAP;
+          s_bound[v] = tau2;
+          uint32_t pos = incl - cnt;
+          for (uint32_t f = flagged; f; f &= f - 1, pos++)
+            if (pos < CAP) s_items[pos] = (uint16_t)((v << 5) | (__ffs(f) - 1));
+          __syncwarp();
+          const uint32_t n_list = min(total, CAP);
+          for (uint32_t e = lane; e < n_list; e += 32) {
+            const uint32_t it = s_items[e];
+            const double dot = fused_dot64<D>(s_gt, g_slab, c + (int)(it & 31u), s_xt, K::X_SLAB,
+                                              warp * K::TV + (int)(it >> 5));
+            const uint32_t res = !(fabs(dot) > (double)s_bound[it >> 5]) ? 0x4000u : (dot >= 0.0 ? 0x8000u : 0u);
+            s_items[e] = (uint16_t)(it | res);
+          }
+          __syncwarp();
+          pos = incl - cnt;
+          for (uint32_t f = flagged; f; f &= f - 1, pos++) {
+            const int p = __ffs(f) - 1;
+            uint32_t res;
+            if (pos < CAP) {
+              res = s_items[pos];
+            } else {
+              const double dot = fused_dot64<D>(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row);
+              res = !(fabs(dot) > (double)tau2) ? 0x4000u : (dot >= 0.0 ? 0x8000u : 0u);
+            }
+            if (res & 0x4000u) open |= 1u << p;
+            else bits = (res & 0x8000u) ? (bits | (1u << p)) : (bits & ~(1u << p));
+          }
+          __syncwarp();
+        }
+        // What is still open goes on the list of turbo_encode_fix_kernel, which runs the reference's
+        // own sequence for the vector and patches these bits of the record.
+        if (settle && (force || open != 0)) {
+          const uint32_t gvec = (uint32_t)((int64_t)batch * g.vpb + v0 + v);
+          fix_list[atomicAdd(fix_count, 1u)] = make_uint2(gvec | ((uint32_t)(c >> 5) << 31), force ? 0xffffffffu : open);
+        }
+        sw[(c >> 5) * K::WS] = bits;
+      }
+    } else if (threadIdx.x == 0) {
+      pkv_report(err, 0, 0, PKV_VEC_DEVICE_WAIT);
+    }
+   }
+  } else if (tp.mode == PKV_TURBO_POLAR_WITH_QJL) {
     // polar.decode (polar.rs:272-278,306-316): de-quantised pairs from the final indices
     {
       const uint32_t mask = (uint32_t)levels - 1u;

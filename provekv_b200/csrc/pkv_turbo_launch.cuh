@@ -30,6 +30,7 @@ inline TurboParams make_params(const pkv_turbo_profile* p) {
   tp.ray_count = p->ray_count;
   tp.skip_issue = pkv_skip_tensor_issue();
   tp.qjl = p->qjl_dev;
+  tp.qjl_rot = p->qjl_rot_dev;
   tp.lut = p->lut_dev;
   return tp;
 }
