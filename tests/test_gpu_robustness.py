@@ -180,3 +180,28 @@ def test_error_word_order_over_two_batches():
     assert run(0, 1) == (L.VEC_NORM_RANGE, 123)
     assert run(1, 1) == (L.VEC_NONFINITE_INPUT, 45)
     assert run(0, 2) == (L.VEC_NONFINITE_INPUT, vpb + 45)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("bits,m", [(4, 32), (8, 32), (3, 64)])
+def test_rotated_domain_sketch_equals_the_residual_sketch(oracle_mod, dim, bits, m):
+    """The two routes to the QJL signs -- the sketch of q = y - p with G S H~ (default for f32 radii) and
+    the sketch of the residual after the inverse transform -- give the same records, which are the
+    oracle's; outlier channels and a zero vector included."""
+    n = 20000
+    signs, qjl = tables.rademacher_signs(dim, SEED), tables.qjl_matrix(dim, m, SEED)
+    x = synthetic_kv(n, dim, seed=31)
+    x[:, 3] *= np.float32(20.0)
+    x[77] = 0.0
+    prof = pk.TurboProfile(dim, bits, signs, qjl, seed=SEED)
+    lib = L.lib()
+    got = prof.encode_batch_compact(x)
+    lib.pkv_test_turbo_encode_legacy(1)
+    try:
+        legacy = prof.encode_batch_compact(x)
+    finally:
+        lib.pkv_test_turbo_encode_legacy(0)
+    assert got == legacy
+    st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=bits, mode=1, radii_codec=0,
+                                               libm_mode=oracle_mod.LIBM_PORTABLE)
+    assert st == 0 and got[L.TQB1_HEADER_BYTES:] == payload.tobytes()
