@@ -85,6 +85,16 @@ const char* pkv_last_cuda_error(void);
 #define PKV_RADII_F32 0        /* RadiusCodecProfileV1::F32 */
 #define PKV_RADII_BLOCK_LOG_U8 1 /* RadiusCodecProfileV1::BlockLogU8 */
 
+/* The reference takes ln / exp of the BlockLogU8 radii from the platform libm through Rust std
+ * (turbo-quant/src/radius.rs:61,143); glibc's binary32 functions are not correctly rounded, so those
+ * bytes are defined by the machine that wrote them.  PKV_LIBM_PORTABLE: the correctly rounded functions
+ * of include/pkv_portable_math.h (the same bits on every machine).  PKV_LIBM_PLATFORM: the bits of this
+ * host's logf / expf; the first profile created with it scans every binary32 argument on the host cores
+ * (a few seconds, once per process and function) and uploads the arguments where the two differ.
+ * PKV_ERR_UNSUPPORTED if the host function is ever more than one unit away from correct rounding. */
+#define PKV_LIBM_PORTABLE 0
+#define PKV_LIBM_PLATFORM 1
+
 typedef struct pkv_fib_config {
   int32_t dim;           /* ambient_dim; kernels: 64 or 128 */
   int32_t block_dim;     /* k; kernels: 4 */
@@ -100,7 +110,7 @@ typedef struct pkv_turbo_config {
   int32_t mode;        /* PKV_TURBO_* */
   int32_t projections; /* QJL rows m (multiple of 8, <= 64 in the kernels) */
   int32_t radii_codec; /* PKV_RADII_* */
-  int32_t reserved;
+  int32_t libm;        /* PKV_LIBM_*: which logf / expf the BlockLogU8 radii use */
   uint64_t seed;       /* written to the TQB1 header only */
 } pkv_turbo_config;
 
@@ -329,6 +339,13 @@ int pkv_turbo_decode_batches_compact(const pkv_turbo_profile* p, const uint8_t* 
 int pkv_tqb1_header_write(const pkv_turbo_profile* p, uint32_t n_vectors, uint8_t* out38);
 int pkv_tqb1_header_parse(const pkv_turbo_profile* p, const uint8_t* bytes, int64_t len,
                           uint32_t* n_vectors);
+
+/* The binary32 arguments (bit patterns, ascending) on which this host's logf (function 0, positive
+ * normal arguments) or expf (function 1, |x| <= 89) differs from the portable function; host-only,
+ * needs no GPU.  keys_out may be null to ask for the count; *all_one_unit = 1 if every difference is
+ * one unit in the last place. */
+int pkv_host_libm_exceptions(int32_t function, uint32_t* keys_out, int64_t capacity, int64_t* count,
+                             int32_t* all_one_unit);
 
 /* Number of kernel launches this process has issued through the library. */
 int64_t pkv_launch_count(void);

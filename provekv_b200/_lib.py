@@ -40,6 +40,7 @@ ARGMIN_PAIRWISE, ARGMIN_SEQUENTIAL = 0, 1
 FIB_NUMERICS_AUTO, FIB_NUMERICS_BATCH, FIB_NUMERICS_SINGLE = 0, 1, 2
 TURBO_POLAR_ONLY, TURBO_POLAR_WITH_QJL = 0, 1
 RADII_F32, RADII_BLOCK_LOG_U8 = 0, 1
+LIBM_PORTABLE, LIBM_PLATFORM = 0, 1
 DST_F32, DST_F16, DST_BF16 = 0, 1, 2  # PKV_DST_*: element type of the patched cache
 FB2_HEADER_BYTES, TQB1_HEADER_BYTES = 19, 38
 
@@ -51,7 +52,7 @@ class FibConfigC(C.Structure):
 
 class TurboConfigC(C.Structure):
     _fields_ = [("dim", C.c_int32), ("bits", C.c_int32), ("mode", C.c_int32),
-                ("projections", C.c_int32), ("radii_codec", C.c_int32), ("reserved", C.c_int32),
+                ("projections", C.c_int32), ("radii_codec", C.c_int32), ("libm", C.c_int32),
                 ("seed", C.c_uint64)]
 
 
@@ -154,6 +155,7 @@ _SIGS = {
                                                  C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_tqb1_header_write": (C.c_int, [_V, C.c_uint32, _V]),
     "pkv_tqb1_header_parse": (C.c_int, [_V, _V, C.c_int64, C.POINTER(C.c_uint32)]),
+    "pkv_host_libm_exceptions": (C.c_int, [C.c_int32, _V, C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
     "pkv_launch_count": (C.c_int64, []),
     "pkv_test_skip_tensor_issue": (C.c_int, [C.c_int]),
     "pkv_test_turbo_encode_legacy": (C.c_int, [C.c_int]),

@@ -130,6 +130,38 @@ __device__ __forceinline__ float pkv_f16_bits_to_f32(uint32_t h) {
   return __uint_as_float(sign | ((exp + 127 - 15) << 23) | (man << 13));
 }
 
+// ---- host libm reproduction (pkv_libm.cu) ---------------------------------
+// Arguments on which the host libm's logf / expf differs from the portable (correctly rounded)
+// function, always by one unit: sorted keys, one direction bit per key, a bitmap in front.
+#define PKV_LIBM_FN_LOG 0
+#define PKV_LIBM_FN_EXP 1
+#define PKV_ULP_HASH_MUL 0x9E3779B1u
+struct PkvUlpTable {
+  const uint32_t* keys;   // argument bit patterns, ascending (unsigned)
+  const uint32_t* dirs;   // bit i set: host bits = portable bits + 1, clear: - 1
+  const uint32_t* bloom;  // 2^bloom_log2 bits, bit (key * PKV_ULP_HASH_MUL) >> (32 - bloom_log2) set for every key
+  uint32_t n;
+  uint32_t bloom_log2;
+};
+int pkv_ulp_table_get(int kind, PkvUlpTable* out);
+
+// The host libm's value of the function at `arg`, from the portable value; a null table = portable.
+__device__ __forceinline__ float pkv_ulp_adjust(const PkvUlpTable& t, float arg, float portable) {
+  if (t.keys == nullptr) return portable;
+  const uint32_t u = __float_as_uint(arg);
+  const uint32_t b = (u * PKV_ULP_HASH_MUL) >> (32u - t.bloom_log2);
+  if (!((__ldg(t.bloom + (b >> 5)) >> (b & 31u)) & 1u)) return portable;
+  uint32_t lo = 0, hi = t.n;  // first key >= u
+  while (lo < hi) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (__ldg(t.keys + mid) < u) lo = mid + 1;
+    else hi = mid;
+  }
+  if (lo >= t.n || __ldg(t.keys + lo) != u) return portable;
+  const bool up = (__ldg(t.dirs + (lo >> 5)) >> (lo & 31u)) & 1u;
+  return __uint_as_float(__float_as_uint(portable) + (up ? 1u : 0xffffffffu));
+}
+
 // ---- host-side objects ---------------------------------------------------
 
 #define PKV_WS_ERR_WORDS 16
@@ -172,6 +204,8 @@ struct pkv_turbo_profile {
   float* qjl_dev;           // projections x dim, then one sign-shortcut threshold per row
   float* qjl_rot_dev;       // projections x dim: G S H~ with unit-length rows (the rotated-domain sketch)
   float* lut_dev;           // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
+  PkvUlpTable logf_table;   // PKV_LIBM_PLATFORM: the host libm's logf / expf (keys null = portable)
+  PkvUlpTable expf_table;
   PkvWorkspace ws;
   std::mutex ws_mutex;
 };

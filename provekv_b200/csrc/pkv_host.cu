@@ -606,6 +606,7 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
   if (with_qjl && (cfg->projections <= 0 || !qjl)) return PKV_ERR_INVALID_ARGUMENT;
   if (cfg->radii_codec != PKV_RADII_F32 && cfg->radii_codec != PKV_RADII_BLOCK_LOG_U8)
     return PKV_ERR_INVALID_ARGUMENT;
+  if (cfg->libm != PKV_LIBM_PORTABLE && cfg->libm != PKV_LIBM_PLATFORM) return PKV_ERR_INVALID_ARGUMENT;
   const int pb = with_qjl ? cfg->bits - 1 : cfg->bits;
   if ((d != 64 && d != 128) || pb > 8) return PKV_ERR_UNSUPPORTED;
   if (with_qjl && (cfg->projections % 32 || cfg->projections > 64)) return PKV_ERR_UNSUPPORTED;
@@ -631,6 +632,16 @@ int pkv_turbo_profile_create(const pkv_turbo_config* cfg, const float* signs, co
   p->qjl_dev = nullptr;
   p->qjl_rot_dev = nullptr;
   p->lut_dev = nullptr;
+  p->logf_table = PkvUlpTable{nullptr, nullptr, nullptr, 0, 0};
+  p->expf_table = PkvUlpTable{nullptr, nullptr, nullptr, 0, 0};
+  if (cfg->libm == PKV_LIBM_PLATFORM && cfg->radii_codec == PKV_RADII_BLOCK_LOG_U8) {
+    int st = pkv_ulp_table_get(PKV_LIBM_FN_LOG, &p->logf_table);
+    if (st == PKV_OK) st = pkv_ulp_table_get(PKV_LIBM_FN_EXP, &p->expf_table);
+    if (st != PKV_OK) {
+      delete p;
+      return st;
+    }
+  }
   const int levels = 1 << pb;
   float lut[1024];
   for (int i = 0; i < levels; i++) {

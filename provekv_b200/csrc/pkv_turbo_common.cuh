@@ -40,6 +40,8 @@ struct TurboParams {
   const float* qjl;    // [m][dim] then m sign-shortcut thresholds
   const float* qjl_rot;  // [m][dim]: rows of G S H~ scaled to unit length (the rotated-domain sketch)
   const float* lut;    // cos[L], sin[L], ray_cos[ray_count], ray_sin[ray_count]
+  PkvUlpTable logf_table;  // BlockLogU8 radii with the host libm's logf / expf; keys null = portable functions
+  PkvUlpTable expf_table;
 };
 
 // fwht_normalized, turbo-quant/src/rotation.rs:379-398: butterflies for

@@ -116,7 +116,7 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
 #pragma unroll
         for (int b = 0; b < 4; b++) {
           const float t = __fadd_rn(mn, __fmul_rn(span, s_q255[(q4 >> (8 * b)) & 0xffu]));
-          const float r = code ? 0.0f : pkv_expf_portable(t);
+          const float r = code ? 0.0f : pkv_ulp_adjust(tp.expf_table, t, pkv_expf_portable(t));
           if (!code && !pkv_finite(r)) code = PKV_VEC_BAD_RADIUS;  // polar.rs:127-133
           y[2 * (4 * k + b)] = r;
         }

@@ -131,7 +131,10 @@ __device__ __noinline__ bool fix_pairs_warp(const uint8_t* xt, int xrow, uint4 s
 // input value (turbo.rs:263, checked first by the reference) or an overflow in the butterflies
 // (PolarCode::from_parts, polar.rs:127-133).
 // The exact logarithm of the BlockLogU8 coder, kept out of line: four call sites, two of them rare.
-__device__ __noinline__ float exact_logf(float r) { return pkv_logf_portable(r); }
+// (with a table of the host libm's deviations: that libm's logf, bit for bit)
+__device__ __noinline__ float exact_logf(float r, const PkvUlpTable& t) {
+  return pkv_ulp_adjust(t, r, pkv_logf_portable(r));
+}
 
 __device__ __noinline__ int classify_bad_vector(const uint8_t* xt, int slab, int row, int dim) {
   for (int i = 0; i < dim; i++)
@@ -533,7 +536,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     // CompressedRadiiV1::compress, BlockLogU8 (radius.rs:58-77), min/max after the bytes (wire.rs:368-371),
     // straight from the radii in the registers (y[2i]; the reconstruction below still uses them).
     // The logarithm is monotone, so min / max of the logs are the logs of the smallest / largest
-    // radius: two exact logarithms per vector (radii within 1e-5 of an extreme are taken exactly
+    // radius: two exact logarithms per vector (radii within 4e-5 of an extreme are taken exactly
     // too, in case the rounded logarithm is not monotone to the last bit there).  The 8-bit codes
     // come from the fast logarithm where that provably gives the reference's code
     // (pkv_fast_radius_code); the rare others are redone with the exact one from a copy of the
@@ -545,8 +548,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       rmin = fminf(rmin, r);
       rmax = fmaxf(rmax, r);
     }
-    float mn = exact_logf(rmin), mx = exact_logf(rmax);
-    const float near_min = __fmul_rn(rmin, 1.00001f), near_max = __fmul_rn(rmax, 0.99999f);
+    float mn = exact_logf(rmin, tp.logf_table), mx = exact_logf(rmax, tp.logf_table);
+    const float near_min = __fmul_rn(rmin, 1.00004f), near_max = __fmul_rn(rmax, 0.99996f);
     bool ties = false;
 #pragma unroll
     for (int i = 0; i < K::P; i++) {
@@ -560,8 +563,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll 1
       for (int i = 0; i < K::P; i++) {
         const float r = rl[i];
-        if (r <= near_min) mn = fminf(mn, exact_logf(r));
-        if (r >= near_max) mx = fmaxf(mx, exact_logf(r));
+        if (r <= near_min) mn = fminf(mn, exact_logf(r, tp.logf_table));
+        if (r >= near_max) mx = fmaxf(mx, exact_logf(r, tp.logf_table));
       }
     }
     float span = __fsub_rn(mx, mn);
@@ -587,7 +590,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       while (unsure) {
         const int i = __ffsll((long long)unsure) - 1;
         unsure &= unsure - 1;
-        float nrm = __fdiv_rn(__fsub_rn(exact_logf(rl[i]), mn), span);
+        float nrm = __fdiv_rn(__fsub_rn(exact_logf(rl[i], tp.logf_table), mn), span);
         nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
         const uint32_t c8 = (uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu;
         const int sh = 8 * (i & 3);

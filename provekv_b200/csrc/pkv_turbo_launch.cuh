@@ -32,6 +32,8 @@ inline TurboParams make_params(const pkv_turbo_profile* p) {
   tp.qjl = p->qjl_dev;
   tp.qjl_rot = p->qjl_rot_dev;
   tp.lut = p->lut_dev;
+  tp.logf_table = p->logf_table;
+  tp.expf_table = p->expf_table;
   return tp;
 }
 

@@ -56,7 +56,7 @@ __device__ __forceinline__ float score_record(const W& w, const TurboParams& tp,
     float r = 0.0f;
     if constexpr (!FIXED) {
       const float t = __fadd_rn(mn, __fmul_rn(span, s_q255[(w(i >> 2) >> (8 * (i & 3))) & 0xffu]));
-      r = code ? 0.0f : pkv_expf_portable(t);
+      r = code ? 0.0f : pkv_ulp_adjust(tp.expf_table, t, pkv_expf_portable(t));
       if (!code && !pkv_finite(r)) code = PKV_VEC_BAD_RADIUS;  // polar.rs:127-133
     }
     return r;

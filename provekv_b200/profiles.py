@@ -133,12 +133,17 @@ class TurboProfile(_ProfileBase):
 
     def __init__(self, dim: int, bits: int, signs: np.ndarray, qjl: np.ndarray | None = None, *,
                  mode: int = L.TURBO_POLAR_WITH_QJL, radii_codec: int = L.RADII_F32, seed: int = 0,
-                 cos_lut: np.ndarray | None = None, sin_lut: np.ndarray | None = None):
+                 cos_lut: np.ndarray | None = None, sin_lut: np.ndarray | None = None,
+                 libm: int = L.LIBM_PORTABLE):
+        """libm (BlockLogU8 radii only): L.LIBM_PORTABLE = correctly rounded logf / expf, the same bytes on
+        every machine; L.LIBM_PLATFORM = this host's libm bit for bit, what the Rust reference writes here
+        (the first such profile of a process scans every binary32 argument on the host: a few seconds)."""
         self.dim, self.bits, self.mode, self.radii_codec, self.seed = dim, bits, mode, radii_codec, seed
+        self.libm = libm
         self.signs = np.ascontiguousarray(signs, dtype=np.float32)
         self.qjl = None if qjl is None else np.ascontiguousarray(qjl, dtype=np.float32)
         self.projections = 0 if self.qjl is None else self.qjl.shape[0]
-        cfg = L.TurboConfigC(dim, bits, mode, self.projections, radii_codec, 0, seed)
+        cfg = L.TurboConfigC(dim, bits, mode, self.projections, radii_codec, libm, seed)
         cl = None if cos_lut is None else np.ascontiguousarray(cos_lut, np.float32)
         sl = None if sin_lut is None else np.ascontiguousarray(sin_lut, np.float32)
         h = C.c_void_p()
@@ -151,7 +156,7 @@ class TurboProfile(_ProfileBase):
     @classmethod
     def from_seed(cls, dim: int, bits: int, projections: int, seed: int, *,
                   mode: int = L.TURBO_POLAR_WITH_QJL, radii_codec: int = L.RADII_F32,
-                  sign_stream: str = "pcg64") -> "TurboProfile":
+                  sign_stream: str = "pcg64", libm: int = L.LIBM_PORTABLE) -> "TurboProfile":
         """sign_stream "chacha8": the Hadamard signs come from the reference's own ChaCha8 bool
         stream (tables.reference_hadamard_signs), which is all a polar-only profile needs from the
         seed; the QJL matrix is NumPy-seeded either way."""
@@ -159,7 +164,7 @@ class TurboProfile(_ProfileBase):
         if sign_stream not in ("pcg64", "chacha8"):
             raise ValueError("sign_stream must be 'pcg64' or 'chacha8'")
         signs = (tables.reference_hadamard_signs if sign_stream == "chacha8" else tables.rademacher_signs)(dim, seed)
-        return cls(dim, bits, signs, qjl, mode=mode, radii_codec=radii_codec, seed=seed)
+        return cls(dim, bits, signs, qjl, mode=mode, radii_codec=radii_codec, seed=seed, libm=libm)
 
     def encode_batch_compact(self, vectors: np.ndarray) -> bytes:
         x = np.ascontiguousarray(vectors, dtype=np.float32).reshape(-1, self.dim)

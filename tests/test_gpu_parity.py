@@ -240,3 +240,49 @@ def test_polar_only_profile_on_the_reference_sign_stream(oracle_mod, dim):
     st, want, _, _ = oracle_mod.turbo_decode(payload, dim, signs, bits=4, mode=L.TURBO_POLAR_ONLY, projections=0,
                                             radii_codec=L.RADII_F32, libm_mode=oracle_mod.LIBM_PORTABLE)
     assert np.array_equal(prof.decode_batch_compact(got).view(np.uint32), want.view(np.uint32))
+
+
+def _c2_vectors():
+    return synthetic_kv(344_064, 64, seed=2, groups=1536)
+
+
+@pytest.mark.parametrize("lossy", [False, True])
+def test_c2_bytes_against_the_host_libm_oracle(oracle_mod, lossy):
+    """What the Rust reference would write on this machine (oracle in PLATFORM mode: host atan2f, logf,
+    expf) against the GPU, C2 at full size.
+    BlockLogU8 radii: a profile created with LIBM_PLATFORM reproduces the host's logf bit for bit, so the
+    radius bytes (codes, min, max) of every vector are equal; a LIBM_PORTABLE profile differs in a few
+    bytes per thousand vectors (the one-unit deviations of glibc's logf), counted and bounded here.
+    Angle buckets: the kernels take atan2f correctly rounded, glibc's differs by a unit on 16 % of the
+    arguments, which moves a bucket only when the angle sits within that unit of a bucket boundary:
+    about 1e-7 of the pairs, i.e. a handful of the 344,064 vectors (their QJL signs follow)."""
+    dim, m = 64, 32
+    rc = L.RADII_BLOCK_LOG_U8 if lossy else L.RADII_F32
+    signs, qjl = _turbo_tables(dim, m)
+    x = _c2_vectors()
+    n = x.shape[0]
+    st, plat, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=4, mode=1, radii_codec=rc,
+                                            libm_mode=oracle_mod.LIBM_PLATFORM, nthreads=8)
+    assert st == 0
+    plat = plat.reshape(n, -1)
+    radii_bytes = 32 + 8 if lossy else 128
+    for libm in ((L.LIBM_PLATFORM, L.LIBM_PORTABLE) if lossy else (L.LIBM_PORTABLE,)):
+        prof = pk.TurboProfile(dim, 4, signs, qjl, radii_codec=rc, seed=SEED, libm=libm)
+        got = np.frombuffer(prof.encode_batch_compact(x), np.uint8)[L.TQB1_HEADER_BYTES:].reshape(n, -1)
+        radii_diff = (got[:, :radii_bytes] != plat[:, :radii_bytes])
+        angle_diff = (got[:, radii_bytes:radii_bytes + 12] != plat[:, radii_bytes:radii_bytes + 12]).any(axis=1)
+        print(f"lossy={lossy} libm={libm}: {int(radii_diff.sum())} radius bytes in {int(radii_diff.any(axis=1).sum())} "
+              f"vectors, {int(angle_diff.sum())} vectors with another angle bucket, of {n}")
+        assert angle_diff.sum() <= 8
+        if not lossy or libm == L.LIBM_PLATFORM:
+            assert radii_diff.sum() == 0
+            assert (got != plat).any(axis=1).sum() == angle_diff.sum()  # nothing else differs
+        else:
+            assert 0 < radii_diff.sum() <= 0.02 * n  # ~5 bytes per 1000 vectors
+        if lossy and libm == L.LIBM_PLATFORM:
+            # decode with the host's expf: bit-identical to the oracle's platform decode
+            wire = oracle_mod.tqb1_header(dim, 4, 1, m, rc, SEED, n) + plat.tobytes()
+            dec = prof.decode_batch_compact(wire)
+            st, want, _, _ = oracle_mod.turbo_decode(plat, dim, signs, bits=4, mode=1, projections=m, radii_codec=rc,
+                                                    libm_mode=oracle_mod.LIBM_PLATFORM, nthreads=8)
+            assert st == 0 and np.array_equal(dec.view(np.uint32), want.view(np.uint32))

@@ -81,3 +81,35 @@ def test_bucket_thresholds_monotone(oracle_mod):
         assert idx.max() == levels - 1 and idx.min() == 0
     assert L.pkvo_angle_bucket(_f32(math.pi), 8) == 0   # normalized == 1.0 -> levels % levels
     assert L.pkvo_angle_bucket(0.0, 8) == 4
+
+
+def test_host_libm_exception_lists_are_exact(oracle_mod):
+    """pkv_host_libm_exceptions: the library's scan of every binary32 argument for the inputs on which
+    the host logf / expf and the portable functions differ.  Checked against the oracle's two libm
+    modes: every listed argument differs by exactly one unit, and a random sample of unlisted
+    arguments does not differ at all."""
+    from provekv_b200 import _lib as L
+    lib, O = L.lib(), oracle_mod.lib()
+    rng = np.random.default_rng(1)
+    for fn, name, lo, hi in ((0, "pkvo_logf", 0x00800000, 0x7f7fffff), (1, "pkvo_expf", 0, 0x42b20000)):
+        n, ok = C.c_int64(0), C.c_int32(0)
+        assert lib.pkv_host_libm_exceptions(fn, None, 0, C.byref(n), C.byref(ok)) == L.OK
+        assert ok.value == 1 and 1000 < n.value < 5_000_000
+        keys = np.zeros(n.value, np.uint32)
+        assert lib.pkv_host_libm_exceptions(fn, keys.ctypes.data_as(C.c_void_p), n.value, C.byref(n), None) == L.OK
+        assert np.all(np.diff(keys.astype(np.int64)) > 0)
+        f = getattr(O, name)
+        for k in keys[rng.integers(0, keys.size, 2000)]:
+            x = float(np.array([k], np.uint32).view(np.float32)[0])
+            a = np.float32(f(x, PORTABLE)).view(np.uint32).astype(np.int64)
+            b = np.float32(f(x, PLATFORM)).view(np.uint32).astype(np.int64)
+            assert abs(int(a) - int(b)) == 1, hex(int(k))
+        listed = set(keys.tolist())
+        sample = rng.integers(lo, hi, 4000, dtype=np.uint32)
+        if fn == 1:
+            sample = sample | (rng.integers(0, 2, 4000, dtype=np.uint32) << np.uint32(31))
+        for k in sample:
+            if int(k) in listed:
+                continue
+            x = float(np.array([k], np.uint32).view(np.float32)[0])
+            assert np.float32(f(x, PORTABLE)).view(np.uint32) == np.float32(f(x, PLATFORM)).view(np.uint32), hex(int(k))
