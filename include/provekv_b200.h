@@ -234,6 +234,17 @@ int pkv_fib_decode_patch_dev_as(const pkv_fib_profile* p, const uint8_t* payload
                                 int64_t payload_batch_stride, const pkv_layout* layout,
                                 void* cache_dev, int32_t dst_dtype, uint64_t* err_dev, void* stream);
 
+/* FibQuantizer::decode (fib-quant/src/codec.rs:506-537), the binary64 decoder KVecCodec::decode runs on a
+ * single FB1 payload (proveKV/src/codec.rs:612-638): widened codewords, StoredRotation::apply_inverse in
+ * binary64 (rotation.rs:118-130), `(value * norm) as f32`.  Its output differs from the batched f32 decoder's
+ * in the last bits (fib-quant/tests/decode_batch_fast_parity.rs allows 1e-4).  `_dev`: records and output in
+ * device memory, addressed like the decode-and-patch calls (n_replicas must be 1).  The host form takes n
+ * bare records ([norm][indices], no header) and writes n x dim floats. */
+int pkv_fib_decode_exact_dev(const pkv_fib_profile* p, const uint8_t* payload_dev, int64_t payload_batch_stride,
+                             const pkv_layout* layout, float* out_dev, uint64_t* err_dev, void* stream);
+int pkv_fib_decode_exact(const pkv_fib_profile* p, const uint8_t* records_host, int64_t n, float* out_host,
+                         int32_t* vec_code, int64_t* vec_index);
+
 /* One launch for a cache made of separately allocated tensors (a framework's per-layer K and V
  * tensors, proveKV/scripts/ppl_validate_multi_agent.py:282-293): batch b of the launch (flattened
  * n_batches index) is written at cache_dev + batch_offsets_dev[b] elements, plus the layout's base,

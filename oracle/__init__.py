@@ -103,6 +103,21 @@ def fib_decode(payload, dim, rot, codebook, *, k=4, norm_format=0, nthreads=1):
     return st, out, code.value, idx.value
 
 
+def fib_decode_exact(payload, dim, rot, codebook, *, k=4, norm_format=0):
+    """FibQuantizer::decode (binary64 inverse rotation) per record -> (status, out [n, dim] f32, code, index)."""
+    cb = _f32(codebook)
+    rec = fib_record_bytes(dim, k, cb.shape[0], norm_format)
+    payload = np.ascontiguousarray(payload, np.uint8).reshape(-1, rec)
+    n = payload.shape[0]
+    rot = np.ascontiguousarray(rot, np.float64)
+    out = np.zeros((n, dim), np.float32)
+    code, idx = C.c_int32(0), C.c_int64(-1)
+    st = lib().pkvo_fib_decode_exact_batch(_p(payload, C.c_uint8), C.c_int64(n), dim, k, cb.shape[0], norm_format,
+                                           _p(rot, C.c_double), _p(cb, C.c_float), _p(out, C.c_float),
+                                           C.byref(code), C.byref(idx))
+    return st, out, code.value, idx.value
+
+
 def turbo_encode(x, signs, qjl, *, bits=4, mode=1, radii_codec=0, libm_mode=LIBM_PORTABLE,
                  nthreads=1):
     x = _f32(x)

@@ -433,6 +433,55 @@ static void fib_dec_range(void* p, int64_t lo, int64_t hi) {
 }
 
 /* decode_batch_fast over n records -> n vectors at out + v*out_stride. */
+/* FibQuantizer::decode (fib-quant/src/codec.rs:506-537): the single-vector decoder keeps binary64 --
+ * codewords widened (codebook.rs:118-130), StoredRotation::apply_inverse (rotation.rs:118-130: per
+ * column, rows ascending, `sum += m * v` in binary64 from 0.0), `(value * norm) as f32`.  Serial: it is
+ * what KVecCodec::decode calls per payload (proveKV/src/codec.rs:612-638). */
+PKVO_API int pkvo_fib_decode_exact_batch(const uint8_t* payload, int64_t n, int dim, int k, int n_codewords,
+                                         int norm_format, const double* rot, const float* codebook,
+                                         float* out, int32_t* vec_code, int64_t* vec_index) {
+  if (dim <= 0 || dim > 512 || k <= 0 || dim % k || dim / k > 128) return PKV_ERR_INVALID_ARGUMENT;
+  const int blocks = dim / k, norm_len = norm_format == PKV_NORM_FP16 ? 2 : 4;
+  const int rec_bytes = pkvo_fib_record_bytes(dim, k, n_codewords, norm_format);
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  for (int64_t v = 0; v < n; v++) {
+    const uint8_t* rec = payload + v * rec_bytes;
+    uint32_t idx[128];
+    double rotated[512];
+    int code = 0;
+    if (!unpack_bits(rec + norm_len, blocks, fib_index_bits(n_codewords), idx)) code = PKV_VEC_PADDING_BITS;
+    for (int b = 0; b < blocks && !code; b++) {
+      if (idx[b] >= (uint32_t)n_codewords) code = PKV_VEC_INDEX_RANGE;
+      else
+        for (int j = 0; j < k; j++) rotated[b * k + j] = (double)codebook[idx[b] * k + j];
+    }
+    double norm = 0.0;
+    if (!code) {
+      if (norm_format == PKV_NORM_FP16) norm = (double)f16_bits_to_f32((uint16_t)(rec[0] | (rec[1] << 8)));
+      else
+        norm = (double)pkv_f32_from_bits((uint32_t)rec[0] | ((uint32_t)rec[1] << 8) | ((uint32_t)rec[2] << 16) |
+                                         ((uint32_t)rec[3] << 24));
+      if (!(isfinite(norm) && norm > 0.0)) code = PKV_VEC_BAD_NORM;
+    }
+    if (!code) {
+      for (int c = 0; c < dim; c++) {
+        double sum = 0.0;
+        for (int r = 0; r < dim; r++) sum += rot[(size_t)r * dim + c] * rotated[r];
+        const float o = (float)(sum * norm);
+        if (!is_finite_f32(o)) code = PKV_VEC_NONFINITE_OUTPUT;
+        out[v * dim + c] = o;
+      }
+    }
+    if (code) {
+      if (vec_code) *vec_code = code;
+      if (vec_index) *vec_index = v;
+      return code;
+    }
+  }
+  return 0;
+}
+
 PKVO_API int pkvo_fib_decode_batch(const uint8_t* payload, int64_t n, int dim, int k,
                                    int n_codewords, int norm_format, const double* rot,
                                    const float* codebook, float* out, int64_t out_stride,

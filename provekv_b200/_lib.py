@@ -132,6 +132,8 @@ _SIGS = {
     "pkv_fib_record_bytes": (C.c_int32, [_V]),
     "pkv_fib_encode_dev": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_decode_patch_dev": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, _V]),
+    "pkv_fib_decode_exact_dev": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, _V]),
+    "pkv_fib_decode_exact": (C.c_int, [_V, _V, C.c_int64, _V, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_fib_decode_patch_dev_as": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, C.c_int32, _V, _V]),
     "pkv_turbo_decode_patch_dev_as": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, C.c_int32, _V, _V]),
     "pkv_fib_decode_patch_dev_multi": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, C.c_int32, _V, _V]),

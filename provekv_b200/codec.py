@@ -260,10 +260,16 @@ class FibQuantAdapter(KVecCodec):
         except L.PkvError as e:
             raise DecompressionFailed(f"fib decode_batch_fast failed: {e}") from e
 
-    def decode(self, payload, seed: int):
-        """codec.rs:612-638 runs the f64 inverse rotation (FibQuantizer::decode), which is not the
-        batched f32 arithmetic this library implements; use decode_batch."""
-        raise NotImplementedError("single-vector fib decode (f64 path) is not provided; use decode_batch")
+    def decode(self, payload, seed: int) -> np.ndarray:
+        """codec.rs:612-638: one FB1 payload through FibQuantizer::decode, i.e. the binary64 inverse
+        rotation (not the batched f32 arithmetic of decode_batch)."""
+        prof = self.build_quantizer(seed)
+        bits, blocks, nlen = self._wire_shape(prof)
+        rec = fb1_parse(bytes(payload), bits, blocks, nlen)
+        try:
+            return prof.decode_exact(rec)[0]
+        except L.PkvError as e:
+            raise DecompressionFailed(f"fib decode failed: {e}") from e
 
 
 class TurboQuantAdapter(KVecCodec):

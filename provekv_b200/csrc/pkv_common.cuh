@@ -245,6 +245,8 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
                                             cudaStream_t s);
 int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g,
                           void* cache, int dst, uint64_t* err, cudaStream_t s);  // g.batch_offsets honoured
+int pkv_launch_fib_decode_exact(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g, float* out,
+                                uint64_t* err, cudaStream_t s);
 int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const PkvGeom& g,
                             uint8_t* payload, uint64_t* err, cudaStream_t s);
 int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,

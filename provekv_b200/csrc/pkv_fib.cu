@@ -195,6 +195,56 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
   }
 }
 
+// FibQuantizer::decode (fib-quant/src/codec.rs:506-537), the decoder behind KVecCodec::decode for one
+// payload (proveKV/src/codec.rs:612-638): binary64 throughout -- codewords widened, x_c = sum over
+// rows of M[row][c] * r_row (rows ascending, separately rounded * and +, rotation.rs:118-130), then
+// (f32)(x_c * norm).  One thread per (vector, column); 128 / D vectors per CTA.  Not a throughput
+// path: the batched decoders above are what pools and shells use.
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+fib_decode_exact_kernel(PkvGeom g, const uint8_t* __restrict__ payload, const double* __restrict__ rot,
+                        const float* __restrict__ codebook, int n_codewords, int idx_bits, int norm_len,
+                        float* __restrict__ out, uint64_t* err) {
+  constexpr int B = D / 4, VPC = kThreads / D == 0 ? 1 : kThreads / D;
+  __shared__ double s_r[VPC][D];
+  __shared__ double s_norm[VPC];
+  __shared__ int s_code[VPC];
+  const int vl = threadIdx.x / D, c = threadIdx.x % D;
+  const int64_t n = (int64_t)g.n_batches * g.vpb;
+  const int64_t gvec = (int64_t)blockIdx.x * VPC + vl;
+  const bool active = vl < VPC && gvec < n;
+  const int batch = active ? (int)(gvec / g.vpb) : 0, v = active ? (int)(gvec % g.vpb) : 0;
+  const uint8_t* r = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v * g.rec_bytes;
+  if (active && c == 0) {
+    int code = 0;
+    const int used = B * idx_bits;
+    for (int pos = used; pos < (((used + 7) >> 3) << 3); pos++)
+      if ((r[norm_len + (pos >> 3)] >> (pos & 7)) & 1) code = PKV_VEC_PADDING_BITS;
+    for (int b = 0; b < B; b++) {
+      uint32_t idx = load_bits(r + norm_len, b * idx_bits, idx_bits);
+      if (idx >= (uint32_t)n_codewords) {
+        if (!code) code = PKV_VEC_INDEX_RANGE;
+        idx = 0;
+      }
+      for (int j = 0; j < 4; j++) s_r[vl][4 * b + j] = (double)codebook[4 * idx + j];
+    }
+    float nf;
+    if (norm_len == 2) nf = pkv_f16_bits_to_f32((uint32_t)r[0] | ((uint32_t)r[1] << 8));
+    else nf = __uint_as_float((uint32_t)r[0] | ((uint32_t)r[1] << 8) | ((uint32_t)r[2] << 16) | ((uint32_t)r[3] << 24));
+    if (!code && !(pkv_finite(nf) && nf > 0.0f)) code = PKV_VEC_BAD_NORM;
+    s_norm[vl] = (double)nf;
+    s_code[vl] = code;
+    if (code) pkv_report(err, 0, gvec, code);
+  }
+  __syncthreads();
+  if (!active || s_code[vl]) return;
+  double sum = 0.0;
+  for (int row = 0; row < D; row++) sum = __dadd_rn(sum, __dmul_rn(rot[row * D + c], s_r[vl][row]));
+  const float o = __double2float_rn(__dmul_rn(sum, s_norm[vl]));
+  if (!pkv_finite(o)) pkv_report(err, 0, gvec, PKV_VEC_NONFINITE_OUTPUT);
+  out[pkv_vec_offset(g.L, batch, v) + c] = o;
+}
+
 template <int D>
 size_t fib_decode_smem(int rec) {
   using K = FibDec<D>;
@@ -524,6 +574,24 @@ int pkv_launch_fib_decode(const pkv_fib_profile* p, const uint8_t* payload, cons
   else return PKV_ERR_UNSUPPORTED;
 #undef PKV_FIB_DEC_DST
 #undef PKV_FIB_DEC
+  pkv_count_launch();
+  return pkv_cuda_status(cudaGetLastError());
+}
+
+int pkv_launch_fib_decode_exact(const pkv_fib_profile* p, const uint8_t* payload, const PkvGeom& g, float* out,
+                                uint64_t* err, cudaStream_t s) {
+  const int64_t n = (int64_t)g.n_batches * g.vpb;
+  if (n == 0) return PKV_OK;
+  const int vpc = p->cfg.dim == 64 ? 2 : 1;
+  const int64_t grid = (n + vpc - 1) / vpc;
+  if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  if (p->cfg.dim == 64)
+    fib_decode_exact_kernel<64><<<(unsigned)grid, kThreads, 0, s>>>(g, payload, p->rot_dev, p->codebook_dev,
+                                                                   p->cfg.codebook_size, p->idx_bits, p->norm_len, out, err);
+  else if (p->cfg.dim == 128)
+    fib_decode_exact_kernel<128><<<(unsigned)grid, kThreads, 0, s>>>(g, payload, p->rot_dev, p->codebook_dev,
+                                                                    p->cfg.codebook_size, p->idx_bits, p->norm_len, out, err);
+  else return PKV_ERR_UNSUPPORTED;
   pkv_count_launch();
   return pkv_cuda_status(cudaGetLastError());
 }

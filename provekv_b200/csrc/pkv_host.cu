@@ -486,6 +486,45 @@ int pkv_fib_decode_patch_dev_multi(const pkv_fib_profile* p, const uint8_t* payl
   return pkv_launch_fib_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
 }
 
+int pkv_fib_decode_exact_dev(const pkv_fib_profile* p, const uint8_t* payload_dev, int64_t payload_batch_stride,
+                             const pkv_layout* layout, float* out_dev, uint64_t* err_dev, void* stream) {
+  if (!p || !out_dev || !payload_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
+  if (((uintptr_t)out_dev | (uintptr_t)payload_dev) & 15) return PKV_ERR_INVALID_ARGUMENT;
+  PkvGeom g;
+  int st = make_geom(layout, p->rec_bytes, payload_batch_stride, pkv_fib_tile_vectors(p->cfg.dim, 0), false, &g);
+  if (st != PKV_OK) return st;
+  if (layout->n_replicas != 1) return PKV_ERR_INVALID_ARGUMENT;
+  return pkv_launch_fib_decode_exact(p, payload_dev, g, out_dev, err_dev, (cudaStream_t)stream);
+}
+
+// FibQuantizer::decode for n records in host memory (no header), n small: one upload, one launch.
+int pkv_fib_decode_exact(const pkv_fib_profile* cp, const uint8_t* records_host, int64_t n, float* out_host,
+                         int32_t* vec_code, int64_t* vec_index) {
+  pkv_fib_profile* p = const_cast<pkv_fib_profile*>(cp);
+  if (!p || !records_host || !out_host || n < 0) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  if (n == 0) return PKV_OK;
+  if (n >= (int64_t)1 << 31) return PKV_ERR_UNSUPPORTED;
+  const int d = p->cfg.dim;
+  std::lock_guard<std::mutex> lock(p->ws_mutex);
+  int st = pkv_ws_prepare(&p->ws, n * p->rec_bytes + 16, n * d * 4);
+  if (st != PKV_OK) return st;
+  cudaStream_t s = 0;
+  pkv_layout L = flat_layout(n, d);
+  const int64_t stride = (n * p->rec_bytes + 15) / 16 * 16;
+  if (cudaError_t ce = cudaMemcpyAsync(p->ws.in, records_host, (size_t)n * p->rec_bytes, cudaMemcpyHostToDevice, s))
+    return pkv_cuda_status(ce);
+  pkv_error_word_reset(p->ws.err, s);
+  st = pkv_fib_decode_exact_dev(p, (const uint8_t*)p->ws.in, stride, &L, (float*)p->ws.out, p->ws.err, s);
+  if (st != PKV_OK) return st;
+  if (cudaError_t ce = cudaMemcpyAsync(out_host, p->ws.out, (size_t)n * d * 4, cudaMemcpyDeviceToHost, s))
+    return pkv_cuda_status(ce);
+  return pkv_error_word_read(p->ws.err, s, vec_code, vec_index);
+}
+
 int pkv_fb2_header_write(const pkv_fib_profile* p, uint32_t n_vectors, uint8_t* out) {
   if (!p || !out) return PKV_ERR_INVALID_ARGUMENT;
   const uint32_t blocks = (uint32_t)p->blocks;

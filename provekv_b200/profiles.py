@@ -88,6 +88,18 @@ class FibProfile(_ProfileBase):
         _raise_vec(st, code.value, idx.value)
         return out
 
+    def decode_exact(self, records: bytes) -> np.ndarray:
+        """FibQuantizer::decode (binary64 inverse rotation) of bare records -> [n, dim] f32."""
+        buf = np.frombuffer(records, np.uint8)
+        if buf.size % self.record_bytes:
+            raise ValueError("records are not a whole number of vectors")
+        n = buf.size // self.record_bytes
+        out = np.empty((n, self.dim), np.float32)
+        code, idx = C.c_int32(0), C.c_int64(-1)
+        st = L.lib().pkv_fib_decode_exact(self.handle, _ptr(buf), n, _ptr(out), C.byref(code), C.byref(idx))
+        _raise_vec(st, code.value, idx.value)
+        return out
+
     def header(self, n_vectors: int) -> bytes:
         buf = (C.c_uint8 * L.FB2_HEADER_BYTES)()
         L.check(L.lib().pkv_fb2_header_write(self.handle, n_vectors, buf))

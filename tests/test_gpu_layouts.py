@@ -310,8 +310,19 @@ def test_per_vector_payloads_fb1_and_tqw1(oracle_mod):
     y = fib.decode_batch(blobs, SEED)
     st, ref, _, _ = oracle_mod.fib_decode(want, d, prof.rotation, prof.codebook)
     assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
-    with pytest.raises(NotImplementedError):
-        fib.decode(blobs[0], SEED)
+    # KVecCodec::decode of one payload: FibQuantizer::decode, binary64 inverse rotation
+    st, ex, _, _ = oracle_mod.fib_decode_exact(want, d, prof.rotation, prof.codebook)
+    assert st == 0
+    for i in (0, 7, 39):
+        assert np.array_equal(fib.decode(blobs[i], SEED).view(np.uint32), ex[i].view(np.uint32))
+    assert np.array_equal(prof.decode_exact(want.tobytes()).view(np.uint32), ex.view(np.uint32))
+    assert np.abs(ex - ref).max() < 1e-4 and not np.array_equal(ex, ref)  # decode_batch_fast_parity.rs:37-47
+    bad = bytearray(want[3].tobytes())
+    bad[2] |= 0x1f  # index 31 of a 32-entry codebook is fine; shrink the codebook to make it out of range
+    small = pk.FibProfile(d, prof.rotation, prof.codebook[:17])
+    with pytest.raises(L.PkvError) as ei:
+        small.decode_exact(bytes(bad))
+    assert ei.value.status == L.VEC_INDEX_RANGE
     with pytest.raises(pk.DecompressionFailed):
         fib.decode_batch([blobs[0][:-1]], SEED)
 
