@@ -87,6 +87,42 @@ __device__ __forceinline__ void pkv_cp_async_wait_all() {
   asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
+// Asynchronous bulk copies (the copy engine moves a contiguous run of bytes, 16-byte aligned, a multiple
+// of 16 long, and signals an mbarrier with the byte count): one instruction stages a whole tile of
+// records or a table.  Plain per-CTA forms only.  Waits are bounded.
+__device__ __forceinline__ uint32_t pkv_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void pkv_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pkv_smem_u32(bar)), "r"(count) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void pkv_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pkv_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void pkv_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   pkv_smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(pkv_smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool pkv_mbar_wait(uint64_t* bar, uint32_t parity, int limit = 1 << 20) {
+  const uint32_t a = pkv_smem_u32(bar);
+  for (int it = 0; it < limit; it++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
 // IEEE binary16 <-> binary32 in integer arithmetic (round to nearest even), the
 // conversion half::f16::from_f32 / to_f32 perform (fib-quant/src/codec.rs:1002,1028).
 __device__ __forceinline__ uint32_t pkv_f32_to_f16_bits(float f) {

@@ -91,12 +91,25 @@ fib_decode_patch_kernel(PkvGeom g, const uint8_t* __restrict__ payload,
   const int nv = min(K::TV, g.vpb - v0);
   const int rec = g.rec_bytes;
 
-  for (int i = threadIdx.x; i < D * D / 4; i += kThreads)
-    pkv_cp_async16(reinterpret_cast<float4*>(s_rot) + i, reinterpret_cast<const float4*>(rot32) + i);
+  // The matrix (16 / 64 KB) and the tile's records arrive by asynchronous bulk copies issued by one
+  // thread and counted by an mbarrier; a ragged last tile (not a multiple of 16 bytes) is copied piecewise.
+  __shared__ __align__(8) uint64_t s_bar;
+  const uint8_t* rec_src = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * rec;
+  const bool rec_bulk = ((nv * rec) & 15) == 0;
+  if (threadIdx.x == 0) {
+    pkv_mbar_init(&s_bar, 1);
+    pkv_mbar_expect_tx(&s_bar, (uint32_t)(D * D * 4 + (rec_bulk ? nv * rec : 0)));
+    pkv_bulk_load(s_rot, rot32, D * D * 4, &s_bar);
+    if (rec_bulk) pkv_bulk_load(s_rec, rec_src, (uint32_t)(nv * rec), &s_bar);
+  }
   if (threadIdx.x < 32) s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
-  stage_in(s_rec, payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * rec, nv * rec);
+  if (!rec_bulk) stage_in(s_rec, rec_src, nv * rec);
   pkv_cp_async_wait_all();
-  __syncthreads();
+  __syncthreads();  // the barrier is initialised for everyone; piecewise copies and the codebook are in
+  if (!__syncthreads_and(pkv_mbar_wait(&s_bar, 0))) {  // the copies never completed: nothing is decoded
+    if (threadIdx.x == 0) pkv_report(err, 0, (int64_t)batch * g.vpb + v0, PKV_VEC_DEVICE_WAIT);
+    return;
+  }
 
   // unpack + validate: one thread per vector (checks in the reference's order)
   for (int v = threadIdx.x; v < K::TV; v += kThreads) {

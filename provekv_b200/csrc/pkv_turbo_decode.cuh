@@ -50,11 +50,25 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   const int v = lane;
 
   const uint8_t* src = payload + (int64_t)batch * g.payload_batch_stride + (int64_t)v0 * g.rec_bytes;
+  // RAW: the warp's run of records is contiguous and starts on a 16-byte boundary (32 records are a
+  // multiple of 16 bytes): one bulk copy signalling the warp's mbarrier when the run is a multiple of
+  // 16 bytes long, 16- and 4-byte copies for the ragged last run otherwise
+  __shared__ __align__(8) uint64_t s_bar[Turbo<D>::NWARPS];
+  bool bulk = false;
   if constexpr (RAW != 0) {
-    const int nw = nv * tp.rec_words, n16 = nw / 4;  // a full tile of 32 records is a multiple of 16 bytes
-    for (int i = lane; i < n16; i += 32)
-      pkv_cp_async16(reinterpret_cast<uint4*>(s_w) + i, reinterpret_cast<const uint4*>(src) + i);
-    for (int i = 4 * n16 + lane; i < nw; i += 32) pkv_cp_async4(s_w + i, reinterpret_cast<const uint32_t*>(src) + i);
+    const int nw = nv * tp.rec_words, n16 = nw / 4;
+    bulk = nv > 0 && (nw & 3) == 0;
+    if (bulk) {
+      if (lane == 0) {
+        pkv_mbar_init(&s_bar[warp], 1);
+        pkv_mbar_expect_tx(&s_bar[warp], (uint32_t)nw * 4u);
+        pkv_bulk_load(s_w, src, (uint32_t)nw * 4u, &s_bar[warp]);
+      }
+    } else {
+      for (int i = lane; i < n16; i += 32)
+        pkv_cp_async16(reinterpret_cast<uint4*>(s_w) + i, reinterpret_cast<const uint4*>(src) + i);
+      for (int i = 4 * n16 + lane; i < nw; i += 32) pkv_cp_async4(s_w + i, reinterpret_cast<const uint32_t*>(src) + i);
+    }
   } else {
     stage_records<D, true>(s_w, reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(src)), nv, tp.rec_words, lane);
   }
@@ -65,6 +79,13 @@ turbo_decode_patch_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__
   if (v < nv) s_off[v] = pkv_dst_offset(g, batch, v0 + v, DST == PKV_DST_F32 ? 4 : 8, err);
   pkv_cp_async_wait_all();
   __syncthreads();  // tables; the warp's own tile only needs warp-level ordering from here on
+  if (bulk) {
+    __syncwarp();
+    if (!__all_sync(0xffffffffu, pkv_mbar_wait(&s_bar[warp], 0))) {  // never completed: nothing is decoded
+      if (lane == 0) pkv_report(err, 0, (int64_t)batch * g.vpb + v0, PKV_VEC_DEVICE_WAIT);
+      return;
+    }
+  }
 
   float y[D];
   if (v < nv) {
