@@ -58,20 +58,23 @@ def gather_layer_shards(local_payload, world_size: int, group=None):
     return out
 
 
-def all_gather_pool(local_payload, pool_payload, group=None):
+def all_gather_pool(local_payload, pool_payload, group=None, async_op=False):
     """Layer-sharded pool build: every rank has encoded an equal, contiguous block of the pool's
     batches (``local_payload``); afterwards ``pool_payload`` (world_size times as large, rank order
     = layer order) holds the whole pool in every rank's own memory.  With one rank the local block
-    is the pool and is copied unless both arguments are the same tensor."""
+    is the pool and is copied unless both arguments are the same tensor.  ``async_op``: returns the
+    collective's work handle (None with one rank); ``wait()`` on it before the pool is read."""
     import torch.distributed as dist
 
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         if pool_payload.numel() != local_payload.numel() * dist.get_world_size(group):
             raise ValueError("the pool must be world_size equal blocks")
-        dist.all_gather_into_tensor(pool_payload.view(-1), local_payload.view(-1), group=group)
-    elif pool_payload.data_ptr() != local_payload.data_ptr():
+        work = dist.all_gather_into_tensor(pool_payload.view(-1), local_payload.view(-1), group=group,
+                                           async_op=async_op)
+        return work if async_op else pool_payload
+    if pool_payload.data_ptr() != local_payload.data_ptr():
         pool_payload.view(-1).copy_(local_payload.view(-1))
-    return pool_payload
+    return None if async_op else pool_payload
 
 
 def gpu_numa_cpus(pci_bus_id: str, sysfs: str = "/sys/bus/pci/devices"):
