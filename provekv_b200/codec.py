@@ -38,6 +38,26 @@ class InvalidPolicy(ProveKvError):
     pass
 
 
+class InvalidShape(ProveKvError):
+    pass
+
+
+class InvalidManifest(ProveKvError):
+    pass
+
+
+class InvalidReceipt(ProveKvError):
+    pass
+
+
+class CorruptPayload(ProveKvError):
+    pass
+
+
+class DimensionMismatch(ProveKvError):
+    pass
+
+
 class CompressionFailed(ProveKvError):
     pass
 
@@ -48,20 +68,66 @@ class DecompressionFailed(ProveKvError):
 
 @dataclass(frozen=True)
 class FibConfig:
-    """proveKV/src/policy.rs:117-145."""
+    """proveKV/src/policy.rs:117-182."""
     k: int = 4
     n: int = 32
     training_samples: int = 2048
     lloyd_restarts: int = 4
     lloyd_iterations: int = 8
 
+    def validate(self) -> None:
+        """policy.rs:147-182, same order of checks and messages."""
+        if self.k == 0:
+            raise InvalidPolicy("fib k must be > 0")
+        if self.n < 2:
+            raise InvalidPolicy("fib N must be >= 2")
+        if self.k > 256:
+            raise InvalidPolicy("fib k must be <= 256")
+        if self.n > 1_048_576:
+            raise InvalidPolicy("fib N must be <= 1,048,576")
+        if self.training_samples == 0:
+            raise InvalidPolicy("fib training_samples must be > 0")
+        if self.lloyd_restarts == 0:
+            raise InvalidPolicy("fib lloyd_restarts must be > 0")
+        if self.lloyd_iterations == 0:
+            raise InvalidPolicy("fib lloyd_iterations must be > 0")
+
+    def as_json(self) -> dict:
+        """Fields in declaration order, as serde writes the struct."""
+        return {"k": self.k, "n": self.n, "training_samples": self.training_samples,
+                "lloyd_restarts": self.lloyd_restarts, "lloyd_iterations": self.lloyd_iterations}
+
 
 @dataclass(frozen=True)
 class TurboConfig:
-    """proveKV/src/policy.rs:218-262; ``lossy_radii`` is RadiiCompression::Lossy."""
+    """proveKV/src/policy.rs:218-290; ``lossy_radii`` is RadiiCompression::Lossy."""
     bits: int = 4
     projections: int = 32
     lossy_radii: bool = False
+
+    def validate(self) -> None:
+        """policy.rs:264-277."""
+        if self.bits < 2 or self.bits > 16:
+            raise InvalidPolicy(f"turbo bits must be 2\u201316, got {self.bits}")
+        if self.projections == 0:
+            raise InvalidPolicy("turbo projections must be > 0")
+
+    def expected_compression_ratio(self) -> float:
+        """policy.rs:279-288."""
+        return 32.0 if self.lossy_radii else 8.0
+
+    def as_json(self) -> dict:
+        """The unit variants of RadiiCompression serialise as their names (policy.rs:208-213)."""
+        return {"bits": self.bits, "projections": self.projections,
+                "radii_compression": "Lossy" if self.lossy_radii else "Lossless"}
+
+    @classmethod
+    def from_json(cls, obj: dict) -> "TurboConfig":
+        """`radii_compression` defaults to Lossless when absent (policy.rs:226 `serde(default)`)."""
+        rc = obj.get("radii_compression", "Lossless")
+        if rc not in ("Lossless", "Lossy"):
+            raise InvalidPolicy(f"unknown radii_compression: {rc}")
+        return cls(int(obj["bits"]), int(obj["projections"]), rc == "Lossy")
 
 
 @functools.lru_cache(maxsize=16)

@@ -219,3 +219,57 @@ def test_shared_pool_built_on_the_gpu_from_the_reference_corpus_layout(oracle_mo
         assert layer.block_digest == layer.compute_digest() == pool_["layer_digests"][li]
     assert pool_["pool_id"] == M.pool_id(pool_["layer_digests"], "cb-digest", "rot-digest", shape, 42)
     assert pool_["pool_size_bytes"] == Lc * 2 * (19 + T * H * 12) and pool_["raw_size_bytes"] == corpus.size * 4
+    manifest, receipt = pool_["manifest"], pool_["receipt"]
+    manifest.validate()
+    receipt.validate()
+    assert receipt.backend == "gpu" and receipt.pool_digest == manifest.pool_id == pool_["pool_id"]
+    assert receipt.layer_digests == pool_["layer_digests"] and receipt.total_tokens == manifest.num_shared_tokens == T
+    assert manifest.compression_ratio == receipt.compression_ratio == corpus.size * 4 / pool_["pool_size_bytes"]
+    assert manifest.shared_codec == "fib_k4_n32_batched" and manifest.build_seed == receipt.seeded_with == 42
+
+
+@pytest.mark.parametrize("lossy", [False, True])
+def test_shell_materialised_on_the_gpu_and_the_injection_trace(oracle_mod, lossy):
+    """materialize_shell encodes an agent's own tokens as one TQB1 blob per (layer, K|V)
+    (proveKV/src/shell.rs:232-296): the blobs equal the oracle's encode of the same gathers, the layer and
+    shell digests chain as in shell.rs:48-67,322-337, the manifest's codec id follows the policy, and an
+    agent with no tokens of its own gets the empty shell of shell.rs:156-196."""
+    from provekv_b200 import manifest as M
+    from provekv_b200 import records as R
+    d, H, Lc, T, seed = 64, 2, 3, 23, 42
+    shape = M.KvTensorShape("gqa", Lc, 8, H, d, 8 * d)
+    policy = R.CompressionPolicy.default_two_tier_lossy() if lossy else R.CompressionPolicy.default_two_tier()
+    pm = R.PoolManifest.new("pool-id", shape, policy, 800, Lc, 1000, 100000, seed, 11)
+    prof = _profiles(d)["turbo_lossy" if lossy else "turbo"]
+    tokens = synthetic_kv(T * Lc * H * 2, d, seed=33).reshape(T, Lc * H * 2 * d)
+    shell, receipt = M.materialize_shell(pm, "agent_3", tokens, seed, profile=prof, materialized_at_unix=12)
+    codec = "turbo_4bit_batched_lossy" if lossy else "turbo_4bit_batched"
+    x = tokens.reshape(T, Lc, H, 2, d)
+    header = oracle_mod.tqb1_header(d, 4, 1, 32, prof.radii_codec, prof.seed, T * H)
+    total = 0
+    for li, layer in enumerate(shell.unique_layers):
+        for side, block in enumerate((layer.key_blocks[0], layer.value_blocks[0])):
+            vectors = np.ascontiguousarray(x[:, li, :, side, :]).reshape(T * H, d)
+            want = header + _oracle_encode(oracle_mod, "turbo", prof, vectors).tobytes()
+            assert block.encoded_payload == want and block.codec == codec and block.original_dim == d
+            total += len(want)
+        assert layer.layer_index == li and layer.block_digest == layer.compute_digest()
+    sm = shell.shell_manifest
+    sm.validate()
+    receipt.validate()
+    assert (sm.shell_codec, sm.num_unique_tokens, sm.num_unique_layers, sm.shell_size_bytes) == (codec, T, Lc, total)
+    assert sm.component_kinds == ["KeyValue"] * Lc and sm.pool_digest == shell.pool_digest == "pool-id"
+    assert (sm.materialize_seed, sm.materialized_at_unix, sm.head_dim, sm.num_kv_heads) == (seed, 12, d, H)
+    assert receipt.shell_digest == M.shell_digest("agent_3", "pool-id", [l.block_digest for l in shell.unique_layers], seed)
+    assert receipt.shell_size_bytes == total and receipt.num_unique_tokens == T
+    trace = M.injection_receipt("agent_3", pm, ["p0", "p1", "p2"], shell, receipt.shell_digest, 13)
+    assert trace.blocks_injected == 2 * Lc and trace.block_traces[1].target_position == 800
+    empty, r0 = M.materialize_shell(pm, "agent_4", np.zeros((0, Lc * H * 2 * d), np.float32), seed)
+    assert empty.unique_layers == [] and r0.shell_size_bytes == 0 and empty.shell_manifest.num_unique_layers == Lc
+    assert r0.shell_digest == M.shell_digest("agent_4", "pool-id", [], seed)
+    bad = tokens.copy()
+    bad[5, 17] = np.inf
+    with pytest.raises(pk.codec.CorruptPayload, match="agent token 5 contains non-finite values"):
+        M.materialize_shell(pm, "agent_3", bad, seed, profile=prof)
+    with pytest.raises(pk.codec.DimensionMismatch):
+        M.materialize_shell(pm, "agent_3", tokens[:, :-1], seed, profile=prof)
