@@ -1254,12 +1254,19 @@ PKVO_API void pkvo_fib_fast_check(const float* x, int64_t n, int dim, const doub
     const double norm = sqrt(acc);
     if (!(norm > 0.0)) continue;
     const double inv = 1.0 / norm;
+    const float invh = (float)inv, invl = (float)(inv - (double)invh);
+    uint32_t min_key = 0xffffffffu;
+    for (int i = 0; i < dim; i++) {
+      const uint32_t k = pkv_fib_mag_key(xv[i]);
+      if (k < min_key) min_key = k;
+    }
+    const int pair_ok = pkv_fib_fast_norm_ok(norm, min_key);
     float nf[512], ne[512];
     for (int i = 0; i < dim; i++) {
-      int certain = 0;
-      nf[i] = pkv_fib_norm_quotient(xv[i], inv, &certain);
+      uint32_t unsure = pair_ok ? 0u : 1u;
+      nf[i] = pkv_fib_norm_quotient(xv[i], invh, invl, &unsure);
       ne[i] = (float)((double)xv[i] / norm);
-      if (!certain) counts[4]++;
+      if (unsure) counts[4]++;
       else if (pkv_f32_bits(nf[i]) != pkv_f32_bits(ne[i])) counts[3]++;
     }
     for (int b = 0; b < blocks; b++) {
@@ -1292,6 +1299,51 @@ PKVO_API void pkvo_fib_fast_check(const float* x, int64_t n, int dim, const doub
   free(m32);
 }
 
+/* Stress of the pair-form normalised element (pkv_fast_paths.h (1)) against the division it stands
+ * for.  mode 0: random x and norm with |x| <= norm.  mode m > 0: quotients placed next to binary32
+ * rounding boundaries -- a random binary32 t in [2^-12, 1), the midpoint above it moved by k 2^-52
+ * relative for a random |k| <= 2^m, and norm = |x| / midpoint, so that x / norm lands within 2^(m-52)
+ * of the boundary.  counts[0] = declared certain but different from (f32)((f64)x / norm),
+ * counts[1] = unsure, counts[2] = cases where the pair form was admissible. */
+static uint64_t pkvo_mix64(uint64_t* st) {
+  uint64_t z = (*st += 0x9e3779b97f4a7c15ull);
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+
+PKVO_API void pkvo_fib_quotient_check(uint64_t seed, int64_t n, int mode, int64_t* counts) {
+  uint64_t st = seed;
+  counts[0] = counts[1] = counts[2] = 0;
+  for (int64_t it = 0; it < n; it++) {
+    const uint64_t a = pkvo_mix64(&st), b = pkvo_mix64(&st);
+    /* x: random sign, exponent in [-20, 20], random significand */
+    const uint32_t xb = (uint32_t)(((a >> 63) << 31) | ((uint64_t)(107 + (a >> 32) % 41) << 23) | (a & 0x7fffffu));
+    const float x = pkv_f32_from_bits(xb);
+    double norm;
+    if (mode == 0) {
+      const double scale = 1.0 + (double)(b >> 11) * 0x1p-53 * 4095.0; /* |x| / norm in (2^-12, 1] */
+      norm = fabs((double)x) * scale;
+    } else {
+      const uint32_t tb = (uint32_t)(((uint64_t)(115 + (b >> 40) % 12) << 23) | (b & 0x7fffffu));
+      const float t = pkv_f32_from_bits(tb), tn = pkv_f32_from_bits(tb + 1u);
+      const double mid = 0.5 * ((double)t + (double)tn);
+      const int64_t span = 1ll << mode, k = (int64_t)((b >> 24) % (uint64_t)(2 * span + 1)) - span;
+      norm = fabs((double)x) / (mid * (1.0 + (double)k * 0x1p-52));
+    }
+    const uint32_t key = pkv_fib_mag_key(x);
+    if (!pkv_fib_fast_norm_ok(norm, key)) continue;
+    counts[2]++;
+    const double inv = 1.0 / norm;
+    const float invh = (float)inv, invl = (float)(inv - (double)invh);
+    uint32_t unsure = 0;
+    const float q = pkv_fib_norm_quotient(x, invh, invl, &unsure);
+    const float ref = (float)((double)x / norm);
+    if (unsure) counts[1]++;
+    else if (pkv_f32_bits(q) != pkv_f32_bits(ref)) counts[0]++;
+  }
+}
+
 /* The same check for the tensor-core rotation of the d = 64 encoder (PKV_FIB_ROT_ERR_TC). */
 PKVO_API void pkvo_fib_tc_check(const float* x, int64_t n, int dim, const double* rot,
                                   const float* codebook, int n_codewords, int order, int64_t* counts) {
@@ -1313,12 +1365,19 @@ PKVO_API void pkvo_fib_tc_check(const float* x, int64_t n, int dim, const double
     const double norm = sqrt(acc);
     if (!(norm > 0.0)) continue;
     const double inv = 1.0 / norm;
+    const float invh = (float)inv, invl = (float)(inv - (double)invh);
+    uint32_t min_key = 0xffffffffu;
+    for (int i = 0; i < dim; i++) {
+      const uint32_t k = pkv_fib_mag_key(xv[i]);
+      if (k < min_key) min_key = k;
+    }
+    const int pair_ok = pkv_fib_fast_norm_ok(norm, min_key);
     float nf[512], ne[512];
     for (int i = 0; i < dim; i++) {
-      int certain = 0;
-      nf[i] = pkv_fib_norm_quotient(xv[i], inv, &certain);
+      uint32_t unsure = pair_ok ? 0u : 1u;
+      nf[i] = pkv_fib_norm_quotient(xv[i], invh, invl, &unsure);
       ne[i] = (float)((double)xv[i] / norm);
-      if (!certain) counts[4]++;
+      if (unsure) counts[4]++;
       else if (pkv_f32_bits(nf[i]) != pkv_f32_bits(ne[i])) counts[3]++;
     }
     for (int b = 0; b < blocks; b++) {

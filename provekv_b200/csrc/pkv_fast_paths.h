@@ -152,27 +152,41 @@ PKV_HD uint32_t pkv_fast_radius_code(float l_approx, float mn, float k, int* cer
 /* ------------------------------------------------------------------------------------------
  * fib-quant encoder shortcuts (fib-quant/src/codec.rs:578-729).
  *
- * (1) Normalised element.  The reference takes n = (f32)((f64)x / norm).  With inv = RN(1/norm)
- * the product q = RN(x * inv) differs from the exact quotient by a relative 3.4e-16 at most, so
- * (f32)q equals the reference unless q lies within a few units in the last place of a binary32
- * rounding boundary.  Those boundaries are where the low 29 bits of q's significand read
- * 0x10000000; the test leaves 32 units of slack on either side (2^-47 relative).  Results in the
- * binary32 subnormal range round at a different bit and are left to the exact path.
+ * (1) Normalised element.  The reference takes n = (f32)((f64)x / norm).  With 1/norm held as a
+ * pair of binary32 numbers, invh + invl = RN64(1/norm) to 2^-48, the quotient is
+ *   x / norm = p + e + x invl (1 + 2^-48),   p = RN(x invh),  e = x invh - p  (one fused operation, exact),
+ * so d = RN(x invl + e) puts p + d within 2^-47 |p| of the true quotient.  n is RN(p + d) unless
+ * p + d lies that close to a binary32 rounding boundary, where |d| >= 2^-25.5 |p|; the test rounds
+ * p + d (1 + 2^-19) and p + d (1 - 2^-19) and accepts when both give the same number (slack
+ * 2^-44.5 |p| at a boundary, six times the error).  Exactness of e needs the product free of
+ * underflow: the caller guarantees 2^-40 <= norm <= 2^40 and every nonzero |x| >= 2^-60
+ * (pkv_fib_fast_norm_ok); everything else takes the division.
  */
-PKV_HD float pkv_fib_norm_quotient(float x, double inv, int* certain) {
-  const double q = PKV_DMUL((double)x, inv);
-  uint64_t u;
 #if defined(__CUDA_ARCH__)
-  u = (uint64_t)__double_as_longlong(q);
+#define PKV_FMAF(a, b, c) fmaf((a), (b), (c))
 #else
-  memcpy(&u, &q, 8);
+#define PKV_FMAF(a, b, c) __builtin_fmaf((a), (b), (c))
 #endif
-  const uint32_t lo29 = (uint32_t)(u & 0x1fffffffull);
-  const uint32_t dist = lo29 > 0x10000000u ? lo29 - 0x10000000u : 0x10000000u - lo29;
-  const uint32_t expo = (uint32_t)((u >> 52) & 0x7ffu);
-  /* exact zero is certain; otherwise demand a normal binary32 result (exponent >= -126) */
-  *certain = (x == 0.0f) || (dist > 32u && expo >= 1023u - 126u);
-  return PKV_D2F(q);
+
+/* 2 * bits(x) - 1 modulo 2^32: drops the sign, orders by magnitude, and sends both zeros to the top,
+ * so an unsigned minimum over a vector is its smallest nonzero magnitude. */
+PKV_HD uint32_t pkv_fib_mag_key(float x) { return 2u * pkv_f32_bits(x) - 1u; }
+
+/* May the pair form be used for a vector with this norm and this minimum of pkv_fib_mag_key? */
+PKV_HD int pkv_fib_fast_norm_ok(double norm, uint32_t min_mag_key) {
+  return norm >= 0x1p-40 && norm <= 0x1p40 && min_mag_key >= 2u * 0x21800000u - 1u; /* 2^-60 */
+}
+
+/* Normalised element by the pair form; *unsure collects a nonzero word when the result is not
+ * certain (the caller then divides). */
+PKV_HD float pkv_fib_norm_quotient(float x, float invh, float invl, uint32_t* unsure) {
+  const float p = PKV_FMUL(x, invh);
+  const float e = PKV_FMAF(x, invh, -p);
+  const float d = PKV_FMAF(x, invl, e);
+  const float r1 = PKV_FMAF(d, 1.0f + 0x1p-19f, p);
+  const float r2 = PKV_FMAF(d, 1.0f - 0x1p-19f, p);
+  *unsure |= pkv_f32_bits(r1) ^ pkv_f32_bits(r2);
+  return r1;
 }
 
 /* (2) Rotated value.  y~ = sum_j M32[r][j] n_j accumulated in binary32 with fused multiply-adds
@@ -189,12 +203,6 @@ PKV_HD float pkv_fib_norm_quotient(float x, double inv, int* certain) {
  * with D_c = |s~ - c|^2 and e_F <= 2^-16 |F_c| (index bits and FMA rounding).  If the gap between
  * best and second best exceeds the two bounds, the reference's strict-less-than scan
  * (gpu-backend/src/simd_nearest.rs:72-79) selects the same codeword in either summation order. */
-#if defined(__CUDA_ARCH__)
-#define PKV_FMAF(a, b, c) fmaf((a), (b), (c))
-#else
-#define PKV_FMAF(a, b, c) __builtin_fmaf((a), (b), (c))
-#endif
-
 /* Score of codeword c (c0..c3, half squared norm hn) for the block s, index in the low bits. */
 PKV_HD float pkv_fib_key(float s0, float s1, float s2, float s3, float c0, float c1, float c2,
                          float c3, float hn, uint32_t c) {
@@ -215,6 +223,23 @@ PKV_HD void pkv_fib_top2(float* best, float* second, float key) {
   const float lo = key < *best ? key : *best, hi = key < *best ? *best : key;
   *second = hi < *second ? hi : *second;
   *best = lo;
+#endif
+}
+
+/* The same for two new keys at once: the second smallest of {best, second, a, b} is the smaller of
+ * max(best, min(a, b)) and min(second, max(a, b)).  With the three-operand minimum of sm_100 that is
+ * five instructions for two keys. */
+PKV_HD void pkv_fib_top2_pair(float* best, float* second, float a, float b) {
+#if defined(__CUDA_ARCH__)
+  const float lo = fminf(a, b), hi = fmaxf(a, b);
+  const float t = fmaxf(*best, lo);
+  float s;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(s) : "f"(*second), "f"(hi), "f"(t));
+  *second = s;
+  *best = fminf(*best, lo);
+#else
+  pkv_fib_top2(best, second, a);
+  pkv_fib_top2(best, second, b);
 #endif
 }
 

@@ -80,17 +80,19 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
   {
     const int v = tid % K::TV, part = tid / K::TV;
     const float* row = s_t + v * K::XS;
-    bool finite = true;
-    double acc = 0.0;
+    double acc = 0.0;  // a non-finite element makes the sum non-finite
+    uint32_t min_key = 0xffffffffu;
 #pragma unroll 8
     for (int i = 0; i < D; i += 4) {
       const float4 t = v < nv ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-      finite = finite && pkv_finite(t.x) && pkv_finite(t.y) && pkv_finite(t.z) && pkv_finite(t.w);
       acc = fma((double)t.x, (double)t.x, acc);
       acc = fma((double)t.y, (double)t.y, acc);
       acc = fma((double)t.z, (double)t.z, acc);
       acc = fma((double)t.w, (double)t.w, acc);
+      min_key = min(min(min_key, min(pkv_fib_mag_key(t.x), pkv_fib_mag_key(t.y))),
+                    min(pkv_fib_mag_key(t.z), pkv_fib_mag_key(t.w)));
     }
+    const bool finite = acc < __longlong_as_double(0x7ff0000000000000ll);
     float xr[K::EPT];
 #pragma unroll
     for (int i = 0; i < K::EPT; i += 4) {
@@ -113,15 +115,17 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
       s_bad[v] = (uint8_t)skip;
     }
     const double inv = __ddiv_rn(1.0, norm);
-    int all_certain = 1;
+    const float invh = __double2float_rn(inv), invl = __double2float_rn(__dsub_rn(inv, (double)invh));
+    uint32_t unsure = pkv_fib_fast_norm_ok(norm, min_key) ? 0u : 1u;
+    float q[K::EPT];
 #pragma unroll
-    for (int i = 0; i < K::EPT; i++) {
-      int certain;
-      const float q = pkv_fib_norm_quotient(xr[i], inv, &certain);
-      all_certain &= certain;
-      s_t[(part * K::EPT + i) * K::TV + v] = skip ? 0.0f : q;
+    for (int i = 0; i < K::EPT; i++) q[i] = pkv_fib_norm_quotient(xr[i], invh, invl, &unsure);
+    if (unsure && !skip) {  // rare: the reference's division
+#pragma unroll
+      for (int i = 0; i < K::EPT; i++) q[i] = __double2float_rn(__ddiv_rn((double)xr[i], norm));
     }
-    if (!all_certain && !skip) atomicOr(&s_flag[v], 1u << 31);  // redo the whole vector exactly
+#pragma unroll
+    for (int i = 0; i < K::EPT; i++) s_t[(part * K::EPT + i) * K::TV + v] = skip ? 0.0f : q[i];
   }
   __syncthreads();
 

@@ -54,7 +54,8 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   }
   if (threadIdx.x < 32) {
     s_cb[threadIdx.x] = __ldg(reinterpret_cast<const float4*>(codebook) + threadIdx.x);
-    s_hn[threadIdx.x] = __ldg(half_norm + threadIdx.x);
+    // entries past the codebook score higher than any real one
+    s_hn[threadIdx.x] = (int)threadIdx.x < n_codewords ? __ldg(half_norm + threadIdx.x) : 3.0e38f;
   }
   const int v = lane, row = warp * K::TV + v;
   // piece c of this thread's row sits at s_xt + (c >> 3) * X_SLAB + (xsw ^ ((c & 7) << 4))
@@ -103,15 +104,17 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   }
 
   // exact norm (codec.rs:1049-1057; the square of a binary32 value is exact in binary64, so the
-  // fused form rounds exactly like the reference's multiply-then-add), certified normalisation
-  bool finite = true;
+  // fused form rounds exactly like the reference's multiply-then-add; a non-finite element makes the
+  // sum non-finite), certified normalisation by the pair form, the division where that is unsure
   double acc = 0.0;
+  uint32_t min_key = 0xffffffffu;
 #pragma unroll
   for (int i = 0; i < D; i++) {
-    finite = finite && pkv_finite(n[i]);
     const double t = (double)n[i];
     acc = fma(t, t, acc);
+    min_key = min(min_key, pkv_fib_mag_key(n[i]));
   }
+  const bool finite = acc < __longlong_as_double(0x7ff0000000000000ll);
   double norm = __dsqrt_rn(acc);
   int bad = 0;
   if (valid) {
@@ -121,16 +124,31 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   }
   const bool skip = bad || !valid;
   if (skip) norm = 1.0;
-  const double inv = __ddiv_rn(1.0, norm);
-  int all_certain = 1;
+  {
+    const double inv = __ddiv_rn(1.0, norm);
+    const float invh = __double2float_rn(inv), invl = __double2float_rn(__dsub_rn(inv, (double)invh));
+    uint32_t unsure = pkv_fib_fast_norm_ok(norm, min_key) ? 0u : 1u;
 #pragma unroll
-  for (int i = 0; i < D; i++) {
-    int certain;
-    const float q = pkv_fib_norm_quotient(n[i], inv, &certain);
-    all_certain &= certain;
-    n[i] = skip ? 0.0f : q;
+    for (int i = 0; i < D; i++) n[i] = pkv_fib_norm_quotient(n[i], invh, invl, &unsure);
+    if (unsure || skip) {
+      // rare: the reference's division element by element, through the tile (x is still there)
+#pragma unroll 1
+      for (int c = 0; c < D / 4; c++) {
+        float4* cell = reinterpret_cast<float4*>(s_xt + (c >> 3) * K::X_SLAB + (xsw ^ ((c & 7) << 4)));
+        float4 t = *cell;
+        t.x = skip ? 0.0f : __double2float_rn(__ddiv_rn((double)t.x, norm));
+        t.y = skip ? 0.0f : __double2float_rn(__ddiv_rn((double)t.y, norm));
+        t.z = skip ? 0.0f : __double2float_rn(__ddiv_rn((double)t.z, norm));
+        t.w = skip ? 0.0f : __double2float_rn(__ddiv_rn((double)t.w, norm));
+        *cell = t;
+      }
+#pragma unroll
+      for (int i = 0; i < D; i += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(s_xt + (i >> 5) * K::X_SLAB + (xsw ^ (((i >> 2) & 7) << 4)));
+        n[i] = t.x; n[i + 1] = t.y; n[i + 2] = t.z; n[i + 3] = t.w;
+      }
+    }
   }
-  const bool whole = !all_certain && !skip;  // some element of n is not certain: redo the vector exactly
 
   // first operand: the exact remainder n_lo = n - n_hi (n_hi = n with its 13 low bits cleared);
   // one product (M_hi)
@@ -208,15 +226,18 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
     float best[K::B], second[K::B];
 #pragma unroll
     for (int b = 0; b < K::B; b++) best[b] = second[b] = __int_as_float(0x7f800000);
-#pragma unroll 2
-    for (int c = 0; c < n_codewords; c++) {
-      const float4 w = s_cb[c];
-      const float hn = s_hn[c];
+    // two codewords per step (the tables hold 32 entries; those past n_codewords never win)
+#pragma unroll 1
+    for (int c = 0; c < n_codewords; c += 2) {
+      const float4 w0 = s_cb[c], w1 = s_cb[c + 1];
+      const float hn0 = s_hn[c], hn1 = s_hn[c + 1];
 #pragma unroll
       for (int b = 0; b < K::B; b++)
-        pkv_fib_top2(&best[b], &second[b],
-                     pkv_fib_key(y[4 * b], y[4 * b + 1], y[4 * b + 2], y[4 * b + 3], w.x, w.y, w.z, w.w, hn,
-                                 (uint32_t)c));
+        pkv_fib_top2_pair(&best[b], &second[b],
+                          pkv_fib_key(y[4 * b], y[4 * b + 1], y[4 * b + 2], y[4 * b + 3], w0.x, w0.y, w0.z, w0.w,
+                                      hn0, (uint32_t)c),
+                          pkv_fib_key(y[4 * b], y[4 * b + 1], y[4 * b + 2], y[4 * b + 3], w1.x, w1.y, w1.z, w1.w,
+                                      hn1, (uint32_t)c + 1u));
     }
 #pragma unroll
     for (int b = 0; b < K::B; b++) {
@@ -225,7 +246,7 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
                                PKV_FIB_ROT_ERR_TC))
         flagged |= 1u << b;
     }
-    if (skip || whole) flagged = 0;
+    if (skip) flagged = 0;
   }
 
   // Second tier: the flagged blocks of one vector at a time, the whole warp on each.  Lane l takes
@@ -294,8 +315,8 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
         rec0 = h | ((uint32_t)lo << 16);
         rec1 = (uint32_t)(lo >> 16);
         rec2 = (uint32_t)(lo >> 48) | (hi << 16);
-        if (whole || flagged) {
-          const uint32_t which = (whole || (flagged & (flagged - 1))) ? PKV_FIB_ENTRY_ALL
+        if (flagged) {
+          const uint32_t which = (flagged & (flagged - 1)) ? PKV_FIB_ENTRY_ALL
                                                                        : (uint32_t)(__ffs(flagged) - 1);
           const uint32_t gvec = (uint32_t)((int64_t)batch * g.vpb + v0 + v);
           flag_list[atomicAdd(flag_count, 1u)] = (gvec << 5) | which;

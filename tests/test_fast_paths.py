@@ -81,3 +81,19 @@ def test_fib_rotation_shortcuts_never_decide_wrong(oracle_mod, check, order):
     assert decided + flagged == n * 16
     assert flagged < 0.004 * n * 16          # a few per mille of the blocks go to the next tier
     assert worst_e9 * 1e-9 < (4.0e-6 if check.endswith("fast_check") else 1.0e-5)
+
+
+@pytest.mark.parametrize("mode,min_unsure,max_unsure", [(0, 1, 200), (5, 4_000_000, 4_000_000), (9, 1_000_000, 3_900_000),
+                                                        (12, 100_000, 600_000), (16, 5_000, 60_000)])
+def test_pair_form_normalised_element_is_never_certain_and_wrong(oracle_mod, mode, min_unsure, max_unsure):
+    """The binary32 pair form of x / norm against the reference's (f32)((f64)x / norm): random
+    arguments (mode 0) and quotients within 2^(mode-52) of a binary32 rounding boundary.  A result
+    declared certain must have the division's bits; next to a boundary nothing may be certain, and the
+    unsure share must fall off once the distance exceeds the slack of 2^-44."""
+    fn = oracle_mod.lib().pkvo_fib_quotient_check
+    fn.argtypes = [C.c_uint64, C.c_int64, C.c_int, C.POINTER(C.c_int64)]
+    out = (C.c_int64 * 3)()
+    fn(2024 + mode, 4_000_000, mode, out)
+    wrong, unsure, tested = list(out)
+    assert tested == 4_000_000 and wrong == 0
+    assert min_unsure <= unsure <= max_unsure
