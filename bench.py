@@ -377,7 +377,7 @@ def single_kernel_names(w):
     d = w["dim"]
     if w["codec"] == "fib":
         enc = "fib_encode_tc_kernel + fib_encode_fix_kernel<64>" if d == 64 else \
-            f"fib_encode_fast_kernel<{d}> + fib_encode_fix_kernel<{d}>"
+            f"fib_encode_tc128_kernel + fib_encode_fix_kernel<{d}>"
         return enc, f"fib_decode_patch_kernel<{d}>"
     return f"turbo_encode_kernel<{d}>", f"turbo_decode_patch_kernel<{d}>"
 
@@ -547,7 +547,7 @@ PHASES = ("fib_encode", "pool_gather", "turbo_encode", "fib_decode_patch", "turb
 
 def pool_kernel_names(d):
     fe = "fib_encode_tc_kernel + fib_encode_fix_kernel<64>" if d == 64 else \
-        f"fib_encode_fast_kernel<{d}> + fib_encode_fix_kernel<{d}>"
+        f"fib_encode_tc128_kernel + fib_encode_fix_kernel<{d}>"
     return {"fib_encode": fe, "turbo_encode": f"turbo_encode_kernel<{d},3,rot> + turbo_encode_fix_kernel<{d}>",
             "fib_decode_patch": f"fib_decode_patch_kernel<{d},f32>",
             "turbo_decode_patch": f"turbo_decode_patch_kernel<{d},3,f32>"}

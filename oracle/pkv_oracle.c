@@ -1285,8 +1285,13 @@ PKVO_API void pkvo_fib_fast_check(const float* x, int64_t n, int dim, const doub
         if (e > worst) worst = e;
       }
       int certain = 0;
-      const uint32_t fast = pkv_fib_block_argmin_fast(yf[0], yf[1], yf[2], yf[3], codebook, hn,
-                                                      n_codewords, &certain);
+      float best = INFINITY, second = INFINITY;
+      for (int c = 0; c < n_codewords; c++)
+        pkv_fib_top2(&best, &second,
+                     pkv_fib_key(yf[0], yf[1], yf[2], yf[3], codebook[4 * c], codebook[4 * c + 1],
+                                 codebook[4 * c + 2], codebook[4 * c + 3], hn[c], (uint32_t)c));
+      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_D(dim));
+      const uint32_t fast = pkv_f32_bits(best) & 31u;
       if (!certain) {
         counts[1]++;
         continue;
@@ -1410,7 +1415,7 @@ PKVO_API void pkvo_fib_tc_check(const float* x, int64_t n, int dim, const double
         pkv_fib_top2(&best, &second,
                      pkv_fib_key(yf[0], yf[1], yf[2], yf[3], codebook[4 * c], codebook[4 * c + 1],
                                  codebook[4 * c + 2], codebook[4 * c + 3], hn[c], (uint32_t)c));
-      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_TC);
+      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_TC_D(dim));
       const uint32_t fast = pkv_f32_bits(best) & 31u;
       if (!certain) {
         counts[1]++;

@@ -190,10 +190,12 @@ PKV_HD float pkv_fib_norm_quotient(float x, float invh, float invl, uint32_t* un
 }
 
 /* (2) Rotated value.  y~ = sum_j M32[r][j] n_j accumulated in binary32 with fused multiply-adds
- * (j ascending) differs from the reference's y = (f32) sum_j M[r][j] n_j (binary64) by at most
- *   |M32 - M| |n| + gamma_64 |M32| |n| + u |y|  <=  (1 + 65 + 1) u * |M_r|_2 |n|_2,  u = 2^-24,
- * and the rows of an orthogonal M and the normalised n have 2-norm 1 (to 1e-7):   4.0e-6. */
+ * (j ascending, D terms) differs from the reference's y = (f32) sum_j M[r][j] n_j (binary64) by at most
+ *   |M32 - M| |n| + gamma_D |M32| |n| + u |y|  <=  (1 + (D + 1) + 1) u * |M_r|_2 |n|_2,  u = 2^-24,
+ * and the rows of an orthogonal M and the normalised n have 2-norm 1 (to 1e-7):
+ * 4.0e-6 for D = 64, 7.9e-6 for D = 128. */
 #define PKV_FIB_ROT_ERR 4.0e-6f
+#define PKV_FIB_ROT_ERR_D(D) ((float)((D) + 3) * 5.97e-8f)
 
 /* (3) Nearest codeword of a 4-block.  Scores F_c = |c|^2/2 - s.c (so |s - c|^2 = 2 F_c + |s|^2) are
  * evaluated with fused multiply-adds; the codeword index rides in the 5 low significand bits of
@@ -254,6 +256,12 @@ PKV_HD void pkv_fib_top2_pair(float* best, float* second, float a, float b) {
 #ifndef PKV_FIB_ROT_ERR_TC
 #define PKV_FIB_ROT_ERR_TC 1.0e-5f
 #endif
+/* D = 128: the same three cut-offs (2.9e-6) and 48 partial products, assumed 1.4e-5 (rounded 2.9e-6,
+ * truncating 5.7e-6). */
+#ifndef PKV_FIB_ROT_ERR_TC128
+#define PKV_FIB_ROT_ERR_TC128 1.7e-5f
+#endif
+#define PKV_FIB_ROT_ERR_TC_D(D) ((D) == 64 ? PKV_FIB_ROT_ERR_TC : PKV_FIB_ROT_ERR_TC128)
 
 /* Is the best key's codeword provably the reference's choice when the rotated block is known to
  * eta per coordinate?  (bound in the comment above with eta for PKV_FIB_ROT_ERR) */
@@ -271,32 +279,9 @@ PKV_HD int pkv_fib_certify_eta(float best, float second, float s0, float s1, flo
   return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
 }
 
-/* Is the best key's codeword provably the reference's choice?  (bound in the comment above) */
+/* The same with the bound of the binary32 fused rotation for D = 64. */
 PKV_HD int pkv_fib_certify(float best, float second, float s0, float s1, float s2, float s3) {
-  const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
-                            PKV_FADD(PKV_FMUL(s2, s2), PKV_FMUL(s3, s3)));
-  const float d1 = PKV_FADD(PKV_FMUL(2.0f, best), ss), d2 = PKV_FADD(PKV_FMUL(2.0f, second), ss);
-  /* B_c = 4 eta sqrt(D_c) + 4 eta^2 + 4 u D_c + 1e-5 |F_c|; certain when d2 - d1 > B_1 + B_2 */
-  const float eta = PKV_FIB_ROT_ERR;
-  const float d2p = d2 > 0.0f ? d2 : 0.0f, d1p = d1 > 0.0f ? d1 : 0.0f;
-  const float fb = pkv_f32_from_bits(pkv_f32_bits(best) & 0x7fffffffu);
-  const float fs = pkv_f32_from_bits(pkv_f32_bits(second) & 0x7fffffffu);
-  const float roots = PKV_FADD(PKV_FSQRT_UP(d1p), PKV_FSQRT_UP(d2p));
-  const float bound = PKV_FADD(
-      PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
-      PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(1.0e-5f, PKV_FADD(fb, fs))));
-  return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
-}
-
-PKV_HD uint32_t pkv_fib_block_argmin_fast(float s0, float s1, float s2, float s3, const float* cb,
-                                          const float* half_norm, int n_codewords, int* certain) {
-  float best = pkv_f32_from_bits(0x7f800000u), second = best;
-  for (int c = 0; c < n_codewords; c++)
-    pkv_fib_top2(&best, &second,
-                 pkv_fib_key(s0, s1, s2, s3, cb[4 * c], cb[4 * c + 1], cb[4 * c + 2], cb[4 * c + 3],
-                             half_norm[c], (uint32_t)c));
-  *certain = pkv_fib_certify(best, second, s0, s1, s2, s3);
-  return pkv_f32_bits(best) & 31u;
+  return pkv_fib_certify_eta(best, second, s0, s1, s2, s3, PKV_FIB_ROT_ERR);
 }
 
 #endif /* PKV_FAST_PATHS_H */

@@ -451,6 +451,7 @@ size_t fib_encode_smem(int rec) {
 
 #include "pkv_fib_encode_fast.cuh"
 #include "pkv_fib_encode_tc.cuh"
+#include "pkv_fib_encode_tc128.cuh"
 
 template <typename F>
 int set_smem(F kernel, size_t bytes) {
@@ -532,6 +533,24 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
         err, scratch, scratch + 1, pkv_skip_tensor_issue());
     pkv_count_launch();
     fib_encode_fix_kernel<64><<<148 * 8, kThreads, 0, s>>>(
+        gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
+        p->cfg.argmin_order, payload, scratch, scratch + 1);
+    pkv_count_launch();
+    return pkv_cuda_status(cudaGetLastError());
+  }
+  if (p->cfg.dim == 128 && p->norm_len == 2 && p->idx_bits == 5) {
+    PkvGeom gf = g;
+    gf.tiles_per_batch = (g.vpb + FibTc128::ROWS - 1) / FibTc128::ROWS;
+    const int64_t tiles = (int64_t)g.n_batches * gf.tiles_per_batch;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t grid = tiles < (int64_t)sms ? tiles : (int64_t)sms;  // persistent: one CTA per SM
+    if ((st = set_smem(fib_encode_tc128_kernel, FibTc128::SMEM)) != PKV_OK) return st;
+    fib_encode_tc128_kernel<<<(unsigned)grid, FibTc128::THREADS, FibTc128::SMEM, s>>>(
+        gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, payload,
+        err, scratch, scratch + 1, pkv_skip_tensor_issue());
+    pkv_count_launch();
+    fib_encode_fix_kernel<128><<<148 * 8, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
         p->cfg.argmin_order, payload, scratch, scratch + 1);
     pkv_count_launch();

@@ -63,7 +63,7 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
     pkv_cp_async16(reinterpret_cast<float4*>(s_m) + i, reinterpret_cast<const float4*>(rot32_t) + i);
   if (tid < 32) {
     s_cb[tid] = __ldg(reinterpret_cast<const float4*>(codebook) + tid);
-    s_hn[tid] = __ldg(half_norm + tid);
+    s_hn[tid] = tid < n_codewords ? __ldg(half_norm + tid) : 3.0e38f;  // padding scores above any real entry
   }
   __syncthreads();
   for (int i = tid; i < nv * (D / 4); i += K::THREADS) {
@@ -161,17 +161,20 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
     float best[2 * VPT], second[2 * VPT];
 #pragma unroll
     for (int k = 0; k < 2 * VPT; k++) best[k] = second[k] = __int_as_float(0x7f800000);
-#pragma unroll 2
-    for (int c = 0; c < n_codewords; c++) {
-      const float4 w = s_cb[c];
-      const float hn = s_hn[c];
+    // two codewords per step (the tables hold 32 entries; those past n_codewords never win)
+#pragma unroll 1
+    for (int c = 0; c < n_codewords; c += 2) {
+      const float4 w0 = s_cb[c], w1 = s_cb[c + 1];
+      const float hn0 = s_hn[c], hn1 = s_hn[c + 1];
 #pragma unroll
       for (int i = 0; i < VPT; i++)
 #pragma unroll
         for (int h = 0; h < 2; h++)
-          pkv_fib_top2(&best[2 * i + h], &second[2 * i + h],
-                       pkv_fib_key(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3],
-                                   w.x, w.y, w.z, w.w, hn, (uint32_t)c));
+          pkv_fib_top2_pair(&best[2 * i + h], &second[2 * i + h],
+                            pkv_fib_key(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3],
+                                        w0.x, w0.y, w0.z, w0.w, hn0, (uint32_t)c),
+                            pkv_fib_key(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3],
+                                        w1.x, w1.y, w1.z, w1.w, hn1, (uint32_t)c + 1u));
     }
 #pragma unroll
     for (int i = 0; i < VPT; i++)
@@ -179,8 +182,8 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
       for (int h = 0; h < 2; h++) {
         const int v = VPT * vg + i, b = h * (K::B / 2) + rg;
         s_idx[v * K::B + b] = (uint8_t)(__float_as_uint(best[2 * i + h]) & 31u);
-        if (!pkv_fib_certify(best[2 * i + h], second[2 * i + h], acc[i][4 * h], acc[i][4 * h + 1],
-                             acc[i][4 * h + 2], acc[i][4 * h + 3]))
+        if (!pkv_fib_certify_eta(best[2 * i + h], second[2 * i + h], acc[i][4 * h], acc[i][4 * h + 1],
+                                 acc[i][4 * h + 2], acc[i][4 * h + 3], PKV_FIB_ROT_ERR_D(D)))
           atomicOr(&s_flag[v], 1u << b);
       }
   }

@@ -24,12 +24,12 @@ def _flat_layout(n_batches, vpb, dim):
                          n_heads=1, token_stride=dim, head_stride=dim)
 
 
-@pytest.mark.parametrize("codec", ["turbo", "fib"])
-def test_bounded_wait_runs_out_and_the_context_stays_usable(oracle_mod, codec):
+@pytest.mark.parametrize("codec,dim", [("turbo", 64), ("fib", 64), ("fib", 128)])
+def test_bounded_wait_runs_out_and_the_context_stays_usable(oracle_mod, codec, dim):
     """With the tensor-core products withheld (test hook) the completion barrier never flips: the
     kernels poll it a few hundred times, report PKV_VEC_DEVICE_WAIT, give their tensor memory back
     and return.  Afterwards the same profile encodes normally and matches the oracle."""
-    dim, n = 64, 5000
+    n = 5000
     x = synthetic_kv(n, dim, seed=3)
     if codec == "turbo":
         signs, qjl = tables.rademacher_signs(dim, SEED), tables.qjl_matrix(dim, 32, SEED)
