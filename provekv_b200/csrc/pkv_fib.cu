@@ -529,8 +529,8 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     const int64_t grid = quads < (int64_t)sms * 3 ? quads : (int64_t)sms * 3;  // persistent: 3 CTAs per SM
     if ((st = set_smem(fib_encode_tc_kernel, FibTc::SMEM)) != PKV_OK) return st;
     fib_encode_tc_kernel<<<(unsigned)grid, FibTc::THREADS, FibTc::SMEM, s>>>(
-        gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, payload,
-        err, scratch, scratch + 1, pkv_skip_tensor_issue());
+        gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->rot_dev,
+        p->cfg.argmin_order, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue());
     pkv_count_launch();
     fib_encode_fix_kernel<64><<<148 * 8, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
@@ -547,8 +547,8 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     const int64_t grid = tiles < (int64_t)sms ? tiles : (int64_t)sms;  // persistent: one CTA per SM
     if ((st = set_smem(fib_encode_tc128_kernel, FibTc128::SMEM)) != PKV_OK) return st;
     fib_encode_tc128_kernel<<<(unsigned)grid, FibTc128::THREADS, FibTc128::SMEM, s>>>(
-        gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, payload,
-        err, scratch, scratch + 1, pkv_skip_tensor_issue());
+        gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->rot_dev,
+        p->cfg.argmin_order, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue());
     pkv_count_launch();
     fib_encode_fix_kernel<128><<<148 * 8, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,

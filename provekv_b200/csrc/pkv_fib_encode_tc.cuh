@@ -9,12 +9,70 @@
 //   y~ = n_lo M_hi^T + n_hi M_hi^T + n_hi M_lo^T        (three 128 x 64 x 64 TF32 products)
 // accumulates in tensor memory (pkv_fast_paths.h gives the error bound PKV_FIB_ROT_ERR_TC).  The
 // thread reads its row back and runs the certified nearest-codeword search on its 16 blocks.
-// Blocks the bound cannot settle are redone by the whole warp in binary32 with fused multiply-adds
-// (bound PKV_FIB_ROT_ERR); what that cannot settle either goes on the list of
-// fib_encode_fix_kernel, which redoes it with the reference's exact f64 sequence.
+// Blocks the bound cannot settle are redone by the whole warp in binary64 (fib_exact_block), which
+// reproduces the reference's value unless it rounds within 2e-14 of a binary32 boundary; those few go
+// on the list of fib_encode_fix_kernel, which redoes them with the reference's exact f64 sequence.
 #pragma once
 
 #include "pkv_tcgen05.cuh"
+
+// Exact tier shared by the tensor-core encoders.  For one block of one vector whose normalised form
+// (exact binary32, the reference's n) is row `trow` of the swizzled tile: the warp evaluates the four
+// rotated values in binary64 from the f64 matrix (lane l takes columns l, l + 32, .., then a
+// butterfly sum, bitwise the same in every lane), which differs from the reference's sequential
+// binary64 sum (rotation.rs:104-115) by at most
+//   (D + 1) 2^-53 + (D / 32 + 6) 2^-53  <  1.6e-14      (sum |M_rj n_j| <= |M_r| |n| = 1 to 1e-6),
+// so the reference's (f32) rounding is known unless the value lies within PKV_FIB_F64_SUM_ERR of a
+// binary32 rounding boundary.  With the exact block, lane c evaluates the reference's distance to
+// codeword c in its operation order (simd_nearest.rs:24-39,62-92) and the warp takes the smallest,
+// lowest index first, which is what the strict-less-than scan returns.  Result: the index, or -1
+// when a rounding was not certain (the block then stays on the list of the fix-up kernel).
+#define PKV_FIB_F64_SUM_ERR 2.0e-14
+template <int D, int X_SLAB>
+__device__ __forceinline__ int fib_exact_block(const uint8_t* s_xt, int trow, int gb, const double* __restrict__ rot,
+                                               const float4* s_cb, int n_codewords, int order, int lane) {
+  double part[4];
+#pragma unroll
+  for (int rr = 0; rr < 4; rr++) {
+    const double* mrow = rot + (size_t)(4 * gb + rr) * D;
+    double a = 0.0;
+#pragma unroll
+    for (int k = 0; k < D / 32; k++) {
+      const int j = lane + 32 * k;
+      a = __dadd_rn(a, __dmul_rn(__ldg(mrow + j), (double)*pkv_tc::tile_at(s_xt, X_SLAB, trow, j)));
+    }
+    part[rr] = a;
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1)
+#pragma unroll
+    for (int rr = 0; rr < 4; rr++) part[rr] = __dadd_rn(part[rr], __shfl_xor_sync(0xffffffffu, part[rr], o));
+  float s[4];
+  bool sure = true;
+#pragma unroll
+  for (int rr = 0; rr < 4; rr++) {
+    s[rr] = __double2float_rn(part[rr]);
+    sure = sure && __double2float_rn(__dadd_rn(part[rr], PKV_FIB_F64_SUM_ERR)) ==
+                       __double2float_rn(__dsub_rn(part[rr], PKV_FIB_F64_SUM_ERR));
+  }
+  const float4 w = s_cb[lane];
+  const int paired = order == PKV_ARGMIN_PAIRWISE ? (n_codewords & ~1) : 0;
+  float dist;
+  if (lane < paired) {
+    const float d0 = __fsub_rn(w.x, s[0]), d1 = __fsub_rn(w.y, s[1]);
+    const float d2 = __fsub_rn(w.z, s[2]), d3 = __fsub_rn(w.w, s[3]);
+    dist = __fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fadd_rn(__fmul_rn(d2, d2), __fmul_rn(d3, d3)));
+  } else {
+    const float d0 = __fsub_rn(s[0], w.x), d1 = __fsub_rn(s[1], w.y);
+    const float d2 = __fsub_rn(s[2], w.z), d3 = __fsub_rn(s[3], w.w);
+    dist = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fmul_rn(d2, d2)), __fmul_rn(d3, d3));
+  }
+  // distances are sums of squares: non-negative, so their bit patterns order like the values
+  const uint32_t key = lane < n_codewords ? __float_as_uint(dist) : 0xffffffffu;
+  const uint32_t least = __reduce_min_sync(0xffffffffu, key);
+  const int idx = __ffs(__ballot_sync(0xffffffffu, key == least)) - 1;
+  return sure ? idx : -1;
+}
 
 struct FibTc {
   static constexpr int D = 64, B = 16, THREADS = 128, NWARPS = 4, TV = 32, ROWS = 128;
@@ -28,8 +86,9 @@ struct FibTc {
 __global__ void __launch_bounds__(FibTc::THREADS, 3)
 fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot_hi,
                      const float* __restrict__ rot_lo, const float* __restrict__ codebook,
-                     const float* __restrict__ half_norm, int n_codewords, uint8_t* __restrict__ payload,
-                     uint64_t* err, uint32_t* flag_count, uint32_t* flag_list, int skip_issue) {
+                     const float* __restrict__ half_norm, int n_codewords, const double* __restrict__ rot,
+                     int argmin_order, uint8_t* __restrict__ payload, uint64_t* err, uint32_t* flag_count,
+                     uint32_t* flag_list, int skip_issue) {
   using K = FibTc;
   using pkv_tc::sw_piece;
   using pkv_tc::tile_at;
@@ -249,48 +308,21 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
     if (skip) flagged = 0;
   }
 
-  // Second tier: the flagged blocks of one vector at a time, the whole warp on each.  Lane l takes
-  // columns 2l, 2l + 1 of the block's four rows in binary32 (n from the tile, M32 = M_hi + M_lo
-  // exactly) and a butterfly sum gives every lane the block; then lane c scores codeword c, two
-  // butterfly minima give best and second best (keys are distinct: the index rides in them), and
-  // the owner keeps a certified result.
+  // Second tier: the flagged blocks of one vector at a time, the whole warp on each, exactly
+  // (fib_exact_block); the owner keeps the result.
   for (unsigned pending = __ballot_sync(0xffffffffu, flagged != 0); pending; pending &= pending - 1) {
     const int src = __ffs(pending) - 1;
     uint32_t todo = __shfl_sync(0xffffffffu, flagged, src);
-    const float2 nn = *reinterpret_cast<const float2*>(tile_at(s_xt, K::X_SLAB, warp * K::TV + src, 2 * lane));
-    const float4 cw = s_cb[lane];
-    const float hn = s_hn[lane];
     while (todo) {
       const int b = __ffs(todo) - 1;
       todo &= todo - 1;
-      float part[4];
-#pragma unroll
-      for (int rr = 0; rr < 4; rr++) {
-        const int r = 4 * b + rr;
-        const float2 mh = *reinterpret_cast<const float2*>(tile_at(s_mh, K::M_SLAB, r, 2 * lane));
-        const float2 ml = *reinterpret_cast<const float2*>(tile_at(s_ml, K::M_SLAB, r, 2 * lane));
-        part[rr] = fmaf(__fadd_rn(mh.y, ml.y), nn.y, __fmul_rn(__fadd_rn(mh.x, ml.x), nn.x));
-      }
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1)
-#pragma unroll
-        for (int rr = 0; rr < 4; rr++) part[rr] = __fadd_rn(part[rr], __shfl_xor_sync(0xffffffffu, part[rr], o));
-      const float inf = __int_as_float(0x7f800000);
-      const float key = lane < n_codewords
-                            ? pkv_fib_key(part[0], part[1], part[2], part[3], cw.x, cw.y, cw.z, cw.w, hn, (uint32_t)lane)
-                            : inf;
-      float best = key;
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) best = fminf(best, __shfl_xor_sync(0xffffffffu, best, o));
-      float second = key == best ? inf : key;
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) second = fminf(second, __shfl_xor_sync(0xffffffffu, second, o));
-      if (lane == src && pkv_fib_certify(best, second, part[0], part[1], part[2], part[3])) {
-        const uint32_t idx = __float_as_uint(best) & 31u;
+      const int idx = fib_exact_block<D, K::X_SLAB>(s_xt, warp * K::TV + src, b, rot, s_cb, n_codewords,
+                                                    argmin_order, lane);
+      if (lane == src && idx >= 0) {
         const int wi = b >> 2, sh = 8 * (b & 3);
 #pragma unroll
         for (int k = 0; k < 4; k++)
-          if (k == wi) idx4[k] = (idx4[k] & ~(0xffu << sh)) | (idx << sh);
+          if (k == wi) idx4[k] = (idx4[k] & ~(0xffu << sh)) | ((uint32_t)idx << sh);
         flagged &= ~(1u << b);
       }
     }

@@ -9,7 +9,7 @@
 // from tensor memory -- warps w and w + 4 both own lanes 32 (w % 4) .. of it -- and runs the
 // certified search on them.  Both threads of a pair run the whole f64 norm chain (its order is the
 // reference's).  Tiers as for d = 64: tensor-core value with PKV_FIB_ROT_ERR_TC128, then the warp
-// in binary32 with PKV_FIB_ROT_ERR_D(128), then the list of fib_encode_fix_kernel<128>.
+// in binary64 (fib_exact_block), then the list of fib_encode_fix_kernel<128>.
 #pragma once
 
 struct FibTc128 {
@@ -23,8 +23,9 @@ struct FibTc128 {
 __global__ void __launch_bounds__(FibTc128::THREADS, 1)
 fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot_hi,
                         const float* __restrict__ rot_lo, const float* __restrict__ codebook,
-                        const float* __restrict__ half_norm, int n_codewords, uint8_t* __restrict__ payload,
-                        uint64_t* err, uint32_t* flag_count, uint32_t* flag_list, int skip_issue) {
+                        const float* __restrict__ half_norm, int n_codewords, const double* __restrict__ rot,
+                        int argmin_order, uint8_t* __restrict__ payload, uint64_t* err, uint32_t* flag_count,
+                        uint32_t* flag_list, int skip_issue) {
   using K = FibTc128;
   using pkv_tc::sw_piece;
   constexpr int D = K::D;
@@ -251,50 +252,21 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
     if (skip) flagged = 0;
   }
 
-  // Second tier: the flagged blocks of one thread at a time, the whole warp on each.  Lane l takes
-  // columns 4l .. 4l + 3 of the block's four rows in binary32 (n from the tile, M32 = M_hi + M_lo
-  // exactly) and a butterfly sum gives every lane the block; then lane c scores codeword c, two
-  // butterfly minima give best and second best, and the owner keeps a certified result.
+  // Second tier: the flagged blocks of one thread at a time, the whole warp on each, exactly
+  // (fib_exact_block); the owner keeps the result.
   for (unsigned pending = __ballot_sync(0xffffffffu, flagged != 0); pending; pending &= pending - 1) {
     const int src = __ffs(pending) - 1;
     uint32_t todo = __shfl_sync(0xffffffffu, flagged, src);
-    const float4 nn = *reinterpret_cast<const float4*>(s_xt + sw_piece(K::X_SLAB, (warp & 3) * 32 + src, lane));
-    const float4 cw = s_cb[lane];
-    const float hn = s_hn[lane];
     while (todo) {
       const int b = __ffs(todo) - 1;
       todo &= todo - 1;
-      float pr[4];
-#pragma unroll
-      for (int rr = 0; rr < 4; rr++) {
-        const int r = 4 * (part * K::HB + b) + rr;
-        const float4 mh = *reinterpret_cast<const float4*>(s_mh + sw_piece(K::M_SLAB, r, lane));
-        const float4 ml = *reinterpret_cast<const float4*>(s_ml + sw_piece(K::M_SLAB, r, lane));
-        float a = __fmul_rn(__fadd_rn(mh.x, ml.x), nn.x);
-        a = fmaf(__fadd_rn(mh.y, ml.y), nn.y, a);
-        a = fmaf(__fadd_rn(mh.z, ml.z), nn.z, a);
-        pr[rr] = fmaf(__fadd_rn(mh.w, ml.w), nn.w, a);
-      }
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1)
-#pragma unroll
-        for (int rr = 0; rr < 4; rr++) pr[rr] = __fadd_rn(pr[rr], __shfl_xor_sync(0xffffffffu, pr[rr], o));
-      const float inf = __int_as_float(0x7f800000);
-      const float key = lane < n_codewords
-                            ? pkv_fib_key(pr[0], pr[1], pr[2], pr[3], cw.x, cw.y, cw.z, cw.w, hn, (uint32_t)lane)
-                            : inf;
-      float best = key;
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) best = fminf(best, __shfl_xor_sync(0xffffffffu, best, o));
-      float second = key == best ? inf : key;
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) second = fminf(second, __shfl_xor_sync(0xffffffffu, second, o));
-      if (lane == src && pkv_fib_certify_eta(best, second, pr[0], pr[1], pr[2], pr[3], PKV_FIB_ROT_ERR_D(128))) {
-        const uint32_t idx = __float_as_uint(best) & 31u;
+      const int idx = fib_exact_block<D, K::X_SLAB>(s_xt, (warp & 3) * 32 + src, part * K::HB + b, rot, s_cb,
+                                                    n_codewords, argmin_order, lane);
+      if (lane == src && idx >= 0) {
         const int wi = b >> 2, sh = 8 * (b & 3);
 #pragma unroll
         for (int k = 0; k < 4; k++)
-          if (k == wi) idx4[k] = (idx4[k] & ~(0xffu << sh)) | (idx << sh);
+          if (k == wi) idx4[k] = (idx4[k] & ~(0xffu << sh)) | ((uint32_t)idx << sh);
         flagged &= ~(1u << b);
       }
     }
