@@ -8,7 +8,9 @@ generators follow the same *algorithms* with NumPy's PCG64 as the random
 source, so a table built here is a valid table of the same distribution but is
 not the table the Rust crate builds for the same seed.  Bit-exactness of the
 codec is defined given equal tables; tables are plain arrays that can also be
-loaded from a dump of the Rust side.
+loaded from a dump of the Rust side.  `rust_streams.py` restates the crates'
+own streams (ziggurat normal, gamma, Householder QR on ChaCha8) as candidates
+for the reference's tables, unverified against the crates.
 
 Reference algorithms followed:
   * Haar rotation        fib-quant/src/rotation.rs:24-58
