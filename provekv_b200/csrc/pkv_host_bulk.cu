@@ -53,10 +53,15 @@ int parse_header(const BulkCodec& c, const uint8_t* b, int64_t len, uint32_t* n)
                  : pkv_fb2_header_parse((const pkv_fib_profile*)c.profile, b, len, n);
 }
 
+// The staging streams get the highest priority the device offers: their kernels are short chunks
+// that feed a transfer pipeline, and when the caller has a long kernel of its own in flight on another
+// stream (a decode-and-patch of the pool, say) the chunks must not queue behind its blocks.
 int prepare_streams(PkvWorkspace* ws) {
+  int least = 0, greatest = 0;
+  if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return PKV_ERR_CUDA;
   for (int i = 0; i < PKV_WS_STREAMS; i++)
     if (!ws->streams[i] &&
-        cudaStreamCreateWithFlags(&ws->streams[i], cudaStreamNonBlocking) != cudaSuccess)
+        cudaStreamCreateWithPriority(&ws->streams[i], cudaStreamNonBlocking, greatest) != cudaSuccess)
       return PKV_ERR_CUDA;
   return PKV_OK;
 }
