@@ -532,7 +532,8 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
         gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->rot_dev,
         p->cfg.argmin_order, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue());
     pkv_count_launch();
-    fib_encode_fix_kernel<64><<<148 * 8, kThreads, 0, s>>>(
+    // the in-kernel exact tier leaves only boundary cases on the list: one CTA per SM is plenty
+    fib_encode_fix_kernel<64><<<sms, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
         p->cfg.argmin_order, payload, scratch, scratch + 1);
     pkv_count_launch();
@@ -550,7 +551,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
         gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->rot_dev,
         p->cfg.argmin_order, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue());
     pkv_count_launch();
-    fib_encode_fix_kernel<128><<<148 * 8, kThreads, 0, s>>>(
+    fib_encode_fix_kernel<128><<<sms, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,
         p->cfg.argmin_order, payload, scratch, scratch + 1);
     pkv_count_launch();
