@@ -181,21 +181,30 @@ struct PkvUlpTable {
 };
 int pkv_ulp_table_get(int kind, PkvUlpTable* out);
 
-// The host libm's value of the function at `arg`, from the portable value; a null table = portable.
-__device__ __forceinline__ float pkv_ulp_adjust(const PkvUlpTable& t, float arg, float portable) {
-  if (t.keys == nullptr) return portable;
+// The host libm's value of the function at `arg`, from the portable value.  Out of line and with the
+// table passed as scalars: the callers sit in long unrolled loops (one call site per radius), and a
+// reference to a member of a kernel's parameter struct would make the compiler copy the whole struct
+// to local memory.
+static __device__ __noinline__ float pkv_ulp_lookup(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ dirs,
+                                             const uint32_t* __restrict__ bloom, uint32_t n, uint32_t bloom_log2,
+                                             float arg, float portable) {
   const uint32_t u = __float_as_uint(arg);
-  const uint32_t b = (u * PKV_ULP_HASH_MUL) >> (32u - t.bloom_log2);
-  if (!((__ldg(t.bloom + (b >> 5)) >> (b & 31u)) & 1u)) return portable;
-  uint32_t lo = 0, hi = t.n;  // first key >= u
+  const uint32_t b = (u * PKV_ULP_HASH_MUL) >> (32u - bloom_log2);
+  if (!((__ldg(bloom + (b >> 5)) >> (b & 31u)) & 1u)) return portable;
+  uint32_t lo = 0, hi = n;  // first key >= u
   while (lo < hi) {
     const uint32_t mid = (lo + hi) >> 1;
-    if (__ldg(t.keys + mid) < u) lo = mid + 1;
+    if (__ldg(keys + mid) < u) lo = mid + 1;
     else hi = mid;
   }
-  if (lo >= t.n || __ldg(t.keys + lo) != u) return portable;
-  const bool up = (__ldg(t.dirs + (lo >> 5)) >> (lo & 31u)) & 1u;
+  if (lo >= n || __ldg(keys + lo) != u) return portable;
+  const bool up = (__ldg(dirs + (lo >> 5)) >> (lo & 31u)) & 1u;
   return __uint_as_float(__float_as_uint(portable) + (up ? 1u : 0xffffffffu));
+}
+// A null table = the portable value.
+__device__ __forceinline__ float pkv_ulp_adjust(const PkvUlpTable t, float arg, float portable) {
+  if (t.keys == nullptr) return portable;
+  return pkv_ulp_lookup(t.keys, t.dirs, t.bloom, t.n, t.bloom_log2, arg, portable);
 }
 
 // ---- host-side objects ---------------------------------------------------

@@ -132,8 +132,11 @@ __device__ __noinline__ bool fix_pairs_warp(const uint8_t* xt, int xrow, uint4 s
 // (PolarCode::from_parts, polar.rs:127-133).
 // The exact logarithm of the BlockLogU8 coder, kept out of line: four call sites, two of them rare.
 // (with a table of the host libm's deviations: that libm's logf, bit for bit)
-__device__ __noinline__ float exact_logf(float r, const PkvUlpTable& t) {
-  return pkv_ulp_adjust(t, r, pkv_logf_portable(r));
+#define PKV_LOGF_TABLE_ARGS tp.logf_table.keys, tp.logf_table.dirs, tp.logf_table.bloom, tp.logf_table.n, tp.logf_table.bloom_log2
+__device__ __noinline__ float exact_logf(float r, const uint32_t* keys, const uint32_t* dirs, const uint32_t* bloom,
+                                         uint32_t n, uint32_t bloom_log2) {
+  const float l = pkv_logf_portable(r);
+  return keys == nullptr ? l : pkv_ulp_lookup(keys, dirs, bloom, n, bloom_log2, r, l);
 }
 
 __device__ __noinline__ int classify_bad_vector(const uint8_t* xt, int slab, int row, int dim) {
@@ -548,7 +551,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       rmin = fminf(rmin, r);
       rmax = fmaxf(rmax, r);
     }
-    float mn = exact_logf(rmin, tp.logf_table), mx = exact_logf(rmax, tp.logf_table);
+    float mn = exact_logf(rmin, PKV_LOGF_TABLE_ARGS), mx = exact_logf(rmax, PKV_LOGF_TABLE_ARGS);
     const float near_min = __fmul_rn(rmin, 1.00004f), near_max = __fmul_rn(rmax, 0.99996f);
     bool ties = false;
 #pragma unroll
@@ -563,8 +566,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
 #pragma unroll 1
       for (int i = 0; i < K::P; i++) {
         const float r = rl[i];
-        if (r <= near_min) mn = fminf(mn, exact_logf(r, tp.logf_table));
-        if (r >= near_max) mx = fmaxf(mx, exact_logf(r, tp.logf_table));
+        if (r <= near_min) mn = fminf(mn, exact_logf(r, PKV_LOGF_TABLE_ARGS));
+        if (r >= near_max) mx = fmaxf(mx, exact_logf(r, PKV_LOGF_TABLE_ARGS));
       }
     }
     float span = __fsub_rn(mx, mn);
@@ -590,7 +593,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       while (unsure) {
         const int i = __ffsll((long long)unsure) - 1;
         unsure &= unsure - 1;
-        float nrm = __fdiv_rn(__fsub_rn(exact_logf(rl[i], tp.logf_table), mn), span);
+        float nrm = __fdiv_rn(__fsub_rn(exact_logf(rl[i], PKV_LOGF_TABLE_ARGS), mn), span);
         nrm = nrm < 0.0f ? 0.0f : (nrm > 1.0f ? 1.0f : nrm);
         const uint32_t c8 = (uint32_t)roundf(__fmul_rn(nrm, 255.0f)) & 0xffu;
         const int sh = 8 * (i & 3);
