@@ -21,7 +21,8 @@ distinct vector once on the decode side.  ``kernels`` gives each kernel's time, 
 fraction of the measured HBM copy bandwidth; ``roofline`` repeats that for the slowest one.  ``e2e``
 is the same step from pinned host buffers: host f32 -> wire blobs on the host through the
 ``*_encode_batches_compact`` calls, wire bytes back to the device, decode-and-patch into the
-device-resident caches, error words read back.  Data are seeded synthetic tensors with the
+device-resident caches, error words read back (the pool's decode-and-patch is launched as soon as its
+records are back and runs under the shell encode's transfers).  Data are seeded synthetic tensors with the
 configurations' shapes and value distributions; no dataset or checkpoint is read.
 
 With ``--impl reference`` the CPU restatement of the reference (oracle/) runs the same step on a
