@@ -5,10 +5,11 @@ Default workload (``--workload c4``): the two-tier pool on the Qwen2.5-0.5B GQA 
 (24 layers x {K,V} x 2 KV heads x head_dim 64): a 32,768-token shared prefix and 64 agents x 512
 unique tokens, every agent's f32 cache holding 32,768 + 64 * 512 = 65,536 positions.  One step =
   1. fib-quant k4_n32 encode of the prefix (FB2 records),
-  2. (more than one GPU) all-gather of the FB2 payload so every rank holds the whole cold pool,
+  2. (more than one GPU) all-gather of the FB2 payload so every rank holds the whole cold pool; it runs
+     on NCCL's stream beside steps 3 and 4,
   3. turbo-quant b=4 (polar 3 bit + 32 QJL signs, f32 radii) encode of the agents' shells (TQB1),
-  4. decode-and-patch of the pool into every owned agent's cache (one decode, one write per agent),
-  5. decode-and-patch of each shell at position n_shared + agent * n_unique of its agent's cache.
+  4. decode-and-patch of each shell at position n_shared + agent * n_unique of its agent's cache,
+  5. decode-and-patch of the pool into every owned agent's cache (one decode, one write per agent).
 At N GPUs the agents (shells, caches) are sharded by agent and the prefix encode by layer; the fixed
 workload is divided, i.e. strong scaling.  ``--workload c3`` is the same on the SmolLM2-1.7B shape
 (800 + 8 x 28 tokens), ``--workload c5`` the Llama-3-8B shape (d = 128, 131,072 + 16 x 2,048 tokens)
@@ -107,8 +108,8 @@ def config_dict(w, args):
         par = (f"{args.gpus} GPU(s): agents (shells, caches) sharded by agent, prefix encode by layer, FB2 payload "
                "all-gathered; no collective inside the codec kernels") if w["shard"] == "agent" else \
               f"{args.gpus} GPU(s): everything sharded by layer, no exchange"
-        step = ("fib encode prefix, all-gather FB2 payload, turbo encode shells, decode-and-patch pool into every "
-                "agent cache, decode-and-patch shells")
+        step = ("fib encode prefix, all-gather FB2 payload (beside the shell chain), turbo encode shells, "
+                "decode-and-patch shells, decode-and-patch pool into every agent cache")
     else:
         par = f"{args.gpus} x the same workload (independent replicas)"
         step = "encode every batch, decode-and-patch every batch"
@@ -543,7 +544,9 @@ def run_single(args, w):
 # ---------------------------------------------------------------------------------------------
 # the two-tier pool (c3, c4, c5)
 # ---------------------------------------------------------------------------------------------
-PHASES = ("fib_encode", "pool_gather", "turbo_encode", "fib_decode_patch", "turbo_decode_patch")
+# order inside a step; the all-gather is launched after the prefix encode and waited for just before the pool decode
+PHASES = ("fib_encode", "pool_gather", "turbo_encode", "turbo_decode_patch", "gather_wait", "fib_decode_patch")
+NOT_KERNELS = ("pool_gather", "gather_wait")
 
 
 def pool_kernel_names(d):
@@ -620,23 +623,26 @@ def run_pool(args, w):
             fib.encode_dev(kv_prefix.data_ptr(), lay_pe, pay_local_c.data_ptr(), ps_p, err.data_ptr(), stream)
             if e:
                 e[1].record()
-            # the all-gather of the pool runs on NCCL's stream beside the shell encode (the decode waits for it)
+            # the all-gather of the pool runs on NCCL's stream beside the whole shell chain; only the pool's
+            # decode waits for it
             work = pdist.all_gather_pool(pay_local_c, pay_pool, async_op=True) if gather else None
             if e:
                 e[2].record()
             turbo.encode_dev(kv_shells.data_ptr(), lay_se, pay_shells.data_ptr(), ps_s, err[1:].data_ptr(), stream)
-            if work is not None:
-                work.wait()
             if e:
                 e[3].record()
-            fib.decode_patch_dev(pay_pool.data_ptr(), ps_p, lay_pd, caches.data_ptr(), err[2:].data_ptr(), stream,
-                                 dst_dtype=dst)
-            if e:
-                e[4].record()
             turbo.decode_patch_dev(pay_shells.data_ptr(), ps_s, lay_sd, caches.data_ptr(), err[3:].data_ptr(),
                                    stream, dst_dtype=dst)
             if e:
+                e[4].record()
+            if work is not None:
+                work.wait()
+            if e:
                 e[5].record()
+            fib.decode_patch_dev(pay_pool.data_ptr(), ps_p, lay_pd, caches.data_ptr(), err[2:].data_ptr(), stream,
+                                 dst_dtype=dst)
+            if e:
+                e[6].record()
 
     def barrier():
         if world > 1:
@@ -658,7 +664,7 @@ def run_pool(args, w):
             b.record()
         torch.cuda.synchronize()
         gather_ms = float(np.median([a.elapsed_time(b) for a, b in gev]))
-    events = [[[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(groups)]
+    events = [[[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(groups)]
               for _ in range(args.steps)]
     launches0 = lib.pkv_launch_count()
     barrier()
@@ -670,8 +676,8 @@ def run_pool(args, w):
         t_wall = time.perf_counter() - t_wall
     launches = lib.pkv_launch_count() - launches0
     assert all(int(v) == -1 for v in err.tolist())
-    phase_ms = [float(np.mean([sum(g[k].elapsed_time(g[k + 1]) for g in ev) for ev in events])) for k in range(5)]
-    step_ms = float(np.mean([sum(g[0].elapsed_time(g[5]) for g in ev) for ev in events]))
+    phase_ms = [float(np.mean([sum(g[k].elapsed_time(g[k + 1]) for g in ev) for ev in events])) for k in range(6)]
+    step_ms = float(np.mean([sum(g[0].elapsed_time(g[6]) for g in ev) for ev in events]))
 
     # ---- end to end from pinned host buffers ------------------------------------------------
     host = []
@@ -788,15 +794,13 @@ def run_pool(args, w):
                 "turbo_decode_patch": n_s * (rec_t + d * esz) * groups}
         kernels = {}
         for k, ph in enumerate(PHASES):
-            if ph == "pool_gather":
+            if ph in NOT_KERNELS:
                 continue
             ms = phase_ms[k]
             kernels[names[ph]] = {"ms": ms, "launches_per_step": groups * (2 if ph in ("fib_encode", "turbo_encode") else 1),
                                   "algorithmic_bytes": algo[ph], "achieved_gbs": algo[ph] / ms / 1e6,
                                   "frac_of_measured_hbm": algo[ph] / ms / 1e6 / peak}
-        if gather:
-            kernels[names["turbo_encode"]]["note"] = "timed together with the pool all-gather running beside it"
-        dom_phase = max((ph for ph in PHASES if ph != "pool_gather"), key=lambda ph: phase_ms[PHASES.index(ph)])
+        dom_phase = max((ph for ph in PHASES if ph not in NOT_KERNELS), key=lambda ph: phase_ms[PHASES.index(ph)])
         dom = kernels[names[dom_phase]]
         clk = clocks.summary()
         gather_bytes = pay_pool.numel() * groups if gather else 0
@@ -806,12 +810,14 @@ def run_pool(args, w):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(w, args),
             "value_unique": (enc_bytes + uniq_dec) / (step_ms * 1e-3) / 1e9,
             "encode_gbs": enc_bytes / ((phase_ms[0] + phase_ms[2]) * 1e-3) / 1e9,
-            "decode_patch_gbs": dec_bytes / ((phase_ms[3] + phase_ms[4]) * 1e-3) / 1e9,
+            "decode_patch_gbs": dec_bytes / ((phase_ms[3] + phase_ms[5]) * 1e-3) / 1e9,
             "f32_bytes_encoded_per_step": enc_bytes, "f32_bytes_patched_per_step": dec_bytes,
             "kernels": kernels,
             "broadcast_ms": gather_ms,
             "broadcast": {"what": "all-gather of the FB2 payload into every rank's HBM (NCCL), timed on its own; inside "
-                                  "a step it runs beside the shell encode" if gather else "none",
+                                  "a step it runs beside the shell encode and decode, and gather_wait_ms is what the "
+                                  "pool decode still waits for" if gather else "none",
+                          "gather_wait_ms": phase_ms[PHASES.index("gather_wait")] if gather else 0.0,
                           "bytes_per_rank": gather_bytes,
                           "bus_gbs": (gather_bytes * (world - 1) / world) / (gather_ms * 1e-3) / 1e9
                           if gather and gather_ms > 0 else None},
