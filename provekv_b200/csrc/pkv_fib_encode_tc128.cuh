@@ -2,22 +2,27 @@
 // Included by pkv_fib.cu inside its unnamed namespace, after pkv_fib_encode_tc.cuh.
 //
 // The three operand tiles of the split product (n, M_hi, M_lo: 64 KB each) fill most of an SM's
-// shared memory, so one persistent CTA of 8 warps runs per SM and two threads share a vector:
-// thread (row, part) normalises elements 64 part .. 64 part + 63 of vector `row`, and after the
+// shared memory, so one persistent CTA runs per SM and PARTS threads share a vector:
+// thread (row, part) normalises elements EPT part .. EPT part + EPT - 1 of vector `row`, and after the
 //   y~ = n_lo M_hi^T + n_hi M_hi^T + n_hi M_lo^T        (three 128 x 128 x 128 TF32 products)
-// reads accumulator columns 64 part .. 64 part + 63 (blocks 16 part .. 16 part + 15) of its row
-// from tensor memory -- warps w and w + 4 both own lanes 32 (w % 4) .. of it -- and runs the
-// certified search on them.  Both threads of a pair run the whole f64 norm chain (its order is the
-// reference's).  Tiers as for d = 64: tensor-core value with PKV_FIB_ROT_ERR_TC128, then the warp
-// in binary64 (fib_exact_block), then the list of fib_encode_fix_kernel<128>.
+// reads accumulator columns EPT part .. (blocks HB part .. HB part + HB - 1) of its row from tensor
+// memory -- warps w, w + 4, .. all own lanes 32 (w % 4) .. of it -- and runs the certified search on
+// them.  Every thread of a vector runs the whole f64 norm chain (its order is the reference's).
+// Tiers as for d = 64: tensor-core value with PKV_FIB_ROT_ERR_TC128, then the warp in binary64
+// (fib_exact_block), then the list of fib_encode_fix_kernel<128>.
 #pragma once
 
 struct FibTc128 {
-  static constexpr int D = 128, HB = 16, THREADS = 256, NWARPS = 8, ROWS = 128, REC = 22;
+  static constexpr int D = 128, PARTS = 2, ROWS = 128, REC = 22;
+  static constexpr int THREADS = ROWS * PARTS, NWARPS = THREADS / 32;
+  static constexpr int EPT = D / PARTS;   // elements normalised / accumulator columns read per thread
+  static constexpr int PPT = EPT / 4;     // 16-byte pieces of the row per thread
+  static constexpr int HB = EPT / 4;      // blocks searched per thread
   static constexpr int X_SLAB = ROWS * 128, X_BYTES = 4 * X_SLAB;  // vector tile: 4 slabs of [128 rows][128 B]
   static constexpr int M_SLAB = D * 128, M_BYTES = 4 * M_SLAB;     // matrix tile: 4 slabs of [128 rows][128 B]
   static constexpr size_t SMEM = 1024 + X_BYTES + 2 * M_BYTES + 32 * sizeof(float4) + 32 * sizeof(float) +
-                                 ROWS * sizeof(int64_t) + ROWS * sizeof(uint32_t) + ROWS * REC + 16;
+                                 ROWS * (sizeof(int64_t) + sizeof(double) + 2 * sizeof(uint32_t)) + ROWS * REC + 16;
+  static_assert(PARTS == 2 || PARTS == 4, "threads per vector");
 };
 
 __global__ void __launch_bounds__(FibTc128::THREADS, 1)
@@ -40,8 +45,10 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   float4* s_cb = reinterpret_cast<float4*>(s_ml + K::M_BYTES);                 // [32] codewords
   float* s_hn = reinterpret_cast<float*>(s_cb + 32);                           // [32] |c|^2 / 2
   int64_t* s_off = reinterpret_cast<int64_t*>(s_hn + 32);                      // [ROWS]
-  uint16_t* s_flag = reinterpret_cast<uint16_t*>(s_off + K::ROWS);             // [ROWS][2] undecided blocks
-  uint8_t* s_rec = reinterpret_cast<uint8_t*>(s_flag + 2 * K::ROWS);           // [ROWS][22]
+  double* s_sq = reinterpret_cast<double*>(s_off + K::ROWS);                   // [ROWS] squared norms
+  uint32_t* s_key = reinterpret_cast<uint32_t*>(s_sq + K::ROWS);               // [ROWS] smallest nonzero magnitude keys
+  uint32_t* s_flag = s_key + K::ROWS;                                          // [ROWS] undecided blocks
+  uint8_t* s_rec = reinterpret_cast<uint8_t*>(s_flag + K::ROWS);               // [ROWS][22]
   s_rec += (16 - (pkv_tc::smem_u32(s_rec) & 15u)) & 15u;
 
   if (warp == 0) pkv_tc::tmem_alloc(&s_tmem, 128);
@@ -64,6 +71,14 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   bool failed = false;
   uint32_t pending_parity = 0;
 
+  // element offset of this thread's row in tile `id` (threads with part == 0 only; 0 past the batch's end)
+  auto row_offset = [&](int64_t id) -> int64_t {
+    if (id >= n_tiles) return 0;
+    const int t = (int)(id % g.tiles_per_batch), b = (int)(id / g.tiles_per_batch);
+    return t * K::ROWS + row < g.vpb ? pkv_vec_offset(g.L, b, t * K::ROWS + row) : 0;
+  };
+  int64_t off_next = part == 0 ? row_offset(blockIdx.x) : 0;  // computed one round ahead, where the row is prefetched
+
   for (int64_t tile_id = blockIdx.x; tile_id < n_tiles; tile_id += gridDim.x) {
   const int tile = (int)(tile_id % g.tiles_per_batch);
   const int batch = (int)(tile_id / g.tiles_per_batch);
@@ -71,7 +86,10 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   const int nv = min(K::ROWS, g.vpb - v0);
   const bool valid = row < nv;
 
-  if (part == 0) s_off[row] = valid ? pkv_vec_offset(g.L, batch, v0 + row) : 0;
+  if (part == 0) {
+    s_off[row] = off_next;
+    s_flag[row] = 0;
+  }
   __syncthreads();  // also: the previous round's records have been copied out
 #pragma unroll 4
   for (int i = threadIdx.x; i < nv * 32; i += K::THREADS) {
@@ -85,39 +103,36 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   pkv_tc::fence_after_sync();
 
   // exact norm over the whole row in the reference's order (codec.rs:1049-1057; see
-  // fib_encode_tc_kernel), this thread's half kept in registers
-  float n[64];
-  double acc = 0.0;
-  uint32_t min_key = 0xffffffffu;
-  auto other_half = [&](int first_piece) {
-#pragma unroll 4
-    for (int c = first_piece; c < first_piece + 16; c++) {
+  // fib_encode_tc_kernel): one thread per vector runs the chain (the conversions to binary64 are what
+  // it costs, so it is not repeated by the other threads of the vector) and shares the sum
+  float n[K::EPT];
+  if (part == 0) {
+    double sq = 0.0;
+    uint32_t key = 0xffffffffu;
+#pragma unroll 8
+    for (int c = 0; c < D / 4; c++) {
       const float4 t = valid ? *reinterpret_cast<const float4*>(s_xt + (c >> 3) * K::X_SLAB + (xsw ^ ((c & 7) << 4)))
                              : make_float4(0.f, 0.f, 0.f, 0.f);
-      acc = fma((double)t.x, (double)t.x, acc);
-      acc = fma((double)t.y, (double)t.y, acc);
-      acc = fma((double)t.z, (double)t.z, acc);
-      acc = fma((double)t.w, (double)t.w, acc);
-      min_key = min(min(min_key, min(pkv_fib_mag_key(t.x), pkv_fib_mag_key(t.y))),
-                    min(pkv_fib_mag_key(t.z), pkv_fib_mag_key(t.w)));
+      sq = fma((double)t.x, (double)t.x, sq);
+      sq = fma((double)t.y, (double)t.y, sq);
+      sq = fma((double)t.z, (double)t.z, sq);
+      sq = fma((double)t.w, (double)t.w, sq);
+      key = min(min(key, min(pkv_fib_mag_key(t.x), pkv_fib_mag_key(t.y))),
+                min(pkv_fib_mag_key(t.z), pkv_fib_mag_key(t.w)));
     }
-  };
-  if (part == 1) other_half(0);
+    s_sq[row] = sq;
+    s_key[row] = key;
+  }
 #pragma unroll
-  for (int i = 0; i < 64; i += 4) {
-    const int c = part * 16 + (i >> 2);
+  for (int i = 0; i < K::EPT; i += 4) {
+    const int c = part * K::PPT + (i >> 2);
     const float4 t = valid ? *reinterpret_cast<const float4*>(s_xt + (c >> 3) * K::X_SLAB + (xsw ^ ((c & 7) << 4)))
                            : make_float4(0.f, 0.f, 0.f, 0.f);
     n[i] = t.x; n[i + 1] = t.y; n[i + 2] = t.z; n[i + 3] = t.w;
   }
-#pragma unroll
-  for (int i = 0; i < 64; i++) {
-    const double t = (double)n[i];
-    acc = fma(t, t, acc);
-    min_key = min(min_key, pkv_fib_mag_key(n[i]));
-  }
-  if (part == 0) other_half(16);
-  __syncthreads();  // every norm chain has read the tile: halves may now be rewritten in place
+  __syncthreads();  // the sums are there, and every chain has read the tile: parts may now be rewritten in place
+  const double acc = s_sq[row];
+  const uint32_t min_key = s_key[row];
   const bool finite = acc < __longlong_as_double(0x7ff0000000000000ll);
   double norm = __dsqrt_rn(acc);
   int bad = 0;
@@ -133,11 +148,11 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
     const float invh = __double2float_rn(inv), invl = __double2float_rn(__dsub_rn(inv, (double)invh));
     uint32_t unsure = pkv_fib_fast_norm_ok(norm, min_key) ? 0u : 1u;
 #pragma unroll
-    for (int i = 0; i < 64; i++) n[i] = pkv_fib_norm_quotient(n[i], invh, invl, &unsure);
+    for (int i = 0; i < K::EPT; i++) n[i] = pkv_fib_norm_quotient(n[i], invh, invl, &unsure);
     if (unsure || skip) {
       // rare: the reference's division element by element, through the tile (x is still there)
 #pragma unroll 1
-      for (int c = part * 16; c < part * 16 + 16; c++) {
+      for (int c = part * K::PPT; c < (part + 1) * K::PPT; c++) {
         float4* cell = reinterpret_cast<float4*>(s_xt + (c >> 3) * K::X_SLAB + (xsw ^ ((c & 7) << 4)));
         float4 t = *cell;
         t.x = skip ? 0.0f : __double2float_rn(__ddiv_rn((double)t.x, norm));
@@ -147,8 +162,8 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
         *cell = t;
       }
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        const int c = part * 16 + (i >> 2);
+      for (int i = 0; i < K::EPT; i += 4) {
+        const int c = part * K::PPT + (i >> 2);
         const float4 t = *reinterpret_cast<const float4*>(s_xt + (c >> 3) * K::X_SLAB + (xsw ^ ((c & 7) << 4)));
         n[i] = t.x; n[i + 1] = t.y; n[i + 2] = t.z; n[i + 3] = t.w;
       }
@@ -157,8 +172,8 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
 
   // first operand: the exact remainder n_lo = n - n_hi; one product (M_hi)
 #pragma unroll
-  for (int i = 0; i < 64; i += 4) {
-    const int c = part * 16 + (i >> 2);
+  for (int i = 0; i < K::EPT; i += 4) {
+    const int c = part * K::PPT + (i >> 2);
     float lo[4];
 #pragma unroll
     for (int k = 0; k < 4; k++)
@@ -184,8 +199,8 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   pkv_tc::fence_after_sync();
   // second operand: n itself (the unit reads n_hi); two products (M_hi, M_lo)
 #pragma unroll
-  for (int i = 0; i < 64; i += 4) {
-    const int c = part * 16 + (i >> 2);
+  for (int i = 0; i < K::EPT; i += 4) {
+    const int c = part * K::PPT + (i >> 2);
     *reinterpret_cast<float4*>(s_xt + (c >> 3) * K::X_SLAB + (xsw ^ ((c & 7) << 4))) =
         make_float4(n[i], n[i + 1], n[i + 2], n[i + 3]);
   }
@@ -211,19 +226,27 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   }
   pkv_tc::fence_after_sync();
 
-  uint32_t idx4[4] = {0, 0, 0, 0};  // four 8-bit indices per word: this thread's 16 blocks
+  // the next tile's rows on their way into L2 while this one is searched (four 128-byte lines per row)
+  if (part == 0) {
+    const int64_t next_id = tile_id + gridDim.x;
+    off_next = row_offset(next_id);
+    if (next_id < n_tiles && (int)(next_id % g.tiles_per_batch) * K::ROWS + row < g.vpb) {
+#pragma unroll
+      for (int q = 0; q < D / 32; q++) asm volatile("prefetch.global.L2 [%0];" ::"l"(x + off_next + 32 * q));
+    }
+  }
+  uint32_t idx4[K::HB / 4] = {};  // four 8-bit indices per word: this thread's blocks
   uint32_t flagged = 0;             // those whose nearest codeword is not settled yet
   {
-    float y[64];
+    float y[K::EPT];
     {
-      float h0[32], h1[32];
-      const uint32_t taddr = s_tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(part * 64);
-      pkv_tc::tmem_load32(taddr, h0);
-      pkv_tc::tmem_load32(taddr + 32, h1);
+      const uint32_t taddr = s_tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(part * K::EPT);
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        y[i] = h0[i];
-        y[32 + i] = h1[i];
+      for (int h = 0; h < K::EPT / 32; h++) {
+        float part32[32];
+        pkv_tc::tmem_load32(taddr + 32 * h, part32);
+#pragma unroll
+        for (int i = 0; i < 32; i++) y[32 * h + i] = part32[i];
       }
     }
     float best[K::HB], second[K::HB];
@@ -265,7 +288,7 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
       if (lane == src && idx >= 0) {
         const int wi = b >> 2, sh = 8 * (b & 3);
 #pragma unroll
-        for (int k = 0; k < 4; k++)
+        for (int k = 0; k < K::HB / 4; k++)
           if (k == wi) idx4[k] = (idx4[k] & ~(0xffu << sh)) | ((uint32_t)idx << sh);
         flagged &= ~(1u << b);
       }
@@ -273,13 +296,13 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
   }
 
   // encode_norm (codec.rs:994-1020), pack_indices (bitpack.rs:4-44): the record is the fp16 norm and
-  // 160 index bits, ten bytes of them from each thread of the pair
+  // 160 index bits, 5 HB of them (a whole number of bytes) from each thread of the vector
   {
     const float nf = __double2float_rn(norm);
     const uint32_t h = pkv_f32_to_f16_bits(nf);
     const bool norm_ok = (h & 0x7fffu) < 0x7c00u && (h & 0x7fffu) != 0;
-    unsigned long long lo = 0;  // stream bits 0..63 of this half
-    uint32_t hi = 0;            // stream bits 64..79
+    unsigned long long lo = 0;  // stream bits 0..63 of this part
+    uint32_t hi = 0;            // stream bits 64..79 (HB = 16 only)
     if (!bad && norm_ok) {
 #pragma unroll
       for (int b = 0; b < K::HB; b++) {
@@ -291,21 +314,18 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
     } else {
       flagged = 0;
     }
-    uint16_t* r16 = reinterpret_cast<uint16_t*>(s_rec + row * K::REC);
-    if (part == 0) r16[0] = (!bad && norm_ok) ? (uint16_t)h : (uint16_t)0;
-    uint16_t* half = r16 + 1 + 5 * part;
-    half[0] = (uint16_t)lo;
-    half[1] = (uint16_t)(lo >> 16);
-    half[2] = (uint16_t)(lo >> 32);
-    half[3] = (uint16_t)(lo >> 48);
-    half[4] = (uint16_t)hi;
-    s_flag[2 * row + part] = (uint16_t)flagged;
+    uint8_t* r8 = s_rec + row * K::REC;
+    if (part == 0) *reinterpret_cast<uint16_t*>(r8) = (!bad && norm_ok) ? (uint16_t)h : (uint16_t)0;
+    uint8_t* mine = r8 + 2 + (5 * K::HB / 8) * part;
+#pragma unroll
+    for (int k = 0; k < 5 * K::HB / 8; k++) mine[k] = k < 8 ? (uint8_t)(lo >> (8 * k)) : (uint8_t)(hi >> (8 * (k - 8)));
+    if (flagged) atomicOr(&s_flag[row], flagged << (K::HB * part));
     if (valid && !bad && !norm_ok && part == 0)
       pkv_report(err, 1, (int64_t)batch * g.vpb + v0 + row, PKV_VEC_NORM_RANGE);
   }
   __syncthreads();
   if (part == 0 && valid) {
-    const uint32_t fl = (uint32_t)s_flag[2 * row] | ((uint32_t)s_flag[2 * row + 1] << 16);
+    const uint32_t fl = s_flag[row];
     if (fl) {
       const uint32_t which = (fl & (fl - 1)) ? PKV_FIB_ENTRY_ALL : (uint32_t)(__ffs(fl) - 1);
       const uint32_t gvec = (uint32_t)((int64_t)batch * g.vpb + v0 + row);
