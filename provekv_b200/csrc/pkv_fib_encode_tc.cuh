@@ -224,10 +224,7 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   __syncthreads();
   if (threadIdx.x == 0 && !skip_issue) {
     pkv_tc::fence_after_sync();
-#pragma unroll 1
-    for (int k = 0; k < D / 8; k++)
-      pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
-                       pkv_tc::smem_desc_sw128(bh + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, k > 0);
+    pkv_tc::mma_tf32_chain<D / 8>(s_tmem, a0, K::X_SLAB, bh, K::M_SLAB, idesc, false);
     pkv_tc::mma_commit(&s_bar);
   }
   // The outcome of a wait is made uniform over the CTA: when it ran out for any thread, every
@@ -249,14 +246,8 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
   __syncthreads();
   if (threadIdx.x == 0) {
     pkv_tc::fence_after_sync();
-#pragma unroll 1
-    for (int k = 0; k < D / 8; k++)
-      pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
-                       pkv_tc::smem_desc_sw128(bh + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, 1u);
-#pragma unroll 1
-    for (int k = 0; k < D / 8; k++)
-      pkv_tc::mma_tf32(s_tmem, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
-                       pkv_tc::smem_desc_sw128(bl + (k >> 2) * K::M_SLAB + (k & 3) * 32), idesc, 1u);
+    pkv_tc::mma_tf32_chain<D / 8>(s_tmem, a0, K::X_SLAB, bh, K::M_SLAB, idesc, true);
+    pkv_tc::mma_tf32_chain<D / 8>(s_tmem, a0, K::X_SLAB, bl, K::M_SLAB, idesc, true);
     pkv_tc::mma_commit(&s_bar);
   }
   if (!__syncthreads_and(pkv_tc::mbar_wait(&s_bar, 1, wait_limit))) {

@@ -76,6 +76,23 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint6
       : "memory");
 }
 
+// The KSTEPS K steps of one product A B^T, operands in the tile layout above with slabs a_slab / b_slab
+// bytes apart.  The descriptors of the steps differ from the first one by constants (the start-address
+// field counts 16-byte units), so the unrolled chain costs two 64-bit additions per step; rebuilding the
+// descriptor in a rolled loop made the lone issuing thread spend about 140 cycles per step on dependent
+// scalar code, more than the tensor cores need for the step itself.
+template <int KSTEPS>
+__device__ __forceinline__ void mma_tf32_chain(uint32_t tmem_d, uint32_t a_addr, uint32_t a_slab, uint32_t b_addr,
+                                               uint32_t b_slab, uint32_t idesc, bool accumulate_first) {
+  const uint64_t da0 = smem_desc_sw128(a_addr), db0 = smem_desc_sw128(b_addr);
+#pragma unroll
+  for (int k = 0; k < KSTEPS; k++) {
+    const uint64_t da = da0 + (uint64_t)(((uint32_t)(k >> 2) * a_slab + (uint32_t)(k & 3) * 32u) >> 4);
+    const uint64_t db = db0 + (uint64_t)(((uint32_t)(k >> 2) * b_slab + (uint32_t)(k & 3) * 32u) >> 4);
+    mma_tf32(tmem_d, da, db, idesc, (k > 0 || accumulate_first) ? 1u : 0u);
+  }
+}
+
 // The barrier gets one arrival when every multiply issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

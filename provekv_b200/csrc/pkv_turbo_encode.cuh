@@ -631,10 +631,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       pkv_tc::fence_after_sync();
       const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, m > 32 ? 64 : 32);
       const uint32_t a0 = pkv_tc::smem_u32(s_xt), b0 = pkv_tc::smem_u32(s_gt);
-#pragma unroll 1
-      for (int k = 0; k < D / 8; k++)
-        pkv_tc::mma_tf32(tmem_d, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
-                         pkv_tc::smem_desc_sw128(b0 + (k >> 2) * g_slab + (k & 3) * 32), idesc, k > 0);
+      pkv_tc::mma_tf32_chain<D / 8>(tmem_d, a0, K::X_SLAB, b0, (uint32_t)g_slab, idesc, false);
       pkv_tc::mma_commit(&s_bar);
     }
     const bool done =
@@ -793,10 +790,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
       pkv_tc::fence_after_sync();
       const uint32_t idesc = pkv_tc::idesc_tf32(K::ROWS, m > 32 ? 64 : 32);
       const uint32_t a0 = pkv_tc::smem_u32(s_xt), b0 = pkv_tc::smem_u32(s_gt);
-#pragma unroll 1
-      for (int k = 0; k < D / 8; k++)  // 8 columns = 32 bytes further along the rows; four steps per slab
-        pkv_tc::mma_tf32(tmem_d, pkv_tc::smem_desc_sw128(a0 + (k >> 2) * K::X_SLAB + (k & 3) * 32),
-                         pkv_tc::smem_desc_sw128(b0 + (k >> 2) * g_slab + (k & 3) * 32), idesc, k > 0);
+      // 8 columns = 32 bytes further along the rows; four steps per slab
+      pkv_tc::mma_tf32_chain<D / 8>(tmem_d, a0, K::X_SLAB, b0, (uint32_t)g_slab, idesc, false);
       pkv_tc::mma_commit(&s_bar);
     }
     const bool done =
