@@ -160,24 +160,6 @@ __device__ __noinline__ float fused_dot(const uint8_t* gt, int g_slab, int p, co
   }
   return (d0 + d1) + (d2 + d3);
 }
-// The same dot in binary64 (second tier of the rotated-domain sketch): the products of binary32
-// values are exact, the sum is good to 1e-14, so what is left between this value and the reference's
-// sequential binary32 dot is that dot's own rounding and the model's error.
-template <int D>
-__device__ __noinline__ double fused_dot64(const uint8_t* gt, int g_slab, int p, const uint8_t* xt, int x_slab,
-                                           int row) {
-  double d0 = 0.0, d1 = 0.0, d2 = 0.0, d3 = 0.0;
-#pragma unroll 4
-  for (int c = 0; c < D / 4; c++) {
-    const float4 g = *reinterpret_cast<const float4*>(gt + sw_piece(g_slab, p, c));
-    const float4 x = *reinterpret_cast<const float4*>(xt + sw_piece(x_slab, row, c));
-    d0 = fma((double)g.x, (double)x.x, d0);
-    d1 = fma((double)g.y, (double)x.y, d1);
-    d2 = fma((double)g.z, (double)x.z, d2);
-    d3 = fma((double)g.w, (double)x.w, d3);
-  }
-  return (d0 + d1) + (d2 + d3);
-}
 __device__ __noinline__ float sequential_dot(const uint8_t* gt, int g_slab, int p, const uint8_t* xt,
                                              int x_slab, int row, int dim) {
   float dot = 0.0f;
@@ -355,10 +337,13 @@ struct TurboEncSmem {
 // of G'' and of res.  With |p|, |x| <= |y| (1 + 1e-6) that is below 21 u |y| + 3 u |q| for d <= 128;
 // the kernel adds PKV_QJL_MODEL_BOUND times an upper bound of |y| to both tiers' bounds.
 // d = 64: eta = 0, c_f = 6 u (the scale 1/8 is exact): 13 u |y| = 7.8e-7 |y|;  d = 128: 21 u |y| = 1.25e-6 |y|.
-// The binary64 tier's own bound is the rounding of the reference's sequential dot, (d + 1) u |g| |res|,
-// plus the 3 u |q| above.
+// The second tier's bound is the rounding of the reference's sequential dot, (d + 1) u |g| |res|, plus
+// the 3 u |q| above, plus the rounding of the tier's own dot: binary32, fused, four chains of d / 4 terms
+// and two levels of additions, at most gamma_(d/4+2) sum |g_j q_j| <= (d / 4 + 3) u |q| (unit rows).
+// A binary64 dot here (no rounding of its own) settled 0.02 % more vectors but cost two conversions
+// per term on the quarter-rate conversion pipe: a fifth of the kernel's time.
 #define PKV_QJL_MODEL_BOUND(D) ((D) == 64 ? 9.0e-7f : 1.45e-6f)
-#define PKV_QJL_SEQ_BOUND(D) ((float)((D) + 4) * 5.9604645e-8f * 1.05f)
+#define PKV_QJL_SEQ_BOUND(D) ((float)((D) + 4 + (D) / 4 + 3) * 5.9604645e-8f * 1.05f)
 template <int D, int PB, bool DIRECT, bool ROT>
 __global__ void __launch_bounds__(TurboEnc<D>::THREADS, D == 64 ? (DIRECT ? 4 : 3) : 2)
 turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
@@ -654,7 +639,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           bits |= (dots[p] >= 0.0f ? 1u : 0u) << p;
         }
         if (!settle || force) flagged = 0;
-        // Binary64 tier for the flagged (vector, row) pairs of the whole warp, spread over the lanes
+        // Second tier (binary32 fused dot) for the flagged (vector, row) pairs of the whole warp, spread over the lanes
         // through a prefix-summed list; pairs beyond the list's capacity are taken by their owner.
         // What this tier leaves open is noted in `open`.
         uint32_t open = 0;
@@ -676,9 +661,9 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
           const uint32_t n_list = min(total, CAP);
           for (uint32_t e = lane; e < n_list; e += 32) {
             const uint32_t it = s_items[e];
-            const double dot = fused_dot64<D>(s_gt, g_slab, c + (int)(it & 31u), s_xt, K::X_SLAB,
-                                              warp * K::TV + (int)(it >> 5));
-            const uint32_t res = !(fabs(dot) > (double)s_bound[it >> 5]) ? 0x4000u : (dot >= 0.0 ? 0x8000u : 0u);
+            const float dot = fused_dot(s_gt, g_slab, c + (int)(it & 31u), s_xt, K::X_SLAB,
+                                        warp * K::TV + (int)(it >> 5), D);
+            const uint32_t res = !(fabsf(dot) > s_bound[it >> 5]) ? 0x4000u : (dot >= 0.0f ? 0x8000u : 0u);
             s_items[e] = (uint16_t)(it | res);
           }
           __syncwarp();
@@ -689,8 +674,8 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
             if (pos < CAP) {
               res = s_items[pos];
             } else {
-              const double dot = fused_dot64<D>(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row);
-              res = !(fabs(dot) > (double)tau2) ? 0x4000u : (dot >= 0.0 ? 0x8000u : 0u);
+              const float dot = fused_dot(s_gt, g_slab, c + p, s_xt, K::X_SLAB, row, D);
+              res = !(fabsf(dot) > tau2) ? 0x4000u : (dot >= 0.0f ? 0x8000u : 0u);
             }
             if (res & 0x4000u) open |= 1u << p;
             else bits = (res & 0x8000u) ? (bits | (1u << p)) : (bits & ~(1u << p));
