@@ -115,17 +115,20 @@ def _encode_layer_blobs(profile, tokens, shape: KvTensorShape, device):
     if d != profile.dim:
         raise ValueError("profile and shape disagree on head_dim")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    x_dev = torch.from_numpy(x).to(dev)
     vpb, rec = T * H, profile.record_bytes
     stride = payload_batch_stride(vpb, rec)
-    payload = torch.zeros((Lc, 2, stride), dtype=torch.uint8, device=dev)
-    err = torch.full((1,), -1, dtype=torch.int64, device=dev)
     lay = L.Layout.make(n_tokens=T, n_heads=H, token_stride=Lc * H * 2 * d, head_stride=2 * d,
                         n_batches=(Lc, 2, 1), batch_stride=(H * 2 * d, d, 0))
-    stream = torch.cuda.current_stream(dev).cuda_stream
-    profile.encode_dev(x_dev.data_ptr(), lay, payload.data_ptr(), stride, err.data_ptr(), stream)
-    read_error_word(err.data_ptr(), stream)
-    host = payload.cpu().numpy()
+    # the library launches on the current device and refuses a profile that lives on another one: the
+    # data, the stream and the launch all belong to `dev`
+    with torch.cuda.device(dev):
+        x_dev = torch.from_numpy(x).to(dev)
+        payload = torch.zeros((Lc, 2, stride), dtype=torch.uint8, device=dev)
+        err = torch.full((1,), -1, dtype=torch.int64, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        profile.encode_dev(x_dev.data_ptr(), lay, payload.data_ptr(), stride, err.data_ptr(), stream)
+        read_error_word(err.data_ptr(), stream)
+        host = payload.cpu().numpy()
     header = profile.header(vpb)
     return [[header + host[li, side, :vpb * rec].tobytes() for side in range(2)] for li in range(Lc)]
 

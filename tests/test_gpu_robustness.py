@@ -205,3 +205,30 @@ def test_rotated_domain_sketch_equals_the_residual_sketch(oracle_mod, dim, bits,
     st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=bits, mode=1, radii_codec=0,
                                                libm_mode=oracle_mod.LIBM_PORTABLE)
     assert st == 0 and got[L.TQB1_HEADER_BYTES:] == payload.tobytes()
+
+
+def test_pool_built_on_the_device_it_names():
+    """build_shared_pool puts data, stream and launch on the device it is given: a profile that lives
+    on that device encodes there whatever device is current, and a profile from another device is refused
+    with the library's status instead of faulting."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from provekv_b200 import manifest as M
+    lib = L.lib()
+    d, H, Lc, T = 64, 2, 2, 19
+    shape = M.KvTensorShape("gqa", Lc, 8, H, d, 8 * d)
+    corpus = synthetic_kv(T * Lc * H * 2, d, seed=4).reshape(T, Lc * H * 2 * d)
+    L.check(lib.pkv_set_device(1))
+    try:
+        with torch.cuda.device(1):
+            prof1 = pk.FibProfile(d, tables.haar_rotation(d, 2), tables.fib_codebook(d, seed=2))
+    finally:
+        L.check(lib.pkv_set_device(0))
+    prof0 = pk.FibProfile(d, tables.haar_rotation(d, 2), tables.fib_codebook(d, seed=2))
+    on1 = M.build_shared_pool(prof1, corpus, shape, 7, "cb", "rot", device="cuda:1", built_at_unix=1)
+    on0 = M.build_shared_pool(prof0, corpus, shape, 7, "cb", "rot", device="cuda:0", built_at_unix=1)
+    assert on1["pool_id"] == on0["pool_id"] and torch.cuda.current_device() == 0
+    with pytest.raises(L.PkvError) as ei:
+        M.build_shared_pool(prof1, corpus, shape, 7, "cb", "rot", device="cuda:0")
+    assert ei.value.status == L.ERR_INVALID_ARGUMENT
