@@ -221,14 +221,7 @@ def dist_setup(torch):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # NCCL's stream gets the high priority: the pool all-gather is a small kernel that has to find SM slots
-        # while the shell encode's blocks occupy the device; at equal priority it ran after them
-        opts = None
-        try:
-            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
-        except Exception:
-            pass
-        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+        dist.init_process_group("nccl", device_id=dev)
     return rank, world, local, dev
 
 
