@@ -5,7 +5,7 @@ The CUDA library is the only implementation: importing the package is cheap and
 works without a GPU, but every codec call needs ``libprovekv_b200.so`` (built
 in-tree by ``provekv_b200._lib.build()`` / ``make -C provekv_b200/csrc``) and a CUDA device.
 """
-from . import _lib, manifest, patch, records, rust_streams, tables
+from . import _lib, kv_pages, manifest, patch, records, rust_streams, tables
 from ._lib import Layout, PkvError
 from .codec import (CODEC_FIB_K4_N32, CODEC_FIB_K4_N32_BATCHED, CODEC_TURBO_8BIT,
                     CODEC_TURBO_8BIT_BATCHED, CompressionFailed, DecompressionFailed, FibConfig,

@@ -24,7 +24,7 @@ from .codec import (CODEC_EXACT_FALLBACK, CODEC_FIB_K4_N32, CODEC_FIB_K4_N32_BAT
                     CODEC_TURBO_8BIT_BATCHED, CODEC_TURBO_8BIT_BATCHED_LOSSY, FibConfig, InvalidManifest,
                     InvalidPolicy, InvalidReceipt, InvalidShape, TurboConfig, turbo_batched_codec_id)
 
-__all__ = ["serde_f64", "serde_text", "digest_of", "KvTensorShape", "CompressionPolicy", "PoolManifest",
+__all__ = ["serde_f64", "serde_f32", "F32", "serde_text", "digest_of", "KvTensorShape", "CompressionPolicy", "PoolManifest",
            "ShellManifest", "PoolBuildReceipt", "ShellMaterializeReceipt", "BlockInjectionTrace",
            "InjectionReceipt", "allowed_shell_codecs", "now_unix", "POOL_MANIFEST_SCHEMA",
            "SHELL_MANIFEST_SCHEMA", "POOL_BUILD_RECEIPT_SCHEMA", "SHELL_MATERIALIZE_RECEIPT_SCHEMA",
@@ -37,36 +37,61 @@ SHELL_MATERIALIZE_RECEIPT_SCHEMA = "shell_materialize_receipt_v1"  # receipt.rs:
 INJECTION_RECEIPT_SCHEMA = "injection_receipt_v1"                  # receipt.rs:8
 
 
-def serde_f64(x: float) -> str:
-    """A binary64 as serde_json writes it: the shortest digits that round-trip, laid out as the `ryu`
-    crate does -- plain decimal with at least one fractional digit while the decimal point falls within
-    (-5, 16] digits of the first one, otherwise `d.ddde<exp>` with no `+` and no leading zeros."""
-    if not math.isfinite(x):
-        return "null"
-    sign = "-" if math.copysign(1.0, x) < 0 else ""
-    if x == 0:
-        return sign + "0.0"
-    text = repr(abs(float(x)))
+def _ryu_layout(digits: str, k: int, max_kk: int, min_kk: int) -> str:
+    """The `ryu` crate's layout of the decimal `digits` x 10^k: plain decimal with at least one fractional
+    digit while the decimal point falls within (min_kk, max_kk] digits of the first one, otherwise
+    `d.ddde<exp>` with no `+` and no leading zeros."""
+    n = len(digits)
+    kk = n + k
+    if 0 <= k and kk <= max_kk:
+        return digits + "0" * k + ".0"
+    if 0 < kk <= max_kk:
+        return digits[:kk] + "." + digits[kk:]
+    if min_kk < kk <= 0:
+        return "0." + "0" * (-kk) + digits
+    if n == 1:
+        return f"{digits}e{kk - 1}"
+    return f"{digits[0]}.{digits[1:]}e{kk - 1}"
+
+
+def _shortest_digits(text: str):
+    """(digits, k) with value = digits x 10^k from a shortest round-trip repr such as '1.5e-07' or '12.34'."""
     mant, _, exp = text.partition("e")
     whole, _, frac = mant.partition(".")
     k = (int(exp) if exp else 0) - len(frac)
     digits = (whole + frac).lstrip("0")
     stripped = digits.rstrip("0")
-    k += len(digits) - len(stripped)
-    digits = stripped
-    n = len(digits)
-    kk = n + k
-    if 0 <= k and kk <= 16:
-        body = digits + "0" * k + ".0"
-    elif 0 < kk <= 16:
-        body = digits[:kk] + "." + digits[kk:]
-    elif -5 < kk <= 0:
-        body = "0." + "0" * (-kk) + digits
-    elif n == 1:
-        body = f"{digits}e{kk - 1}"
-    else:
-        body = f"{digits[0]}.{digits[1:]}e{kk - 1}"
-    return sign + body
+    return stripped, k + len(digits) - len(stripped)
+
+
+def serde_f64(x: float) -> str:
+    """A binary64 as serde_json writes it: the shortest digits that round-trip, in the `ryu` layout
+    (decimal point within (-5, 16] digits of the first digit, else exponent form); non-finite -> null."""
+    if not math.isfinite(x):
+        return "null"
+    sign = "-" if math.copysign(1.0, x) < 0 else ""
+    if x == 0:
+        return sign + "0.0"
+    digits, k = _shortest_digits(repr(abs(float(x))))
+    return sign + _ryu_layout(digits, k, 16, -5)
+
+
+def serde_f32(x) -> str:
+    """A binary32 as serde_json writes it: shortest digits that round-trip as binary32, `ryu` layout with the
+    decimal point within (-6, 13] digits of the first digit."""
+    import numpy as np
+    v = np.float32(x)
+    if not np.isfinite(v):
+        return "null"
+    sign = "-" if np.signbit(v) else ""
+    if v == 0:
+        return sign + "0.0"
+    digits, k = _shortest_digits(np.format_float_scientific(abs(v), unique=True, trim="-"))
+    return sign + _ryu_layout(digits, k, 13, -6)
+
+
+class F32(float):
+    """Marks a number that `serde_text` writes as binary32."""
 
 
 def serde_text(obj) -> str:
@@ -79,6 +104,8 @@ def serde_text(obj) -> str:
         return "false"
     if isinstance(obj, int):
         return str(obj)
+    if isinstance(obj, F32):
+        return serde_f32(obj)
     if isinstance(obj, float):
         return serde_f64(obj)
     if isinstance(obj, str):

@@ -7,6 +7,8 @@ proveKV/src/policy.rs:117-127,216-223,292-298); the rule cases follow the refere
 """
 import json
 
+import numpy as np
+
 import blake3
 import pytest
 
@@ -213,3 +215,23 @@ def test_shell_digest_and_injection_trace_order():
     assert [(t.layer, t.source, t.source_digest, t.target_position) for t in rec.block_traces] == \
         [(0, "pool", "p0", 0), (0, "shell", "s0", 800), (1, "pool", "p1", 0), (1, "shell", "s1", 800)]
     assert rec.blocks_injected == 4 and rec.injected_at_unix == 7
+
+
+def test_binary32_numbers_print_with_their_own_shortest_digits():
+    """serde_json prints an f32 field from its binary32 value (ryu's f32 layout: plain digits for decimal
+    exponents in (-6, 13], scientific outside), not from the value widened to f64."""
+    from provekv_b200.records import F32, serde_f32
+    cases = {1.0: "1.0", 0.1: "0.1", -0.0: "-0.0", 1.5e-7: "1.5e-7", 1e-5: "0.00001", 1e-6: "0.000001",
+             1e-7: "1e-7", 123456789.0: "123456790.0", 1e12: "1000000000000.0", 1e13: "1e13",
+             16777216.0: "16777216.0", 3.4028235e38: "3.4028235e38", 1.17549435e-38: "1.1754944e-38",
+             1e-45: "1e-45", 1.0 / 3.0: "0.33333334", 9999999.0: "9999999.0"}
+    for v, text in cases.items():
+        assert serde_f32(v) == text, (v, serde_f32(v), text)
+    assert R.serde_text({"a": [F32(0.1), float(np.float32(0.1))]}) == '{"a":[0.1,0.10000000149011612]}'
+    rng = np.random.default_rng(3)
+    bits = rng.integers(0, 0x7F800000, 4000, dtype=np.uint32) | (rng.integers(0, 2, 4000, dtype=np.uint32) << 31)
+    for f in bits.view(np.float32):
+        t = serde_f32(float(f))
+        assert np.float32(t) == f                                   # round trip
+        digits = t.replace("-", "").replace(".", "").split("e")[0].strip("0")
+        assert len(digits) <= 9
