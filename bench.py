@@ -71,6 +71,14 @@ WORKLOADS = {
                       desc="C2 turbo polar-only 4-bit angles, f32 radii, 8 agents x 28 tokens"),
     "c1": dict(kind="single", agents=1, layers=24, heads=32, tokens=1024, dim=64, cache_tokens=1024, n_shared=0,
                codec="fib", desc="C1 fib k4_n32 cold tier: 24x{K,V}x32 heads x 1024 tokens x 64"),
+    "c1_hadamard": dict(kind="single", agents=1, layers=24, heads=32, tokens=1024, dim=64, cache_tokens=1024,
+                        n_shared=0, codec="fib", hadamard=True,
+                        desc="C1 with the Walsh-Hadamard rotation of the reference's gpu build on encode (not "
+                             "wire-compatible with the stored-matrix pools): 24x{K,V}x32 heads x 1024 tokens x 64"),
+    "c5s_fib_hadamard": dict(kind="single", agents=1, layers=32, heads=8, tokens=2048, dim=128, cache_tokens=2048,
+                             n_shared=0, codec="fib", hadamard=True,
+                             desc="C5 scaled fib prefix with the Walsh-Hadamard rotation on encode: "
+                                  "32x{K,V}x8 heads x 2048 tokens x 128"),
     "c5s_fib": dict(kind="single", agents=1, layers=32, heads=8, tokens=2048, dim=128, cache_tokens=2048,
                     n_shared=0, codec="fib",
                     desc="C5 scaled, fib k4_n32 prefix: 32x{K,V}x8 heads x 2048 tokens x 128"),
@@ -240,9 +248,16 @@ def cpu_single_rate(w, seconds_budget, nthreads):
     dim = w["dim"]
     rot, cb, signs, qjl = cpu_tables(dim)
     if w["codec"] == "fib":
+        if w.get("hadamard"):
+            from provekv_b200 import tables
+            rot = tables.hadamard_rotation_matrix(dim, SEED)
+
         def run(x):
             t0 = time.perf_counter()
-            st, payload, _, _ = oracle.fib_encode(x, rot, cb, nthreads=nthreads)
+            if w.get("hadamard"):
+                st, payload, _, _ = oracle.fib_encode_hadamard(x, SEED, cb, nthreads=nthreads)
+            else:
+                st, payload, _, _ = oracle.fib_encode(x, rot, cb, nthreads=nthreads)
             assert st == 0
             st, _, _, _ = oracle.fib_decode(payload, dim, rot, cb, nthreads=nthreads)
             assert st == 0
@@ -370,6 +385,10 @@ def make_single_profile(w):
     import provekv_b200 as pk
     from provekv_b200 import _lib as L
     if w["codec"] == "fib":
+        if w.get("hadamard"):
+            from provekv_b200 import tables
+            return pk.FibProfile(w["dim"], None, tables.fib_codebook(w["dim"], seed=SEED),
+                                 numerics=L.FIB_NUMERICS_BATCH, hadamard_seed=SEED)
         return pk.FibProfile.from_seed(w["dim"], SEED)
     return pk.TurboProfile.from_seed(w["dim"], w["bits"], TURBO_PROJ, SEED, mode=w["mode"],
                                      radii_codec=L.RADII_BLOCK_LOG_U8 if w["lossy"] else L.RADII_F32)
@@ -377,6 +396,8 @@ def make_single_profile(w):
 
 def single_kernel_names(w):
     d = w["dim"]
+    if w["codec"] == "fib" and w.get("hadamard"):
+        return f"fib_encode_wht_kernel<{d}>", f"fib_decode_patch_kernel<{d}>"
     if w["codec"] == "fib":
         enc = "fib_encode_tc_kernel + fib_encode_fix_kernel<64>" if d == 64 else \
             f"fib_encode_tc128_kernel + fib_encode_fix_kernel<{d}>"

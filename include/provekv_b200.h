@@ -197,6 +197,22 @@ int pkv_error_word_read(const uint64_t* err_dev, void* stream, int32_t* code, in
  * encodes with the exact f64 kernel only. */
 int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, const float* codebook,
                            pkv_fib_profile** out);
+/* A profile whose batch encoder rotates with the f32 Walsh-Hadamard transform that the reference's
+ * `gpu` build applies in FibQuantizer::encode_batch (fib-quant/src/codec.rs:612-656 ->
+ * gpu_backend::hadamard_batch; arithmetic of gpu-backend/src/fallback.rs:12-62: butterflies for step =
+ * 1, 2, 4, .., then x sign_i from the 64-bit LCG seeded with rotation_seed (:76-88), then x 1/sqrt(dim))
+ * instead of the stored matrix.  The transform costs dim*log2(dim) additions per vector instead of
+ * 2*dim*dim multiply-adds, and every step is a binary32 operation, so the bytes are the reference's
+ * without a second tier.  NOT wire-compatible with pools encoded through the stored matrix: the
+ * reference's decoders (and pkv_fib_decode_*) invert `rotation` whatever the encoder applied.
+ * As in the reference the transform is taken for batches of at least 16 vectors
+ * (GpuContext::GPU_MIN_BATCH_SIZE, gpu-backend/src/lib.rs:61-63) and the stored matrix below that;
+ * cfg->numerics = PKV_FIB_NUMERICS_BATCH takes it for every batch size, PKV_FIB_NUMERICS_SINGLE is
+ * PKV_ERR_INVALID_ARGUMENT (encode() has no such path).
+ * rotation: the stored matrix the decoders use (and small batches encode with); NULL = the transform
+ * itself written out as a matrix, so that decode inverts what encode applied. */
+int pkv_fib_profile_create_hadamard(const pkv_fib_config* cfg, uint64_t rotation_seed, const double* rotation,
+                                    const float* codebook, pkv_fib_profile** out);
 int pkv_fib_profile_destroy(pkv_fib_profile* p);
 /* Bytes per vector in the FB2 payload: norm (2 or 4) + ceil(5*dim/4/8). */
 int32_t pkv_fib_record_bytes(const pkv_fib_profile* p);

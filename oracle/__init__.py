@@ -87,6 +87,37 @@ def fib_encode(x, rot, codebook, *, k=4, norm_format=0, argmin_order=0, numerics
     return st, out, code.value, idx.value
 
 
+def fib_encode_hadamard(x, rotation_seed, codebook, *, k=4, norm_format=0, argmin_order=0, nthreads=1):
+    """encode_batch of the reference's `gpu` build for a large batch (fib-quant/src/codec.rs:612-656): the
+    f32 Walsh-Hadamard rotation of gpu-backend/src/fallback.rs:12-88.  -> (status, payload [n, rec], code, index)."""
+    x = _f32(x)
+    n, d = x.shape
+    cb = _f32(codebook)
+    rec = fib_record_bytes(d, k, cb.shape[0], norm_format)
+    out = np.zeros((n, rec), np.uint8)
+    code, idx = C.c_int32(0), C.c_int64(-1)
+    st = lib().pkvo_fib_encode_batch_hadamard(_p(x, C.c_float), C.c_int64(n), d, k, cb.shape[0], norm_format,
+                                              argmin_order, C.c_uint64(rotation_seed), _p(cb, C.c_float),
+                                              _p(out, C.c_uint8), nthreads, C.byref(code), C.byref(idx))
+    return st, out, code.value, idx.value
+
+
+def hadamard_batch(data, seed):
+    """gpu_backend::hadamard_batch_cpu (fallback.rs:12-62) on a copy of data [n, dim] -> [n, dim] f32."""
+    out = _f32(data).copy()
+    n, d = out.shape
+    st = lib().pkvo_hadamard_batch(_p(out, C.c_float), C.c_int64(n), d, C.c_uint64(seed))
+    if st:
+        raise ValueError(f"pkvo_hadamard_batch: status {st}")
+    return out
+
+
+def hadamard_signs(padded_dim, seed):
+    out = np.zeros(padded_dim, np.float32)
+    lib().pkvo_hadamard_signs(padded_dim, C.c_uint64(seed), _p(out, C.c_float))
+    return out
+
+
 def fib_decode(payload, dim, rot, codebook, *, k=4, norm_format=0, nthreads=1):
     """-> (status, out [n, dim] f32, vec_code, vec_index)."""
     cb = _f32(codebook)

@@ -205,6 +205,49 @@ PKVO_API int pkvo_fib_record_bytes(int dim, int k, int n_codewords, int norm_for
   return (norm_format == PKV_NORM_FP16 ? 2 : 4) + (blocks * fib_index_bits(n_codewords) + 7) / 8;
 }
 
+/* gpu-backend/src/fallback.rs:76-88: one LCG step per coordinate, bit 32 of the state picks the sign. */
+PKVO_API void pkvo_hadamard_signs(int padded_dim, uint64_t seed, float* signs) {
+  uint64_t state = seed;
+  for (int i = 0; i < padded_dim; i++) {
+    state = state * 6364136223846793005ull + 1442695040888963407ull;
+    signs[i] = ((state >> 32) & 1) == 0 ? -1.0f : 1.0f;
+  }
+}
+
+static int next_pow2(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
+/* One vector of hadamard_batch_cpu (gpu-backend/src/fallback.rs:26-59): zero-padded to a power of two,
+ * butterflies for step = 1, 2, 4, .., then x sign, then x 1 / sqrt(padded) (f32), truncated back. */
+static void pkvo_hadamard_one(float* v, int dim, const float* signs) {
+  const int pd = next_pow2(dim);
+  float padded[1024];
+  for (int i = 0; i < pd; i++) padded[i] = i < dim ? v[i] : 0.0f;
+  for (int step = 1; step < pd; step *= 2)
+    for (int i = 0; i < pd; i += 2 * step)
+      for (int j = 0; j < step; j++) {
+        float a = padded[i + j], b = padded[i + j + step];
+        padded[i + j] = a + b;
+        padded[i + j + step] = a - b;
+      }
+  for (int i = 0; i < pd; i++) padded[i] *= signs[i];
+  const float scale = 1.0f / sqrtf((float)pd);
+  for (int i = 0; i < pd; i++) padded[i] *= scale;
+  for (int i = 0; i < dim; i++) v[i] = padded[i];
+}
+
+/* hadamard_batch_cpu over n vectors in place; dim <= 1024. */
+PKVO_API int pkvo_hadamard_batch(float* data, int64_t n, int dim, uint64_t seed) {
+  if (dim <= 0 || dim > 1024) return PKV_ERR_INVALID_ARGUMENT;
+  float signs[1024];
+  pkvo_hadamard_signs(next_pow2(dim), seed, signs);
+  for (int64_t v = 0; v < n; v++) pkvo_hadamard_one(data + v * dim, dim, signs);
+  return 0;
+}
+
 typedef struct {
   const float* x;
   int64_t n;
@@ -212,6 +255,7 @@ typedef struct {
   const double* rot;
   const float* codebook;
   uint8_t* payload;
+  const float* wht_signs; /* non-null: the Hadamard rotation of the reference's `gpu` build, +-1 per padded coordinate */
   /* results */
   int pass0_code;
   int64_t pass0_index;
@@ -237,6 +281,11 @@ static int fib_encode_one(const fib_enc_job* J, int64_t v, int batch_numerics, u
   if (norm == 0.0) return PKV_VEC_ZERO_NORM; /* :603 */
   double nrm[512];
   float rotated[512];
+  if (J->wht_signs) {
+    /* codec.rs:607-609 then gpu_backend::hadamard_batch (:619) on the f32 values */
+    for (int i = 0; i < d; i++) rotated[i] = (float)((double)x[i] / norm);
+    pkvo_hadamard_one(rotated, d, J->wht_signs);
+  } else {
   for (int i = 0; i < d; i++) {
     double q = (double)x[i] / norm;
     /* batch path rounds to f32 (:607-609) and widens again (:662); single keeps f64 (:481) */
@@ -248,6 +297,7 @@ static int fib_encode_one(const fib_enc_job* J, int64_t v, int batch_numerics, u
     double sum = 0.0;
     for (int j = 0; j < d; j++) sum += row[j] * nrm[j];
     rotated[r] = (float)sum; /* :483, :664 */
+  }
   }
   uint32_t idx[128];
   for (int b = 0; b < blocks; b++)
@@ -350,12 +400,44 @@ PKVO_API int pkvo_fib_encode_batch(const float* x, int64_t n, int dim, int k, in
   if (vec_index) *vec_index = -1;
   if (n == 0) return PKV_ERR_EMPTY_BATCH; /* FibCodeV1::encode_batch, :226 */
   fib_enc_job J = {x, n, dim, k, n_codewords, norm_format, argmin_order, numerics, rot, codebook,
-                   payload, 0, -1, 0, -1};
+                   payload, NULL, 0, -1, 0, -1};
   fib_enc_ctx C;
   C.J = &J;
   C.rec_bytes = pkvo_fib_record_bytes(dim, k, n_codewords, norm_format);
   C.batch_numerics = numerics == PKV_FIB_NUMERICS_BATCH ||
                      (numerics == PKV_FIB_NUMERICS_AUTO && n >= 4); /* :587 */
+  pthread_mutex_init(&C.mu, NULL);
+  parallel_for(n, nthreads, fib_enc_range, &C);
+  pthread_mutex_destroy(&C.mu);
+  int code = J.pass0_code ? J.pass0_code : J.pass1_code;
+  int64_t index = J.pass0_code ? J.pass0_index : J.pass1_index;
+  if (code) {
+    if (vec_code) *vec_code = code;
+    if (vec_index) *vec_index = index;
+  }
+  return code;
+}
+
+/* The same batch when the reference is built with its `gpu` feature and the batch is large enough
+ * (n >= 16, dim >= 64: fib-quant/src/codec.rs:612-656): the normalised f32 vectors go through
+ * gpu_backend::hadamard_batch instead of the stored rotation; the rest is finish_batch_encode as above. */
+PKVO_API int pkvo_fib_encode_batch_hadamard(const float* x, int64_t n, int dim, int k, int n_codewords,
+                                            int norm_format, int argmin_order, uint64_t rotation_seed,
+                                            const float* codebook, uint8_t* payload, int nthreads,
+                                            int32_t* vec_code, int64_t* vec_index) {
+  if (dim <= 0 || dim > 512 || k <= 0 || dim % k || n_codewords < 1 || dim / k > 128)
+    return PKV_ERR_INVALID_ARGUMENT;
+  if (vec_code) *vec_code = 0;
+  if (vec_index) *vec_index = -1;
+  if (n == 0) return PKV_ERR_EMPTY_BATCH;
+  float signs[1024];
+  pkvo_hadamard_signs(next_pow2(dim), rotation_seed, signs);
+  fib_enc_job J = {x, n, dim, k, n_codewords, norm_format, argmin_order, PKV_FIB_NUMERICS_BATCH, NULL, codebook,
+                   payload, signs, 0, -1, 0, -1};
+  fib_enc_ctx C;
+  C.J = &J;
+  C.rec_bytes = pkvo_fib_record_bytes(dim, k, n_codewords, norm_format);
+  C.batch_numerics = 1;
   pthread_mutex_init(&C.mu, NULL);
   parallel_for(n, nthreads, fib_enc_range, &C);
   pthread_mutex_destroy(&C.mu);
@@ -1347,6 +1429,59 @@ PKVO_API void pkvo_fib_quotient_check(uint64_t seed, int64_t n, int mode, int64_
     if (unsure) counts[1]++;
     else if (pkv_f32_bits(q) != pkv_f32_bits(ref)) counts[0]++;
   }
+}
+
+/* The score search on biased integer keys (pkv_fast_paths.h (3b)) for exactly known rotated blocks
+ * (eta = 0, the Hadamard encoder): y holds n blocks of 4 values with |block| <= 1.  counts[0] = blocks
+ * declared certain (by the key gap or by pkv_fib_certify_abs) whose index differs from the reference's
+ * scan, counts[1] = undecided, counts[2] = certain, counts[3] = certain by the key gap alone,
+ * counts[4] = scores that left the binade (must be 0). */
+PKVO_API int pkvo_fib_biased_search_check(const float* y, int64_t n, const float* codebook, int n_codewords,
+                                          int order, int64_t* counts) {
+  float off, e_f, hn_off[32], nc[32][4];
+  uint32_t quick_gap;
+  for (int k = 0; k < 5; k++) counts[k] = 0;
+  if (n_codewords > 32 || !pkv_fib_search_bias(codebook, n_codewords, &off, &e_f, &quick_gap)) return 1;
+  const uint32_t binade = pkv_f32_bits(off) & 0xff800000u;
+  for (int c = 0; c < n_codewords; c++) {
+    double s = 0.0;
+    for (int j = 0; j < 4; j++) {
+      s += (double)codebook[4 * c + j] * codebook[4 * c + j];
+      nc[c][j] = -codebook[4 * c + j];
+    }
+    hn_off[c] = (float)(0.5 * s) + off; /* what the kernel forms: RN(RN(|c|^2 / 2) + off) */
+  }
+  for (int64_t v = 0; v < n; v++) {
+    const float* s = y + 4 * v;
+    uint32_t best = 0xffffffffu, second = 0xffffffffu;
+    for (int c = 0; c < n_codewords; c++) {
+      const uint32_t key = pkv_fib_biased_key(s[0], s[1], s[2], s[3], nc[c][0], nc[c][1], nc[c][2], nc[c][3],
+                                              hn_off[c], (uint32_t)c);
+      float f = __builtin_fmaf(s[0], nc[c][0], hn_off[c]);
+      f = __builtin_fmaf(s[1], nc[c][1], f);
+      f = __builtin_fmaf(s[2], nc[c][2], f);
+      f = __builtin_fmaf(s[3], nc[c][3], f);
+      if ((pkv_f32_bits(f) & 0xff800000u) != binade) counts[4]++;
+      if (key < best) {
+        second = best;
+        best = key;
+      } else if (key < second) {
+        second = key;
+      }
+    }
+    int certain = (second >> 5) - (best >> 5) > quick_gap;
+    if (certain) counts[3]++;
+    else
+      certain = pkv_fib_certify_abs(pkv_fib_key_score(best, off), pkv_fib_key_score(second, off), s[0], s[1], s[2],
+                                    s[3], 0.0f, e_f);
+    if (!certain) {
+      counts[1]++;
+      continue;
+    }
+    counts[2]++;
+    if ((int)(best & 31u) != pkvo_nearest_codeword(s, codebook, n_codewords, 4, order)) counts[0]++;
+  }
+  return 0;
 }
 
 /* The same check for the tensor-core rotation of the d = 64 encoder (PKV_FIB_ROT_ERR_TC). */

@@ -128,6 +128,7 @@ _SIGS = {
     "pkv_error_word_reset": (C.c_int, [_V, _V]),
     "pkv_error_word_read": (C.c_int, [_V, _V, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "pkv_fib_profile_create": (C.c_int, [C.POINTER(FibConfigC), _V, _V, C.POINTER(_V)]),
+    "pkv_fib_profile_create_hadamard": (C.c_int, [C.POINTER(FibConfigC), C.c_uint64, _V, _V, C.POINTER(_V)]),
     "pkv_fib_profile_destroy": (C.c_int, [_V]),
     "pkv_fib_record_bytes": (C.c_int32, [_V]),
     "pkv_fib_encode_dev": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),

@@ -279,6 +279,63 @@ PKV_HD int pkv_fib_certify_eta(float best, float second, float s0, float s1, flo
   return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
 }
 
+/* The same test for scores kept with an absolute error of at most e_f each (the biased scores of
+ * pkv_fib_search.cuh): the relative term for the index bits and the fused roundings gives way to
+ * 2 e_f per distance. */
+PKV_HD int pkv_fib_certify_abs(float f1, float f2, float s0, float s1, float s2, float s3, float eta, float e_f) {
+  const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
+                            PKV_FADD(PKV_FMUL(s2, s2), PKV_FMUL(s3, s3)));
+  const float d1 = PKV_FADD(PKV_FMUL(2.0f, f1), ss), d2 = PKV_FADD(PKV_FMUL(2.0f, f2), ss);
+  const float d2p = d2 > 0.0f ? d2 : 0.0f, d1p = d1 > 0.0f ? d1 : 0.0f;
+  const float roots = PKV_FADD(PKV_FSQRT_UP(d1p), PKV_FSQRT_UP(d2p));
+  const float bound = PKV_FADD(PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
+                               PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(4.2f, e_f)));
+  return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
+}
+
+/* (3b) The same search on biased scores (csrc/pkv_fib_search.cuh gives the layout of the keys).
+ * off = 1.5 * 2^k with k the smallest exponent whose binade [2^k, 2^(k+1)) holds off + F for every
+ * score F = |c|^2 / 2 - s . c of a block with |s| <= 1.001; e_f = 2.5 ulps of that binade bounds the
+ * error of a kept score (the start value and four fused operations, half an ulp each); quick_gap is a
+ * gap of the two best scores, in ulps of the binade, above which pkv_fib_certify_abs with eta = 0 holds
+ * for every block: it asks for 2 (F2 - F1) > 1.05 (2.5e-7 (d1 + d2) + 4.2 e_f), squared distances stay
+ * below (1.001 + max |c|)^2, and 0.63 = 0.525 * 1.2 leaves room for the roundings of that test itself.
+ * Returns 0 when no binade below 2^99 holds the scores (or the codebook is not finite). */
+static inline int pkv_fib_search_bias(const float* codebook, int n_codewords, float* off, float* e_f,
+                                      uint32_t* quick_gap) {
+  double hmax = 0.0, cmax = 0.0;
+  for (int c = 0; c < n_codewords; c++) {
+    double s = 0.0;
+    for (int j = 0; j < 4; j++) s += (double)codebook[4 * c + j] * (double)codebook[4 * c + j];
+    if (0.5 * s > hmax) hmax = 0.5 * s;
+    if (__builtin_sqrt(s) > cmax) cmax = __builtin_sqrt(s);
+  }
+  const double fmax = 1.001 * (hmax + 1.001 * cmax) + 1.0e-30;
+  if (!(fmax < __builtin_ldexp(1.0, 98))) return 0;
+  int k = -100;
+  while (__builtin_ldexp(1.0, k - 1) < fmax) k++;
+  const double ulp_b = __builtin_ldexp(1.0, k - 23), dmax = (1.001 + cmax) * (1.001 + cmax);
+  *off = (float)__builtin_ldexp(1.5, k);
+  *e_f = (float)(2.5 * ulp_b);
+  *quick_gap = (uint32_t)__builtin_ceil(0.63 * (5.05e-7 * dmax + 10.5 * ulp_b) / ulp_b) + 1u;
+  return 1;
+}
+
+/* Key of codeword c (negated coordinates nc0..nc3, start value hn_off = RN(|c|^2 / 2 + off)). */
+PKV_HD uint32_t pkv_fib_biased_key(float s0, float s1, float s2, float s3, float nc0, float nc1, float nc2,
+                                   float nc3, float hn_off, uint32_t c) {
+  float f = PKV_FMAF(s0, nc0, hn_off);
+  f = PKV_FMAF(s1, nc1, f);
+  f = PKV_FMAF(s2, nc2, f);
+  f = PKV_FMAF(s3, nc3, f);
+  return pkv_f32_bits(f) * 32u + c;
+}
+
+/* The score a key was made from (exact: the biased score and off lie in the same binade). */
+PKV_HD float pkv_fib_key_score(uint32_t key, float off) {
+  return PKV_FSUB(pkv_f32_from_bits((pkv_f32_bits(off) & 0xf8000000u) | (key >> 5)), off);
+}
+
 /* The same with the bound of the binary32 fused rotation for D = 64. */
 PKV_HD int pkv_fib_certify(float best, float second, float s0, float s1, float s2, float s3) {
   return pkv_fib_certify_eta(best, second, s0, s1, s2, s3, PKV_FIB_ROT_ERR);

@@ -11,8 +11,11 @@
 // in f64.
 #include <mutex>
 
+#include <string.h>
+
 #include "pkv_common.cuh"
 #include "pkv_fast_paths.h"
+#include "pkv_turbo_common.cuh"  // the packed butterfly network (pkv_fib_encode_wht.cuh)
 
 namespace {
 
@@ -449,9 +452,11 @@ size_t fib_encode_smem(int rec) {
          (size_t)K::TV * rec + 32;
 }
 
+#include "pkv_fib_search.cuh"
 #include "pkv_fib_encode_fast.cuh"
 #include "pkv_fib_encode_tc.cuh"
 #include "pkv_fib_encode_tc128.cuh"
+#include "pkv_fib_encode_wht.cuh"
 
 template <typename F>
 int set_smem(F kernel, size_t bytes) {
@@ -489,6 +494,32 @@ int pkv_launch_fib_encode(const pkv_fib_profile* p, const float* x, const PkvGeo
   const int64_t grid = (int64_t)g.n_batches * g.tiles_per_batch;
   if (grid == 0) return PKV_OK;
   if (grid > 0x7fffffff) return PKV_ERR_UNSUPPORTED;
+  // A Hadamard profile: the reference's `gpu` build takes the transform for batches of at least 16
+  // vectors (GpuContext::GPU_MIN_BATCH_SIZE, gpu-backend/src/lib.rs:61-63; dim >= 64 always holds here)
+  // and the stored matrix below that; PKV_FIB_NUMERICS_BATCH forces the transform for every size.
+  if (p->hadamard && (p->cfg.numerics == PKV_FIB_NUMERICS_BATCH || g.vpb >= 16)) {
+    FibWhtParams prm;
+    memcpy(prm.sgn_scale, p->wht_sgn_scale, sizeof(prm.sgn_scale));
+    PkvGeom gf = g;
+    int st;
+#define PKV_FIB_WHT(DIM)                                                                              \
+  {                                                                                                   \
+    gf.tiles_per_batch = (g.vpb + FibWht<DIM>::TV - 1) / FibWht<DIM>::TV;                             \
+    const int64_t tiles = (int64_t)g.n_batches * gf.tiles_per_batch;                                  \
+    if (tiles > 0x7fffffff) return PKV_ERR_UNSUPPORTED;                                               \
+    const size_t sm = FibWht<DIM>::smem(g.rec_bytes);                                                 \
+    if ((st = set_smem(fib_encode_wht_kernel<DIM>, sm)) != PKV_OK) return st;                         \
+    fib_encode_wht_kernel<DIM><<<(unsigned)tiles, FibWht<DIM>::THREADS, sm, s>>>(                     \
+        gf, x, prm, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len, \
+        p->cfg.argmin_order, FibSearchBias{p->search_off, p->search_ef, 32u, p->search_quick_gap}, payload, err); \
+  }
+    if (p->cfg.dim == 64) PKV_FIB_WHT(64)
+    else if (p->cfg.dim == 128) PKV_FIB_WHT(128)
+    else return PKV_ERR_UNSUPPORTED;
+#undef PKV_FIB_WHT
+    pkv_count_launch();
+    return pkv_cuda_status(cudaGetLastError());
+  }
   // The shortcuts are proven for the batch numerics; list entries hold 27-bit vector indices.
   if (batch_numerics && p->orthonormal && (int64_t)g.n_batches * g.vpb <= ((int64_t)1 << 27)) {
     if (p->cfg.dim == 64) return launch_fib_encode_fast<64>(p, x, g, payload, err, s);
@@ -666,6 +697,8 @@ extern "C" int pkv_fib_encode_dev_static(const pkv_fib_profile* p, const float* 
   // the shortcut encoder implements the batch numerics only (fib-quant/src/codec.rs:586-589)
   const bool batch_numerics = p->cfg.numerics == PKV_FIB_NUMERICS_BATCH ||
                               (p->cfg.numerics == PKV_FIB_NUMERICS_AUTO && g.vpb >= 4);
+  if (p->hadamard)  // that encoder keeps no list, so it allocates nothing anyway
+    return pkv_launch_fib_encode(p, x_dev, g, payload_dev, err_dev, batch_numerics, (cudaStream_t)stream);
   if (!batch_numerics || !p->orthonormal) return PKV_ERR_UNSUPPORTED;
   if ((int64_t)g.n_batches * g.vpb > PKV_FIB_STATIC_MAX_VECTORS) return PKV_ERR_STATIC_SCRATCH_TOO_SMALL;
   int dev = -1;

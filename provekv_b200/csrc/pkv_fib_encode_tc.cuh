@@ -16,6 +16,29 @@
 
 #include "pkv_tcgen05.cuh"
 
+// The reference's nearest codeword of one block whose rotated values s0..s3 are exact: lane c evaluates
+// the distance to codeword c in the reference's operation order (simd_nearest.rs:24-39,62-92) and the
+// warp takes the smallest, lowest index first, which is what the strict-less-than scan returns.
+__device__ __forceinline__ int fib_block_nearest_warp(float s0, float s1, float s2, float s3, const float4* s_cb,
+                                                      int n_codewords, int order, int lane) {
+  const float4 w = s_cb[lane];
+  const int paired = order == PKV_ARGMIN_PAIRWISE ? (n_codewords & ~1) : 0;
+  float dist;
+  if (lane < paired) {
+    const float d0 = __fsub_rn(w.x, s0), d1 = __fsub_rn(w.y, s1);
+    const float d2 = __fsub_rn(w.z, s2), d3 = __fsub_rn(w.w, s3);
+    dist = __fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fadd_rn(__fmul_rn(d2, d2), __fmul_rn(d3, d3)));
+  } else {
+    const float d0 = __fsub_rn(s0, w.x), d1 = __fsub_rn(s1, w.y);
+    const float d2 = __fsub_rn(s2, w.z), d3 = __fsub_rn(s3, w.w);
+    dist = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fmul_rn(d2, d2)), __fmul_rn(d3, d3));
+  }
+  // distances are sums of squares: non-negative, so their bit patterns order like the values
+  const uint32_t key = lane < n_codewords ? __float_as_uint(dist) : 0xffffffffu;
+  const uint32_t least = __reduce_min_sync(0xffffffffu, key);
+  return __ffs(__ballot_sync(0xffffffffu, key == least)) - 1;
+}
+
 // Exact tier shared by the tensor-core encoders.  For one block of one vector whose normalised form
 // (exact binary32, the reference's n) is row `trow` of the swizzled tile: the warp evaluates the four
 // rotated values in binary64 from the f64 matrix (lane l takes columns l, l + 32, .., then a
@@ -55,22 +78,7 @@ __device__ __forceinline__ int fib_exact_block(const uint8_t* s_xt, int trow, in
     sure = sure && __double2float_rn(__dadd_rn(part[rr], PKV_FIB_F64_SUM_ERR)) ==
                        __double2float_rn(__dsub_rn(part[rr], PKV_FIB_F64_SUM_ERR));
   }
-  const float4 w = s_cb[lane];
-  const int paired = order == PKV_ARGMIN_PAIRWISE ? (n_codewords & ~1) : 0;
-  float dist;
-  if (lane < paired) {
-    const float d0 = __fsub_rn(w.x, s[0]), d1 = __fsub_rn(w.y, s[1]);
-    const float d2 = __fsub_rn(w.z, s[2]), d3 = __fsub_rn(w.w, s[3]);
-    dist = __fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fadd_rn(__fmul_rn(d2, d2), __fmul_rn(d3, d3)));
-  } else {
-    const float d0 = __fsub_rn(s[0], w.x), d1 = __fsub_rn(s[1], w.y);
-    const float d2 = __fsub_rn(s[2], w.z), d3 = __fsub_rn(s[3], w.w);
-    dist = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fmul_rn(d2, d2)), __fmul_rn(d3, d3));
-  }
-  // distances are sums of squares: non-negative, so their bit patterns order like the values
-  const uint32_t key = lane < n_codewords ? __float_as_uint(dist) : 0xffffffffu;
-  const uint32_t least = __reduce_min_sync(0xffffffffu, key);
-  const int idx = __ffs(__ballot_sync(0xffffffffu, key == least)) - 1;
+  const int idx = fib_block_nearest_warp(s[0], s[1], s[2], s[3], s_cb, n_codewords, order, lane);
   return sure ? idx : -1;
 }
 

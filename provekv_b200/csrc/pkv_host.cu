@@ -340,6 +340,8 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
   p->half_norm_dev = nullptr;
   p->rot_hi_dev = nullptr;
   p->rot_lo_dev = nullptr;
+  p->hadamard = 0;
+  memset(p->wht_sgn_scale, 0, sizeof(p->wht_sgn_scale));
   const int d = cfg->dim;
   // The error bounds of the shortcut encoders (pkv_fast_paths.h) take |M_r|_2 = 1 and an orthogonal
   // M.  A table that is not (scaled, truncated, not a rotation at all) is still a valid input of the
@@ -378,6 +380,13 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
     for (int j = 0; j < 4; j++) s += (double)cb[4 * c + j] * (double)cb[4 * c + j];
     hn[c] = (float)(0.5 * s);
   }
+  // Bias of the encoders' score search (pkv_fast_paths.h (3b)); a codebook no binade can hold leaves the
+  // exact kernel only
+  p->search_off = 2.0e30f;
+  p->search_ef = 0.0f;
+  p->search_quick_gap = 0xffffffffu;
+  if (!pkv_fib_search_bias(cb, cfg->codebook_size, &p->search_off, &p->search_ef, &p->search_quick_gap))
+    p->orthonormal = 0;
   for (int r = 0; r < d; r++)
     for (int j = 0; j < d; j++) r32[j * d + r] = (float)rotation[r * d + j];
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot_dev, sizeof(double) * d * d);
@@ -411,6 +420,48 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
     return PKV_ERR_CUDA;
   }
   *out = p;
+  return PKV_OK;
+}
+
+// generate_signs_impl, gpu-backend/src/fallback.rs:76-88: one step of the 64-bit LCG per coordinate,
+// bit 32 of the state picks the sign; the scale is `1.0 / (dim as f32).sqrt()` (:52).
+static void wht_signed_scale(int dim, uint64_t seed, float* out) {
+  const float scale = 1.0f / sqrtf((float)dim);
+  uint64_t state = seed;
+  for (int i = 0; i < dim; i++) {
+    state = state * 6364136223846793005ull + 1442695040888963407ull;
+    out[i] = ((state >> 32) & 1) ? scale : -scale;
+  }
+}
+
+int pkv_fib_profile_create_hadamard(const pkv_fib_config* cfg, uint64_t rotation_seed, const double* rotation,
+                                    const float* codebook, pkv_fib_profile** out) {
+  if (!cfg || !codebook || !out) return PKV_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (cfg->numerics == PKV_FIB_NUMERICS_SINGLE) return PKV_ERR_INVALID_ARGUMENT;  // the transform exists in encode_batch only
+  if (cfg->dim != 64 && cfg->dim != 128) return cfg->dim > 0 ? PKV_ERR_UNSUPPORTED : PKV_ERR_INVALID_ARGUMENT;
+  const int d = cfg->dim;
+  float ss[128];
+  wht_signed_scale(d, rotation_seed, ss);
+  double* own = nullptr;
+  if (!rotation) {
+    // the transform written out as a matrix, M[r][j] = ss[r] * (-1)^popcount(r & j), so that the decoders
+    // invert what this profile's encoder applied
+    own = new (std::nothrow) double[(size_t)d * d];
+    if (!own) return PKV_ERR_CUDA;
+    for (int r = 0; r < d; r++)
+      for (int j = 0; j < d; j++) own[r * d + j] = (__builtin_popcount(r & j) & 1) ? -(double)ss[r] : (double)ss[r];
+  }
+  const int st = pkv_fib_profile_create(cfg, rotation ? rotation : own, codebook, out);
+  delete[] own;
+  if (st != PKV_OK) return st;
+  if (!((*out)->search_off < 1.0e30f)) {  // no bias fits this codebook, and this encoder has no exact kernel behind it
+    pkv_fib_profile_destroy(*out);
+    *out = nullptr;
+    return PKV_ERR_UNSUPPORTED;
+  }
+  (*out)->hadamard = 1;
+  memcpy((*out)->wht_sgn_scale, ss, sizeof(float) * d);
   return PKV_OK;
 }
 

@@ -43,10 +43,19 @@ class FibProfile(_ProfileBase):
     """fib-quant k=4 profile: dense rotation (dim x dim f64) + N x 4 f32 codebook."""
     _destroy = "pkv_fib_profile_destroy"
 
-    def __init__(self, dim: int, rotation: np.ndarray, codebook: np.ndarray, *,
+    def __init__(self, dim: int, rotation, codebook: np.ndarray, *,
                  norm_format: int = L.NORM_FP16, argmin_order: int = L.ARGMIN_PAIRWISE,
-                 numerics: int = L.FIB_NUMERICS_AUTO):
+                 numerics: int = L.FIB_NUMERICS_AUTO, hadamard_seed: int | None = None):
+        """hadamard_seed: encode batches with the f32 Walsh-Hadamard rotation of the reference's `gpu` build
+        (fib-quant/src/codec.rs:612-656, gpu-backend/src/fallback.rs:12-88) seeded with it; `rotation` is then
+        what the decoders invert and may be None (= the transform itself as a matrix).  Such payloads are not
+        wire-compatible with pools encoded through the stored matrix."""
         self.dim = dim
+        self.hadamard_seed = hadamard_seed
+        if rotation is None:
+            if hadamard_seed is None:
+                raise ValueError("a rotation matrix is required unless hadamard_seed is given")
+            rotation = tables.hadamard_rotation_matrix(dim, hadamard_seed)
         self.rotation = np.ascontiguousarray(rotation, dtype=np.float64).reshape(dim, dim)
         self.codebook = np.ascontiguousarray(codebook, dtype=np.float32)
         self.block_dim = self.codebook.shape[1]
@@ -54,8 +63,12 @@ class FibProfile(_ProfileBase):
         cfg = L.FibConfigC(dim, self.block_dim, self.codebook_size, norm_format, argmin_order, numerics)
         self.norm_format, self.argmin_order, self.numerics = norm_format, argmin_order, numerics
         h = C.c_void_p()
-        L.check(L.lib().pkv_fib_profile_create(C.byref(cfg), _ptr(self.rotation), _ptr(self.codebook),
-                                               C.byref(h)))
+        if hadamard_seed is None:
+            L.check(L.lib().pkv_fib_profile_create(C.byref(cfg), _ptr(self.rotation), _ptr(self.codebook),
+                                                   C.byref(h)))
+        else:
+            L.check(L.lib().pkv_fib_profile_create_hadamard(C.byref(cfg), C.c_uint64(hadamard_seed & (2 ** 64 - 1)),
+                                                            _ptr(self.rotation), _ptr(self.codebook), C.byref(h)))
         self.handle = h
         self.record_bytes = L.lib().pkv_fib_record_bytes(h)
 

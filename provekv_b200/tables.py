@@ -28,6 +28,9 @@ import numpy as np
 _MASK64 = (1 << 64) - 1
 
 
+_M64 = (1 << 64) - 1
+
+
 def _rng(seed: int) -> np.random.Generator:
     return np.random.Generator(np.random.PCG64(seed & _MASK64))
 
@@ -48,6 +51,29 @@ def haar_rotation(dim: int, seed: int) -> np.ndarray:
     q = q.copy()
     q[:, flip] *= -1.0
     return np.ascontiguousarray(q, dtype=np.float64)
+
+
+def lcg_hadamard_signs(dim: int, seed: int) -> np.ndarray:
+    """gpu-backend/src/fallback.rs:76-88: one step of state = state * 6364136223846793005 + 1442695040888963407
+    (mod 2^64) per coordinate; bit 32 of the state set -> +1, clear -> -1."""
+    state, out = seed & _M64, np.empty(dim, np.float32)
+    for i in range(dim):
+        state = (state * 6364136223846793005 + 1442695040888963407) & _M64
+        out[i] = 1.0 if (state >> 32) & 1 else -1.0
+    return out
+
+
+def hadamard_rotation_matrix(dim: int, seed: int) -> np.ndarray:
+    """The transform of gpu-backend/src/fallback.rs:12-62 for a power-of-two dim as a dim x dim f64 matrix:
+    M[r][j] = sign_r * (1 / sqrt(dim) in f32) * (-1)^popcount(r & j).  Orthogonal to f32 rounding of the
+    scale; a profile whose decoders hold it inverts what the Hadamard encoder applied."""
+    if dim & (dim - 1):
+        raise ValueError("dim must be a power of two")
+    scale = np.float32(1.0) / np.sqrt(np.float32(dim))
+    signs = lcg_hadamard_signs(dim, seed).astype(np.float64) * float(scale)
+    r = np.arange(dim)
+    parity = np.array([[bin(a & b).count("1") & 1 for b in r] for a in r])
+    return np.where(parity == 1, -1.0, 1.0) * signs[:, None]
 
 
 def rademacher_signs(dim: int, seed: int) -> np.ndarray:

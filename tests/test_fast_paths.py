@@ -101,3 +101,36 @@ def test_pair_form_normalised_element_is_never_certain_and_wrong(oracle_mod, mod
     wrong, unsure, tested = list(out)
     assert tested == 4_000_000 and wrong == 0
     assert min_unsure <= unsure <= max_unsure
+
+
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("n_codewords,scale", [(32, 1.0), (21, 1.0), (32, 3.7), (6, 0.04)])
+def test_biased_key_search_never_decides_wrong(oracle_mod, order, n_codewords, scale):
+    """The integer-key score search of the Hadamard encoder: typical blocks of unit vectors, blocks of norm
+    one (a vector concentrated in one block), and blocks placed on or a few units in the last place beside the
+    bisector of two codewords.  No certified block may differ from the reference's scan, and no score may
+    leave the binade the keys are ordered in."""
+    import numpy as np
+    from provekv_b200 import tables
+    cb = np.ascontiguousarray(tables.fib_codebook(64, 4, n_codewords, 42, 512, 2, 4) * np.float32(scale), np.float32)
+    rng = np.random.default_rng(7 + n_codewords)
+    n = 200_000
+    typical = rng.standard_normal((n, 4)).astype(np.float32) * np.float32(0.125)
+    full = rng.standard_normal((n // 4, 4))
+    full = (full / np.linalg.norm(full, axis=1, keepdims=True) * rng.choice([1.0, 0.999, 0.5], (n // 4, 1))).astype(np.float32)
+    a, b = rng.integers(0, n_codewords, n), rng.integers(0, n_codewords, n)
+    mid = 0.5 * (cb[a].astype(np.float64) + cb[b].astype(np.float64))
+    mid += rng.choice([0.0, 1e-8, 1e-7, 1e-6], (n, 1)) * rng.standard_normal((n, 4))
+    mid = mid.astype(np.float32)
+    mid = mid[np.linalg.norm(mid, axis=1) <= 1.0]
+    y = np.ascontiguousarray(np.concatenate([typical, full, mid]), np.float32)
+    fn = oracle_mod.lib().pkvo_fib_biased_search_check
+    fn.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64)]
+    out = (C.c_int64 * 5)()
+    assert fn(y.ctypes.data, y.shape[0], cb.ctypes.data, n_codewords, order, out) == 0
+    wrong, undecided, certain, by_gap, out_of_binade = list(out)
+    assert wrong == 0 and out_of_binade == 0
+    assert certain + undecided == y.shape[0]
+    assert by_gap > 0.98 * (typical.shape[0] + full.shape[0])      # the quick test settles ordinary blocks
+    assert undecided > 0.2 * mid.shape[0]                           # and the bisector cases do reach the exact tier
+    print(n_codewords, scale, "undecided", undecided / y.shape[0], "by gap", by_gap / y.shape[0])

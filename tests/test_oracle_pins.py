@@ -236,3 +236,34 @@ def test_chacha_stream_of_the_reference_sign_generator():
     expect = tables.chacha8_next_u32((42 + 0xA11CE55ED5A5EED5) & (2 ** 64 - 1), 128)
     assert [v > 0 for v in s] == [w >= 1 << 31 for w in expect]
     assert np.array_equal(s[:64], tables.reference_hadamard_signs(64, 42))  # a prefix of one stream
+
+
+def test_hadamard_rotation_pins():
+    """What gpu-backend/src/fallback.rs:312-364 states about hadamard_batch_cpu: a unit impulse comes out
+    with magnitude 1/sqrt(dim) everywhere, a 768-vector is padded to 1024 and truncated back, equal inputs
+    give equal outputs; and the LCG signs (:76-88) against a restatement in Python integers."""
+    import oracle
+    from provekv_b200 import tables
+    d = np.zeros((2, 8), np.float32)
+    d[:, 0] = 1.0
+    out = oracle.hadamard_batch(d, 42)
+    assert np.all(np.abs(np.abs(out) - 1.0 / np.sqrt(np.float32(8))) < 1e-5)
+    z = np.zeros((1, 768), np.float32)
+    z[0, 0] = 1.0
+    out = oracle.hadamard_batch(z, 42)
+    assert out.shape == (1, 768) and np.any(out != 0.0) and np.all(np.abs(out) == np.float32(1.0 / 32.0))
+    v = np.arange(1.0, 9.0, dtype=np.float32)[None]
+    assert np.array_equal(oracle.hadamard_batch(v, 42), oracle.hadamard_batch(v.copy(), 42))
+    for seed in (0, 42, 2 ** 64 - 1, 0x9E3779B97F4A7C15):
+        assert np.array_equal(oracle.hadamard_signs(128, seed), tables.lcg_hadamard_signs(128, seed))
+    # the transform equals its matrix form, and that matrix is orthogonal
+    m = tables.hadamard_rotation_matrix(128, 7)
+    x = np.random.default_rng(0).standard_normal((5, 128)).astype(np.float32)
+    assert np.abs(oracle.hadamard_batch(x, 7) - x.astype(np.float64) @ m.T).max() < 1e-6
+    assert np.abs(m @ m.T - np.eye(128)).max() < 1e-7
+    # the encoder built on it: the record of a vector is a function of that vector alone
+    cb = tables.fib_codebook(64, seed=42)
+    x = np.random.default_rng(1).standard_normal((40, 64)).astype(np.float32)
+    st, a, _, _ = oracle.fib_encode_hadamard(x, 3, cb)
+    st2, b, _, _ = oracle.fib_encode_hadamard(x[10:30], 3, cb, nthreads=3)
+    assert st == 0 and st2 == 0 and np.array_equal(a[10:30], b)
