@@ -1441,7 +1441,7 @@ PKVO_API int pkvo_fib_biased_search_check(const float* y, int64_t n, const float
   float off, e_f, hn_off[32], nc[32][4];
   uint32_t quick_gap;
   for (int k = 0; k < 5; k++) counts[k] = 0;
-  if (n_codewords > 32 || !pkv_fib_search_bias(codebook, n_codewords, &off, &e_f, &quick_gap)) return 1;
+  if (n_codewords > 32 || !pkv_fib_search_bias(codebook, n_codewords, 0.0, &off, &e_f, &quick_gap)) return 1;
   const uint32_t binade = pkv_f32_bits(off) & 0xff800000u;
   for (int c = 0; c < n_codewords; c++) {
     double s = 0.0;

@@ -232,8 +232,8 @@ struct pkv_fib_profile {
   float* half_norm_dev; // |c|^2 / 2 per codeword
   float* rot_hi_dev;    // [r][j] (f32) M[r][j] with the 13 low significand bits cleared (TF32 operand)
   float* rot_lo_dev;    // [r][j] (f32) M[r][j] - rot_hi, exact
-  uint32_t search_quick_gap;
-  float search_off, search_ef;  // bias of the encoders' score search and its error bound (pkv_fib_search.cuh)
+  uint32_t search_quick_gap;  // for a rotation error of 0 (the Hadamard encoder)
+  float search_off, search_ef;  // bias of the Hadamard encoder score search and its error bound (pkv_fib_search.cuh)
   int hadamard;         // 1: encode_batch rotates by the f32 Walsh-Hadamard transform (pkv_fib_profile_create_hadamard)
   float wht_sgn_scale[128];  // sign_i / sqrt(dim) of that transform
   PkvWorkspace ws;

@@ -297,11 +297,12 @@ PKV_HD int pkv_fib_certify_abs(float f1, float f2, float s0, float s1, float s2,
  * off = 1.5 * 2^k with k the smallest exponent whose binade [2^k, 2^(k+1)) holds off + F for every
  * score F = |c|^2 / 2 - s . c of a block with |s| <= 1.001; e_f = 2.5 ulps of that binade bounds the
  * error of a kept score (the start value and four fused operations, half an ulp each); quick_gap is a
- * gap of the two best scores, in ulps of the binade, above which pkv_fib_certify_abs with eta = 0 holds
- * for every block: it asks for 2 (F2 - F1) > 1.05 (2.5e-7 (d1 + d2) + 4.2 e_f), squared distances stay
- * below (1.001 + max |c|)^2, and 0.63 = 0.525 * 1.2 leaves room for the roundings of that test itself.
+ * gap of the two best scores, in ulps of the binade, above which pkv_fib_certify_abs with this eta holds
+ * for every block: it asks for 2 (F2 - F1) > 1.05 (4 eta (sqrt d1 + sqrt d2) + 8 eta^2 + 2.5e-7 (d1 + d2)
+ * + 4.2 e_f), squared distances stay below dmax = (1.001 + max |c|)^2, and 0.63 = 0.525 * 1.2 leaves room
+ * for the roundings of that test itself.
  * Returns 0 when no binade below 2^99 holds the scores (or the codebook is not finite). */
-static inline int pkv_fib_search_bias(const float* codebook, int n_codewords, float* off, float* e_f,
+static inline int pkv_fib_search_bias(const float* codebook, int n_codewords, double eta, float* off, float* e_f,
                                       uint32_t* quick_gap) {
   double hmax = 0.0, cmax = 0.0;
   for (int c = 0; c < n_codewords; c++) {
@@ -317,7 +318,8 @@ static inline int pkv_fib_search_bias(const float* codebook, int n_codewords, fl
   const double ulp_b = __builtin_ldexp(1.0, k - 23), dmax = (1.001 + cmax) * (1.001 + cmax);
   *off = (float)__builtin_ldexp(1.5, k);
   *e_f = (float)(2.5 * ulp_b);
-  *quick_gap = (uint32_t)__builtin_ceil(0.63 * (5.05e-7 * dmax + 10.5 * ulp_b) / ulp_b) + 1u;
+  const double gap = 0.63 * (8.0 * eta * __builtin_sqrt(dmax) + 8.0 * eta * eta + 5.05e-7 * dmax + 10.5 * ulp_b) / ulp_b;
+  *quick_gap = gap < 4.0e9 ? (uint32_t)__builtin_ceil(gap) + 1u : 0xffffffffu;
   return 1;
 }
 

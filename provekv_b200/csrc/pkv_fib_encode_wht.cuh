@@ -135,22 +135,24 @@ fib_encode_wht_kernel(PkvGeom g, const float* __restrict__ x, const __grid_const
 #pragma unroll
   for (int i = 0; i < K::B / 4; i++) idx4[i] = 0;
   uint32_t flagged = 0;
+  unsigned long long yp[K::B / 2][4];  // the rotated row, two blocks per operand; n is not used again
+  fib_search_pack<D, 0, K::B>(n, yp);
 #pragma unroll
   for (int h = 0; h < K::B / K::HB; h++) {
     uint32_t best[K::HB], second[K::HB];
-    if (h == 0) fib_search_keys<D, 0, K::HB>(n, s_tab, n_codewords, bias.mult, best, second);
-    else fib_search_keys<D, (D > 4 * K::HB ? 4 * K::HB : 0), K::HB>(n, s_tab, n_codewords, bias.mult, best, second);
+    if (h == 0) fib_search_keys<K::B, 0, K::HB>(yp, s_tab, n_codewords, bias.mult, best, second);
+    else fib_search_keys<K::B, (K::B > K::HB ? K::HB : 0), K::HB>(yp, s_tab, n_codewords, bias.mult, best, second);
 #pragma unroll
     for (int b = 0; b < K::HB; b++) {
-      const int gb = K::HB * h + b, e = 4 * gb;
+      const int gb = K::HB * h + b;
       idx4[gb >> 2] |= (best[b] & 31u) << (8 * (gb & 3));
-      // Quick test on the keys themselves: squared distances of points of the unit ball stay below 4
-      // (pkv_fib_search.cuh takes |c| and |s| <= 1.001 into the choice of the binade; larger codebooks
-      // get a larger binade, and quick_gap is derived from it on the host), so a score gap above
-      // 0.525 (2.5e-7 * 8 + 4.2 e_f) certifies without looking at the block.
+      // Quick test on the keys themselves: a gap of the two best scores above a constant derived on the
+      // host from the codebook (pkv_fast_paths.h (3b)) certifies without looking at the block.
       if ((second[b] >> 5) - (best[b] >> 5) > bias.quick_gap) continue;
-      if (!pkv_fib_certify_abs(fib_search_score(best[b], bias.off), fib_search_score(second[b], bias.off), n[e],
-                               n[e + 1], n[e + 2], n[e + 3], 0.0f, bias.e_f))
+      float sb[4];
+      fib_search_block<K::B>(yp, gb, sb);
+      if (!pkv_fib_certify_abs(fib_search_score(best[b], bias.off), fib_search_score(second[b], bias.off), sb[0],
+                               sb[1], sb[2], sb[3], 0.0f, bias.e_f))
         flagged |= 1u << gb;
     }
   }

@@ -8,10 +8,12 @@
 // significand bits and order like the values, so
 //     key = bits(F_c + off) * 32 + c   (mod 2^32)
 // keeps the whole significand, carries the codeword index in its five low bits and orders, as an
-// unsigned integer, first by score and then by index.  That is one integer multiply-add on the FMA
-// pipe where the float keys of pkv_fib_key needed a logic operation on the half-rate integer pipe, and
-// the four fused multiply-adds of a score run as packed two-lane operations on two blocks at a time:
-// 5.5 issue slots per (block, codeword) pair instead of 7.5.
+// unsigned integer, first by score and then by index.  The index is merged by one integer multiply-add
+// (FMA pipe) where the float keys of pkv_fib_key need a logic operation, and the four fused multiply-adds
+// of a score run as packed two-lane operations on two blocks at a time: 6.1 instructions per (block,
+// codeword) pair instead of 9.0, measured on the bare loop.  Used by the Hadamard encoder, whose 128
+// registers per thread (four CTAs per SM) it makes possible.  The tensor-core encoders keep the float keys:
+// with this form they measured slower (d = 64: 0.59 against 0.55 ms on 1.5 M vectors).
 //
 // Error of a kept score against the exact F_c: the start value |c|^2 / 2 + off and the four fused
 // operations each round to the binade's grid, ulp_b = 2^(k-23): at most 2.5 ulp_b =: e_f.
@@ -74,15 +76,33 @@ __device__ __forceinline__ void fib_search_fill(FibSearchTab* tab, const float* 
   tab->hn2[c] = pkv_pack2(h, h);
 }
 
-// Best and second-best key of NB consecutive blocks (NB even) whose rotated values start at y[E0].
+// The rotated values of NB consecutive blocks (NB even) starting at y[E0], as two-lane operands: lane 0
+// holds block 2q, lane 1 block 2q + 1.  Callers keep only this form alive during the search (the scalar
+// copy beside it would cost 4 NB more registers, which the compiler recovers by re-packing inside the loop).
 template <int D, int E0, int NB>
-__device__ __forceinline__ void fib_search_keys(const float (&y)[D], const FibSearchTab* tab, int n_codewords,
-                                                uint32_t mult, uint32_t (&best)[NB], uint32_t (&second)[NB]) {
-  unsigned long long yp[NB / 2][4];  // (block 2q, block 2q + 1), coordinate j
+__device__ __forceinline__ void fib_search_pack(const float (&y)[D], unsigned long long (&yp)[NB / 2][4]) {
 #pragma unroll
   for (int q = 0; q < NB / 2; q++)
 #pragma unroll
     for (int j = 0; j < 4; j++) yp[q][j] = pkv_pack2(y[E0 + 8 * q + j], y[E0 + 8 * q + 4 + j]);
+}
+// The four values of block b.
+template <int NB>
+__device__ __forceinline__ void fib_search_block(const unsigned long long (&yp)[NB / 2][4], int b, float (&s)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    uint32_t lo, hi;
+    pkv_unpack2(yp[b >> 1][j], lo, hi);
+    s[j] = __uint_as_float((b & 1) ? hi : lo);
+  }
+}
+
+// Best and second-best key of the NB blocks from block B0 on (both even) of a packed row of NBT blocks.
+template <int NBT, int B0, int NB>
+__device__ __forceinline__ void fib_search_keys(const unsigned long long (&ypt)[NBT / 2][4], const FibSearchTab* tab,
+                                                int n_codewords, uint32_t mult, uint32_t (&best)[NB],
+                                                uint32_t (&second)[NB]) {
+  const unsigned long long (*yp)[4] = &ypt[B0 / 2];
 #pragma unroll
   for (int b = 0; b < NB; b++) best[b] = second[b] = 0xffffffffu;
   // two codewords per step (the table holds 32 entries; those past n_codewords never win)

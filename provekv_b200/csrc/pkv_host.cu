@@ -380,13 +380,13 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
     for (int j = 0; j < 4; j++) s += (double)cb[4 * c + j] * (double)cb[4 * c + j];
     hn[c] = (float)(0.5 * s);
   }
-  // Bias of the encoders' score search (pkv_fast_paths.h (3b)); a codebook no binade can hold leaves the
-  // exact kernel only
+  // Bias of the Hadamard encoder's score search (pkv_fast_paths.h (3b)); 2e30 marks a codebook that no
+  // binade can hold (pkv_fib_profile_create_hadamard refuses it)
   p->search_off = 2.0e30f;
   p->search_ef = 0.0f;
   p->search_quick_gap = 0xffffffffu;
-  if (!pkv_fib_search_bias(cb, cfg->codebook_size, &p->search_off, &p->search_ef, &p->search_quick_gap))
-    p->orthonormal = 0;
+  if (!pkv_fib_search_bias(cb, cfg->codebook_size, 0.0, &p->search_off, &p->search_ef, &p->search_quick_gap))
+    p->search_off = 2.0e30f;
   for (int r = 0; r < d; r++)
     for (int j = 0; j < d; j++) r32[j * d + r] = (float)rotation[r * d + j];
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->rot_dev, sizeof(double) * d * d);
