@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/codec_golden.npz.
+"""Regenerates tests/golden/codec_golden.npz and tests/golden/hadamard_golden.npz.
 
 The reference is Rust and cannot run here, so these vectors are outputs of the
 CPU oracle (oracle/pkv_oracle.c), frozen so that (a) a later change of the oracle
@@ -63,6 +63,27 @@ def main():
     out["libc"] = np.array("-".join(platform.libc_ver()))
     np.savez_compressed(os.path.join(HERE, "codec_golden.npz"), **out)
     print("wrote", len(out), "arrays")
+    hadamard()
+
+
+HADAMARD_SEED = 0x9E3779B97F4A7C15
+
+
+def hadamard():
+    """hadamard_golden.npz: the Walsh-Hadamard rotation of the reference's `gpu` build (gpu-backend/src/
+    fallback.rs:12-88) on the same inputs, and the fib records encoded through it (fib-quant/src/codec.rs:612-656)."""
+    out = {"seed": np.array(HADAMARD_SEED, dtype=np.uint64)}
+    for d, n in ((64, 24), (128, 20)):
+        x = inputs(n, d)
+        cb = tables.fib_codebook(d, seed=SEED)
+        out[f"x_{d}"], out[f"cb_{d}"] = x, cb
+        out[f"rotated_{d}"] = oracle.hadamard_batch(x, HADAMARD_SEED)
+        for order in (0, 1):
+            st, p, _, _ = oracle.fib_encode_hadamard(x, HADAMARD_SEED, cb, argmin_order=order)
+            assert st == 0
+            out[f"fib_payload_{d}_order{order}"] = p
+    np.savez_compressed(os.path.join(HERE, "hadamard_golden.npz"), **out)
+    print("wrote", len(out), "arrays (hadamard)")
 
 
 if __name__ == "__main__":

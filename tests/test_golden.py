@@ -56,3 +56,43 @@ def test_cuda_reproduces_golden(d):
                                       GOLD[f"turbo_{tag}_platform_payload_{d}"]):
             # the host libm put every pair of these vectors into the same bucket
             assert wire[38:] == GOLD[f"turbo_{tag}_platform_payload_{d}"].tobytes()
+
+
+HGOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "hadamard_golden.npz"))
+
+
+def _wht_numpy(x, seed):
+    """gpu-backend/src/fallback.rs:26-59 in NumPy binary32 arithmetic (power-of-two dim), written
+    independently of the oracle's C: butterflies for step = 1, 2, 4, .., then the signs, then the scale."""
+    from provekv_b200 import tables
+    v = np.array(x, dtype=np.float32)
+    d = v.shape[1]
+    step = 1
+    while step < d:
+        w = v.reshape(-1, d // (2 * step), 2, step)
+        a, b = w[:, :, 0, :].copy(), w[:, :, 1, :].copy()
+        w[:, :, 0, :], w[:, :, 1, :] = a + b, a - b
+        step *= 2
+    v = v * tables.lcg_hadamard_signs(d, seed)
+    return v * (np.float32(1.0) / np.sqrt(np.float32(d)))
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_oracle_reproduces_hadamard_golden(oracle_mod, d):
+    seed, x, cb = int(HGOLD["seed"]), HGOLD[f"x_{d}"], HGOLD[f"cb_{d}"]
+    assert _beq(oracle_mod.hadamard_batch(x, seed), HGOLD[f"rotated_{d}"])
+    assert _beq(_wht_numpy(x, seed), HGOLD[f"rotated_{d}"])
+    for order in (0, 1):
+        st, p, _, _ = oracle_mod.fib_encode_hadamard(x, seed, cb, argmin_order=order)
+        assert st == 0 and _beq(p, HGOLD[f"fib_payload_{d}_order{order}"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d", [64, 128])
+def test_cuda_reproduces_hadamard_golden(d):
+    import provekv_b200 as pk
+    from provekv_b200 import _lib as L
+    seed, x, cb = int(HGOLD["seed"]), HGOLD[f"x_{d}"], HGOLD[f"cb_{d}"]
+    for order in (0, 1):
+        prof = pk.FibProfile(d, None, cb, argmin_order=order, hadamard_seed=seed)   # AUTO numerics: >= 16 vectors
+        assert prof.encode_batch_compact(x)[19:] == HGOLD[f"fib_payload_{d}_order{order}"].tobytes()
