@@ -286,7 +286,13 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* p, const uint8_t* bytes_
 /* Many equal-sized batches in one call: vectors_host is [n_batches][vectors_per_batch][dim],
  * out_host receives n_batches FB2 blobs of 19 + vectors_per_batch*record_bytes bytes each, i.e.
  * what proveKV/src/pool.rs:265-266 obtains from one encode_batch_compact call per (layer, K|V).
- * Copies and kernels of successive chunks overlap; vec_index is the global vector index. */
+ * Copies and kernels of successive chunks overlap; vec_index is the global vector index.
+ * When the status is a per-vector code (>= 16) out_host is still complete: the record of every vector
+ * the encoder refused (zero norm, non-finite input, norm outside the wire format) is all zero bytes -- a
+ * norm field no accepted vector can have -- and every other record is the one a call without the refused
+ * vectors would have produced.  The reference fails the whole batch (fib-quant/src/codec.rs:594-610);
+ * callers that keep refused vectors raw (fib-quant/src/kv/codec.rs:264-286) read the verdict per vector
+ * from the records. */
 int pkv_fib_encode_batches_compact(const pkv_fib_profile* p, const float* vectors_host,
                                    int64_t n_batches, int64_t vectors_per_batch, uint8_t* out_host,
                                    int64_t out_capacity, int32_t* vec_code, int64_t* vec_index);

@@ -603,15 +603,6 @@ def _gpu_profile(profile: KvCompressionProfileV1, rotation, codebook):
     return FibProfile(fp.ambient_dim, rotation, cb, numerics=L.FIB_NUMERICS_SINGLE)
 
 
-def _sequential_norms(x: np.ndarray) -> np.ndarray:
-    """l2_norm (codec.rs:1049-1057): binary64 squares added in element order, then the root."""
-    acc = np.zeros(x.shape[0], np.float64)
-    x64 = x.astype(np.float64)
-    for j in range(x.shape[1]):
-        acc += x64[:, j] * x64[:, j]
-    return np.sqrt(acc)
-
-
 def encode_kv_tensor(shape: KvTensorShapeV1, layout: KvCacheLayoutV1, profile: KvCompressionProfileV1, values,
                      rotation, codebook, gpu_profile=None, recorded_unix_seconds: int | None = None
                      ) -> KvEncodedTensorV1:
@@ -658,29 +649,38 @@ def encode_kv_tensor(shape: KvTensorShapeV1, layout: KvCacheLayoutV1, profile: K
         raise KvError(f"unknown axis policy {profile.axis_policy}")
     records = None
     if not raw.all():
-        norms = _sequential_norms(x)
-        with np.errstate(over="ignore"):
-            h = norms.astype(np.float32).astype(np.float16)
-        refused = {"zero norm vector is not valid on the normal FibQuant encode path": norms == 0.0,
-                   "corrupt payload: norm cannot be represented as finite positive fp16":
-                       (norms != 0.0) & (~np.isfinite(h) | (h <= 0))}
+        # One launch over every vector; the ones the policy keeps raw ride along as a codable stand-in.
+        # The encoder's verdict comes back in the records: a refused vector's record is all zero bytes
+        # (include/provekv_b200.h, pkv_fib_encode_batches_compact), and the call's status names the first one.
+        from . import _lib as L
+        from .profiles import encode_batches_compact
         xg = x
-        for text, mask in refused.items():
-            mask = mask & ~raw
+        if raw.any():
+            xg = x.copy()
+            xg[raw] = 0.0
+            xg[raw, 0] = 1.0
+        prof = gpu_profile or _gpu_profile(profile, rotation, codebook)
+        rec = prof.record_bytes
+        wire = np.zeros(L.FB2_HEADER_BYTES + n_vec * rec, np.uint8)
+        try:
+            encode_batches_compact(prof, xg.ctypes.data, 1, n_vec, wire.ctypes.data, wire.size)
+        except L.PkvError as e:
+            if e.status < 16:        # not a per-vector verdict
+                raise
+        records = wire[L.FB2_HEADER_BYTES:].reshape(n_vec, rec)
+        norm_len = _norm_format_len(profile.fib_profile.norm_format)
+        refused = ~raw & ~records[:, :norm_len].any(axis=1)
+        # the reference's two refusals (input is finite here): a vector of zeros has norm zero, anything else
+        # the encoder refuses has a norm its wire format cannot hold (codec.rs:603, :1003-1017)
+        zero = refused & ~x.any(axis=1)
+        for text, mask in (("zero norm vector is not valid on the normal FibQuant encode path", zero),
+                           ("corrupt payload: norm cannot be represented as finite positive "
+                            + ("fp16" if norm_len == 2 else "f32"), refused & ~zero)):
             if mask.any():
                 if not keep_raw:
                     raise KvError(text)
                 reason[mask] = "encode_fallback:" + text
                 raw |= mask
-        if raw.any():  # raw vectors still ride through the launch: give them a codable stand-in
-            xg = x.copy()
-            xg[raw] = 0.0
-            xg[raw, 0] = 1.0
-        prof = gpu_profile or _gpu_profile(profile, rotation, codebook)
-        from . import _lib as L
-        wire = prof.encode_batch_compact(xg)
-        rec = prof.record_bytes
-        records = np.frombuffer(wire, np.uint8)[L.FB2_HEADER_BYTES:].reshape(n_vec, rec)
 
     pages, compressed, raw_blocks, reasons = [], 0, 0, []
     for page_id in range(geo.page_count(shape)):

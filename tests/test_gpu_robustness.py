@@ -232,3 +232,42 @@ def test_pool_built_on_the_device_it_names():
     with pytest.raises(L.PkvError) as ei:
         M.build_shared_pool(prof1, corpus, shape, 7, "cb", "rot", device="cuda:0")
     assert ei.value.status == L.ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("numerics,norm_format,hadamard", [(1, 0, False), (2, 0, False), (1, 1, False), (1, 0, True)])
+def test_refused_vectors_leave_zero_records_and_the_rest_intact(oracle_mod, dim, numerics, norm_format, hadamard):
+    """A per-vector status from the batched host call still delivers the whole payload: refused vectors as
+    all-zero records, every other record as if the refused vectors had not been there."""
+    import numpy as np
+    from provekv_b200 import _lib as L
+    from provekv_b200 import tables
+    from provekv_b200.profiles import FibProfile, encode_batches_compact
+    from kvgen import synthetic_kv
+    rot, cb = tables.haar_rotation(dim, 42), tables.fib_codebook(dim, seed=42)
+    prof = FibProfile(dim, rot, cb, numerics=numerics, norm_format=norm_format, hadamard_seed=7 if hadamard else None)
+    nb, vpb = 3, 700
+    x = synthetic_kv(nb * vpb, dim, seed=11)
+    bad = {5: 0.0, 701: None, 1399: 0.0, 2099: np.nan}        # 701: finite elements, norm beyond the wire format
+    clean = x.copy()
+    for i, v in bad.items():
+        x[i] = (np.sign(x[i]) * np.float32(3e38) if norm_format else x[i] * np.float32(3e4)) if v is None else v
+        clean[i] = 0.0
+        clean[i, 0] = 1.0
+    H, rec = L.FB2_HEADER_BYTES, prof.record_bytes
+    out = np.full((nb, H + vpb * rec), 0xAB, np.uint8)
+    with pytest.raises(L.PkvError) as e:
+        encode_batches_compact(prof, x.ctypes.data, nb, vpb, out.ctypes.data, out.size)
+    # the reference's first loop (non-finite, zero norm) reports before the norm format is looked at
+    assert e.value.status in (L.VEC_ZERO_NORM, L.VEC_NONFINITE_INPUT) and e.value.vector_index == 5
+    got = out[:, H:].reshape(nb * vpb, rec)
+    if hadamard:
+        st, want, _, _ = oracle_mod.fib_encode_hadamard(clean, 7, cb, norm_format=norm_format, nthreads=4)
+    else:
+        st, want, _, _ = oracle_mod.fib_encode(clean, rot, cb, norm_format=norm_format, numerics=numerics, nthreads=4)
+    assert st == 0
+    keep = np.ones(nb * vpb, bool)
+    keep[list(bad)] = False
+    assert np.array_equal(got[keep], want[keep])
+    assert not got[~keep].any()
