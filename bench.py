@@ -405,6 +405,42 @@ def single_kernel_names(w):
     return f"turbo_encode_kernel<{d}>", f"turbo_decode_patch_kernel<{d}>"
 
 
+def measure_score(torch, w, prof, kv, payload, pstride, n_batches, vpb, flush, steps, dev):
+    """Compressed-domain scoring beside the metric (outside its timed region): queries taken from the workload's
+    own vectors are prepared on the device, then scored against every record, one query per pass over the
+    records and eight queries per pass -> dict for the JSON line's "score" key."""
+    d, rec, n_vec = w["dim"], prof.record_bytes, n_batches * vpb
+    m = prof.projections if hasattr(prof, "projections") else TURBO_PROJ
+    nq = 8
+    queries = kv.reshape(-1, d)[:nq].contiguous()
+    rot = torch.empty((nq, d), dtype=torch.float32, device=dev)
+    proj = torch.empty((nq, max(m, 1)), dtype=torch.float32, device=dev)
+    scores = torch.empty((nq, n_vec), dtype=torch.float32, device=dev)
+    err = torch.full((1,), -1, dtype=torch.int64, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    prof.prepare_queries_dev(queries.data_ptr(), nq, rot.data_ptr(), proj.data_ptr(), err.data_ptr(), stream)
+    peak, _ = measured_hbm_peak()
+    out = {"records": n_vec, "record_bytes": rec, "queries_prepared_on_device": nq}
+    for label, q in (("one_query", 1), ("eight_queries", nq)):
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+        for i in range(-3, steps):
+            if flush is not None:
+                flush.zero_()
+            if i >= 0:
+                ev[i][0].record()
+            prof.score_queries_dev(payload.data_ptr(), pstride, n_batches, vpb, rot.data_ptr(), proj.data_ptr(), q,
+                                   scores.data_ptr(), err.data_ptr(), stream)
+            if i >= 0:
+                ev[i][1].record()
+        torch.cuda.synchronize()
+        ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+        nbytes = (rec + 4 * q) * n_vec
+        out[label] = {"ms": ms, "scores_per_s": q * n_vec / (ms * 1e-3), "algorithmic_bytes": nbytes,
+                      "achieved_gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peak}
+    assert int(err[0]) == -1, "the score kernel reported a record"
+    return out
+
+
 def measure_single(torch, w, steps, warmup, dev, seed, cache_dtype="f32"):
     """Device-timed encode and decode-and-patch of a single-codec workload -> dict."""
     import provekv_b200 as pk
@@ -463,10 +499,14 @@ def measure_single(torch, w, steps, warmup, dev, seed, cache_dtype="f32"):
     enc_bytes = (4 * d + rec) * n_vec
     dec_bytes = (rec + d * cache.element_size()) * n_vec
     enc_name, dec_name = single_kernel_names(w)
+    launches = int(L.lib().pkv_launch_count() - launches0)  # of the timed region; the scoring below is outside it
+    score = measure_score(torch, w, prof, kv, payload, pstride, n_batches, vpb, flush, steps, dev) \
+        if w["codec"] == "turbo" else None
     return {
+        "score": score,
         "prof": prof, "payload": payload, "pstride": pstride, "n_vec": n_vec, "vpb": vpb, "n_batches": n_batches,
         "rec": rec, "err": err, "kv": kv, "flush": flush, "f32_bytes": f32_bytes, "big": big,
-        "launches": int(L.lib().pkv_launch_count() - launches0),
+        "launches": launches,
         "enc_ms": enc_ms, "dec_ms": dec_ms, "step_ms": enc_ms + dec_ms,
         "kernels": {
             enc_name: {"ms": enc_ms, "algorithmic_bytes": enc_bytes, "achieved_gbs": enc_bytes / enc_ms / 1e6,
@@ -553,6 +593,8 @@ def run_single(args, w):
             "ms_x_sm_mhz": step_ms * clk["sm_mhz"] if clk.get("sm_mhz") else None,
             "wall_ms_timed_region": t_wall * 1e3,
         }
+        if m.get("score"):
+            line["score"] = m["score"]
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             gbs, _, sample = cpu_single_rate(w, 8.0, cores)

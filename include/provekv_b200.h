@@ -350,6 +350,25 @@ int pkv_turbo_score_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
                         const float* rotated_query_dev, const float* projected_query_dev,
                         float* scores_dev, uint64_t* err_dev, void* stream);
 
+/* The same for n_queries prepared queries in one pass over the records (a group of query heads that
+ * share a KV head, or the queries of several positions): rotated_queries_dev is [n_queries][dim],
+ * projected_queries_dev [n_queries][projections], scores_dev [n_queries][n_batches * vectors_per_batch].
+ * Each score is the value pkv_turbo_score_dev gives for that query alone; up to eight queries share one
+ * read of the records. */
+int pkv_turbo_score_queries_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                                int64_t payload_batch_stride, int64_t n_batches, int64_t vectors_per_batch,
+                                const float* rotated_queries_dev, const float* projected_queries_dev,
+                                int64_t n_queries, float* scores_dev, uint64_t* err_dev, void* stream);
+
+/* TurboQuantizer::prepare_query (turbo-quant/src/turbo.rs:322-337) for queries that already live on the
+ * device: rotated_dev[q] = FastHadamardRotation::apply(query q) (polar.rs:336-343), projected_dev[q] = the
+ * QJL matrix times query q with every product rounded and the row summed in order (qjl.rs:266-281);
+ * projected_dev is ignored for polar-only profiles.  A query, rotated query or projection that is not
+ * finite is reported as PKV_VEC_NONFINITE_INPUT with the query's index (the reference's
+ * check_finite_vector at each of the three places). */
+int pkv_turbo_prepare_queries_dev(const pkv_turbo_profile* p, const float* queries_dev, int64_t n_queries,
+                                  float* rotated_dev, float* projected_dev, uint64_t* err_dev, void* stream);
+
 /* TurboQuantAdapter::{encode,decode}_batch_compact (proveKV/src/codec.rs:248-326). */
 int pkv_turbo_encode_batch_compact(const pkv_turbo_profile* p, const float* vectors_host, int64_t n,
                                    uint8_t* out_host, int64_t out_capacity, int64_t* out_len,

@@ -140,6 +140,8 @@ _SIGS = {
     "pkv_fib_decode_patch_dev_multi": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, C.c_int32, _V, _V]),
     "pkv_turbo_decode_patch_dev_multi": (C.c_int, [_V, _V, C.c_int64, C.POINTER(Layout), _V, _V, C.c_int32, _V, _V]),
     "pkv_turbo_score_dev": (C.c_int, [_V, _V, C.c_int64, C.c_int64, C.c_int64, _V, _V, _V, _V, _V]),
+    "pkv_turbo_score_queries_dev": (C.c_int, [_V, _V, C.c_int64, C.c_int64, C.c_int64, _V, _V, C.c_int64, _V, _V, _V]),
+    "pkv_turbo_prepare_queries_dev": (C.c_int, [_V, _V, C.c_int64, _V, _V, _V, _V]),
     "pkv_fib_encode_dev_static": (C.c_int, [_V, _V, C.POINTER(Layout), _V, C.c_int64, _V, _V]),
     "pkv_fib_encode_batch_compact": (C.c_int, [_V, _V, C.c_int64, _V, C.c_int64, C.POINTER(C.c_int64),
                                                C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),

@@ -872,26 +872,45 @@ int pkv_turbo_decode_patch_dev_multi(const pkv_turbo_profile* p, const uint8_t* 
   return pkv_launch_turbo_decode(p, payload_dev, g, cache_dev, dst_dtype, err_dev, (cudaStream_t)stream);
 }
 
-int pkv_turbo_score_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
-                        int64_t payload_batch_stride, int64_t n_batches, int64_t vectors_per_batch,
-                        const float* rotated_query_dev, const float* projected_query_dev,
-                        float* scores_dev, uint64_t* err_dev, void* stream) {
-  if (!p || !payload_dev || !rotated_query_dev || !scores_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
+int pkv_turbo_score_queries_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                                int64_t payload_batch_stride, int64_t n_batches, int64_t vectors_per_batch,
+                                const float* rotated_queries_dev, const float* projected_queries_dev,
+                                int64_t n_queries, float* scores_dev, uint64_t* err_dev, void* stream) {
+  if (!p || !payload_dev || !rotated_queries_dev || !scores_dev || !err_dev) return PKV_ERR_INVALID_ARGUMENT;
   if (int ds = pkv_check_device(p->device)) return ds;
-  if (p->cfg.mode == PKV_TURBO_POLAR_WITH_QJL && !projected_query_dev) return PKV_ERR_INVALID_ARGUMENT;
-  if (((uintptr_t)payload_dev & 15) || ((uintptr_t)rotated_query_dev & 3) || ((uintptr_t)scores_dev & 3))
+  if (p->cfg.mode == PKV_TURBO_POLAR_WITH_QJL && !projected_queries_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)payload_dev & 15) || ((uintptr_t)rotated_queries_dev & 3) || ((uintptr_t)scores_dev & 3) ||
+      ((uintptr_t)projected_queries_dev & 3))
     return PKV_ERR_INVALID_ARGUMENT;
-  if (n_batches < 0 || vectors_per_batch < 0 || n_batches >= ((int64_t)1 << 31) ||
+  if (n_batches < 0 || vectors_per_batch < 0 || n_queries < 0 || n_batches >= ((int64_t)1 << 31) ||
       vectors_per_batch >= ((int64_t)1 << 31))
     return PKV_ERR_INVALID_ARGUMENT;
-  if (n_batches == 0 || vectors_per_batch == 0) return PKV_OK;
+  if (n_batches == 0 || vectors_per_batch == 0 || n_queries == 0) return PKV_OK;
   pkv_layout L = flat_layout(vectors_per_batch, p->cfg.dim);
   L.n_batches[0] = (int32_t)n_batches;
   PkvGeom g;
   int st = make_geom(&L, p->rec_bytes, payload_batch_stride, pkv_turbo_tile_vectors(p->cfg.dim), false, &g);
   if (st != PKV_OK) return st;
-  return pkv_launch_turbo_score(p, payload_dev, g, rotated_query_dev, projected_query_dev, scores_dev, err_dev,
-                                (cudaStream_t)stream);
+  return pkv_launch_turbo_score(p, payload_dev, g, rotated_queries_dev, projected_queries_dev, n_queries, scores_dev,
+                                err_dev, (cudaStream_t)stream);
+}
+
+int pkv_turbo_score_dev(const pkv_turbo_profile* p, const uint8_t* payload_dev,
+                        int64_t payload_batch_stride, int64_t n_batches, int64_t vectors_per_batch,
+                        const float* rotated_query_dev, const float* projected_query_dev,
+                        float* scores_dev, uint64_t* err_dev, void* stream) {
+  return pkv_turbo_score_queries_dev(p, payload_dev, payload_batch_stride, n_batches, vectors_per_batch,
+                                     rotated_query_dev, projected_query_dev, 1, scores_dev, err_dev, stream);
+}
+
+int pkv_turbo_prepare_queries_dev(const pkv_turbo_profile* p, const float* queries_dev, int64_t n_queries,
+                                  float* rotated_dev, float* projected_dev, uint64_t* err_dev, void* stream) {
+  if (!p || !queries_dev || !rotated_dev || !err_dev || n_queries < 0) return PKV_ERR_INVALID_ARGUMENT;
+  if (int ds = pkv_check_device(p->device)) return ds;
+  if (p->cfg.mode == PKV_TURBO_POLAR_WITH_QJL && !projected_dev) return PKV_ERR_INVALID_ARGUMENT;
+  if (((uintptr_t)queries_dev | (uintptr_t)rotated_dev | (uintptr_t)projected_dev) & 3) return PKV_ERR_INVALID_ARGUMENT;
+  return pkv_launch_turbo_prepare_queries(p, queries_dev, n_queries, rotated_dev, projected_dev, err_dev,
+                                          (cudaStream_t)stream);
 }
 
 int pkv_tqb1_header_write(const pkv_turbo_profile* p, uint32_t n_vectors, uint8_t* out) {

@@ -20,8 +20,12 @@ struct TurboScoreSmem {
   }
   // the per-pair table of q_a cos_k + q_b sin_k is kept for up to 128 angle levels (16 KB at d = 64)
   static __host__ __device__ bool has_inner_table(int levels) { return levels <= 128; }
-  static __host__ __device__ size_t table_bytes(int levels) {
-    return sizeof(float) * (256 + 2 * levels + D + 64 + (has_inner_table(levels) ? (D / 2) * levels : 0));
+  // per query: the rotated query, the projected query and the inner table
+  static __host__ __device__ size_t query_floats(int levels) {
+    return D + 64 + (has_inner_table(levels) ? (D / 2) * levels : 0);
+  }
+  static __host__ __device__ size_t table_bytes(int levels, int n_queries) {
+    return sizeof(float) * (256 + 2 * levels + (size_t)n_queries * query_floats(levels));
   }
 };
 
@@ -139,23 +143,27 @@ __device__ __forceinline__ float score_record(const W& w, const TurboParams& tp,
   return score;
 }
 
-template <int D, int PB, int RAW>
+// MULTI = false is the one-query launch: without the loop over the queries the compiler keeps the kernel
+// at 72 registers (seven CTAs per SM); with it, it holds the unpacked record across the queries (155).
+template <int D, int PB, int RAW, bool MULTI>
 __global__ void __launch_bounds__(Turbo<D>::THREADS)
 turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payload,
                    const float* __restrict__ rotated_query, const float* __restrict__ projected_query,
-                   float qjl_scale, float* __restrict__ scores, uint64_t* err) {
+                   int n_queries, int64_t score_stride, float qjl_scale, float* __restrict__ scores, uint64_t* err) {
   using K = Turbo<D>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int pb = PB ? PB : tp.polar_bits;
   const int levels = 1 << pb;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if constexpr (!MULTI) n_queries = 1;
   float* s_q255 = reinterpret_cast<float*>(smem);  // [256]
   float* s_lut = s_q255 + 256;                     // (cos, sin)[L]
-  float* s_q = s_lut + 2 * levels;                 // [D] rotated query
-  float* s_p = s_q + D;                            // [64] projected query
-  float* s_inner = s_p + 64;                       // [P][L]: q_a cos_k + q_b sin_k, the same for every record
+  // per query, QF floats apart: [D] rotated query, [64] projected query, [P][L] q_a cos_k + q_b sin_k (the
+  // part of a pair's term that is the same for every record)
+  float* s_qbase = s_lut + 2 * levels;
+  const int QF = (int)TurboScoreSmem<D>::query_floats(levels);
   const bool inner_table = TurboScoreSmem<D>::has_inner_table(levels);
-  uint32_t* s_w = reinterpret_cast<uint32_t*>(smem + TurboScoreSmem<D>::table_bytes(levels) +
+  uint32_t* s_w = reinterpret_cast<uint32_t*>(smem + TurboScoreSmem<D>::table_bytes(levels, n_queries) +
                                               warp * TurboScoreSmem<D>::warp_bytes(tp.rec_words));
 
   const int64_t tile_id = (int64_t)blockIdx.x * K::NWARPS + warp;
@@ -183,28 +191,29 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
   }
   for (int i = threadIdx.x; i < 2 * levels; i += K::THREADS)
     pkv_cp_async4(s_lut + (i < levels ? 2 * i : 2 * (i - levels) + 1), tp.lut + i);
-  for (int i = threadIdx.x; i < D; i += K::THREADS) pkv_cp_async4(s_q + i, rotated_query + i);
-  for (int i = threadIdx.x; i < tp.projections; i += K::THREADS) pkv_cp_async4(s_p + i, projected_query + i);
+  for (int i = threadIdx.x; i < n_queries * D; i += K::THREADS)
+    pkv_cp_async4(s_qbase + (i / D) * QF + (i % D), rotated_query + i);
+  for (int i = threadIdx.x; i < n_queries * tp.projections; i += K::THREADS)
+    pkv_cp_async4(s_qbase + (i / tp.projections) * QF + D + (i % tp.projections), projected_query + i);
   if (tp.lossy)
     for (int i = threadIdx.x; i < 256; i += K::THREADS) s_q255[i] = __fdiv_rn((float)i, 255.0f);
   pkv_cp_async_wait_all();
   __syncthreads();
   if (inner_table) {  // polar.rs:361: (q_a * theta.cos() + q_b * theta.sin()), the record-independent part
-    for (int e = threadIdx.x; e < K::P * levels; e += K::THREADS) {
-      const int i = e / levels, k = e - i * levels;
-      s_inner[e] = __fadd_rn(__fmul_rn(s_q[2 * i], s_lut[2 * k]), __fmul_rn(s_q[2 * i + 1], s_lut[2 * k + 1]));
+    for (int e = threadIdx.x; e < n_queries * K::P * levels; e += K::THREADS) {
+      const int qi = e / (K::P * levels), r = e - qi * (K::P * levels);
+      const int i = r / levels, k = r - i * levels;
+      const float* s_q = s_qbase + qi * QF;
+      s_qbase[qi * QF + D + 64 + r] =
+          __fadd_rn(__fmul_rn(s_q[2 * i], s_lut[2 * k]), __fmul_rn(s_q[2 * i + 1], s_lut[2 * k + 1]));
     }
     __syncthreads();
   }
 
   if (v >= nv) return;
-  int code = 0;
-  float score;
-  if constexpr (raw == 2) {  // odd record stride: word reads of the raw tile are conflict-free
-    const uint32_t* wr = s_w + v * tp.rec_words;
-    score = score_record<D, PB, true>([&](int k) { return wr[k]; }, tp, pb, levels, s_q255, s_lut, s_q, s_p,
-                                      s_inner, inner_table, qjl_scale, code);
-  } else if constexpr (raw == 1) {
+  const int64_t gvec = (int64_t)batch * g.vpb + v0 + v;
+  // the record stays where it is (registers or the tile) while the queries take their turns
+  if constexpr (raw == 1) {
     // the record in registers: RW words loaded 16 bytes at a time from this lane's run of the raw tile
     constexpr int NWT = K::P * (PB ? PB : 1) / 32 + 2;  // angle words + up to two sign words
     constexpr int RW = (K::P + NWT + 3) & ~3;
@@ -215,21 +224,79 @@ turbo_score_kernel(PkvGeom g, TurboParams tp, const uint8_t* __restrict__ payloa
       const uint4 u = 4 * k < tp.rec_words ? w4[k] : make_uint4(0u, 0u, 0u, 0u);
       rw[4 * k] = u.x; rw[4 * k + 1] = u.y; rw[4 * k + 2] = u.z; rw[4 * k + 3] = u.w;
     }
-    score = score_record<D, PB, true>([&](int k) { return rw[k]; }, tp, pb, levels, s_q255, s_lut, s_q, s_p, s_inner,
-                                inner_table, qjl_scale, code);
+#pragma unroll 1
+    for (int qi = 0; qi < n_queries; qi++) {
+      const float* s_q = s_qbase + qi * QF;
+      int code = 0;
+      const float score = score_record<D, PB, true>([&](int k) { return rw[k]; }, tp, pb, levels, s_q255, s_lut, s_q,
+                                                    s_q + D, s_q + D + 64, inner_table, qjl_scale, code);
+      if (code) pkv_report(err, 0, gvec, code);
+      scores[(int64_t)qi * score_stride + gvec] = score;
+    }
   } else {
-    const uint32_t* w = s_w + v;
-    score = score_record<D, PB, false>([&](int k) { return w[k * K::WS]; }, tp, pb, levels, s_q255, s_lut, s_q, s_p,
-                                s_inner, inner_table, qjl_scale, code);
+#pragma unroll 1
+    for (int qi = 0; qi < n_queries; qi++) {
+      const float* s_q = s_qbase + qi * QF;
+      int code = 0;
+      float score;
+      if constexpr (raw == 2) {  // odd record stride: word reads of the raw tile are conflict-free
+        const uint32_t* wr = s_w + v * tp.rec_words;
+        score = score_record<D, PB, true>([&](int k) { return wr[k]; }, tp, pb, levels, s_q255, s_lut, s_q, s_q + D,
+                                          s_q + D + 64, inner_table, qjl_scale, code);
+      } else {
+        const uint32_t* w = s_w + v;
+        score = score_record<D, PB, false>([&](int k) { return w[k * K::WS]; }, tp, pb, levels, s_q255, s_lut, s_q,
+                                           s_q + D, s_q + D + 64, inner_table, qjl_scale, code);
+      }
+      if (code) pkv_report(err, 0, gvec, code);
+      scores[(int64_t)qi * score_stride + gvec] = score;
+    }
   }
-  const int64_t gvec = (int64_t)batch * g.vpb + v0 + v;
-  if (code) pkv_report(err, 0, gvec, code);
-  scores[gvec] = score;
+}
+
+// TurboQuantizer::prepare_query (turbo-quant/src/turbo.rs:322-337) for a batch of queries, one CTA of 64
+// threads per query.  Thread 0 runs FastHadamardRotation::apply (polar.rs:336-343) with the encoder's own
+// transform; thread j < projections sums row j of the QJL matrix against the query in order, every product
+// rounded (qjl.rs:275-279).  A query, a rotated query or a projection that is not finite is reported with the
+// query's index (the reference's check_finite_vector at each of the three places).
+template <int D>
+__global__ void __launch_bounds__(64)
+turbo_prepare_query_kernel(TurboParams tp, const float* __restrict__ queries, float* __restrict__ rotated,
+                           float* __restrict__ projected, uint64_t* err) {
+  __shared__ float s_x[D];
+  const int64_t qi = blockIdx.x;
+  const float* q = queries + qi * D;
+  for (int i = threadIdx.x; i < D; i += 64) s_x[i] = q[i];
+  __syncthreads();
+  bool bad = false;
+  if (threadIdx.x == 0) {
+    float y[D];
+#pragma unroll
+    for (int i = 0; i < D; i++) {
+      y[i] = s_x[i];
+      bad = bad || !pkv_finite(y[i]);
+    }
+    fwht_forward_signed<D>(y, tp.sgn, tp.scale);
+#pragma unroll
+    for (int i = 0; i < D; i++) {
+      bad = bad || !pkv_finite(y[i]);
+      rotated[qi * D + i] = y[i];
+    }
+  }
+  if ((int)threadIdx.x < tp.projections) {
+    const float* grow = tp.qjl + (size_t)threadIdx.x * D;
+    float sum = 0.0f;
+#pragma unroll 8
+    for (int k = 0; k < D; k++) sum = __fadd_rn(sum, __fmul_rn(__ldg(grow + k), s_x[k]));
+    projected[qi * tp.projections + threadIdx.x] = sum;
+    bad = bad || !pkv_finite(sum);
+  }
+  if (bad) pkv_report(err, 0, qi, PKV_VEC_NONFINITE_INPUT);
 }
 
 template <int D>
-size_t turbo_score_smem(const TurboParams& tp) {
-  return TurboScoreSmem<D>::table_bytes(1 << tp.polar_bits) +
+size_t turbo_score_smem(const TurboParams& tp, int n_queries) {
+  return TurboScoreSmem<D>::table_bytes(1 << tp.polar_bits, n_queries) +
          Turbo<D>::NWARPS * TurboScoreSmem<D>::warp_bytes(tp.rec_words);
 }
 

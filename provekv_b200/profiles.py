@@ -269,6 +269,22 @@ class TurboProfile(_ProfileBase):
                                             err_ptr, stream))
 
 
+    def score_queries_dev(self, payload_ptr: int, payload_batch_stride: int, n_batches: int, vectors_per_batch: int,
+                          rotated_ptr: int, projected_ptr: int, n_queries: int, scores_ptr: int, err_ptr: int,
+                          stream: int = 0) -> None:
+        """score_dev for n_queries prepared queries ([n_queries][dim] / [n_queries][projections] on the device)
+        in one pass over the records; scores are [n_queries][n_batches * vectors_per_batch]."""
+        L.check(L.lib().pkv_turbo_score_queries_dev(self.handle, payload_ptr, payload_batch_stride, n_batches,
+                                                    vectors_per_batch, rotated_ptr, projected_ptr, n_queries,
+                                                    scores_ptr, err_ptr, stream))
+
+    def prepare_queries_dev(self, queries_ptr: int, n_queries: int, rotated_ptr: int, projected_ptr: int,
+                            err_ptr: int, stream: int = 0) -> None:
+        """TurboQuantizer::prepare_query (turbo.rs:322-337) on the device for [n_queries][dim] f32 queries."""
+        L.check(L.lib().pkv_turbo_prepare_queries_dev(self.handle, queries_ptr, n_queries, rotated_ptr,
+                                                      projected_ptr, err_ptr, stream))
+
+
 def read_error_word(err_ptr: int, stream: int = 0) -> None:
     """Synchronise the stream and raise PkvError if a kernel reported a vector."""
     code, idx = C.c_int32(0), C.c_int64(-1)

@@ -83,3 +83,63 @@ def test_score_reports_the_first_malformed_record(oracle_mod):
     with pytest.raises(pk.PkvError) as e:
         pk.read_error_word(err.data_ptr())
     assert e.value.status == L.VEC_BAD_RADIUS and e.value.vector_index == 57
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("n_queries", [1, 3, 8, 11])
+def test_queries_prepared_and_scored_on_the_device(oracle_mod, dim, case, n_queries):
+    """Queries that live on the device: prepare_query there (bits of the oracle's rotated / projected
+    query), then all of them against the records in shared passes (bits of the oracle's scores, query by query)."""
+    import torch
+    bits, mode, m, rc = case
+    signs, qjl = _tables(dim, m)
+    n_batches, vpb = 2, 333
+    n = n_batches * vpb
+    x = synthetic_kv(n, dim, seed=n + bits + n_queries)
+    queries = synthetic_kv(n_queries, dim, seed=70 + n_queries)
+    st, payload, _, _ = oracle_mod.turbo_encode(x, signs, qjl, bits=bits, mode=mode, radii_codec=rc,
+                                               libm_mode=oracle_mod.LIBM_PORTABLE)
+    assert st == 0
+    prof = pk.TurboProfile(dim, bits, signs, qjl, mode=mode, radii_codec=rc, seed=SEED)
+    qd = torch.from_numpy(queries).cuda()
+    rot = torch.full((n_queries, dim), 7.0, dtype=torch.float32, device="cuda")
+    proj = torch.full((n_queries, max(m, 1)), 7.0, dtype=torch.float32, device="cuda")
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    prof.prepare_queries_dev(qd.data_ptr(), n_queries, rot.data_ptr(), proj.data_ptr(), err.data_ptr())
+    pk.read_error_word(err.data_ptr())
+    rec = prof.record_bytes
+    stride = pool.payload_batch_stride(vpb, rec)
+    host = np.zeros((n_batches, stride), np.uint8)
+    host[:, :vpb * rec] = payload.reshape(n_batches, vpb * rec)
+    dev = torch.from_numpy(host).cuda()
+    scores = torch.full((n_queries, n), 123.0, dtype=torch.float32, device="cuda")
+    prof.score_queries_dev(dev.data_ptr(), stride, n_batches, vpb, rot.data_ptr(), proj.data_ptr(), n_queries,
+                           scores.data_ptr(), err.data_ptr())
+    pk.read_error_word(err.data_ptr())
+    rot_h, proj_h, got = rot.cpu().numpy(), proj.cpu().numpy(), scores.cpu().numpy()
+    for q in range(n_queries):
+        st, r_ref, p_ref = oracle_mod.turbo_prepare_query(queries[q], signs, qjl)
+        assert st == 0 and np.array_equal(rot_h[q].view(np.uint32), r_ref.view(np.uint32)), q
+        if m:
+            assert np.array_equal(proj_h[q, :m].view(np.uint32), p_ref.view(np.uint32)), q
+        st, want, _, _ = oracle_mod.turbo_score(payload, dim, r_ref, p_ref, bits=bits, mode=mode, projections=m,
+                                               radii_codec=rc, libm_mode=oracle_mod.LIBM_PORTABLE)
+        assert st == 0 and np.array_equal(got[q].view(np.uint32), want.view(np.uint32)), q
+
+
+def test_a_query_that_is_not_finite_is_reported_by_its_index():
+    import torch
+    dim = 64
+    signs, qjl = _tables(dim, 32)
+    prof = pk.TurboProfile(dim, 4, signs, qjl, seed=SEED)
+    queries = synthetic_kv(5, dim, seed=1)
+    queries[3, 17] = np.inf
+    qd = torch.from_numpy(queries).cuda()
+    rot = torch.zeros((5, dim), dtype=torch.float32, device="cuda")
+    proj = torch.zeros((5, 32), dtype=torch.float32, device="cuda")
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    prof.prepare_queries_dev(qd.data_ptr(), 5, rot.data_ptr(), proj.data_ptr(), err.data_ptr())
+    with pytest.raises(pk.PkvError) as e:
+        pk.read_error_word(err.data_ptr())
+    assert e.value.status == L.VEC_NONFINITE_INPUT and e.value.vector_index == 3
