@@ -93,6 +93,16 @@ def test_profile_is_bound_to_its_device():
                 fib.decode_batch_compact(fib_wire)
             with pytest.raises(L.PkvError):
                 tq.decode_batch_compact(tq_wire)
+            rq = torch.zeros(2 * dim, dtype=torch.float32, device="cuda")
+            pq = torch.zeros(2 * 32, dtype=torch.float32, device="cuda")
+            sc = torch.zeros(2 * n, dtype=torch.float32, device="cuda")
+            with pytest.raises(L.PkvError) as ei:
+                tq.prepare_queries_dev(xd.data_ptr(), 2, rq.data_ptr(), pq.data_ptr(), err.data_ptr())
+            assert ei.value.status == L.ERR_INVALID_ARGUMENT
+            with pytest.raises(L.PkvError) as ei:
+                tq.score_queries_dev(out.data_ptr(), n * 256, 1, n, rq.data_ptr(), pq.data_ptr(), 2, sc.data_ptr(),
+                                     err.data_ptr())
+            assert ei.value.status == L.ERR_INVALID_ARGUMENT
             torch.cuda.synchronize()
             assert int(err[0]) == -1
         assert lib.pkv_launch_count() == launches
