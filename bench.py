@@ -19,7 +19,10 @@ workloads (c1, c2, ...) time one encoder / decoder pair.
 ``value`` = f32 KV bytes encoded + f32 KV bytes written into caches, over all ranks, per second of
 device time (CUDA events, max over ranks), inputs resident in HBM.  ``value_unique`` counts every
 distinct vector once on the decode side.  ``kernels`` gives each kernel's time, algorithmic bytes and
-fraction of the measured HBM copy bandwidth; ``roofline`` repeats that for the slowest one.  ``e2e``
+fraction of the measured HBM copy bandwidth and, under ``alu``, the arithmetic ceiling beside it (the
+separately rounded binary32 operations the reference's contract fixes per vector, at one per lane and
+clock); ``roofline`` repeats the HBM figures for the slowest one.  ``cpu_baseline`` is the oracle on all
+host cores, ``cpu_baseline.one_thread`` the same on one.  ``e2e``
 is the same step from pinned host buffers: host f32 -> wire blobs on the host through the
 ``*_encode_batches_compact`` calls, wire bytes back to the device, decode-and-patch into the
 device-resident caches, error words read back (the pool's decode-and-patch is launched as soon as its
@@ -94,6 +97,25 @@ WORKLOADS = {
 # ---------------------------------------------------------------------------------------------
 # shared helpers
 # ---------------------------------------------------------------------------------------------
+def alu_roof(kind, d, n_vec, ms, sm_mhz, sms=148):
+    """The arithmetic ceiling beside the HBM one: separately rounded binary32 operations the reference's
+    contract fixes per vector on the f32 pipe (what runs on the tensor cores is left out), at one operation per
+    lane and clock (128 lanes per SM) -> {"f32_ops_per_vector", "roof_ms", "frac"} (frac = roof_ms / ms).
+      fib decode      2 d^2          the un-fused multiply and add of every matrix element (rotation.rs:136-149)
+      fib encode      11 * 32 * d/4  4 sub, 4 mul, 3 add per (block, codeword) (simd_nearest.rs:24-94); the rotation's
+                                     2 d^2 runs on the tensor cores, the norm chain in binary64
+      turbo encode    d log2 d + 7 d/2  forward butterflies, per pair 2 mul + add + sqrt + 3 for the residual; the
+                                     sketch's 2 m d runs on the tensor cores
+      turbo decode    d log2 d + 2 d    two products per pair from the table, butterflies, scale and sign"""
+    lg = int(math.log2(d))
+    ops = {"fib_decode_patch": 2 * d * d, "fib_encode": 11 * 32 * (d // 4),
+           "turbo_encode": d * lg + 7 * (d // 2), "turbo_decode_patch": d * lg + 2 * d}[kind]
+    mhz = sm_mhz or 1965.0
+    roof_ms = ops * n_vec / (sms * 128 * mhz * 1e6) * 1e3
+    return {"f32_ops_per_vector": ops, "roof_ms": roof_ms, "frac": roof_ms / ms if ms > 0 else None,
+            "at_sm_mhz": mhz}
+
+
 def fib_record_bytes(d):
     return 2 + (5 * (d // 4) + 7) // 8
 
@@ -573,6 +595,9 @@ def run_single(args, w):
         dom = names[0] if enc_ms >= dec_ms else names[1]
         k = m["kernels"][dom]
         clk = clocks.summary()
+        kinds = (f"{kind}_encode", f"{kind}_decode_patch")
+        for nm, kd in zip(names, kinds):
+            m["kernels"][nm]["alu"] = alu_roof(kd, d, n_vec, m["kernels"][nm]["ms"], clk.get("sm_mhz"))
         line = {
             "metric": METRIC, "value": total_f32 / (step_ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
@@ -598,7 +623,9 @@ def run_single(args, w):
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             gbs, _, sample = cpu_single_rate(w, 8.0, cores)
-            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+            gbs1, _, sample1 = cpu_single_rate(w, 3.0, 1)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                                    "one_thread": {"value": gbs1, "cores": 1, "sample": sample1}}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -866,6 +893,10 @@ def run_pool(args, w):
         dom_phase = max((ph for ph in PHASES if ph not in NOT_KERNELS), key=lambda ph: phase_ms[PHASES.index(ph)])
         dom = kernels[names[dom_phase]]
         clk = clocks.summary()
+        per_rank = {"fib_encode": n_p_enc * groups, "turbo_encode": n_s * groups,
+                    "fib_decode_patch": n_p_dec * groups, "turbo_decode_patch": n_s * groups}
+        for ph, nv_ph in per_rank.items():  # decode-and-patch: one decode per vector whatever the replica count
+            kernels[names[ph]]["alu"] = alu_roof(ph, d, nv_ph, kernels[names[ph]]["ms"], clk.get("sm_mhz"))
         gather_bytes = pay_pool.numel() * groups if gather else 0
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -904,8 +935,10 @@ def run_pool(args, w):
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             v, u, _, sample = cpu_pool_rate(w, 10.0, cores)
+            v1, u1, _, sample1 = cpu_pool_rate(w, 3.0, 1)
             line["cpu_baseline"] = {"value": v, "value_unique": u, "unit": "GB/s", "cores": cores, "kind": "port",
-                                    "sample": sample}
+                                    "sample": sample,
+                                    "one_thread": {"value": v1, "value_unique": u1, "cores": 1, "sample": sample1}}
         if world == 1 and not args.no_c2:
             caches = kv_prefix = kv_shells = None  # the closures above hold the names, not the tensors
             torch.cuda.empty_cache()
