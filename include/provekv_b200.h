@@ -64,6 +64,17 @@ enum {
 };
 
 const char* pkv_status_string(int status);
+/* Counters of the certify-or-flag tiers on the current device since the last reset (a shortcut's answer is
+ * used only where it is proven to be the reference's; these count what was not proven and went on):
+ *   counts8[0] fib blocks settled by an encoder's in-kernel exact tier
+ *   counts8[1] fib list entries (a block or a whole vector) redone by the exact f64 kernel
+ *   counts8[4] turbo pairs whose angle bucket was taken with the exact atan2f
+ *   counts8[5] turbo (vector, projection) signs retaken by the binary32 dot
+ *   counts8[6] turbo signs or list entries redone with the reference's own sequence
+ * the others are zero.  Both calls synchronise the device. */
+int pkv_stats_read(uint64_t* counts8);
+int pkv_stats_reset(void);
+
 int pkv_version(void);
 /* Text of the CUDA runtime error behind the calling thread's most recent PKV_ERR_CUDA ("" if none). */
 const char* pkv_last_cuda_error(void);

@@ -303,6 +303,8 @@ int pkv_launch_turbo_decode(const pkv_turbo_profile* p, const uint8_t* payload, 
 int pkv_launch_turbo_score(const pkv_turbo_profile* p, const uint8_t* payload, const PkvGeom& g,
                            const float* rotated, const float* projected, int64_t n_queries, float* scores,
                            uint64_t* err, cudaStream_t s);
+int pkv_fib_stats_copy(unsigned long long* out4, int reset);
+int pkv_turbo_stats_copy(unsigned long long* out4, int reset);
 int pkv_launch_turbo_prepare_queries(const pkv_turbo_profile* p, const float* queries, int64_t n_queries,
                                      float* rotated, float* projected, uint64_t* err, cudaStream_t s);
 int pkv_fib_tile_vectors(int dim, int encode);

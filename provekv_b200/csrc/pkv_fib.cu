@@ -19,6 +19,15 @@
 
 namespace {
 
+// Counters of the certify-or-flag tiers since the last reset (pkv_stats_read): [0] blocks settled by an
+// encoder's in-kernel exact tier, [1] list entries redone by fib_encode_fix_kernel with the reference's f64
+// sequence.  One atomic per warp and tile at most.
+__device__ unsigned long long g_fib_stats[4];
+__device__ __forceinline__ void fib_count_flagged(uint32_t flagged, int lane) {
+  const unsigned n = __reduce_add_sync(0xffffffffu, (unsigned)__popc(flagged));
+  if (lane == 0 && n) atomicAdd(&g_fib_stats[0], (unsigned long long)n);
+}
+
 constexpr int kThreads = 128;
 
 __device__ __forceinline__ uint32_t load_bits(const uint8_t* bytes, int pos, int width) {
@@ -717,4 +726,11 @@ extern "C" int pkv_fib_encode_dev_static(const pkv_fib_profile* p, const float* 
   }
   return pkv_launch_fib_encode_fast_with_scratch(p, x_dev, g, payload_dev, err_dev, scratch,
                                                  (cudaStream_t)stream);
+}
+
+int pkv_fib_stats_copy(unsigned long long* out, int reset) {
+  static const unsigned long long zeros[4] = {0, 0, 0, 0};
+  if (out && cudaMemcpyFromSymbol(out, g_fib_stats, sizeof(zeros)) != cudaSuccess) return PKV_ERR_CUDA;
+  if (reset && cudaMemcpyToSymbol(g_fib_stats, zeros, sizeof(zeros)) != cudaSuccess) return PKV_ERR_CUDA;
+  return PKV_OK;
 }

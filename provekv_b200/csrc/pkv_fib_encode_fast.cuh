@@ -258,6 +258,7 @@ fib_encode_fix_kernel(PkvGeom g, const float* __restrict__ x, const double* __re
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
   const float4* cb4 = reinterpret_cast<const float4*>(codebook);
   const uint32_t count = *flag_count;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && count) atomicAdd(&g_fib_stats[1], (unsigned long long)count);
 
   for (uint32_t base = (uint32_t)gw * 8u; base < count; base += (uint32_t)nw * 8u) {
     const int r = lane & 3;

@@ -307,6 +307,7 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
     if (skip) flagged = 0;
   }
 
+  fib_count_flagged(flagged, lane);
   // Second tier: the flagged blocks of one vector at a time, the whole warp on each, exactly
   // (fib_exact_block); the owner keeps the result.
   for (unsigned pending = __ballot_sync(0xffffffffu, flagged != 0); pending; pending &= pending - 1) {

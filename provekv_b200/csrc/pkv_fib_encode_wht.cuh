@@ -159,6 +159,7 @@ fib_encode_wht_kernel(PkvGeom g, const float* __restrict__ x, const __grid_const
   if (skip) flagged = 0;
   __syncwarp();  // the warp's rows of y are in the tile
 
+  fib_count_flagged(flagged, lane);
   // exact tier: the flagged blocks of one vector at a time, lane c on codeword c
   for (unsigned pending = __ballot_sync(0xffffffffu, flagged != 0); pending; pending &= pending - 1) {
     const int src = __ffs(pending) - 1;

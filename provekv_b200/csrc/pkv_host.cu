@@ -913,6 +913,25 @@ int pkv_turbo_prepare_queries_dev(const pkv_turbo_profile* p, const float* queri
                                           (cudaStream_t)stream);
 }
 
+int pkv_stats_read(uint64_t* counts8) {
+  if (!counts8) return PKV_ERR_INVALID_ARGUMENT;
+  unsigned long long f[4] = {0, 0, 0, 0}, t[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return PKV_ERR_CUDA;
+  if (int st = pkv_fib_stats_copy(f, 0)) return st;
+  if (int st = pkv_turbo_stats_copy(t, 0)) return st;
+  for (int i = 0; i < 4; i++) {
+    counts8[i] = f[i];
+    counts8[4 + i] = t[i];
+  }
+  return PKV_OK;
+}
+
+int pkv_stats_reset(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return PKV_ERR_CUDA;
+  if (int st = pkv_fib_stats_copy(nullptr, 1)) return st;
+  return pkv_turbo_stats_copy(nullptr, 1);
+}
+
 int pkv_tqb1_header_write(const pkv_turbo_profile* p, uint32_t n_vectors, uint8_t* out) {
   if (!p || !out) return PKV_ERR_INVALID_ARGUMENT;
   const uint16_t ver = 1, rot = 1;  // rotation flag 1 = FastHadamard, wire.rs:583-589

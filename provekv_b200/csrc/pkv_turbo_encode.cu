@@ -82,3 +82,9 @@ int pkv_launch_turbo_encode(const pkv_turbo_profile* p, const float* x, const Pk
   return pkv_cuda_status(cudaGetLastError());
 }
 
+int pkv_turbo_stats_copy(unsigned long long* out, int reset) {
+  static const unsigned long long zeros[4] = {0, 0, 0, 0};
+  if (out && cudaMemcpyFromSymbol(out, pkv_turbo::g_turbo_stats, sizeof(zeros)) != cudaSuccess) return PKV_ERR_CUDA;
+  if (reset && cudaMemcpyToSymbol(pkv_turbo::g_turbo_stats, zeros, sizeof(zeros)) != cudaSuccess) return PKV_ERR_CUDA;
+  return PKV_OK;
+}

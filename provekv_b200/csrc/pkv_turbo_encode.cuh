@@ -22,6 +22,11 @@
 
 namespace pkv_turbo {
 
+// Counters of the certify-or-flag tiers since the last reset (pkv_stats_read): [0] pairs whose angle bucket
+// went to the exact atan2f tier, [1] (vector, row) signs retaken by the binary32 dot, [2] list entries settled
+// by turbo_encode_fix_kernel with the reference's own sequence.  One atomic per warp and tile at most.
+static __device__ unsigned long long g_turbo_stats[4];
+
 // Entries of the per-warp list of (vector, row) pairs awaiting the second tier (at most 64: the
 // list and the 32 residual norms share the 256 bytes that held the vector offsets).
 #ifndef PKV_QJL_LIST_CAP
@@ -267,6 +272,7 @@ turbo_encode_fix_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x, 
   float* s_lut = s_g + m * (D + 1);              // (cos, sin)[levels]
   float* s_scr = s_lut + 2 * (1 << tp.polar_bits);  // [4][D]
   const uint32_t n = *count;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && n) atomicAdd(&g_turbo_stats[2], (unsigned long long)n);
   if ((uint32_t)blockIdx.x * 4u >= n) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int levels = 1 << tp.polar_bits;
@@ -497,6 +503,10 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
     if constexpr (ROT) force = rmax >= 0x7149f2cau;  // radii beyond 1e30: the residual might overflow
   }
   if (!valid) unc = 0;
+  {
+    const unsigned n_unc = __reduce_add_sync(0xffffffffu, (unsigned)__popcll(unc));
+    if (lane == 0 && n_unc) atomicAdd(&g_turbo_stats[0], (unsigned long long)n_unc);
+  }
   for (unsigned pending = __ballot_sync(0xffffffffu, unc != 0); pending; pending &= pending - 1) {
     const int src = __ffs(pending) - 1;  // settle lane src's undecided pairs, all lanes helping
     const unsigned long long um =
@@ -652,6 +662,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         }
         const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
         if (total) {
+          if (lane == 0) atomicAdd(&g_turbo_stats[1], (unsigned long long)total);
           constexpr uint32_t CAP = PKV_QJL_LIST_CAP;
           s_bound[v] = tau2;
           uint32_t pos = incl - cnt;
@@ -813,6 +824,7 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
         }
         const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
         if (total) {
+          if (lane == 0) atomicAdd(&g_turbo_stats[1], (unsigned long long)total);
           constexpr uint32_t CAP = PKV_QJL_LIST_CAP;
           float* s_rn = reinterpret_cast<float*>(s_off);                   // [32] (the offsets are spent)
           uint16_t* list = reinterpret_cast<uint16_t*>(s_rn + K::TV);      // [CAP]
@@ -827,7 +839,10 @@ turbo_encode_kernel(PkvGeom g, TurboParams tp, const float* __restrict__ x,
             const int r = warp * K::TV + (int)(it >> 5), p = c + (int)(it & 31u);
             float dot = fused_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
             const float tau = fmaf(s_thr[p], s_rn[it >> 5], PKV_QJL_ABS_BOUND);
-            if (!(fabsf(dot) > tau)) dot = sequential_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
+            if (!(fabsf(dot) > tau)) {  // third tier, in the kernel for this variant: counted with the list entries
+              dot = sequential_dot(s_gt, g_slab, p, s_xt, K::X_SLAB, r, D);
+              atomicAdd(&g_turbo_stats[2], 1ull);
+            }
             list[e] = (uint16_t)(it | (dot >= 0.0f ? 0x8000u : 0u));
           }
           __syncwarp();

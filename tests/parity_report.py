@@ -6,6 +6,7 @@ oracle, decode-and-patch on the GPU and compare the f32 output with the oracle's
 
 Inputs are seeded synthetic tensors with the shapes and value distributions of the configurations
 (no model captures or datasets are involved)."""
+import ctypes as C
 import os
 import sys
 import time
@@ -42,7 +43,10 @@ def kv_tensor(torch, A, shape, T, seed, outliers=False):
 
 def run(torch, name, note, shape, A, T, codec, **kw):
     d = shape.head_dim
-    if codec == "fib":
+    if codec == "fib" and kw.get("hadamard"):
+        prof = pk.FibProfile(d, None, tables.fib_codebook(d, seed=SEED), numerics=L.FIB_NUMERICS_BATCH,
+                             hadamard_seed=SEED)
+    elif codec == "fib":
         prof = pk.FibProfile(d, tables.haar_rotation(d, SEED), tables.fib_codebook(d, seed=SEED))
     else:
         prof = pk.TurboProfile.from_seed(d, kw.get("bits", 4), 32 if kw.get("mode", 1) else 0, SEED,
@@ -57,12 +61,22 @@ def run(torch, name, note, shape, A, T, codec, **kw):
     payload = torch.zeros((nb, stride), dtype=torch.uint8, device="cuda")
     err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
     lay = pool.kv_tensor_layout(shape, A, T)
+    L.check(L.lib().pkv_stats_reset())
     prof.encode_dev(kv.data_ptr(), lay, payload.data_ptr(), stride, err.data_ptr())
     pk.read_error_word(err.data_ptr())
+    stats = (C.c_uint64 * 8)()
+    L.check(L.lib().pkv_stats_read(stats))
+    if codec == "fib":   # blocks settled by the in-kernel exact tier / list entries redone by the exact kernel
+        tiers = f"{stats[0]:,} blocks in-kernel, {stats[1]:,} entries to the f64 kernel (of {n * d // 4:,} blocks)"
+    else:                # exact atan2f pairs / binary32 re-dots / list entries redone with the reference's sequence
+        tiers = (f"{stats[4]:,} pairs exact atan2f (of {n * d // 2:,}), {stats[5]:,} signs re-dotted, "
+                 f"{stats[6]:,} entries to the exact kernel (of {n * (32 if kw.get('mode', 1) else 0):,} signs)")
     got = payload[:, :vpb * rec].cpu().numpy().reshape(n, rec)
     gathered = kv.permute(0, 1, 2, 4, 3, 5).reshape(n, d).cpu().numpy()
     t0 = time.perf_counter()
-    if codec == "fib":
+    if codec == "fib" and kw.get("hadamard"):
+        st, want, _, _ = oracle_mod.fib_encode_hadamard(gathered, SEED, prof.codebook, nthreads=NTHREADS)
+    elif codec == "fib":
         st, want, _, _ = oracle_mod.fib_encode(gathered, prof.rotation, prof.codebook, nthreads=NTHREADS)
     else:
         st, want, _, _ = oracle_mod.turbo_encode(gathered, prof.signs, prof.qjl, bits=kw.get("bits", 4),
@@ -99,7 +113,7 @@ def run(torch, name, note, shape, A, T, codec, **kw):
     bad_words = int((dec.view(np.uint32) != ref.view(np.uint32)).sum())
     rel = float(((out - kv) ** 2).sum() / (kv ** 2).sum())
     print(f"| {name} | {note} | {n:,} | {got.size:,} | {bad_bytes} | {plat_bytes} | {dec.size:,} | {bad_words} | "
-          f"{diff.max():.1e} | {rel:.3f} | {t_cpu:.1f} s |", flush=True)
+          f"{diff.max():.1e} | {rel:.3f} | {tiers} | {t_cpu:.1f} s |", flush=True)
     del kv, out, payload
     torch.cuda.empty_cache()
     return bad_bytes + bad_words
@@ -110,10 +124,12 @@ def main():
     S, Q, M = pool.SMOLLM2_1_7B, pool.QWEN25_0_5B, pool.LLAMA3_8B
     print("| config | what | vectors | record bytes compared | mismatching bytes | bytes differing from the host-libm "
           "oracle | decoded f32 compared | mismatching words | max abs diff | reconstruction MSE / signal | "
-          "oracle encode time |")
-    print("|---|---|---|---|---|---|---|---|---|---|---|")
+          "flagged by the shortcuts and recomputed | oracle encode time |")
+    print("|---|---|---|---|---|---|---|---|---|---|---|---|")
     bad = 0
     bad += run(torch, "C1", "fib k4_n32, 24x2x32x1024x64, full size", S, 1, 1024, "fib")
+    bad += run(torch, "C1", "the same vectors through the Walsh-Hadamard rotation of the reference's gpu build "
+               "(not wire-compatible with the row above)", S, 1, 1024, "fib", hadamard=True)
     bad += run(torch, "C2", "turbo b=4 (polar 3 + QJL 32), f32 radii, 8 agents x 28 tokens, full size", S, 8, 28, "turbo")
     bad += run(torch, "C2", "same, BlockLogU8 radii, host-libm profile against the host-libm oracle", S, 8, 28, "turbo", lossy=True)
     bad += run(torch, "C2", "turbo polar-only 4-bit angles, f32 radii", S, 8, 28, "turbo", mode=0)

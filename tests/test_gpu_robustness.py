@@ -281,3 +281,29 @@ def test_refused_vectors_leave_zero_records_and_the_rest_intact(oracle_mod, dim,
     keep[list(bad)] = False
     assert np.array_equal(got[keep], want[keep])
     assert not got[~keep].any()
+
+
+@pytest.mark.gpu
+def test_tier_counters_count_what_the_shortcuts_did_not_settle():
+    """pkv_stats_read: after a reset and one encode of each codec the counters hold a small, non-zero share
+    of the work (the shortcuts settle almost everything), and a reset clears them."""
+    import numpy as np
+    lib = L.lib()
+    dim, n = 64, 40_000
+    x = synthetic_kv(n, dim, seed=21)
+    fib = pk.FibProfile(dim, tables.haar_rotation(dim, 1), tables.fib_codebook(dim, seed=1))
+    tq = pk.TurboProfile(dim, 4, tables.rademacher_signs(dim, 1), tables.qjl_matrix(dim, 32, 1), seed=1)
+    counts = (C.c_uint64 * 8)()
+    L.check(lib.pkv_stats_reset())
+    L.check(lib.pkv_stats_read(counts))
+    assert list(counts) == [0] * 8
+    fib.encode_batch_compact(x)
+    L.check(lib.pkv_stats_read(counts))
+    blocks = n * dim // 4
+    assert 0 < counts[0] < 0.01 * blocks and counts[1] < 1e-3 * blocks and list(counts)[4:] == [0] * 4
+    tq.encode_batch_compact(x)
+    L.check(lib.pkv_stats_read(counts))
+    assert 0 < counts[4] < 0.01 * n * 32 and 0 < counts[5] < 0.05 * n * 32 and 0 < counts[6] < 0.01 * n * 32
+    L.check(lib.pkv_stats_reset())
+    L.check(lib.pkv_stats_read(counts))
+    assert list(counts) == [0] * 8
