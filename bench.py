@@ -82,6 +82,10 @@ WORKLOADS = {
                              n_shared=0, codec="fib", hadamard=True,
                              desc="C5 scaled fib prefix with the Walsh-Hadamard rotation on encode: "
                                   "32x{K,V}x8 heads x 2048 tokens x 128"),
+    "ops": dict(kind="ops", dim=64, codec="fib",
+                desc="the gpu-backend operators on the fib encode path, stand-alone: hadamard_batch in place on "
+                     "24x{K,V}x32x1024 vectors of 64 (C1's tensor), on 1,048,576 x 128 and on 131,072 x 1024; "
+                     "codebook_lookup_batch (k=4, N=32) on C1's tensor"),
     "c5s_fib": dict(kind="single", agents=1, layers=32, heads=8, tokens=2048, dim=128, cache_tokens=2048,
                     n_shared=0, codec="fib",
                     desc="C5 scaled, fib k4_n32 prefix: 32x{K,V}x8 heads x 2048 tokens x 128"),
@@ -539,6 +543,78 @@ def measure_single(torch, w, steps, warmup, dev, seed, cache_dtype="f32"):
     }
 
 
+def run_ops(args, w):
+    """Device time of pkv_hadamard_batch_dev and pkv_codebook_lookup_batch_dev (CUDA events, inputs larger than
+    L2, resident in HBM), each checked against the oracle on a sample first -> one JSON line."""
+    import torch
+
+    import oracle
+    from provekv_b200 import _lib as L
+    from provekv_b200 import tables
+    dev = torch.device("cuda", 0)
+    L.check(L.lib().pkv_set_device(0))
+    lib = L.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    peak, peak_kind = measured_hbm_peak()
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    clocks = ClockSampler(0)
+    clocks.__enter__()
+    kernels = {}
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+        for e in ev:
+            e[0].record()
+            fn()
+            e[1].record()
+        torch.cuda.synchronize()
+        return float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+
+    launches0 = lib.pkv_launch_count()
+    for n, d in ((24 * 2 * 32 * 1024, 64), (1 << 20, 128), (1 << 17, 1024)):
+        x = torch.randn((n, d), generator=gen, device=dev)
+        chk = x[:4096].clone()
+        L.check(lib.pkv_hadamard_batch_dev(chk.data_ptr(), 4096, d, SEED, stream))
+        assert np.array_equal(chk.cpu().numpy().view(np.uint32),
+                              oracle.hadamard_batch(x[:4096].cpu().numpy(), SEED).view(np.uint32)), d
+        ms = timed(lambda: L.check(lib.pkv_hadamard_batch_dev(x.data_ptr(), n, d, SEED, stream)))
+        nbytes = 8 * n * d  # every element read once and written once
+        kname = f"hadamard_batch_narrow_kernel<{d // 4}>" if d <= 64 else f"hadamard_batch_kernel<{d // 32}>"
+        kernels[f"{kname} ({n} x {d})"] = {
+            "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+            "frac_of_measured_hbm": nbytes / ms / 1e6 / peak}
+        del x
+    n, d = 24 * 2 * 32 * 1024, 64
+    x = torch.randn((n, d), generator=gen, device=dev) * 0.125
+    cb_h = tables.fib_codebook(d, seed=SEED)
+    cb = torch.from_numpy(cb_h).to(dev)
+    idx = torch.empty((n, d // 4), dtype=torch.int32, device=dev)
+    ms = timed(lambda: L.check(lib.pkv_codebook_lookup_batch_dev(x.data_ptr(), cb.data_ptr(), n, d, 4, 32,
+                                                                 idx.data_ptr(), stream)))
+    assert np.array_equal(idx[:4096].cpu().numpy().view(np.uint32), oracle.codebook_lookup(x[:4096].cpu().numpy(), cb_h))
+    nbytes = (4 * d + d) * n  # f32 in, one u32 per 4-block out
+    kernels[f"codebook_lookup_kernel ({n} x {d}, k=4, N=32)"] = {
+        "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+        "frac_of_measured_hbm": nbytes / ms / 1e6 / peak,
+        "alu": alu_roof("fib_encode", d, n, ms, None)}
+    clocks.__exit__()
+    clk = clocks.summary()
+    name, k = next(iter(kernels.items()))
+    print(json.dumps({
+        "metric": METRIC, "value": k["achieved_gbs"] / 2, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": k["ms"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["desc"], "step": "one launch of each operator", "l2": "inputs larger than L2"},
+        "kernels": kernels,
+        "roofline": {"bound": "hbm", "kernel": name, "achieved": k["achieved_gbs"], "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": k["frac_of_measured_hbm"],
+                     "algorithmic_bytes_per_launch": k["algorithmic_bytes"], "traffic": None},
+        "gpu_launches": int(lib.pkv_launch_count() - launches0), "clocks": clk}))
+
+
 def run_single(args, w):
     import torch
     import torch.distributed as dist
@@ -972,6 +1048,8 @@ def main():
         run_reference(args, w)
     elif w["kind"] == "pool":
         run_pool(args, w)
+    elif w["kind"] == "ops":
+        run_ops(args, w)
     else:
         run_single(args, w)
 

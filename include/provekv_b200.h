@@ -197,6 +197,22 @@ int pkv_payload_download(const uint8_t* payload_dev, int64_t payload_batch_strid
 int pkv_error_word_reset(uint64_t* err_dev, void* stream);
 int pkv_error_word_read(const uint64_t* err_dev, void* stream, int32_t* code, int64_t* vector_index);
 
+/* ---- the gpu-backend crate's operators on the fib encode path ------------ */
+/* gpu_backend::hadamard_batch (gpu-backend/src/lib.rs:66-90): data_dev holds n vectors of dim f32, transformed
+ * in place with the arithmetic of hadamard_batch_cpu (gpu-backend/src/fallback.rs:12-62): zero-padded to the
+ * next power of two, butterflies (a, b) -> (a + b, a - b) for step = 1, 2, 4, .., x sign_i (64-bit LCG from
+ * `seed`, :76-88), x 1/sqrt(padded dim), truncated back to dim; bit for bit.  Padded dims up to 1024
+ * (PKV_ERR_UNSUPPORTED beyond).  Bound by HBM: every element is read once and written once. */
+int pkv_hadamard_batch_dev(float* data_dev, int64_t n, int32_t dim, uint64_t seed, void* stream);
+/* gpu_backend::codebook_lookup_batch (gpu-backend/src/lib.rs:196-239) with the arithmetic of
+ * codebook_lookup_cpu (fallback.rs:254-305): input_dev n x dim f32, codebook_dev n_codewords x k f32,
+ * indices_dev n * (dim / k) u32 in (vector, block) order; per block the squared distances summed in
+ * coordinate order, strict less-than scan from index 0 (ties and non-finite distances as the scan leaves
+ * them).  k = 4 and n_codewords <= 32 (PKV_ERR_UNSUPPORTED otherwise; the crate's own GPU path has the
+ * same limits); all three pointers 16-byte aligned. */
+int pkv_codebook_lookup_batch_dev(const float* input_dev, const float* codebook_dev, int64_t n, int32_t dim,
+                                  int32_t k, int32_t n_codewords, uint32_t* indices_dev, void* stream);
+
 /* ---- fib-quant --------------------------------------------------------- */
 /* rotation: dim x dim f64 row-major (StoredRotation.matrix, fib-quant/src/rotation.rs:51-56);
  * codebook: codebook_size x block_dim f32 row-major (fib-quant/src/codebook.rs:28-29).

@@ -112,6 +112,20 @@ def hadamard_batch(data, seed):
     return out
 
 
+def codebook_lookup(x, codebook):
+    """gpu_backend::codebook_lookup_cpu (fallback.rs:254-305) -> u32 indices [n, dim / k]."""
+    x = _f32(x)
+    cb = _f32(codebook)
+    n, d = x.shape
+    k = cb.shape[1]
+    out = np.zeros((n, d // k), np.uint32)
+    st = lib().pkvo_codebook_lookup(_p(x, C.c_float), _p(cb, C.c_float), C.c_int64(n), d, k, cb.shape[0],
+                                    _p(out, C.c_uint32))
+    if st:
+        raise ValueError(f"pkvo_codebook_lookup: status {st}")
+    return out
+
+
 def hadamard_signs(padded_dim, seed):
     out = np.zeros(padded_dim, np.float32)
     lib().pkvo_hadamard_signs(padded_dim, C.c_uint64(seed), _p(out, C.c_float))

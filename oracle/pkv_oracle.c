@@ -248,6 +248,33 @@ PKVO_API int pkvo_hadamard_batch(float* data, int64_t n, int dim, uint64_t seed)
   return 0;
 }
 
+/* codebook_lookup_cpu (gpu-backend/src/fallback.rs:254-305): per k-block the squared distances summed in
+ * coordinate order from 0.0, strict less-than scan from index 0 against +inf. */
+PKVO_API int pkvo_codebook_lookup(const float* input, const float* codebook, int64_t n, int dim, int k,
+                                  int n_codewords, uint32_t* out) {
+  if (dim <= 0 || k <= 0 || dim % k || n_codewords < 1) return PKV_ERR_INVALID_ARGUMENT;
+  const int blocks = dim / k;
+  for (int64_t v = 0; v < n; v++)
+    for (int b = 0; b < blocks; b++) {
+      const float* s = input + v * dim + (int64_t)b * k;
+      uint32_t best_idx = 0;
+      float best_dist = INFINITY;
+      for (int c = 0; c < n_codewords; c++) {
+        float dist = 0.0f;
+        for (int j = 0; j < k; j++) {
+          const float delta = s[j] - codebook[c * k + j];
+          dist += delta * delta;
+        }
+        if (dist < best_dist) {
+          best_dist = dist;
+          best_idx = (uint32_t)c;
+        }
+      }
+      out[v * blocks + b] = best_idx;
+    }
+  return 0;
+}
+
 typedef struct {
   const float* x;
   int64_t n;
@@ -1372,7 +1399,8 @@ PKVO_API void pkvo_fib_fast_check(const float* x, int64_t n, int dim, const doub
         pkv_fib_top2(&best, &second,
                      pkv_fib_key(yf[0], yf[1], yf[2], yf[3], codebook[4 * c], codebook[4 * c + 1],
                                  codebook[4 * c + 2], codebook[4 * c + 3], hn[c], (uint32_t)c));
-      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_D(dim));
+      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_D(dim),
+                                    pkv_fib_score_abs(codebook, n_codewords));
       const uint32_t fast = pkv_f32_bits(best) & 31u;
       if (!certain) {
         counts[1]++;
@@ -1550,7 +1578,8 @@ PKVO_API void pkvo_fib_tc_check(const float* x, int64_t n, int dim, const double
         pkv_fib_top2(&best, &second,
                      pkv_fib_key(yf[0], yf[1], yf[2], yf[3], codebook[4 * c], codebook[4 * c + 1],
                                  codebook[4 * c + 2], codebook[4 * c + 3], hn[c], (uint32_t)c));
-      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_TC_D(dim));
+      certain = pkv_fib_certify_eta(best, second, yf[0], yf[1], yf[2], yf[3], PKV_FIB_ROT_ERR_TC_D(dim),
+                                    pkv_fib_score_abs(codebook, n_codewords));
       const uint32_t fast = pkv_f32_bits(best) & 31u;
       if (!certain) {
         counts[1]++;

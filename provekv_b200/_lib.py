@@ -129,6 +129,8 @@ _SIGS = {
     "pkv_stats_reset": (C.c_int, []),
     "pkv_error_word_reset": (C.c_int, [_V, _V]),
     "pkv_error_word_read": (C.c_int, [_V, _V, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
+    "pkv_hadamard_batch_dev": (C.c_int, [_V, C.c_int64, C.c_int32, C.c_uint64, _V]),
+    "pkv_codebook_lookup_batch_dev": (C.c_int, [_V, _V, C.c_int64, C.c_int32, C.c_int32, C.c_int32, _V, _V]),
     "pkv_fib_profile_create": (C.c_int, [C.POINTER(FibConfigC), _V, _V, C.POINTER(_V)]),
     "pkv_fib_profile_create_hadamard": (C.c_int, [C.POINTER(FibConfigC), C.c_uint64, _V, _V, C.POINTER(_V)]),
     "pkv_fib_profile_destroy": (C.c_int, [_V]),

@@ -232,6 +232,7 @@ struct pkv_fib_profile {
   float* half_norm_dev; // |c|^2 / 2 per codeword
   float* rot_hi_dev;    // [r][j] (f32) M[r][j] with the 13 low significand bits cleared (TF32 operand)
   float* rot_lo_dev;    // [r][j] (f32) M[r][j] - rot_hi, exact
+  float score_abs;            // rounding of the fused scores of the dense encoders' search (pkv_fast_paths.h (3))
   uint32_t search_quick_gap;  // for a rotation error of 0 (the Hadamard encoder)
   float search_off, search_ef;  // bias of the Hadamard encoder score search and its error bound (pkv_fib_search.cuh)
   int hadamard;         // 1: encode_batch rotates by the f32 Walsh-Hadamard transform (pkv_fib_profile_create_hadamard)

@@ -202,9 +202,13 @@ PKV_HD float pkv_fib_norm_quotient(float x, float invh, float invl, uint32_t* un
  * the score, so best and second-best come from three min/max operations per codeword.  With
  * |s~ - s|_2 <= 2 PKV_FIB_ROT_ERR the reference's rounded distances satisfy
  *   | d_c - (2 F_c + |s~|^2) | <= 4 eta sqrt(D_c) + 4 eta^2 + 4 u D_c + e_F,   eta = PKV_FIB_ROT_ERR,
- * with D_c = |s~ - c|^2 and e_F <= 2^-16 |F_c| (index bits and FMA rounding).  If the gap between
- * best and second best exceeds the two bounds, the reference's strict-less-than scan
- * (gpu-backend/src/simd_nearest.rs:72-79) selects the same codeword in either summation order. */
+ * with D_c = |s~ - c|^2 and e_F <= 2^-17 |F_c| (the index bits) + 4 u A_c (the four fused roundings, each
+ * at most u times a partial sum no larger than A_c = |c|^2 / 2 + |s~| |c|; when |c|^2 is close to 2 s.c the
+ * score itself is small and a bound relative to |F_c| alone would not cover them).  The encoders pass
+ * score_abs = 4 u (max |c|^2 / 2 + 1.001 max |c|) for blocks of normalised vectors (pkv_fib_score_abs);
+ * the stand-alone lookup forms it from the block's own norm.  If the gap between best and second best
+ * exceeds the two bounds, the reference's strict-less-than scan (gpu-backend/src/simd_nearest.rs:72-79)
+ * selects the same codeword in either summation order. */
 /* Score of codeword c (c0..c3, half squared norm hn) for the block s, index in the low bits. */
 PKV_HD float pkv_fib_key(float s0, float s1, float s2, float s3, float c0, float c1, float c2,
                          float c3, float hn, uint32_t c) {
@@ -265,7 +269,8 @@ PKV_HD void pkv_fib_top2_pair(float* best, float* second, float a, float b) {
 
 /* Is the best key's codeword provably the reference's choice when the rotated block is known to
  * eta per coordinate?  (bound in the comment above with eta for PKV_FIB_ROT_ERR) */
-PKV_HD int pkv_fib_certify_eta(float best, float second, float s0, float s1, float s2, float s3, float eta) {
+PKV_HD int pkv_fib_certify_eta(float best, float second, float s0, float s1, float s2, float s3, float eta,
+                               float score_abs) {
   const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
                             PKV_FADD(PKV_FMUL(s2, s2), PKV_FMUL(s3, s3)));
   const float d1 = PKV_FADD(PKV_FMUL(2.0f, best), ss), d2 = PKV_FADD(PKV_FMUL(2.0f, second), ss);
@@ -273,15 +278,16 @@ PKV_HD int pkv_fib_certify_eta(float best, float second, float s0, float s1, flo
   const float fb = pkv_f32_from_bits(pkv_f32_bits(best) & 0x7fffffffu);
   const float fs = pkv_f32_from_bits(pkv_f32_bits(second) & 0x7fffffffu);
   const float roots = PKV_FADD(PKV_FSQRT_UP(d1p), PKV_FSQRT_UP(d2p));
+  /* two scores, each doubled in its distance: 4 score_abs */
   const float bound = PKV_FADD(
-      PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
+      PKV_FADD(PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta), PKV_FMUL(4.0f, score_abs)),
       PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(1.0e-5f, PKV_FADD(fb, fs))));
   return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
 }
 
 /* The same test for scores kept with an absolute error of at most e_f each (the biased scores of
- * pkv_fib_search.cuh): the relative term for the index bits and the fused roundings gives way to
- * 2 e_f per distance. */
+ * pkv_fib_search.cuh): the terms for the index bits and the fused roundings give way to 2 e_f per
+ * distance. */
 PKV_HD int pkv_fib_certify_abs(float f1, float f2, float s0, float s1, float s2, float s3, float eta, float e_f) {
   const float ss = PKV_FADD(PKV_FADD(PKV_FMUL(s0, s0), PKV_FMUL(s1, s1)),
                             PKV_FADD(PKV_FMUL(s2, s2), PKV_FMUL(s3, s3)));
@@ -291,6 +297,19 @@ PKV_HD int pkv_fib_certify_abs(float f1, float f2, float s0, float s1, float s2,
   const float bound = PKV_FADD(PKV_FADD(PKV_FMUL(4.0f * eta, roots), 8.0f * eta * eta),
                                PKV_FADD(PKV_FMUL(2.5e-7f, PKV_FADD(d1p, d2p)), PKV_FMUL(4.2f, e_f)));
   return PKV_FSUB(d2, d1) > PKV_FMUL(1.05f, bound);
+}
+
+/* score_abs of the encoders: blocks of a normalised vector have |s| <= 1.001 (rounding of the normalisation,
+ * bounded error of an approximate rotation). */
+static inline float pkv_fib_score_abs(const float* codebook, int n_codewords) {
+  double hmax = 0.0, cmax = 0.0;
+  for (int c = 0; c < n_codewords; c++) {
+    double s = 0.0;
+    for (int j = 0; j < 4; j++) s += (double)codebook[4 * c + j] * (double)codebook[4 * c + j];
+    if (0.5 * s > hmax) hmax = 0.5 * s;
+    if (__builtin_sqrt(s) > cmax) cmax = __builtin_sqrt(s);
+  }
+  return (float)(4.0 * 5.9604645e-8 * 1.01 * (hmax + 1.001 * cmax));
 }
 
 /* (3b) The same search on biased scores (csrc/pkv_fib_search.cuh gives the layout of the keys).
@@ -336,11 +355,6 @@ PKV_HD uint32_t pkv_fib_biased_key(float s0, float s1, float s2, float s3, float
 /* The score a key was made from (exact: the biased score and off lie in the same binade). */
 PKV_HD float pkv_fib_key_score(uint32_t key, float off) {
   return PKV_FSUB(pkv_f32_from_bits((pkv_f32_bits(off) & 0xf8000000u) | (key >> 5)), off);
-}
-
-/* The same with the bound of the binary32 fused rotation for D = 64. */
-PKV_HD int pkv_fib_certify(float best, float second, float s0, float s1, float s2, float s3) {
-  return pkv_fib_certify_eta(best, second, s0, s1, s2, s3, PKV_FIB_ROT_ERR);
 }
 
 #endif /* PKV_FAST_PATHS_H */

@@ -32,7 +32,7 @@ template <int D>
 __global__ void __launch_bounds__(FibFast<D>::THREADS, D == 128 ? 2 : 3)
 fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot32_t,
                        const float* __restrict__ codebook, const float* __restrict__ half_norm,
-                       int n_codewords, int idx_bits, int norm_len, uint8_t* __restrict__ payload,
+                       int n_codewords, int idx_bits, int norm_len, float score_abs, uint8_t* __restrict__ payload,
                        uint64_t* err, uint32_t* flag_count, uint32_t* flag_list) {
   using K = FibFast<D>;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -183,7 +183,7 @@ fib_encode_fast_kernel(PkvGeom g, const float* __restrict__ x, const float* __re
         const int v = VPT * vg + i, b = h * (K::B / 2) + rg;
         s_idx[v * K::B + b] = (uint8_t)(__float_as_uint(best[2 * i + h]) & 31u);
         if (!pkv_fib_certify_eta(best[2 * i + h], second[2 * i + h], acc[i][4 * h], acc[i][4 * h + 1],
-                                 acc[i][4 * h + 2], acc[i][4 * h + 3], PKV_FIB_ROT_ERR_D(D)))
+                                 acc[i][4 * h + 2], acc[i][4 * h + 3], PKV_FIB_ROT_ERR_D(D), score_abs))
           atomicOr(&s_flag[v], 1u << b);
       }
   }

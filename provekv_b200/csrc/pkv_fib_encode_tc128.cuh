@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(FibTc128::THREADS, 1)
 fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __restrict__ rot_hi,
                         const float* __restrict__ rot_lo, const float* __restrict__ codebook,
                         const float* __restrict__ half_norm, int n_codewords, const double* __restrict__ rot,
-                        int argmin_order, uint8_t* __restrict__ payload, uint64_t* err, uint32_t* flag_count,
+                        int argmin_order, float score_abs, uint8_t* __restrict__ payload, uint64_t* err, uint32_t* flag_count,
                         uint32_t* flag_list, int skip_issue) {
   using K = FibTc128;
   using pkv_tc::sw_piece;
@@ -260,7 +260,7 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
     for (int b = 0; b < K::HB; b++) {
       idx4[b >> 2] |= (__float_as_uint(best[b]) & 31u) << (8 * (b & 3));
       if (!pkv_fib_certify_eta(best[b], second[b], y[4 * b], y[4 * b + 1], y[4 * b + 2], y[4 * b + 3],
-                               PKV_FIB_ROT_ERR_TC128))
+                               PKV_FIB_ROT_ERR_TC128, score_abs))
         flagged |= 1u << b;
     }
     if (skip) flagged = 0;

@@ -380,6 +380,7 @@ int pkv_fib_profile_create(const pkv_fib_config* cfg, const double* rotation, co
     for (int j = 0; j < 4; j++) s += (double)cb[4 * c + j] * (double)cb[4 * c + j];
     hn[c] = (float)(0.5 * s);
   }
+  p->score_abs = pkv_fib_score_abs(cb, cfg->codebook_size);
   // Bias of the Hadamard encoder's score search (pkv_fast_paths.h (3b)); 2e30 marks a codebook that no
   // binade can hold (pkv_fib_profile_create_hadamard refuses it)
   p->search_off = 2.0e30f;
