@@ -546,6 +546,8 @@ def measure_single(torch, w, steps, warmup, dev, seed, cache_dtype="f32"):
 def run_ops(args, w):
     """Device time of pkv_hadamard_batch_dev and pkv_codebook_lookup_batch_dev (CUDA events, inputs larger than
     L2, resident in HBM), each checked against the oracle on a sample first -> one JSON line."""
+    if int(os.environ.get("RANK", "0")) != 0:  # a one-GPU measurement: the other ranks of a torchrun launch leave
+        return
     import torch
 
     import oracle

@@ -141,7 +141,8 @@ fib_encode_wht_kernel(PkvGeom g, const float* __restrict__ x, const __grid_const
   for (int h = 0; h < K::B / K::HB; h++) {
     uint32_t best[K::HB], second[K::HB];
     if (h == 0) fib_search_keys<K::B, 0, K::HB>(yp, s_tab, n_codewords, bias.mult, best, second);
-    else fib_search_keys<K::B, (K::B > K::HB ? K::HB : 0), K::HB>(yp, s_tab, n_codewords, bias.mult, best, second);
+    if constexpr (K::B > K::HB)  // d = 128: the second half of the blocks
+      if (h == 1) fib_search_keys<K::B, K::HB, K::HB>(yp, s_tab, n_codewords, bias.mult, best, second);
 #pragma unroll
     for (int b = 0; b < K::HB; b++) {
       const int gb = K::HB * h + b;
