@@ -673,12 +673,17 @@ def encode_kv_tensor(shape: KvTensorShapeV1, layout: KvCacheLayoutV1, profile: K
         # the reference's two refusals (input is finite here): a vector of zeros has norm zero, anything else
         # the encoder refuses has a norm its wire format cannot hold (codec.rs:603, :1003-1017)
         zero = refused & ~x.any(axis=1)
-        for text, mask in (("zero norm vector is not valid on the normal FibQuant encode path", zero),
-                           ("corrupt payload: norm cannot be represented as finite positive "
-                            + ("fp16" if norm_len == 2 else "f32"), refused & ~zero)):
+        texts = ("zero norm vector is not valid on the normal FibQuant encode path",
+                 "corrupt payload: norm cannot be represented as finite positive "
+                 + ("fp16" if norm_len == 2 else "f32"))
+        if refused.any() and not keep_raw:
+            # fail-closed: the reference stops at the first refused vector of its page -> batch -> layer -> head
+            # -> token walk (codec.rs:72-101); a flat index is ((batch, layer, head), token)
+            idx = np.flatnonzero(refused)
+            first = idx[np.lexsort((idx, (idx % T) // geo.tokens_per_page))[0]]
+            raise KvError(texts[0] if zero[first] else texts[1])
+        for text, mask in ((texts[0], zero), (texts[1], refused & ~zero)):
             if mask.any():
-                if not keep_raw:
-                    raise KvError(text)
                 reason[mask] = "encode_fallback:" + text
                 raw |= mask
 

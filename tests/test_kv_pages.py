@@ -209,8 +209,17 @@ def test_pages_encoded_and_decoded_on_the_gpu(oracle_mod, dim):
     strict = K.KvCompressionProfileV1.from_parts("kv-strict", s, fp, "blake3:codebook", prof.rotation_digest,
                                                  "per_token", K.KvPageGeometryV1(4, dim, rec))
     strict.fallback_mode = "fail_closed"
-    with pytest.raises(K.KvError, match="zero norm"):
+    # the reference's walk (page, batch, layer, head, token) meets the out-of-range norm of (0, 1, 1, 4) before the
+    # zero vector of (1, 2, 0, 5): both lie in page 1
+    with pytest.raises(K.KvError, match="norm cannot be represented"):
         K.encode_kv_tensor(s, lay, strict, x, rot, cb)
+    x2 = x.copy()
+    x2[0, 1, 1, 4] = x[0, 1, 1, 3]
+    with pytest.raises(K.KvError, match="zero norm"):
+        K.encode_kv_tensor(s, lay, strict, x2, rot, cb)
+    x2[1, 0, 0, 2] *= np.float32(3.0e4)        # page 0 comes before page 1 whatever the batch
+    with pytest.raises(K.KvError, match="norm cannot be represented"):
+        K.encode_kv_tensor(s, lay, strict, x2, rot, cb)
     rawp = K.KvCompressionProfileV1.from_parts("kv-raw", s, fp, "blake3:codebook", prof.rotation_digest, "raw",
                                                K.KvPageGeometryV1(11, dim, rec))
     allraw = K.encode_kv_tensor(s, lay, rawp, x, rot, cb)
