@@ -736,7 +736,9 @@ def decode_kv_pages(encoded: KvEncodedTensorV1, rotation, codebook, gpu_profile=
     ctx = encoded.context()
     d, T = shape.head_dim, shape.tokens
     out = np.zeros((shape.vector_count(), d), np.float32)
-    coded_at, coded_rec, raw_blocks, page_digests = [], [], 0, []
+    # blocks in the order the reference walks them; where two name the same vector the later one stays, as in
+    # its copy_from_slice per block
+    at, raw_vals, coded_rec, is_raw, raw_blocks, page_digests = [], [], [], [], 0, []
     for page in encoded.pages:
         page.validate(shape, ctx)
         if page.profile_digest != r["profile_digest"]:
@@ -746,16 +748,26 @@ def decode_kv_pages(encoded: KvEncodedTensorV1, rotation, codebook, gpu_profile=
             if blk.batch >= shape.batch or blk.layer >= shape.layers or blk.kv_head >= shape.kv_heads or \
                     blk.token >= T:
                 raise KvError("kv block index outside shape")
-            v = ((blk.batch * shape.layers + blk.layer) * shape.kv_heads + blk.kv_head) * T + blk.token
+            at.append(((blk.batch * shape.layers + blk.layer) * shape.kv_heads + blk.kv_head) * T + blk.token)
+            is_raw.append(blk.raw_fallback)
             if blk.raw_fallback:
                 raw_blocks += 1
-                out[v] = blk.values
+                raw_vals.append(blk.values)
             else:
-                coded_at.append(v)
                 coded_rec.append(blk.record)
-    if coded_at:
-        prof = gpu_profile or _gpu_profile(profile, rotation, codebook)
-        out[np.asarray(coded_at)] = prof.decode_exact(b"".join(coded_rec))
+    if at:
+        is_raw = np.asarray(is_raw, bool)
+        vals = np.empty((len(at), d), np.float32)
+        if raw_vals:
+            vals[is_raw] = np.asarray(raw_vals, np.float32).reshape(-1, d)
+        if coded_rec:
+            prof = gpu_profile or _gpu_profile(profile, rotation, codebook)
+            vals[~is_raw] = prof.decode_exact(b"".join(coded_rec))
+        at = np.asarray(at)
+        last = np.zeros(out.shape[0], np.int64) - 1
+        np.maximum.at(last, at, np.arange(at.size))   # the last block naming each vector
+        keep = last[last >= 0]
+        out[at[keep]] = vals[keep]
     receipt = {"schema_version": KV_RECEIPT_SCHEMA, "operation_kind": "decode",
                "decoded_digest": kv_tensor_digest(out), "profile_digest": r["profile_digest"],
                "shape_digest": shape.digest(), "page_digests": page_digests,
