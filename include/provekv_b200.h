@@ -436,6 +436,13 @@ int64_t pkv_launch_count(void);
  * GPU.  The payload of such a launch is not valid.  Process-wide; switch it off again after use. */
 int pkv_test_skip_tensor_issue(int on);
 
+/* Test hook, no counterpart in the reference.  While rotated_dev is not NULL the fib encoders that rotate on
+ * the tensor cores (fp16 norm, 5-bit indices, d = 64 / 128) also store every vector's rotated values as the
+ * tensor cores delivered them, dim f32 per vector in launch order, so that the error bound assumed for the
+ * unit's accumulation (PKV_FIB_ROT_ERR_TC) can be measured against the exact rotation.  The buffer must hold
+ * n_vectors * dim floats of every launch made while the hook is on.  Process-wide; NULL switches it off. */
+int pkv_test_capture_rotated(float* rotated_dev);
+
 /* Test hook, no counterpart in the reference.  For PolarWithQjl profiles with f32 radii the turbo
  * encoder takes the QJL sketch in the rotated domain (no inverse transform in the common case); while
  * this is switched on it takes the sketch of the residual, as every other profile does, so that tests

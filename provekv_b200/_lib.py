@@ -125,6 +125,7 @@ _SIGS = {
     "pkv_stream_synchronize": (C.c_int, [_V]),
     "pkv_payload_upload": (C.c_int, [_V, C.c_int64, C.c_int32, C.c_int64, C.c_int64, _V, C.c_int64, _V]),
     "pkv_payload_download": (C.c_int, [_V, C.c_int64, C.c_int64, C.c_int64, _V, C.c_int64, C.c_int32, _V]),
+    "pkv_test_capture_rotated": (C.c_int, [_V]),
     "pkv_stats_read": (C.c_int, [C.POINTER(C.c_uint64)]),
     "pkv_stats_reset": (C.c_int, []),
     "pkv_error_word_reset": (C.c_int, [_V, _V]),

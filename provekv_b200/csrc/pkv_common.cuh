@@ -285,6 +285,7 @@ int pkv_ws_prepare(PkvWorkspace* ws, int64_t in_bytes, int64_t out_bytes);
 void pkv_count_launch();
 cudaMemPool_t pkv_scratch_pool();  // the library's stream-ordered pool of the current device (scratch lists)
 int pkv_skip_tensor_issue();  // test hook, see pkv_test_skip_tensor_issue
+float* pkv_rotated_capture();  // test hook, see pkv_test_capture_rotated
 int pkv_turbo_encode_legacy();  // test hook, see pkv_test_turbo_encode_legacy
 
 // launchers implemented in pkv_fib.cu / pkv_turbo.cu

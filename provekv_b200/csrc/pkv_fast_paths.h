@@ -256,7 +256,9 @@ PKV_HD void pkv_fib_top2_pair(float* best, float* second, float a, float b) {
  * The vendor does not specify the rounding inside the accumulation of the 24 partial products;
  * 7e-6 sum|n_j M_rj| is assumed for it (a correctly rounded binary32 accumulation of 24 partial
  * sums stays below 1.4e-6, one that truncates below 2.9e-6).  With |M_r| = |n| = 1:   1.0e-5.
- * (Measured: with the bound set to 2e-6 the encoder still reproduced every byte of 25 M blocks.) */
+ * (Measured: with the bound set to 2e-6 the encoder still reproduced every byte of 25 M blocks; the largest
+ * error of the unit's output against the exact rotation over 60,000 captured vectors was 8.3e-7 at D = 64 and
+ * 7.2e-7 at D = 128, pkv_test_capture_rotated.) */
 #ifndef PKV_FIB_ROT_ERR_TC
 #define PKV_FIB_ROT_ERR_TC 1.0e-5f
 #endif

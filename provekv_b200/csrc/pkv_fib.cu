@@ -570,7 +570,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     if ((st = set_smem(fib_encode_tc_kernel, FibTc::SMEM)) != PKV_OK) return st;
     fib_encode_tc_kernel<<<(unsigned)grid, FibTc::THREADS, FibTc::SMEM, s>>>(
         gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->rot_dev,
-        p->cfg.argmin_order, p->score_abs, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue());
+        p->cfg.argmin_order, p->score_abs, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue(), pkv_rotated_capture());
     pkv_count_launch();
     // the in-kernel exact tier leaves only boundary cases on the list: one CTA per SM is plenty
     fib_encode_fix_kernel<64><<<sms, kThreads, 0, s>>>(
@@ -589,7 +589,7 @@ int pkv_launch_fib_encode_fast_with_scratch(const pkv_fib_profile* p, const floa
     if ((st = set_smem(fib_encode_tc128_kernel, FibTc128::SMEM)) != PKV_OK) return st;
     fib_encode_tc128_kernel<<<(unsigned)grid, FibTc128::THREADS, FibTc128::SMEM, s>>>(
         gf, x, p->rot_hi_dev, p->rot_lo_dev, p->codebook_dev, p->half_norm_dev, p->cfg.codebook_size, p->rot_dev,
-        p->cfg.argmin_order, p->score_abs, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue());
+        p->cfg.argmin_order, p->score_abs, payload, err, scratch, scratch + 1, pkv_skip_tensor_issue(), pkv_rotated_capture());
     pkv_count_launch();
     fib_encode_fix_kernel<128><<<sms, kThreads, 0, s>>>(
         gf, x, p->rot_dev, p->codebook_dev, p->cfg.codebook_size, p->idx_bits, p->norm_len,

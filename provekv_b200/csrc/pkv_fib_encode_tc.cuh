@@ -96,7 +96,7 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
                      const float* __restrict__ rot_lo, const float* __restrict__ codebook,
                      const float* __restrict__ half_norm, int n_codewords, const double* __restrict__ rot,
                      int argmin_order, float score_abs, uint8_t* __restrict__ payload, uint64_t* err, uint32_t* flag_count,
-                     uint32_t* flag_list, int skip_issue) {
+                     uint32_t* flag_list, int skip_issue, float* __restrict__ y_capture) {
   using K = FibTc;
   using pkv_tc::sw_piece;
   using pkv_tc::tile_at;
@@ -279,6 +279,11 @@ fib_encode_tc_kernel(PkvGeom g, const float* __restrict__ x, const float* __rest
         y[i] = h0[i];
         y[32 + i] = h1[i];
       }
+    }
+    if (y_capture != nullptr && valid) {  // test hook: the rotated values as the tensor cores delivered them
+      float4* dst = reinterpret_cast<float4*>(y_capture + ((int64_t)batch * g.vpb + v0 + v) * D);
+#pragma unroll
+      for (int i = 0; i < D; i += 4) dst[i >> 2] = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
     }
     // certified nearest codeword of the 16 blocks (pkv_fast_paths.h)
     float best[K::B], second[K::B];

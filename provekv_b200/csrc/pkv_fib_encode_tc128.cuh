@@ -30,7 +30,7 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
                         const float* __restrict__ rot_lo, const float* __restrict__ codebook,
                         const float* __restrict__ half_norm, int n_codewords, const double* __restrict__ rot,
                         int argmin_order, float score_abs, uint8_t* __restrict__ payload, uint64_t* err, uint32_t* flag_count,
-                        uint32_t* flag_list, int skip_issue) {
+                        uint32_t* flag_list, int skip_issue, float* __restrict__ y_capture) {
   using K = FibTc128;
   using pkv_tc::sw_piece;
   constexpr int D = K::D;
@@ -239,6 +239,11 @@ fib_encode_tc128_kernel(PkvGeom g, const float* __restrict__ x, const float* __r
 #pragma unroll
         for (int i = 0; i < 32; i++) y[32 * h + i] = part32[i];
       }
+    }
+    if (y_capture != nullptr && valid) {  // test hook: the rotated values as the tensor cores delivered them
+      float4* dst = reinterpret_cast<float4*>(y_capture + ((int64_t)batch * g.vpb + v0 + row) * D + part * K::EPT);
+#pragma unroll
+      for (int i = 0; i < K::EPT; i += 4) dst[i >> 2] = make_float4(y[i], y[i + 1], y[i + 2], y[i + 3]);
     }
     float best[K::HB], second[K::HB];
 #pragma unroll

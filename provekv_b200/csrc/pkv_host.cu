@@ -14,6 +14,7 @@ namespace {
 
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_skip_tensor_issue{0};
+std::atomic<float*> g_rotated_capture{nullptr};
 std::atomic<int> g_turbo_encode_legacy{0};
 
 int grow(void** ptr, int64_t* cap, int64_t need) {
@@ -208,6 +209,7 @@ int pkv_make_geom(const pkv_layout* L, int rec_bytes, int64_t payload_batch_stri
 }
 void pkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 int pkv_skip_tensor_issue() { return g_skip_tensor_issue.load(std::memory_order_relaxed); }
+float* pkv_rotated_capture() { return g_rotated_capture.load(std::memory_order_relaxed); }
 int pkv_turbo_encode_legacy() { return g_turbo_encode_legacy.load(std::memory_order_relaxed); }
 
 extern "C" {
@@ -220,6 +222,11 @@ int pkv_test_turbo_encode_legacy(int on) {
   g_turbo_encode_legacy.store(on ? 1 : 0);
   return PKV_OK;
 }
+int pkv_test_capture_rotated(float* rotated_dev) {
+  g_rotated_capture.store(rotated_dev, std::memory_order_relaxed);
+  return PKV_OK;
+}
+
 int pkv_test_skip_tensor_issue(int on) {
   g_skip_tensor_issue.store(on ? 1 : 0);
   return PKV_OK;

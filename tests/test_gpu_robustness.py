@@ -307,3 +307,42 @@ def test_tier_counters_count_what_the_shortcuts_did_not_settle():
     L.check(lib.pkv_stats_reset())
     L.check(lib.pkv_stats_read(counts))
     assert list(counts) == [0] * 8
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,bound", [(64, 1.0e-5), (128, 1.7e-5)])
+def test_tensor_core_rotation_stays_inside_its_assumed_bound(dim, bound):
+    """The bound of the tensor-core tier contains a term assumed for the unit's accumulation rounding
+    (PKV_FIB_ROT_ERR_TC / _TC128).  With the capture hook on, the encoder also stores the rotated values as
+    the unit delivered them; their distance from the exact rotation (binary64, the reference's (f32) of it)
+    must stay inside the bound, with margin."""
+    import numpy as np
+    import torch
+    lib = L.lib()
+    n = 60_000
+    rot, cb = tables.haar_rotation(dim, 42), tables.fib_codebook(dim, seed=42)
+    prof = pk.FibProfile(dim, rot, cb, numerics=L.FIB_NUMERICS_BATCH)
+    rng = np.random.default_rng(5)
+    x = synthetic_kv(n, dim, seed=31)
+    x[: n // 4] = rng.standard_normal((n // 4, dim)).astype(np.float32) * np.float32(1e-4)
+    x[n // 4: n // 2, rng.integers(0, dim)] *= np.float32(300.0)   # vectors concentrated in one coordinate
+    xd = torch.from_numpy(x).cuda()
+    cap = torch.full((n, dim), float("nan"), dtype=torch.float32, device="cuda")
+    out = torch.zeros(n * prof.record_bytes, dtype=torch.uint8, device="cuda")
+    err = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    L.check(lib.pkv_test_capture_rotated(cap.data_ptr()))
+    try:
+        prof.encode_dev(xd.data_ptr(), _flat_layout(1, n, dim), out.data_ptr(), n * prof.record_bytes, err.data_ptr())
+        torch.cuda.synchronize()
+    finally:
+        L.check(lib.pkv_test_capture_rotated(None))
+    pk.read_error_word(err.data_ptr())
+    got = cap.cpu().numpy()
+    assert np.isfinite(got).all()
+    x64 = x.astype(np.float64)
+    norm = np.sqrt((x64 * x64).sum(1, keepdims=True))
+    nrm = (x64 / norm).astype(np.float32).astype(np.float64)          # codec.rs:607-609
+    exact = (nrm @ rot.T).astype(np.float32)                           # rotation.rs:104-115, then (f32)
+    worst = float(np.abs(got.astype(np.float64) - exact.astype(np.float64)).max())
+    print(f"tensor-core rotation d={dim}: largest error {worst:.3e}, bound {bound:.1e}")
+    assert worst < 0.5 * bound, worst
