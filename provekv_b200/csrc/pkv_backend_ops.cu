@@ -28,7 +28,7 @@ struct WhtSigns {
 // with the bit clear): inside a lane's V-group for step < V, across lanes (shuffle) for step < 32 V,
 // across the lane's groups beyond that.  fallback.rs:34-46 runs the stages in the same order.
 template <int E>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, E >= 16 ? 3 : 8)
 hadamard_batch_kernel(float* __restrict__ data, int64_t n, int dim, WhtSigns sg, float scale, int vec_ok) {
   constexpr int V = E < 4 ? E : 4, G = E / V;  // elements per group, groups per lane
   __shared__ uint32_t s_neg[32];
