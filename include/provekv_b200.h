@@ -318,7 +318,7 @@ int pkv_fib_decode_batch_compact(const pkv_fib_profile* p, const uint8_t* bytes_
  * the encoder refused (zero norm, non-finite input, norm outside the wire format) is all zero bytes -- a
  * norm field no accepted vector can have -- and every other record is the one a call without the refused
  * vectors would have produced.  The reference fails the whole batch (fib-quant/src/codec.rs:594-610);
- * callers that keep refused vectors raw (fib-quant/src/kv/codec.rs:264-286) read the verdict per vector
+ * callers that keep refused vectors raw (fib-quant/src/kv/codec.rs:264-286) read the outcome per vector
  * from the records. */
 int pkv_fib_encode_batches_compact(const pkv_fib_profile* p, const float* vectors_host,
                                    int64_t n_batches, int64_t vectors_per_batch, uint8_t* out_host,

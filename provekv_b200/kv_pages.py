@@ -650,7 +650,7 @@ def encode_kv_tensor(shape: KvTensorShapeV1, layout: KvCacheLayoutV1, profile: K
     records = None
     if not raw.all():
         # One launch over every vector; the ones the policy keeps raw ride along as a codable stand-in.
-        # The encoder's verdict comes back in the records: a refused vector's record is all zero bytes
+        # The encoder's answer comes back in the records: a refused vector's record is all zero bytes
         # (include/provekv_b200.h, pkv_fib_encode_batches_compact), and the call's status names the first one.
         from . import _lib as L
         from .profiles import encode_batches_compact
@@ -665,7 +665,7 @@ def encode_kv_tensor(shape: KvTensorShapeV1, layout: KvCacheLayoutV1, profile: K
         try:
             encode_batches_compact(prof, xg.ctypes.data, 1, n_vec, wire.ctypes.data, wire.size)
         except L.PkvError as e:
-            if e.status < 16:        # not a per-vector verdict
+            if e.status < 16:        # not a per-vector status
                 raise
         records = wire[L.FB2_HEADER_BYTES:].reshape(n_vec, rec)
         norm_len = _norm_format_len(profile.fib_profile.norm_format)
