@@ -445,6 +445,59 @@ class KvCompressionProfileV1:
         return json_digest(KV_PROFILE_SCHEMA, self.as_json())
 
 
+KV_STRATEGIES = ("raw", "fib_quant_per_token", "fib_quant_per_channel", "role_aware_kivi_style_baseline",
+                 "experimental_fib_quant_role_aware")
+
+
+@dataclass
+class KvCompressionPolicyV1:
+    """kv/policy.rs:27-66."""
+    strategy: str = "raw"
+    protected_policy: KvProtectedPolicyV1 = field(default_factory=KvProtectedPolicyV1)
+    require_calibration: bool = False
+    allow_raw_fallback: bool = True
+
+    @classmethod
+    def raw(cls) -> "KvCompressionPolicyV1":
+        return cls()
+
+    @classmethod
+    def role_aware_baseline(cls) -> "KvCompressionPolicyV1":
+        return cls("role_aware_kivi_style_baseline", KvProtectedPolicyV1(0, 1, [], []), False, True)
+
+    def as_json(self) -> dict:
+        return {"strategy": self.strategy, "protected_policy": self.protected_policy.as_json(),
+                "require_calibration": self.require_calibration, "allow_raw_fallback": self.allow_raw_fallback}
+
+
+def decide_kv_compression(policy: KvCompressionPolicyV1, shape: KvTensorShapeV1, layer: int, head: int, token: int,
+                          has_calibration: bool) -> dict:
+    """kv/policy.rs:117-190: the decision for one logical vector as
+    ``{"action", "axis_policy", "reasons"}`` (KvCompressionDecisionV1's fields, variants by their serde names)."""
+    shape.validate()
+    policy.protected_policy.validate_for_shape(shape)
+    if layer >= shape.layers or head >= shape.kv_heads or token >= shape.tokens:
+        raise KvError("kv policy index outside shape")
+    if policy.strategy not in KV_STRATEGIES:
+        raise KvError(f"unknown kv compression strategy {policy.strategy}")
+    if policy.protected_policy.is_protected(shape, layer, head, token):
+        return {"action": "keep_raw", "axis_policy": "raw", "reasons": ["protected_region"]}
+    if policy.require_calibration and not has_calibration:
+        return {"action": "keep_raw" if policy.allow_raw_fallback else "need_calibration", "axis_policy": "raw",
+                "reasons": ["calibration_missing"]}
+    role_reason = ["key_role_axis"] if shape.role == "key" else ["value_role_axis"]
+    role_axis = "per_channel" if shape.role == "key" else "per_token"
+    if policy.strategy == "raw":
+        return {"action": "keep_raw", "axis_policy": "raw", "reasons": ["raw_strategy"]}
+    if policy.strategy == "fib_quant_per_token":
+        return {"action": "compress", "axis_policy": "per_token", "reasons": role_reason}
+    if policy.strategy == "fib_quant_per_channel":
+        return {"action": "compress", "axis_policy": "per_channel", "reasons": role_reason}
+    if policy.strategy == "role_aware_kivi_style_baseline":
+        return {"action": "compress", "axis_policy": role_axis, "reasons": role_reason}
+    return {"action": "compress", "axis_policy": role_axis, "reasons": ["experimental_role_aware"]}
+
+
 def _norm_format_len(fmt: str) -> int:
     return 2 if fmt == "fp16_paper" else 4
 

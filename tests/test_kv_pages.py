@@ -226,3 +226,80 @@ def test_pages_encoded_and_decoded_on_the_gpu(oracle_mod, dim):
     assert allraw.receipt["compressed_blocks"] == 0 and allraw.receipt["fallback_reasons"] == ["raw_axis_policy"]
     back, _ = K.decode_kv_pages(allraw, rot, cb)
     assert np.array_equal(back, x)
+
+
+def _tiny(role="value", tokens=4, axis="per_channel", seed=13):
+    """The fixture of the reference's own kv tests (fib-quant/tests/kv_*.rs): one head of dim 8, k = 2, N = 8."""
+    s = K.KvTensorShapeV1(role, "mha", 1, 1, 1, 1, tokens, 8, "f32", "post_rope" if role == "key" else "not_applicable")
+    fp = K.FibQuantProfileV1.paper_default(8, 2, 8, seed)
+    import dataclasses
+    fp = dataclasses.replace(fp, training_samples=64, lloyd_restarts=1, lloyd_iterations=1)
+    p = K.KvCompressionProfileV1.from_parts("fixture", s, fp, "blake3:codebook", "blake3:rotation", axis,
+                                            K.KvPageGeometryV1(2, 8, 64))
+    return s, K.KvCacheLayoutV1.canonical(s), p
+
+
+def test_axis_without_an_encoder_keeps_every_vector_raw():
+    """fib-quant/tests/kv_encode_decode_reference.rs:63-72: a per-channel profile stores 4 raw blocks, no coded
+    one, and decodes to the input exactly; no table and no GPU is involved."""
+    s, lay, p = _tiny()
+    values = (np.sin((np.arange(32, dtype=np.float32) + np.float32(1.0)) * np.float32(0.07)) + np.float32(0.25)).astype(np.float32)
+    enc = K.encode_kv_tensor(s, lay, p, values, None, None)
+    assert enc.receipt["compressed_blocks"] == 0 and enc.receipt["raw_fallback_blocks"] == 4
+    assert enc.receipt["encoded_pages"] == 2 and len(enc.receipt["page_digests"]) == len(enc.pages) == 2
+    assert enc.receipt["fallback_reasons"] == ["unsupported_axis_raw_fallback"]      # kv/codec.rs:287-298
+    dec, dr = K.decode_kv_pages(enc, None, None)
+    assert np.array_equal(dec.reshape(-1), values) and dr["decoded_pages"] == 2 and dr["raw_fallback_blocks"] == 4
+    # kv_corruption_rejection.rs:43-44: a tampered page digest rejects the decode
+    enc.pages[0].page_digest += "-tampered"
+    with pytest.raises(K.KvError):
+        K.decode_kv_pages(enc, None, None)
+
+
+def test_shape_contract_round_trips_and_bounded_shapes():
+    """kv_shape_contracts.rs:28-62 (digests survive a JSON round trip) and kv_property_shapes.rs (every bounded
+    shape validates with its canonical layout and a two-token page geometry)."""
+    s, lay, p = _tiny("key", axis="per_token", seed=11)
+    again = K.KvTensorShapeV1(**{k: v for k, v in json.loads(K.serde_text(s.as_json())).items()})
+    assert again.digest() == s.digest()
+    lj = json.loads(K.serde_text(lay.as_json()))
+    assert K.KvCacheLayoutV1(lj["batch_stride"], lj["layer_stride"], lj["head_stride"], lj["token_stride"]).digest(s) == \
+        lay.digest(s)
+    assert json.loads(K.serde_text(p.as_json()))["fib_profile"]["radius_method"] == "k2_closed_form"
+    for batch in (1, 2):
+        for layers in (1, 2):
+            for heads in (1, 2, 3):
+                for tokens in (1, 2, 5, 7):
+                    for mult in (1, 2, 3, 4):
+                        sh = K.KvTensorShapeV1("key", "mha", batch, layers, heads, heads, tokens, 2 * mult, "f32", "post_rope")
+                        sh.validate()
+                        sh.validate_block_dim(2)
+                        K.KvCacheLayoutV1.canonical(sh).validate_for_shape(sh)
+                        K.KvPageGeometryV1(min(tokens, 2), 2 * mult, 64).validate_for_shape(sh)
+
+
+def test_policy_decisions():
+    """kv_policy_role_aware.rs: the role-aware baseline compresses keys per channel and values per token; a
+    protected layer or a missing calibration keeps the vector raw."""
+    def shape(role):
+        return K.KvTensorShapeV1(role, "gqa", 1, 2, 2, 4, 8, 16, "f32", "pre_rope" if role == "key" else "not_applicable")
+    pol = K.KvCompressionPolicyV1.role_aware_baseline()
+    key = K.decide_kv_compression(pol, shape("key"), 0, 0, 1, True)
+    value = K.decide_kv_compression(pol, shape("value"), 0, 0, 1, True)
+    assert (key["action"], key["axis_policy"], key["reasons"]) == ("compress", "per_channel", ["key_role_axis"])
+    assert (value["action"], value["axis_policy"], value["reasons"]) == ("compress", "per_token", ["value_role_axis"])
+    assert K.decide_kv_compression(pol, shape("value"), 0, 0, 7, True)["reasons"] == ["protected_region"]  # last token
+    pol = K.KvCompressionPolicyV1("fib_quant_per_token", K.KvProtectedPolicyV1(1, 0, [1], []), True, True)
+    assert K.decide_kv_compression(pol, shape("value"), 0, 0, 0, False)["action"] == "keep_raw"
+    assert K.decide_kv_compression(pol, shape("value"), 1, 0, 3, True)["reasons"] == ["protected_region"]
+    pol.protected_policy.first_tokens_raw = 0
+    missing = K.decide_kv_compression(pol, shape("value"), 0, 0, 2, False)
+    assert (missing["action"], missing["reasons"]) == ("keep_raw", ["calibration_missing"])
+    pol.allow_raw_fallback = False
+    assert K.decide_kv_compression(pol, shape("value"), 0, 0, 2, False)["action"] == "need_calibration"
+    assert K.decide_kv_compression(K.KvCompressionPolicyV1.raw(), shape("key"), 0, 0, 2, True)["reasons"] == ["raw_strategy"]
+    exp = K.KvCompressionPolicyV1("experimental_fib_quant_role_aware")
+    assert K.decide_kv_compression(exp, shape("key"), 0, 0, 2, True) == \
+        {"action": "compress", "axis_policy": "per_channel", "reasons": ["experimental_role_aware"]}
+    with pytest.raises(K.KvError, match="outside shape"):
+        K.decide_kv_compression(pol, shape("value"), 2, 0, 0, True)
