@@ -123,7 +123,11 @@ def test_biased_key_search_never_decides_wrong(oracle_mod, order, n_codewords, s
     mid += rng.choice([0.0, 1e-8, 1e-7, 1e-6], (n, 1)) * rng.standard_normal((n, 4))
     mid = mid.astype(np.float32)
     mid = mid[np.linalg.norm(mid, axis=1) <= 1.0]
-    y = np.ascontiguousarray(np.concatenate([typical, full, mid]), np.float32)
+    # scores near zero (|c|^2 = 2 s.c): s = c / 2, and the point halfway to a bisector point
+    half = np.concatenate([0.5 * cb[a[:20000]].astype(np.float64) * rng.uniform(0.999999, 1.000001, (20000, 1)),
+                           0.25 * (cb[a[:20000]].astype(np.float64) + cb[b[:20000]].astype(np.float64))]).astype(np.float32)
+    half = half[np.linalg.norm(half, axis=1) <= 1.0]
+    y = np.ascontiguousarray(np.concatenate([typical, full, mid, half]), np.float32)
     fn = oracle_mod.lib().pkvo_fib_biased_search_check
     fn.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64)]
     out = (C.c_int64 * 5)()
@@ -134,3 +138,34 @@ def test_biased_key_search_never_decides_wrong(oracle_mod, order, n_codewords, s
     assert by_gap > 0.98 * (typical.shape[0] + full.shape[0])      # the quick test settles ordinary blocks
     assert undecided > 0.2 * mid.shape[0]                           # and the bisector cases do reach the exact tier
     print(n_codewords, scale, "undecided", undecided / y.shape[0], "by gap", by_gap / y.shape[0])
+
+
+@pytest.mark.parametrize("check", ["pkvo_fib_fast_check", "pkvo_fib_tc_check"])
+def test_fib_rotation_shortcuts_with_scores_near_zero(oracle_mod, check):
+    """Unit vectors whose rotated blocks sit at half a codeword (that codeword's score |c|^2/2 - s.c is ~0, so a
+    bound relative to the score alone would not cover the roundings of the fused evaluation) or halfway to
+    the midpoint of two codewords; one block carries the rest of the norm.  No certified block may be wrong."""
+    import numpy as np
+    from provekv_b200 import tables
+    dim, n = 64, 6000
+    rot = np.ascontiguousarray(tables.haar_rotation(dim, 42), dtype=np.float64)
+    cb = np.ascontiguousarray(tables.fib_codebook(dim, seed=42), dtype=np.float32)
+    rng = np.random.default_rng(17)
+    a, b = rng.integers(0, 32, (n, 15)), rng.integers(0, 32, (n, 15))
+    half = 0.5 * cb[a].astype(np.float64) * rng.uniform(0.999999, 1.000001, (n, 15, 1))
+    quarter = 0.25 * (cb[a].astype(np.float64) + cb[b].astype(np.float64))
+    y = np.where(rng.random((n, 15, 1)) < 0.5, half, quarter)
+    rest = np.sqrt(np.maximum(1.0 - (y ** 2).sum((1, 2)), 0.0))            # the 16th block completes the unit norm
+    last = rng.standard_normal((n, 4))
+    last *= (rest / np.linalg.norm(last, axis=1))[:, None]
+    yv = np.concatenate([y.reshape(n, 60), last], axis=1)
+    x = np.ascontiguousarray((yv @ rot).astype(np.float32))                  # x = M^T y
+    fn = getattr(oracle_mod.lib(), check)
+    fn.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                   C.POINTER(C.c_int64)]
+    for order in (0, 1):
+        out = (C.c_int64 * 6)()
+        fn(x.ctypes.data, n, dim, rot.ctypes.data, cb.ctypes.data, 32, order, out)
+        wrong, flagged, decided, quot_wrong, quot_uncertain, worst_e9 = list(out)
+        assert wrong == 0 and quot_wrong == 0 and decided + flagged == n * 16
+        assert decided > 0.5 * n * 16

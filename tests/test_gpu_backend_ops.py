@@ -76,8 +76,11 @@ def test_codebook_lookup_indices(oracle_mod, dim, n_codewords):
     mid += rng.choice([0.0, 1e-8, 3e-7], mid.shape[:2] + (1,)) * rng.standard_normal(mid.shape)
     blocks[800:1400] = mid.astype(np.float32)                 # on and beside the bisector of two codewords
     blocks[1400:1500] = cb[a[:100]]                           # exactly on a codeword
-    blocks[1500:1600] = (2.0 * cb[a[:100]].astype(np.float64) * rng.uniform(0.999, 1.001, (100, dim // 4, 1))
-                         ).astype(np.float32)                 # |c|^2 close to 2 s.c: scores near zero
+    blocks[1500:1600] = (0.5 * cb[a[:100]].astype(np.float64) * rng.uniform(0.999999, 1.000001, (100, dim // 4, 1))
+                         ).astype(np.float32)                 # s = c / 2: |c|^2 = 2 s.c, that codeword's score is ~0
+    blocks[1600:1700] = (0.25 * (cb[a[:100]].astype(np.float64) + cb[b[:100]].astype(np.float64))
+                         ).astype(np.float32)                 # halfway to a bisector point: two scores near zero
+    blocks[1700:1800] = (2.0 * cb[a[:100]].astype(np.float64)).astype(np.float32)
     x = blocks.reshape(n, dim)
     got, want = _lookup_gpu(x, cb), oracle_mod.codebook_lookup(x, cb)
     assert np.array_equal(got, want), np.argwhere(got != want)[:5]
