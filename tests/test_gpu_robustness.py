@@ -346,3 +346,27 @@ def test_tensor_core_rotation_stays_inside_its_assumed_bound(dim, bound):
     worst = float(np.abs(got.astype(np.float64) - exact.astype(np.float64)).max())
     print(f"tensor-core rotation d={dim}: largest error {worst:.3e}, bound {bound:.1e}")
     assert worst < 0.5 * bound, worst
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim", [64, 128])
+def test_blocks_at_half_a_codeword_encode_like_the_oracle(oracle_mod, dim):
+    """Rotated blocks at half a codeword or halfway to a midpoint of two: the fused scores are near zero there,
+    where the certification must rely on the absolute term of its bound."""
+    import numpy as np
+    n, nb = 8000, dim // 4
+    rot, cb = tables.haar_rotation(dim, 42), tables.fib_codebook(dim, seed=42)
+    rng = np.random.default_rng(23)
+    a, b = rng.integers(0, 32, (n, nb - 1)), rng.integers(0, 32, (n, nb - 1))
+    half = 0.5 * cb[a].astype(np.float64) * rng.uniform(0.999999, 1.000001, (n, nb - 1, 1))
+    quarter = 0.25 * (cb[a].astype(np.float64) + cb[b].astype(np.float64))
+    y = np.where(rng.random((n, nb - 1, 1)) < 0.5, half, quarter)
+    rest = np.sqrt(np.maximum(1.0 - (y ** 2).sum((1, 2)), 0.0))
+    last = rng.standard_normal((n, 4))
+    last *= (rest / np.linalg.norm(last, axis=1))[:, None]
+    x = (np.concatenate([y.reshape(n, dim - 4), last], axis=1) @ rot).astype(np.float32)
+    for order in (L.ARGMIN_PAIRWISE, L.ARGMIN_SEQUENTIAL):
+        prof = pk.FibProfile(dim, rot, cb, argmin_order=order, numerics=L.FIB_NUMERICS_BATCH)
+        got = np.frombuffer(prof.encode_batch_compact(x), np.uint8)[L.FB2_HEADER_BYTES:].reshape(n, -1)
+        st, want, _, _ = oracle_mod.fib_encode(x, rot, cb, argmin_order=order, numerics=L.FIB_NUMERICS_BATCH, nthreads=4)
+        assert st == 0 and np.array_equal(got, want)
